@@ -1,0 +1,496 @@
+"""Drop-in for the reference's pybind module ``EmbCacheLib`` (src/pybind.cc:16-71).
+
+Same names, argument order and error behaviour (shape mismatches raise ``RuntimeError`` as
+the reference's ``CHECK`` does); every operation runs in ``libhades_b200.so`` on the
+current CUDA stream.  New capabilities have new names (``cudaLookupFetch``,
+``cudaUniqueSegSum``, ...); no reference name changes meaning.
+
+Differences that a caller can observe:
+
+* kernels run on torch's current stream, not on the legacy default stream
+  (the reference launches ``<<<grid, block>>>`` with no stream, e.g. src/cuda/uva_fetch.cu:39);
+* a CUDA error raises instead of ending the process (src/utils.h:12-24 calls ``exit``);
+* ``IndexCache`` keeps its state in HBM.  ``name``/``create`` select a process-local
+  registry entry instead of a POSIX shared-memory segment, and ``pin_memory`` is accepted
+  and ignored (there is no host copy to pin);
+* ``IndexCache.add`` applies ids in input order per set, which is the reference's result at
+  ``OMP_NUM_THREADS=1`` (its multi-threaded result depends on thread timing).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import LOOKUP_SETASSOC, LOOKUP_SORTED, MOVER_AUTO, MOVER_BULK, MOVER_LSU  # noqa: F401
+
+_REGISTRY: dict[str, "IndexCache"] = {}
+
+
+def _check(cond: bool, what: str) -> None:
+    if not cond:
+        raise RuntimeError(f"Check failed: {what}")
+
+
+def _idx_bytes(t: torch.Tensor) -> int:
+    if t.dtype == torch.int64:
+        return 8
+    if t.dtype == torch.int32:
+        return 4
+    raise RuntimeError("ID can only be int32 or int64")  # src/utils.h:48
+
+
+def _check_float(t: torch.Tensor) -> None:
+    if t.dtype not in (torch.float32, torch.float64):
+        raise RuntimeError("Type can only be float or double")  # src/utils.h:35
+
+
+def _row_bytes(t: torch.Tensor) -> int:
+    dim = 1 if t.dim() == 1 else t.size(1)
+    return dim * t.element_size()
+
+
+def _dev_ptr(t: torch.Tensor, what: str) -> int:
+    """Device-usable address of a tensor: CUDA memory, or pinned host memory (the
+    reference's UVA arguments, registered with cudaPin)."""
+    if t.is_cuda or t.is_pinned() or t.data_ptr() in _PINNED:
+        if not t.is_contiguous():
+            raise RuntimeError(f"{what} must be contiguous")
+        return t.data_ptr()
+    raise RuntimeError(f"{what} must be a CUDA tensor or pinned host memory (cudaPin)")
+
+
+class IndexCache:
+    """IndexCache(cache_size, name, create, pin_memory=True), src/pybind.cc:17-33."""
+
+    def __init__(self, cache_size: int, name: str, create: bool, pin_memory: bool = True,
+                 lookup_mode: int = LOOKUP_SETASSOC):
+        self._lib = _lib.load()
+        self._name = name
+        self.lookup_mode = lookup_mode
+        if create:
+            h = C.c_void_p()
+            _lib.check(self._lib.hb_index_create(int(cache_size), C.byref(h)))
+            self._h = h
+            self._owner = True
+            self._device = torch.cuda.current_device()
+            _REGISTRY[name] = self
+        else:
+            if name not in _REGISTRY:
+                raise RuntimeError(f"fail to open {name}: no such index in this process")
+            other = _REGISTRY[name]
+            self._h = other._h
+            self._owner = False
+            self._device = other._device
+
+    def __del__(self):
+        if getattr(self, "_owner", False) and getattr(self, "_h", None):
+            try:
+                self._lib.hb_index_destroy(self._h)
+            except Exception:
+                pass
+            if _REGISTRY.get(self._name) is self:
+                _REGISTRY.pop(self._name, None)
+            self._h = None
+
+    # --- sizes -------------------------------------------------------------------------
+    def get_size(self) -> int:
+        return self._lib.hb_index_size(self._h)
+
+    def get_capacity(self) -> int:
+        return self._lib.hb_index_capacity(self._h)
+
+    def get_space(self) -> int:
+        return self._lib.hb_index_space(self._h)
+
+    def get_valid_entries_num(self) -> int:
+        out = C.c_int64(0)
+        _lib.check(self._lib.hb_index_valid_entries(self._h, C.byref(out), _lib.stream_ptr()))
+        return out.value
+
+    # --- reference surface: CPU tensors in and out --------------------------------------
+    def _to_dev(self, ids: torch.Tensor) -> torch.Tensor:
+        _check(ids.dtype == torch.int64, "ids.dtype == int64")
+        return ids.contiguous().to(f"cuda:{self._device}", non_blocking=False)
+
+    def add(self, ids: torch.Tensor) -> torch.Tensor:
+        out = self.cuda_add(self._to_dev(ids))
+        return out if ids.is_cuda else out.cpu()
+
+    def lookup(self, ids: torch.Tensor) -> torch.Tensor:
+        """CPU lookup of the reference (src/cache/cache.h:213-222): returns the slots and
+        applies the LRU side effect of every hit, in batch order."""
+        dev = self._to_dev(ids)
+        locs = self.cudalookup(dev)
+        self.cuda_touch_lru(locs)
+        return locs if ids.is_cuda else locs.cpu()
+
+    def reset(self, ids: torch.Tensor) -> None:
+        dev = self._to_dev(ids)
+        _lib.check(self._lib.hb_index_reset(self._h, dev.data_ptr(), dev.numel(), _lib.stream_ptr()))
+
+    def getall(self, length: int):
+        dev = f"cuda:{self._device}"
+        ids = torch.zeros(length, dtype=torch.int64, device=dev)
+        locs = torch.full((length,), -1, dtype=torch.int64, device=dev)
+        n = C.c_int64(0)
+        _lib.check(self._lib.hb_index_getall(self._h, ids.data_ptr(), locs.data_ptr(), int(length),
+                                             C.byref(n), _lib.stream_ptr()))
+        return ids.cpu(), locs.cpu()
+
+    def cudalookup(self, ids: torch.Tensor, mode: int | None = None) -> torch.Tensor:
+        """GPU lookup (src/cache/lookup.cu:64-85): CUDA ids in, CUDA slots out, LRU
+        counters untouched."""
+        _check(ids.is_cuda and ids.dtype == torch.int64, "ids is a CUDA int64 tensor")
+        ids = ids.contiguous()
+        locs = torch.empty_like(ids)
+        _lib.check(self._lib.hb_index_lookup(self._h, ids.data_ptr(), ids.numel(), locs.data_ptr(),
+                                             None, self.lookup_mode if mode is None else mode,
+                                             _lib.stream_ptr()))
+        return locs
+
+    # --- device-side extensions ------------------------------------------------------------
+    def cuda_add(self, ids: torch.Tensor) -> torch.Tensor:
+        _check(ids.is_cuda and ids.dtype == torch.int64, "ids is a CUDA int64 tensor")
+        ids = ids.contiguous()
+        locs = torch.empty_like(ids)
+        need = self._lib.hb_index_add_workspace_bytes(ids.numel())
+        ws = _lib.workspace(need)
+        _lib.check(self._lib.hb_index_add(self._h, ids.data_ptr(), ids.numel(), locs.data_ptr(),
+                                          ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
+        return locs
+
+    def cuda_touch_lru(self, locs: torch.Tensor) -> None:
+        need = self._lib.hb_index_touch_lru_workspace_bytes(locs.numel())
+        ws = _lib.workspace(need)
+        _lib.check(self._lib.hb_index_touch_lru(self._h, locs.data_ptr(), locs.numel(),
+                                                ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
+
+    def cuda_lookup_found(self, ids: torch.Tensor, mode: int | None = None):
+        """(slots, found mask) in one launch."""
+        ids = ids.contiguous()
+        locs = torch.empty_like(ids)
+        found = torch.empty(ids.shape, dtype=torch.bool, device=ids.device)
+        _lib.check(self._lib.hb_index_lookup(self._h, ids.data_ptr(), ids.numel(), locs.data_ptr(),
+                                             found.data_ptr(),
+                                             self.lookup_mode if mode is None else mode,
+                                             _lib.stream_ptr()))
+        return locs, found
+
+    def build_sorted(self) -> None:
+        _lib.check(self._lib.hb_index_build_sorted(self._h, _lib.stream_ptr()))
+
+    def export_state(self):
+        cap = self.get_capacity()
+        dev = f"cuda:{self._device}"
+        ids = torch.empty(cap, dtype=torch.int64, device=dev)
+        lru = torch.empty(cap, dtype=torch.int32, device=dev)
+        _lib.check(self._lib.hb_index_export(self._h, ids.data_ptr(), lru.data_ptr(), _lib.stream_ptr()))
+        return ids, lru
+
+    def import_state(self, line_ids: torch.Tensor, lru: torch.Tensor) -> None:
+        cap = self.get_capacity()
+        _check(line_ids.numel() == cap and lru.numel() == cap, "state tensors have capacity entries")
+        dev = f"cuda:{self._device}"
+        line_ids = line_ids.to(dev, torch.int64).contiguous()
+        lru = lru.to(dev, torch.int32).contiguous()
+        _lib.check(self._lib.hb_index_import(self._h, line_ids.data_ptr(), lru.data_ptr(),
+                                             _lib.stream_ptr()))
+
+    @property
+    def handle(self) -> C.c_void_p:
+        return self._h
+
+
+# ---------------------------------------------------------------------------------------
+# host pinning: src/cuda/pin_memory.cu:9-26
+# ---------------------------------------------------------------------------------------
+_PINNED: dict[int, int] = {}
+
+
+def _cudart():
+    return torch.cuda.cudart()
+
+
+def cudaPin(tensor: torch.Tensor) -> None:
+    ptr_, size = tensor.data_ptr(), tensor.numel() * tensor.element_size()
+    cudaPinPtr(ptr_, size)
+
+
+def cudaUnpin(tensor: torch.Tensor) -> None:
+    cudaUnpinPtr(tensor.data_ptr())
+
+
+def cudaPinPtr(ptr: int, size: int) -> None:
+    err = _cudart().cudaHostRegister(ptr, size, 0)
+    if int(err) != 0:
+        raise RuntimeError(f"cudaHostRegister failed with error {int(err)}")
+    _PINNED[ptr] = size
+
+
+def cudaUnpinPtr(ptr: int) -> None:
+    err = _cudart().cudaHostUnregister(ptr)
+    if int(err) != 0:
+        raise RuntimeError(f"cudaHostUnregister failed with error {int(err)}")
+    _PINNED.pop(ptr, None)
+
+
+# ---------------------------------------------------------------------------------------
+# row movers: src/cuda/ops.h:15-31
+# ---------------------------------------------------------------------------------------
+def cudaFetch(src, src_index, dst, dst_index, mover: int = MOVER_AUTO) -> None:
+    """dst[dst_index] = src[src_index] (src/cuda/uva_fetch.cu:28-45)."""
+    _check(src.size(1) == dst.size(1), "src.size(1) == dst.size(1)")
+    _check(dst_index.numel() == src_index.numel(), "dst_index.numel() == src_index.numel()")
+    _check_float(src)
+    _check(dst_index.dtype == src_index.dtype, "index dtypes match")
+    lib = _lib.load()
+    _lib.check(lib.hb_rows_gather(_dev_ptr(src, "src"), _dev_ptr(src_index, "src_index"),
+                                  _dev_ptr(dst, "dst"), _dev_ptr(dst_index, "dst_index"),
+                                  src_index.numel(), _row_bytes(src), _idx_bytes(src_index), mover,
+                                  _lib.stream_ptr()))
+
+
+def cudaFetch2(src, src_index, dst, mover: int = MOVER_AUTO) -> None:
+    """dst[i] = src[src_index[i]], 1-D or 2-D (src/cuda/uva_fetch.cu:72-106)."""
+    _check(src.dim() in (1, 2), "src.sizes().size() == 1 || src.sizes().size() == 2")
+    _check(src.dim() == dst.dim(), "src.sizes().size() == dst.sizes().size()")
+    if src.dim() == 2:
+        _check(src.size(1) == dst.size(1), "src.size(1) == dst.size(1)")
+    _check_float(src)
+    lib = _lib.load()
+    _lib.check(lib.hb_rows_gather(_dev_ptr(src, "src"), _dev_ptr(src_index, "src_index"),
+                                  _dev_ptr(dst, "dst"), None, src_index.numel(), _row_bytes(src),
+                                  _idx_bytes(src_index), mover, _lib.stream_ptr()))
+
+
+def cudaFetchWithCache2(cpu_src, gpu_src, src_index, index_map, dst, found=None) -> None:
+    """Cached fetch through a dense index map (src/cuda/uva_fetch.cu:149-192)."""
+    _check(gpu_src.dim() in (1, 2), "gpu_src.sizes().size() == 1 || gpu_src.sizes().size() == 2")
+    _check(gpu_src.dim() == cpu_src.dim(), "gpu_src.sizes().size() == cpu_src.sizes().size()")
+    _check(gpu_src.dim() == dst.dim(), "gpu_src.sizes().size() == dst.sizes().size()")
+    if gpu_src.dim() == 2:
+        _check(gpu_src.size(1) == cpu_src.size(1), "gpu_src.size(1) == cpu_src.size(1)")
+        _check(gpu_src.size(1) == dst.size(1), "gpu_src.size(1) == dst.size(1)")
+    _check_float(gpu_src)
+    _check(src_index.dtype == index_map.dtype, "index dtypes match")
+    lib = _lib.load()
+    _lib.check(lib.hb_rows_gather_cached(_dev_ptr(cpu_src, "cpu_src"), _dev_ptr(gpu_src, "gpu_src"),
+                                         _dev_ptr(src_index, "src_index"),
+                                         _dev_ptr(index_map, "index_map"), _dev_ptr(dst, "dst"),
+                                         _lib.ptr(found), src_index.numel(), _row_bytes(gpu_src),
+                                         _idx_bytes(src_index), _lib.stream_ptr()))
+
+
+def cudaSet(src, dst, dst_index, mover: int = MOVER_AUTO) -> None:
+    """dst[dst_index[i]] = src[i] (src/cuda/uva_set.cu:35-69)."""
+    _check(src.dim() in (1, 2), "src.sizes().size() == 1 || src.sizes().size() == 2")
+    _check(src.dim() == dst.dim(), "src.sizes().size() == dst.sizes().size()")
+    if src.dim() == 2:
+        _check(src.size(1) == dst.size(1), "src.size(1) == dst.size(1)")
+    _check_float(src)
+    lib = _lib.load()
+    _lib.check(lib.hb_rows_scatter(_dev_ptr(src, "src"), _dev_ptr(dst, "dst"),
+                                   _dev_ptr(dst_index, "dst_index"), dst_index.numel(),
+                                   _row_bytes(src), _idx_bytes(dst_index), mover, _lib.stream_ptr()))
+
+
+def cudaSetWithCache(src, cpu_dst, gpu_dst, dst_index, index_map) -> None:
+    """Cached set through a dense index map (src/cuda/uva_set.cu:112-154)."""
+    _check(gpu_dst.dim() in (1, 2), "gpu_dst.sizes().size() == 1 || gpu_dst.sizes().size() == 2")
+    _check(gpu_dst.dim() == cpu_dst.dim(), "gpu_dst.sizes().size() == cpu_dst.sizes().size()")
+    _check(gpu_dst.dim() == src.dim(), "gpu_dst.sizes().size() == src.sizes().size()")
+    if gpu_dst.dim() == 2:
+        _check(gpu_dst.size(1) == cpu_dst.size(1), "gpu_dst.size(1) == cpu_dst.size(1)")
+        _check(gpu_dst.size(1) == src.size(1), "gpu_dst.size(1) == src.size(1)")
+    _check_float(gpu_dst)
+    _check(dst_index.dtype == index_map.dtype, "index dtypes match")
+    lib = _lib.load()
+    _lib.check(lib.hb_rows_scatter_cached(_dev_ptr(src, "src"), _dev_ptr(cpu_dst, "cpu_dst"),
+                                          _dev_ptr(gpu_dst, "gpu_dst"),
+                                          _dev_ptr(dst_index, "dst_index"),
+                                          _dev_ptr(index_map, "index_map"), dst_index.numel(),
+                                          _row_bytes(gpu_dst), _idx_bytes(dst_index),
+                                          _lib.stream_ptr()))
+
+
+def cudaCombine(src, dst, dst_index, mover: int = MOVER_AUTO) -> None:
+    """dst[dst_index[i]] = src[i] (src/cuda/uva_fetch.cu:212-228)."""
+    _check(src.size(1) == dst.size(1), "src.size(1) == dst.size(1)")
+    _check_float(src)
+    lib = _lib.load()
+    _lib.check(lib.hb_rows_scatter(_dev_ptr(src, "src"), _dev_ptr(dst, "dst"),
+                                   _dev_ptr(dst_index, "dst_index"), dst_index.numel(),
+                                   _row_bytes(src), _idx_bytes(dst_index), mover, _lib.stream_ptr()))
+
+
+# ---------------------------------------------------------------------------------------
+# split and owner search: src/cuda/ops.h:11,35-41
+# ---------------------------------------------------------------------------------------
+def cudaSplit(ids: torch.Tensor, mask: torch.Tensor):
+    """[local_mask, remote_hot_mask, remote_cold_mask] (src/cuda/split.cu:12-56)."""
+    _check(ids.is_cuda and mask.is_cuda, "ids and mask are CUDA tensors")
+    _check(ids.dtype == torch.int64, "ids.dtype == int64")
+    _check(mask.dtype == torch.int8, "mask.dtype == int8")
+    n = ids.numel()
+    out = [torch.zeros(n, dtype=torch.bool, device=ids.device) for _ in range(3)]
+    lib = _lib.load()
+    _lib.check(lib.hb_split_masks(ids.contiguous().data_ptr(), n, mask.data_ptr(),
+                                  out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(),
+                                  _lib.stream_ptr()))
+    return out
+
+
+def cudaReminder(input: torch.Tensor, local_num_gpus: int) -> torch.Tensor:
+    """in % local_num_gpus (src/cuda/binary_search.cu:76-89)."""
+    out = torch.empty_like(input)
+    lib = _lib.load()
+    _lib.check(lib.hb_owner_mod(_dev_ptr(input, "in"), input.size(0), _idx_bytes(input),
+                                int(local_num_gpus), out.data_ptr(), _lib.stream_ptr()))
+    return out
+
+
+def cudaBinarySearch(input: torch.Tensor, range_partition: torch.Tensor,
+                     local_num_gpus: int) -> torch.Tensor:
+    """(upper_bound(range_partition, in) - 1) * g + in % g (src/cuda/binary_search.cu:45-59)."""
+    _check(input.dtype == range_partition.dtype, "in and range_partition dtypes match")
+    out = torch.empty_like(input)
+    lib = _lib.load()
+    _lib.check(lib.hb_owner_range(_dev_ptr(input, "in"), input.size(0), _idx_bytes(input),
+                                  _dev_ptr(range_partition, "range_partition"),
+                                  range_partition.size(0), int(local_num_gpus), out.data_ptr(),
+                                  _lib.stream_ptr()))
+    return out
+
+
+def cudaBinarySearch2(input: torch.Tensor, range: torch.Tensor) -> torch.Tensor:
+    """upper_bound(range, in) (src/cuda/binary_search.cu:61-74)."""
+    _check(input.dtype == range.dtype, "in and range dtypes match")
+    out = torch.empty_like(input)
+    lib = _lib.load()
+    _lib.check(lib.hb_upper_bound(_dev_ptr(input, "in"), input.size(0), _idx_bytes(input),
+                                  _dev_ptr(range, "range"), range.size(0), out.data_ptr(),
+                                  _lib.stream_ptr()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# new entry points (no counterpart name in the reference module)
+# ---------------------------------------------------------------------------------------
+def cudaLookupFetch(index: IndexCache, ids, cache_rows, backing_rows, out_rows=None,
+                    mode: int | None = None, mover: int = MOVER_AUTO, want_locs: bool = True):
+    """Fused IndexCache lookup + cached fetch: returns (out_rows, locs, found)."""
+    _check(ids.is_cuda and ids.dtype == torch.int64, "ids is a CUDA int64 tensor")
+    ids = ids.contiguous()
+    n = ids.numel()
+    if out_rows is None:
+        out_rows = torch.empty((n, cache_rows.size(1)), dtype=cache_rows.dtype, device=ids.device)
+    _check(out_rows.size(1) == cache_rows.size(1), "out_rows.size(1) == cache_rows.size(1)")
+    if backing_rows is not None:
+        _check(backing_rows.size(1) == cache_rows.size(1), "backing_rows.size(1) == cache_rows.size(1)")
+    locs = torch.empty(n, dtype=torch.int64, device=ids.device) if want_locs else None
+    found = torch.empty(n, dtype=torch.bool, device=ids.device)
+    lib = _lib.load()
+    _lib.check(lib.hb_lookup_fetch(index.handle, ids.data_ptr(), n, _dev_ptr(cache_rows, "cache_rows"),
+                                   None if backing_rows is None else _dev_ptr(backing_rows, "backing_rows"),
+                                   _row_bytes(cache_rows), out_rows.data_ptr(), _lib.ptr(locs),
+                                   found.data_ptr(), index.lookup_mode if mode is None else mode,
+                                   mover, _lib.stream_ptr()))
+    return out_rows, locs, found
+
+
+def cudaAccumulate(src, dst, dst_index, cnt=None) -> None:
+    """dst[dst_index[i]] += src[i]; cnt[dst_index[i]] += 1 (unique indices, fp32)."""
+    _check(src.dtype == torch.float32 and dst.dtype == torch.float32, "fp32 rows")
+    _check(src.dim() == 2 and dst.dim() == 2 and src.size(1) == dst.size(1), "src.size(1) == dst.size(1)")
+    if cnt is not None:
+        _check(cnt.dtype == torch.int32, "cnt.dtype == int32")
+    lib = _lib.load()
+    _lib.check(lib.hb_rows_accumulate_f32(src.data_ptr(), dst.data_ptr(), dst_index.data_ptr(),
+                                          _lib.ptr(cnt), dst_index.numel(), src.size(1),
+                                          _idx_bytes(dst_index), _lib.stream_ptr()))
+
+
+def cudaSplitCompact(ids: torch.Tensor, mask: torch.Tensor, want_masks: bool = True):
+    """cudaSplit fused with the nonzero() calls that follow it: returns
+    (masks or None, index tensor, counts[3] on the device).  index holds the positions of the
+    local ids, then the remote-hot ones, then the remote-cold ones."""
+    _check(ids.is_cuda and ids.dtype == torch.int64, "ids is a CUDA int64 tensor")
+    _check(mask.dtype == torch.int8, "mask.dtype == int8")
+    n = ids.numel()
+    masks = [torch.zeros(n, dtype=torch.bool, device=ids.device) for _ in range(3)] if want_masks else None
+    index = torch.empty(n, dtype=torch.int64, device=ids.device)
+    counts = torch.empty(3, dtype=torch.int64, device=ids.device)
+    lib = _lib.load()
+    ws = _lib.workspace(lib.hb_partition_workspace_bytes(n, 3))
+    mp = [m.data_ptr() for m in masks] if masks else [None, None, None]
+    _lib.check(lib.hb_split_compact(ids.contiguous().data_ptr(), n, mask.data_ptr(), mp[0], mp[1], mp[2],
+                                    index.data_ptr(), counts.data_ptr(), ws.data_ptr(), ws.numel(),
+                                    _lib.stream_ptr()))
+    return masks, index, counts
+
+
+def cudaBucketPack(ids, rows, cnt, num_buckets: int, range_partition=None, local_num_gpus: int | None = None):
+    """Bucket (ids, rows, cnt) by owner, stable inside a bucket.  Returns
+    (ids, rows, cnt, counts[num_buckets] on the device).  owner = id % num_buckets, or the
+    cudaBinarySearch rule when range_partition is given."""
+    _check(ids.is_cuda and ids.dtype == torch.int64, "ids is a CUDA int64 tensor")
+    n = ids.numel()
+    g = int(local_num_gpus) if local_num_gpus is not None else int(num_buckets)
+    out_ids = torch.empty_like(ids)
+    out_rows = torch.empty_like(rows) if rows is not None else None
+    out_cnt = torch.empty_like(cnt) if cnt is not None else None
+    counts = torch.empty(num_buckets, dtype=torch.int64, device=ids.device)
+    lib = _lib.load()
+    ws = _lib.workspace(lib.hb_partition_workspace_bytes(n, num_buckets))
+    _lib.check(lib.hb_bucket_pack(ids.contiguous().data_ptr(), _lib.ptr(rows), _lib.ptr(cnt), n,
+                                  _row_bytes(rows) if rows is not None else 0, int(num_buckets),
+                                  _lib.ptr(range_partition),
+                                  range_partition.numel() if range_partition is not None else 0, g,
+                                  out_ids.data_ptr(), _lib.ptr(out_rows), _lib.ptr(out_cnt),
+                                  counts.data_ptr(), ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
+    return out_ids, out_rows, out_cnt, counts
+
+
+def cudaGradSplit3(ids, rows, hot_mask, local_mask):
+    """(ids, rows) reordered as hot | cold-local | cold-remote; counts[3] on the device."""
+    _check(ids.is_cuda and ids.dtype == torch.int64, "ids is a CUDA int64 tensor")
+    _check(hot_mask.dtype == torch.bool and local_mask.dtype == torch.bool, "bool masks")
+    n = ids.numel()
+    out_ids = torch.empty_like(ids)
+    out_rows = torch.empty_like(rows)
+    counts = torch.empty(3, dtype=torch.int64, device=ids.device)
+    lib = _lib.load()
+    ws = _lib.workspace(lib.hb_partition_workspace_bytes(n, 3))
+    _lib.check(lib.hb_grad_split3(ids.contiguous().data_ptr(), rows.data_ptr(), hot_mask.data_ptr(),
+                                  local_mask.data_ptr(), n, _row_bytes(rows), out_ids.data_ptr(),
+                                  out_rows.data_ptr(), counts.data_ptr(), ws.data_ptr(), ws.numel(),
+                                  _lib.stream_ptr()))
+    return out_ids, out_rows, counts
+
+
+def cudaUniqueSegSum(ids, grads, cnt=None, mean: bool = False, id_bits: int = 64, sync: bool = True):
+    """Sorted unique ids, per-id fp32 sum (or mean) of the rows, per-id counts;
+    deterministic.  With sync=True the outputs are sliced to the number of unique ids
+    (one device-to-host read, as torch.unique does); with sync=False the full-size
+    buffers and the device count are returned."""
+    _check(ids.is_cuda and ids.dtype == torch.int64, "ids is a CUDA int64 tensor")
+    _check(grads.dtype == torch.float32 and grads.dim() == 2, "grads is a 2-D fp32 tensor")
+    _check(grads.size(0) == ids.numel(), "grads.size(0) == ids.numel()")
+    n, dim = ids.numel(), grads.size(1)
+    dev = ids.device
+    uniq = torch.empty(n, dtype=torch.int64, device=dev)
+    sums = torch.empty((n, dim), dtype=torch.float32, device=dev)
+    counts = torch.empty(n, dtype=torch.int64, device=dev)
+    num = torch.zeros(1, dtype=torch.int64, device=dev)
+    lib = _lib.load()
+    ws = _lib.workspace(lib.hb_unique_segsum_workspace_bytes(n, dim))
+    _lib.check(lib.hb_unique_segsum_f32(ids.contiguous().data_ptr(), grads.contiguous().data_ptr(),
+                                        _lib.ptr(cnt), n, dim, int(id_bits), int(mean),
+                                        uniq.data_ptr(), sums.data_ptr(), counts.data_ptr(),
+                                        num.data_ptr(), ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
+    if not sync:
+        return uniq, sums, counts, num
+    u = int(num.item())
+    return uniq[:u], sums[:u], counts[:u]

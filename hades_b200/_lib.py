@@ -1,0 +1,130 @@
+"""ctypes binding of ``libhades_b200.so`` (see ``include/hades_b200.h``).
+
+There is no CPU or PyTorch fallback: if the library is missing, or a call fails, an
+exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "libhades_b200.so"
+
+HB_OK = 0
+LOOKUP_SETASSOC = 0
+LOOKUP_SORTED = 1
+MOVER_AUTO = 0
+MOVER_LSU = 1
+MOVER_BULK = 2
+
+_p = C.c_void_p
+_i64 = C.c_int64
+_int = C.c_int
+_sz = C.c_size_t
+_f32 = C.c_float
+
+# name -> (restype, argtypes); every symbol that include/hades_b200.h declares
+PROTOTYPES: dict[str, tuple] = {
+    "hb_last_error": (C.c_char_p, []),
+    "hb_version": (_int, []),
+    "hb_launch_count": (_i64, []),
+    "hb_device_status": (_int, [_p, _p]),
+    "hb_index_create": (_int, [_i64, _p]),
+    "hb_index_destroy": (_int, [_p]),
+    "hb_index_size": (_i64, [_p]),
+    "hb_index_capacity": (_i64, [_p]),
+    "hb_index_space": (_i64, [_p]),
+    "hb_index_lines": (_i64, [_p]),
+    "hb_index_valid_entries": (_int, [_p, _p, _p]),
+    "hb_index_add_workspace_bytes": (_sz, [_i64]),
+    "hb_index_add": (_int, [_p, _p, _i64, _p, _p, _sz, _p]),
+    "hb_index_lookup": (_int, [_p, _p, _i64, _p, _p, _int, _p]),
+    "hb_index_touch_lru_workspace_bytes": (_sz, [_i64]),
+    "hb_index_touch_lru": (_int, [_p, _p, _i64, _p, _sz, _p]),
+    "hb_index_reset": (_int, [_p, _p, _i64, _p]),
+    "hb_index_getall": (_int, [_p, _p, _p, _i64, _p, _p]),
+    "hb_index_build_sorted": (_int, [_p, _p]),
+    "hb_index_export": (_int, [_p, _p, _p, _p]),
+    "hb_index_import": (_int, [_p, _p, _p, _p]),
+    "hb_rows_gather": (_int, [_p, _p, _p, _p, _i64, _i64, _int, _int, _p]),
+    "hb_rows_scatter": (_int, [_p, _p, _p, _i64, _i64, _int, _int, _p]),
+    "hb_rows_gather_cached": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _int, _p]),
+    "hb_rows_scatter_cached": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _int, _p]),
+    "hb_rows_accumulate_f32": (_int, [_p, _p, _p, _p, _i64, _i64, _int, _p]),
+    "hb_lookup_fetch": (_int, [_p, _p, _i64, _p, _p, _i64, _p, _p, _p, _int, _int, _p]),
+    "hb_partition_workspace_bytes": (_sz, [_i64, _int]),
+    "hb_split_masks": (_int, [_p, _i64, _p, _p, _p, _p, _p]),
+    "hb_split_compact": (_int, [_p, _i64, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "hb_owner_mod": (_int, [_p, _i64, _int, _i64, _p, _p]),
+    "hb_owner_range": (_int, [_p, _i64, _int, _p, _i64, _i64, _p, _p]),
+    "hb_upper_bound": (_int, [_p, _i64, _int, _p, _i64, _p, _p]),
+    "hb_bucket_pack": (_int, [_p, _p, _p, _i64, _i64, _int, _p, _i64, _i64, _p, _p, _p, _p, _p, _sz, _p]),
+    "hb_grad_split3": (_int, [_p, _p, _p, _p, _i64, _i64, _p, _p, _p, _p, _sz, _p]),
+    "hb_unique_segsum_workspace_bytes": (_sz, [_i64, _i64]),
+    "hb_unique_segsum_f32": (_int, [_p, _p, _p, _i64, _i64, _int, _int, _p, _p, _p, _p, _p, _sz, _p]),
+}
+
+_LIB: C.CDLL | None = None
+
+
+class HadesError(RuntimeError):
+    """A libhades_b200 call returned a non-zero status."""
+
+
+def load() -> C.CDLL:
+    """Load the C-ABI library; fails loudly when it has not been built."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m hades_b200._build` "
+            "(nvcc, sm_100a). hades_b200 has no CPU fallback.")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in PROTOTYPES.items():
+        fn = getattr(lib, name)  # AttributeError here = header and library out of sync
+        fn.restype = res
+        fn.argtypes = args
+    _LIB = lib
+    return lib
+
+
+def check(rc: int) -> None:
+    if rc != HB_OK:
+        msg = load().hb_last_error().decode(errors="replace")
+        raise HadesError(f"libhades_b200 status {rc}: {msg}")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+_WORKSPACES: dict[int, torch.Tensor] = {}
+
+
+def workspace(nbytes: int) -> torch.Tensor:
+    """A per-device scratch buffer of at least nbytes, reused across calls on the
+    current stream."""
+    dev = torch.cuda.current_device()
+    ws = _WORKSPACES.get(dev)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(int(nbytes * 1.25), 1 << 20), dtype=torch.uint8, device=f"cuda:{dev}")
+        _WORKSPACES[dev] = ws
+    return ws
+
+
+def device_status() -> int:
+    out = C.c_int(0)
+    check(load().hb_device_status(C.byref(out), stream_ptr()))
+    return out.value
+
+
+def launch_count() -> int:
+    return load().hb_launch_count()

@@ -1,0 +1,260 @@
+// Hot/cold split (+ compaction), owner search, owner bucketing ("pack") and the
+// 3-way gradient split.
+#include "partition_core.cuh"
+
+namespace hb {
+namespace {
+
+constexpr int kBlock = 256;
+
+// ---- hot/cold split masks: src/cuda/split.cu:34-44 -------------------------------
+__global__ void split_masks_kernel(const int64_t* __restrict__ ids, int64_t n,
+                                   const int8_t* __restrict__ table, uint8_t* __restrict__ local,
+                                   uint8_t* __restrict__ hot, uint8_t* __restrict__ cold) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int8_t v = __ldg(table + __ldg(ids + i));
+  local[i] = v == 0;
+  hot[i] = v == 1;
+  cold[i] = v == 2;
+}
+
+// split + the nonzero() calls that follow it in python/EmbCache/dist_emb.py:174-191
+struct SplitCompactPolicy {
+  const int64_t* ids;
+  const int8_t* table;
+  uint8_t* local;
+  uint8_t* hot;
+  uint8_t* cold;
+  int64_t* index_out;
+  int64_t n;
+  __device__ __forceinline__ int classify(int64_t i) const {
+    const int8_t v = __ldg(table + __ldg(ids + i));
+    return (v >= 0 && v <= 2) ? (int)v : -1;
+  }
+  __device__ __forceinline__ void emit(int64_t i, int c, int64_t pos, int64_t start,
+                                       bool active) const {
+    if (active) index_out[start + pos] = i;
+    if (local && i < n) {  // any other table value leaves all three masks false
+      local[i] = c == 0;
+      hot[i] = c == 1;
+      cold[i] = c == 2;
+    }
+  }
+};
+
+// ---- owner search: src/cuda/binary_search.cu ---------------------------------------
+template <typename T>
+__device__ __forceinline__ int64_t upper_bound_dev(const T* a, int64_t n, T v) {
+  int64_t lo = 0, hi = n;
+  while (lo < hi) {
+    const int64_t mid = (lo + hi) >> 1;
+    if (a[mid] <= v) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+template <typename T>
+__global__ void owner_mod_kernel(const T* __restrict__ in, int64_t n, int64_t g,
+                                 T* __restrict__ out) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i < n) out[i] = (T)(in[i] % (T)g);
+}
+
+template <typename T>
+__global__ void owner_range_kernel(const T* __restrict__ in, int64_t n,
+                                   const T* __restrict__ range, int64_t parts, int64_t g,
+                                   T* __restrict__ out) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const T v = in[i];
+  out[i] = (T)((upper_bound_dev(range, parts, v) - 1) * g + v % (T)g);
+}
+
+template <typename T>
+__global__ void upper_bound_kernel(const T* __restrict__ in, int64_t n,
+                                   const T* __restrict__ sorted, int64_t m, T* __restrict__ out) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i < n) out[i] = (T)upper_bound_dev(sorted, m, in[i]);
+}
+
+// ---- owner bucketing: python/EmbCache/sparse_optim.py:36-55 --------------------------
+struct OwnerFn {
+  const int64_t* range;  // nullable: owner = id % g
+  int64_t parts;
+  int64_t g;
+  __device__ __forceinline__ int operator()(int64_t id) const {
+    if (!range) return (int)mod_nonneg(id, g);
+    return (int)((upper_bound_dev(range, parts, id) - 1) * g + mod_nonneg(id, g));
+  }
+};
+
+struct BucketPackPolicy {
+  OwnerFn owner;
+  int num_buckets;
+  const int64_t* ids;
+  const char* rows;
+  const int64_t* cnt;
+  int64_t row_bytes;
+  int vb;
+  int64_t* out_ids;
+  char* out_rows;
+  int64_t* out_cnt;
+  __device__ __forceinline__ int classify(int64_t i) const {
+    const int64_t id = __ldg(ids + i);
+    if (id < 0) return -1;
+    const int o = owner(id);
+    return (o >= 0 && o < num_buckets) ? o : -1;
+  }
+  __device__ __forceinline__ void emit(int64_t i, int, int64_t pos, int64_t start,
+                                       bool active) const {
+    const int64_t d = start + pos;
+    if (active) {
+      out_ids[d] = ids[i];
+      if (cnt) out_cnt[d] = cnt[i];
+    }
+    if (rows)
+      warp_move_rows(rows + i * row_bytes, out_rows + d * row_bytes, active, row_bytes, vb);
+  }
+};
+
+// ---- 3-way gradient split: python/EmbCache/sparse_optim.py:243-259 --------------------
+// class 0 = hot, 1 = cold local (~hot & local), 2 = cold remote (~hot & ~local)
+struct GradSplitPolicy {
+  const int64_t* ids;
+  const char* rows;
+  const uint8_t* hot;
+  const uint8_t* local;
+  int64_t row_bytes;
+  int vb;
+  int64_t* out_ids;
+  char* out_rows;
+  __device__ __forceinline__ int classify(int64_t i) const {
+    if (hot[i]) return 0;
+    return local[i] ? 1 : 2;
+  }
+  __device__ __forceinline__ void emit(int64_t i, int, int64_t pos, int64_t start,
+                                       bool active) const {
+    const int64_t d = start + pos;
+    if (active) out_ids[d] = ids[i];
+    warp_move_rows(rows + i * row_bytes, out_rows + d * row_bytes, active, row_bytes, vb);
+  }
+};
+
+int grid_for(int64_t n) { return (int)(n > 0 ? ceil_div(n, kBlock) : 1); }
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" {
+
+size_t hb_partition_workspace_bytes(int64_t n, int num_classes) {
+  return partition_workspace_bytes(n, num_classes);
+}
+
+int hb_split_masks(const int64_t* ids, int64_t n, const int8_t* mask_table, uint8_t* local_mask,
+                   uint8_t* hot_mask, uint8_t* cold_mask, hb_stream_t stream) {
+  HB_CHECK_ARG(n >= 0, "hb_split_masks: negative n");
+  HB_CHECK_ARG(n == 0 || (ids && mask_table && local_mask && hot_mask && cold_mask),
+               "hb_split_masks: null argument");
+  if (n == 0) return HB_OK;
+  HB_LAUNCH(split_masks_kernel, grid_for(n), kBlock, 0, (cudaStream_t)stream, ids, n, mask_table,
+            local_mask, hot_mask, cold_mask);
+  return HB_OK;
+}
+
+int hb_split_compact(const int64_t* ids, int64_t n, const int8_t* mask_table, uint8_t* local_mask,
+                     uint8_t* hot_mask, uint8_t* cold_mask, int64_t* index_out, int64_t* counts,
+                     void* workspace, size_t workspace_bytes, hb_stream_t stream) {
+  HB_CHECK_ARG(n >= 0 && n < ((int64_t)1 << 31), "hb_split_compact: n out of range");
+  HB_CHECK_ARG(counts != nullptr, "hb_split_compact: counts is null");
+  HB_CHECK_ARG(n == 0 || (ids && mask_table && index_out), "hb_split_compact: null argument");
+  const bool masks = local_mask || hot_mask || cold_mask;
+  HB_CHECK_ARG(!masks || (local_mask && hot_mask && cold_mask),
+               "hb_split_compact: give all three masks or none");
+  SplitCompactPolicy pol{ids, mask_table, local_mask, hot_mask, cold_mask, index_out, n};
+  return run_partition(pol, n, 3, workspace, workspace_bytes, counts, (cudaStream_t)stream);
+}
+
+#define HB_INT_SWITCH(idx_bytes, T, ...) \
+  if ((idx_bytes) == 8) {                \
+    typedef int64_t T;                   \
+    __VA_ARGS__                          \
+  } else {                               \
+    typedef int32_t T;                   \
+    __VA_ARGS__                          \
+  }
+
+int hb_owner_mod(const void* in, int64_t n, int idx_bytes, int64_t g, void* out,
+                 hb_stream_t stream) {
+  HB_CHECK_ARG(n >= 0 && g > 0, "hb_owner_mod: bad sizes");
+  HB_CHECK_ARG(idx_bytes == 4 || idx_bytes == 8, "hb_owner_mod: ids must be int32 or int64");
+  HB_CHECK_ARG(n == 0 || (in && out), "hb_owner_mod: null argument");
+  if (n == 0) return HB_OK;
+  HB_INT_SWITCH(idx_bytes, T, {
+    HB_LAUNCH(owner_mod_kernel<T>, grid_for(n), kBlock, 0, (cudaStream_t)stream, (const T*)in, n, g,
+              (T*)out);
+  })
+  return HB_OK;
+}
+
+int hb_owner_range(const void* in, int64_t n, int idx_bytes, const void* range_partition,
+                   int64_t num_part, int64_t g, void* out, hb_stream_t stream) {
+  HB_CHECK_ARG(n >= 0 && g > 0 && num_part > 0, "hb_owner_range: bad sizes");
+  HB_CHECK_ARG(idx_bytes == 4 || idx_bytes == 8, "hb_owner_range: ids must be int32 or int64");
+  HB_CHECK_ARG(n == 0 || (in && out && range_partition), "hb_owner_range: null argument");
+  if (n == 0) return HB_OK;
+  HB_INT_SWITCH(idx_bytes, T, {
+    HB_LAUNCH(owner_range_kernel<T>, grid_for(n), kBlock, 0, (cudaStream_t)stream, (const T*)in, n,
+              (const T*)range_partition, num_part, g, (T*)out);
+  })
+  return HB_OK;
+}
+
+int hb_upper_bound(const void* in, int64_t n, int idx_bytes, const void* sorted, int64_t m,
+                   void* out, hb_stream_t stream) {
+  HB_CHECK_ARG(n >= 0 && m >= 0, "hb_upper_bound: bad sizes");
+  HB_CHECK_ARG(idx_bytes == 4 || idx_bytes == 8, "hb_upper_bound: values must be int32 or int64");
+  HB_CHECK_ARG(n == 0 || (in && out && (m == 0 || sorted)), "hb_upper_bound: null argument");
+  if (n == 0) return HB_OK;
+  HB_INT_SWITCH(idx_bytes, T, {
+    HB_LAUNCH(upper_bound_kernel<T>, grid_for(n), kBlock, 0, (cudaStream_t)stream, (const T*)in, n,
+              (const T*)sorted, m, (T*)out);
+  })
+  return HB_OK;
+}
+
+int hb_bucket_pack(const int64_t* ids, const void* rows, const int64_t* cnt, int64_t n,
+                   int64_t row_bytes, int num_buckets, const int64_t* range_partition,
+                   int64_t num_part, int64_t g, int64_t* out_ids, void* out_rows, int64_t* out_cnt,
+                   int64_t* counts, void* workspace, size_t workspace_bytes, hb_stream_t stream) {
+  HB_CHECK_ARG(n >= 0 && n < ((int64_t)1 << 31), "hb_bucket_pack: n out of range");
+  HB_CHECK_ARG(g > 0 && num_buckets > 0, "hb_bucket_pack: bad bucket parameters");
+  HB_CHECK_ARG(counts != nullptr, "hb_bucket_pack: counts is null");
+  HB_CHECK_ARG(n == 0 || (ids && out_ids), "hb_bucket_pack: null ids");
+  HB_CHECK_ARG(!rows || (out_rows && row_bytes > 0), "hb_bucket_pack: rows without output");
+  HB_CHECK_ARG(!cnt || out_cnt, "hb_bucket_pack: cnt without output");
+  HB_CHECK_ARG(!range_partition || num_part > 0, "hb_bucket_pack: empty range partition");
+  BucketPackPolicy pol{{range_partition, num_part, g}, num_buckets, ids, (const char*)rows, cnt,
+                       row_bytes, rows ? payload_vec_bytes(row_bytes, rows, out_rows) : 1,
+                       out_ids, (char*)out_rows, out_cnt};
+  return run_partition(pol, n, num_buckets, workspace, workspace_bytes, counts,
+                       (cudaStream_t)stream);
+}
+
+int hb_grad_split3(const int64_t* ids, const void* rows, const uint8_t* hot_mask,
+                   const uint8_t* local_mask, int64_t n, int64_t row_bytes, int64_t* out_ids,
+                   void* out_rows, int64_t* counts, void* workspace, size_t workspace_bytes,
+                   hb_stream_t stream) {
+  HB_CHECK_ARG(n >= 0 && n < ((int64_t)1 << 31) && row_bytes > 0, "hb_grad_split3: bad sizes");
+  HB_CHECK_ARG(counts != nullptr, "hb_grad_split3: counts is null");
+  HB_CHECK_ARG(n == 0 || (ids && rows && hot_mask && local_mask && out_ids && out_rows),
+               "hb_grad_split3: null argument");
+  GradSplitPolicy pol{ids, (const char*)rows, hot_mask, local_mask, row_bytes,
+                      payload_vec_bytes(row_bytes, rows, out_rows), out_ids, (char*)out_rows};
+  return run_partition(pol, n, 3, workspace, workspace_bytes, counts, (cudaStream_t)stream);
+}
+
+}  // extern "C"

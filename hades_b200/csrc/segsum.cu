@@ -1,0 +1,480 @@
+// Hot-node local aggregation: sorted unique ids, per-id fp32 sum (or mean) of the
+// duplicate-id gradient rows, per-id counts.  Replaces only_unique_grads /
+// unique_grads (python/EmbCache/sparse_optim.py:132-157: torch.unique +
+// index_add_).
+//
+// Deterministic, no floating-point atomics:
+//   1. radix sort of (id, position) pairs (CUB), stable
+//   2. run heads compacted into unique ids + run starts (partition core, 1 class)
+//   3. main pass: the sorted positions are cut into fixed chunks of R rows; a
+//      group of G lanes (G*4 floats wide) walks its chunk in order, reading
+//      gradient rows through the permutation, broadcasting positions with warp
+//      shuffles and adding in registers.  A run that lies inside the chunk is
+//      written straight to its output row.  A run that crosses a chunk boundary
+//      leaves a partial row (head partial: the run began earlier; tail partial:
+//      it goes on) and the chunk where it begins enters it in a fix-up list.
+//   4. fix-up: partials of a crossing run are added in chunk order (short runs by
+//      one lane group, long runs by a whole CTA in a fixed strided+sequential
+//      order).
+// The order of additions depends only on the sorted order and the chunk size, so
+// two runs on the same input give the same bits.  Counts are integers, so they
+// use atomicAdd (order cannot change an integer sum).
+#include <cub/device/device_radix_sort.cuh>
+
+#include "partition_core.cuh"
+
+namespace hb {
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kShortSpan = 16;   // crossing runs over at most this many chunks: group fix-up
+constexpr int kLongBlock = 512;
+
+struct SegArgs {
+  const int64_t* keys;        // sorted ids [n]
+  const uint32_t* perm;       // position in the input of each sorted element [n]
+  const int64_t* run_start;   // [U] first sorted position of each run
+  const int64_t* num_runs;    // device scalar U
+  const float* grads;         // [n][dim]
+  const int64_t* cnt_in;      // nullable [n]
+  int64_t n;
+  int64_t dim;
+  int64_t col0;               // first column of this pass
+  int cols;                   // columns of this pass (<= 32*VEC*VPL)
+  int chunk;                  // R
+  int64_t num_chunks;
+  int mean;                   // divide by the count
+  float* sums;                // [U][dim]
+  unsigned long long* counts; // [U], zeroed before the main pass
+  float* head_part;           // [num_chunks][cols]
+  float* tail_part;           // [num_chunks][cols]
+  int2* short_list;           // (chunk, run)
+  int2* long_list;
+  int* list_counts;           // [0] short, [1] long
+};
+
+template <int VEC> struct VecF;
+template <> struct VecF<4> { using T = float4; };
+template <> struct VecF<1> { using T = float; };
+
+__device__ __forceinline__ void vadd(float4& a, const float4& b) {
+  a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+}
+__device__ __forceinline__ void vadd(float& a, const float& b) { a += b; }
+__device__ __forceinline__ void vzero(float4& a) { a = make_float4(0.f, 0.f, 0.f, 0.f); }
+__device__ __forceinline__ void vzero(float& a) { a = 0.f; }
+__device__ __forceinline__ void vdiv(float4& a, float d) { a.x /= d; a.y /= d; a.z /= d; a.w /= d; }
+__device__ __forceinline__ void vdiv(float& a, float d) { a /= d; }
+
+__device__ __forceinline__ int64_t run_of(const int64_t* run_start, int64_t U, int64_t pos) {
+  int64_t lo = 0, hi = U;  // upper_bound(run_start, pos) - 1
+  while (lo < hi) {
+    const int64_t mid = (lo + hi) >> 1;
+    if (__ldg(run_start + mid) <= pos) lo = mid + 1; else hi = mid;
+  }
+  return lo - 1;
+}
+
+__device__ __forceinline__ float denominator(const SegArgs& a, unsigned long long c) {
+  // unique_grads starts its counts from ones when cnt is given (sparse_optim.py:145-148)
+  return (float)(a.cnt_in ? (long long)c + 1 : (long long)c);
+}
+
+// ---- main pass -------------------------------------------------------------------
+template <int VEC, int G, int VPL>
+__global__ void __launch_bounds__(kBlock) segsum_main_kernel(SegArgs a) {
+  using V = typename VecF<VEC>::T;
+  constexpr int U = (8 / VPL) < G ? (8 / VPL) : G;  // rows whose loads are in flight together
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & (G - 1);
+  const int grp_in_warp = lane / G;
+  const unsigned grp_shift = grp_in_warp * G;
+  const unsigned grp_mask = G == 32 ? 0xffffffffu : ((1u << G) - 1u);
+  const int64_t c = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) / G;
+  const bool live = c < a.num_chunks;
+  const int64_t U_runs = *a.num_runs;
+  const int64_t j0 = live ? c * a.chunk : 0;
+  const int64_t j1 = live ? ((j0 + a.chunk < a.n) ? j0 + a.chunk : a.n) : 0;
+  const int vpr = a.cols / VEC;  // vectors per row in this pass
+
+  int64_t u = live ? run_of(a.run_start, U_runs, j0) : 0;
+  bool first_partial = live && __ldg(a.run_start + u) < j0;  // chunk starts inside a run
+  bool have = first_partial;  // a run is open
+  V acc[VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) vzero(acc[v]);
+  unsigned long long cacc = 0;
+
+  auto flush = [&](bool tail) {
+    // write the open run: complete -> output row; crossing -> partial row
+    float* dst;
+    bool complete = !first_partial && !tail;
+    if (complete) dst = a.sums + u * a.dim + a.col0;
+    else if (first_partial) dst = a.head_part + c * a.cols;
+    else dst = a.tail_part + c * a.cols;
+    if (complete && a.mean) {
+      const float d = denominator(a, cacc);
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) vdiv(acc[v], d);
+    }
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      const int k = sub + v * G;
+      if (k < vpr) reinterpret_cast<V*>(dst)[k] = acc[v];
+    }
+    if (sub == 0 && a.col0 == 0 && cacc) atomicAdd(a.counts + u, cacc);
+  };
+
+  const int steps = a.chunk / G;  // uniform trip count (chunk is a multiple of 32)
+  for (int sidx = 0; sidx < steps; ++sidx) {
+    const int64_t j = j0 + (int64_t)sidx * G + sub;
+    const bool valid = j < j1;
+    uint32_t p = 0;
+    bool head = false;
+    long long cv = 1;
+    if (valid) {
+      p = __ldg(a.perm + j);
+      const int64_t k = __ldg(a.keys + j);
+      head = j == 0 || __ldg(a.keys + j - 1) != k;
+      if (a.cnt_in) cv = __ldg(a.cnt_in + p);
+    }
+    const unsigned hb_all = __ballot_sync(0xffffffffu, head);
+    const unsigned vb_all = __ballot_sync(0xffffffffu, valid);
+    const unsigned heads = (hb_all >> grp_shift) & grp_mask;
+    const unsigned valids = (vb_all >> grp_shift) & grp_mask;
+#pragma unroll 1
+    for (int t0 = 0; t0 < G; t0 += U) {
+      V val[U][VPL];
+      long long cvs[U];
+#pragma unroll
+      for (int x = 0; x < U; ++x) {
+        const uint32_t px = __shfl_sync(0xffffffffu, p, t0 + x, G);
+        cvs[x] = __shfl_sync(0xffffffffu, cv, t0 + x, G);
+        if ((valids >> (t0 + x)) & 1u) {
+          const V* src = reinterpret_cast<const V*>(a.grads + (int64_t)px * a.dim + a.col0);
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) {
+            const int k = sub + v * G;
+            if (k < vpr) val[x][v] = __ldg(src + k);
+          }
+        }
+      }
+#pragma unroll
+      for (int x = 0; x < U; ++x) {
+        if (!((valids >> (t0 + x)) & 1u)) continue;
+        if ((heads >> (t0 + x)) & 1u) {
+          if (have) {
+            flush(false);
+            ++u;
+          }
+          first_partial = false;
+          have = true;
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) vzero(acc[v]);
+          cacc = 0;
+        }
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+          const int k = sub + v * G;
+          if (k < vpr) vadd(acc[v], val[x][v]);
+        }
+        cacc += (unsigned long long)cvs[x];
+      }
+    }
+  }
+  if (live && have) {
+    // does the open run go on after this chunk?
+    const bool tail = j1 < a.n && __ldg(a.keys + j1) == __ldg(a.keys + j1 - 1);
+    if (tail && !first_partial && sub == 0 && a.col0 == 0) {
+      // this chunk holds the head of a crossing run: enter it in a fix-up list
+      const int64_t run_end = (u + 1 < U_runs) ? __ldg(a.run_start + u + 1) : a.n;
+      const int64_t last_chunk = (run_end - 1) / a.chunk;
+      const bool is_short = (last_chunk - c) <= kShortSpan;
+      const int slot = atomicAdd(a.list_counts + (is_short ? 0 : 1), 1);
+      (is_short ? a.short_list : a.long_list)[slot] = make_int2((int)c, (int)u);
+    }
+    flush(tail);
+  }
+}
+
+// ---- fix-up of short crossing runs: one lane group per entry ---------------------------
+template <int VEC, int G, int VPL>
+__global__ void __launch_bounds__(kBlock) segsum_fix_short_kernel(SegArgs a) {
+  using V = typename VecF<VEC>::T;
+  const int sub = threadIdx.x & (G - 1);
+  const int64_t grp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) / G;
+  const int64_t ngrp = ((int64_t)gridDim.x * blockDim.x) / G;
+  const int count = a.list_counts[0];
+  const int64_t U_runs = *a.num_runs;
+  const int vpr = a.cols / VEC;
+  for (int64_t e = grp; e < count; e += ngrp) {
+    const int2 ent = a.short_list[e];
+    const int64_t c = ent.x, u = ent.y;
+    const int64_t run_end = (u + 1 < U_runs) ? __ldg(a.run_start + u + 1) : a.n;
+    const int64_t last_chunk = (run_end - 1) / a.chunk;
+    V acc[VPL];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      const int k = sub + v * G;
+      if (k < vpr) acc[v] = reinterpret_cast<const V*>(a.tail_part + c * a.cols)[k];
+    }
+    for (int64_t cc = c + 1; cc <= last_chunk; ++cc) {
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        const int k = sub + v * G;
+        if (k < vpr) vadd(acc[v], reinterpret_cast<const V*>(a.head_part + cc * a.cols)[k]);
+      }
+    }
+    if (a.mean) {
+      const float d = denominator(a, a.counts[u]);
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) vdiv(acc[v], d);
+    }
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      const int k = sub + v * G;
+      if (k < vpr) reinterpret_cast<V*>(a.sums + u * a.dim + a.col0)[k] = acc[v];
+    }
+  }
+}
+
+// ---- fix-up of long crossing runs: one CTA per entry ---------------------------------------
+// thread t owns float column (t % cols) of strand (t / cols); strand s adds the
+// partials c+1+s, c+1+s+S, ... in order; strand sums are then added 0,1,2,...
+__global__ void __launch_bounds__(kLongBlock) segsum_fix_long_kernel(SegArgs a) {
+  extern __shared__ float s_part[];  // [strands][cols]
+  const int count = a.list_counts[1];
+  const int64_t U_runs = *a.num_runs;
+  const int cols = a.cols;
+  const int strands = kLongBlock / cols;  // cols <= kLongBlock
+  for (int64_t e = blockIdx.x; e < count; e += gridDim.x) {
+    const int2 ent = a.long_list[e];
+    const int64_t c = ent.x, u = ent.y;
+    const int64_t run_end = (u + 1 < U_runs) ? __ldg(a.run_start + u + 1) : a.n;
+    const int64_t last_chunk = (run_end - 1) / a.chunk;
+    {
+      const int col = threadIdx.x % cols;
+      const int strand = threadIdx.x / cols;
+      if (strand < strands) {
+        float acc = 0.f;
+        for (int64_t cc = c + 1 + strand; cc <= last_chunk; cc += strands)
+          acc += a.head_part[cc * cols + col];
+        s_part[strand * cols + col] = acc;
+      }
+    }
+    __syncthreads();
+    for (int col = threadIdx.x; col < cols; col += kLongBlock) {
+      float acc = a.tail_part[c * cols + col];
+      for (int s = 0; s < strands; ++s) acc += s_part[s * cols + col];
+      if (a.mean) acc /= denominator(a, a.counts[u]);
+      a.sums[u * a.dim + a.col0 + col] = acc;
+    }
+    __syncthreads();
+  }
+}
+
+// ---- small helpers ----------------------------------------------------------------------------
+__global__ void iota_u32_kernel(uint32_t* p, int64_t n) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i < n) p[i] = (uint32_t)i;
+}
+
+// counts -> the denominators the reference reports (1 + sum of cnt when cnt is given)
+__global__ void finish_counts_kernel(const unsigned long long* __restrict__ raw,
+                                     const int64_t* __restrict__ num_runs, int plus_one,
+                                     int64_t* __restrict__ out, int64_t n) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i < n && i < *num_runs) out[i] = (int64_t)raw[i] + plus_one;
+}
+
+struct RunHeadPolicy {
+  const int64_t* keys;
+  int64_t* uniq;
+  int64_t* run_start;
+  __device__ __forceinline__ int classify(int64_t i) const {
+    return (i == 0 || __ldg(keys + i - 1) != __ldg(keys + i)) ? 0 : -1;
+  }
+  __device__ __forceinline__ void emit(int64_t i, int, int64_t pos, int64_t, bool active) const {
+    if (!active) return;
+    uniq[pos] = keys[i];
+    run_start[pos] = i;
+  }
+};
+
+int choose_chunk(int64_t n) {
+  // at least ~16 chunks per SM, between 32 and 128 rows
+  int64_t target = n / ((int64_t)sm_count() * 16);
+  int r = 32;
+  while (r * 2 <= target && r < 128) r *= 2;
+  return r;
+}
+
+size_t sort_temp_bytes(int64_t n) {
+  size_t bytes = 0;
+  cub::DoubleBuffer<int64_t> k(nullptr, nullptr);
+  cub::DoubleBuffer<uint32_t> v(nullptr, nullptr);
+  cub::DeviceRadixSort::SortPairs(nullptr, bytes, k, v, (int)n, 0, 64, (cudaStream_t)0);
+  return bytes;
+}
+
+struct SegPlan {
+  int64_t *k0, *k1;
+  uint32_t *p0, *p1;
+  void* sort_temp;
+  size_t sort_temp_bytes;
+  int64_t* run_start;
+  unsigned long long* raw_counts;
+  float *head_part, *tail_part;
+  int2 *short_list, *long_list;
+  int* list_counts;
+  void* part_ws;
+  size_t part_ws_bytes;
+  int chunk;
+  int64_t num_chunks;
+  int cols_max;
+  size_t total;
+};
+
+SegPlan make_plan(void* ws, int64_t n, int64_t dim) {
+  SegPlan s;
+  Carver cv(ws ? ws : (void*)256);  // a null workspace still yields the sizes
+  const int64_t m = n > 0 ? n : 1;
+  s.k0 = cv.take<int64_t>(m);
+  s.k1 = cv.take<int64_t>(m);
+  s.p0 = cv.take<uint32_t>(m);
+  s.p1 = cv.take<uint32_t>(m);
+  s.sort_temp_bytes = sort_temp_bytes(m);
+  s.sort_temp = cv.take<char>(s.sort_temp_bytes);
+  s.run_start = cv.take<int64_t>(m + 1);
+  s.raw_counts = cv.take<unsigned long long>(m);
+  s.chunk = choose_chunk(m);
+  s.num_chunks = ceil_div(m, s.chunk);
+  s.cols_max = (int)(dim < 512 ? dim : 512);
+  s.head_part = cv.take<float>((size_t)s.num_chunks * s.cols_max);
+  s.tail_part = cv.take<float>((size_t)s.num_chunks * s.cols_max);
+  s.short_list = cv.take<int2>(s.num_chunks);
+  s.long_list = cv.take<int2>(s.num_chunks);
+  s.list_counts = cv.take<int>(4);
+  s.part_ws_bytes = partition_workspace_bytes(m, 1);
+  s.part_ws = cv.take<char>(s.part_ws_bytes);
+  s.total = cv.used() + 256;
+  return s;
+}
+
+template <int VEC, int G, int VPL>
+int launch_pass(const SegArgs& a, cudaStream_t st) {
+  const int64_t threads = a.num_chunks * G;
+  HB_LAUNCH((segsum_main_kernel<VEC, G, VPL>), (int)ceil_div(threads, kBlock), kBlock, 0, st, a);
+  int fix_grid = (int)ceil_div(a.num_chunks * G, kBlock);
+  const int cap = sm_count() * 8;
+  if (fix_grid > cap) fix_grid = cap;
+  HB_LAUNCH((segsum_fix_short_kernel<VEC, G, VPL>), fix_grid, kBlock, 0, st, a);
+  const int strands = kLongBlock / a.cols > 0 ? kLongBlock / a.cols : 1;
+  const size_t smem = (size_t)strands * a.cols * sizeof(float);
+  HB_LAUNCH(segsum_fix_long_kernel, sm_count(), kLongBlock, smem, st, a);
+  return HB_OK;
+}
+
+int dispatch_pass(const SegArgs& a, bool vec4, cudaStream_t st) {
+  if (vec4) {
+    const int vpr = a.cols / 4;
+    if (vpr > 64) return launch_pass<4, 32, 4>(a, st);
+    if (vpr > 32) return launch_pass<4, 32, 2>(a, st);
+    if (vpr > 16) return launch_pass<4, 32, 1>(a, st);
+    if (vpr > 8) return launch_pass<4, 16, 1>(a, st);
+    if (vpr > 4) return launch_pass<4, 8, 1>(a, st);
+    if (vpr > 2) return launch_pass<4, 4, 1>(a, st);
+    if (vpr > 1) return launch_pass<4, 2, 1>(a, st);
+    return launch_pass<4, 1, 1>(a, st);
+  }
+  const int vpr = a.cols;
+  if (vpr > 64) return launch_pass<1, 32, 4>(a, st);
+  if (vpr > 32) return launch_pass<1, 32, 2>(a, st);
+  if (vpr > 16) return launch_pass<1, 32, 1>(a, st);
+  if (vpr > 8) return launch_pass<1, 16, 1>(a, st);
+  if (vpr > 4) return launch_pass<1, 8, 1>(a, st);
+  if (vpr > 2) return launch_pass<1, 4, 1>(a, st);
+  if (vpr > 1) return launch_pass<1, 2, 1>(a, st);
+  return launch_pass<1, 1, 1>(a, st);
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" {
+
+size_t hb_unique_segsum_workspace_bytes(int64_t n, int64_t dim) {
+  return make_plan(nullptr, n, dim).total;
+}
+
+int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* cnt_in, int64_t n,
+                         int64_t dim, int id_bits, int mean, int64_t* uniq_ids, float* sums,
+                         int64_t* counts, int64_t* num_unique, void* workspace,
+                         size_t workspace_bytes, hb_stream_t stream) {
+  HB_CHECK_ARG(n >= 0 && n < ((int64_t)1 << 31) && dim > 0, "hb_unique_segsum_f32: bad sizes");
+  HB_CHECK_ARG(num_unique != nullptr, "hb_unique_segsum_f32: num_unique is null");
+  HB_CHECK_ARG(n == 0 || (ids && grads && uniq_ids && sums), "hb_unique_segsum_f32: null argument");
+  HB_CHECK_ARG(id_bits >= 1 && id_bits <= 64, "hb_unique_segsum_f32: id_bits must be in [1, 64]");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (n == 0) {
+    HB_CUDA(cudaMemsetAsync(num_unique, 0, sizeof(int64_t), st));
+    return HB_OK;
+  }
+  SegPlan s = make_plan(workspace, n, dim);
+  if (!workspace || workspace_bytes < s.total) {
+    set_error("hb_unique_segsum_f32: workspace of %zu bytes needed, %zu given", s.total,
+              workspace_bytes);
+    return HB_ERR_WORKSPACE;
+  }
+  // 1. sort (id, position)
+  HB_CUDA(cudaMemcpyAsync(s.k0, ids, n * sizeof(int64_t), cudaMemcpyDeviceToDevice, st));
+  HB_LAUNCH(iota_u32_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, s.p0, n);
+  cub::DoubleBuffer<int64_t> keys(s.k0, s.k1);
+  cub::DoubleBuffer<uint32_t> perm(s.p0, s.p1);
+  HB_CUDA(cub::DeviceRadixSort::SortPairs(s.sort_temp, s.sort_temp_bytes, keys, perm, (int)n, 0,
+                                          id_bits, st));
+  count_library_launches(1 + (id_bits + 7) / 8);
+  // 2. run heads -> unique ids, run starts, U
+  RunHeadPolicy pol{keys.Current(), uniq_ids, s.run_start};
+  int rc = run_partition(pol, n, 1, s.part_ws, s.part_ws_bytes, num_unique, st);
+  if (rc != HB_OK) return rc;
+  // 3./4. column passes
+  HB_CUDA(cudaMemsetAsync(s.raw_counts, 0, n * sizeof(unsigned long long), st));
+  const bool vec4 = (dim % 4 == 0) && (((uintptr_t)grads | (uintptr_t)sums) & 15) == 0;
+  SegArgs a;
+  a.keys = keys.Current();
+  a.perm = perm.Current();
+  a.run_start = s.run_start;
+  a.num_runs = num_unique;
+  a.grads = grads;
+  a.cnt_in = cnt_in;
+  a.n = n;
+  a.dim = dim;
+  a.chunk = s.chunk;
+  a.num_chunks = s.num_chunks;
+  a.mean = mean;
+  a.sums = sums;
+  a.counts = s.raw_counts;
+  a.head_part = s.head_part;
+  a.tail_part = s.tail_part;
+  a.short_list = s.short_list;
+  a.long_list = s.long_list;
+  a.list_counts = s.list_counts;
+  const int tile = vec4 ? 512 : 128;
+  for (int64_t col0 = 0; col0 < dim; col0 += tile) {
+    a.col0 = col0;
+    a.cols = (int)((dim - col0) < tile ? (dim - col0) : tile);
+    if (col0 == 0) HB_CUDA(cudaMemsetAsync(s.list_counts, 0, 4 * sizeof(int), st));
+    rc = dispatch_pass(a, vec4, st);
+    if (rc != HB_OK) return rc;
+  }
+  if (counts) {
+    HB_LAUNCH(finish_counts_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, s.raw_counts,
+              num_unique, (cnt_in && mean) ? 1 : 0, counts, n);
+  }
+  return HB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,246 @@
+/*
+ * libhades_b200 -- C ABI of the B200 (sm_100a) embedding-cache / sparse-gradient
+ * hot path.  Plain pointers and sizes only; no torch types.  Every entry point
+ * returns an hb_status (0 = success) and never exits the process;
+ * hb_last_error() gives the message of the last failure on the calling thread.
+ *
+ * Unless stated otherwise every pointer is a DEVICE pointer (pinned host memory
+ * mapped into the device address space also works for the row movers, as it
+ * does for the reference's UVA kernels), every call is asynchronous on the
+ * given stream (a cudaStream_t passed as void*), and the caller owns all
+ * buffers.  Kernels need "workspace" scratch are given it by the caller:
+ * hb_xxx_workspace_bytes() tells how much.
+ *
+ * Each declaration cites the reference interface (HADES, path inside the
+ * reference project) that it replaces.
+ */
+#ifndef HADES_B200_H_
+#define HADES_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum hb_status {
+  HB_OK = 0,
+  HB_ERR_INVALID = 1,     /* bad argument (shape, dtype size, null pointer, alignment) */
+  HB_ERR_CUDA = 2,        /* a CUDA runtime call failed */
+  HB_ERR_WORKSPACE = 3,   /* caller workspace too small */
+  HB_ERR_UNSUPPORTED = 4, /* valid request that this build does not implement */
+  HB_ERR_TIMEOUT = 5,     /* a bounded device-side wait ran out */
+  HB_ERR_CAPACITY = 6     /* a fixed-capacity buffer would overflow */
+} hb_status;
+
+typedef void* hb_stream_t; /* cudaStream_t */
+
+const char* hb_last_error(void);
+int hb_version(void);
+/* Number of kernels this library has launched in this process (all threads). */
+int64_t hb_launch_count(void);
+/* Kernels that wait on hardware barriers do so with an iteration limit; one that
+ * gives up records an hb_status in a per-device word instead of trapping.  This
+ * call synchronises the stream, returns that word (0 = none) and clears it. */
+int hb_device_status(int* status_host, hb_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Cache index: 8-way set-associative ID -> slot map, state resident in HBM.   */
+/* Replaces SACacheIndex / IndexCache (src/cache/cache.h:11-257,               */
+/* src/cache/cache_line.h:7-103, bound in src/pybind.cc:17-33).                */
+/* slot = (id % lines) * 8 + way; -1 = absent.  ids must be >= 0.              */
+/* ------------------------------------------------------------------------- */
+typedef struct hb_index hb_index_t;
+
+#define HB_WAYS 8
+
+/* Lookup algorithm.  Both give identical outputs. */
+#define HB_LOOKUP_SETASSOC 0 /* probe the 64-byte line id % lines              */
+#define HB_LOOKUP_SORTED 1   /* warp-cooperative search of the sorted view     */
+
+/* IndexCache(cache_size, ...) ctor, src/cache/cache.h:138-167: lines =
+ * ceil(cache_size/8); capacity rounds up to a multiple of 8.  Allocates the
+ * state on the current device. */
+int hb_index_create(int64_t cache_size, hb_index_t** out);
+int hb_index_destroy(hb_index_t* h);
+/* get_size / get_capacity / get_space, src/cache/cache.h:176-194 */
+int64_t hb_index_size(const hb_index_t* h);
+int64_t hb_index_capacity(const hb_index_t* h);
+int64_t hb_index_space(const hb_index_t* h);
+int64_t hb_index_lines(const hb_index_t* h);
+/* get_valid_entries_num, src/cache/cache.h:178-183.  Synchronises the stream. */
+int hb_index_valid_entries(hb_index_t* h, int64_t* out_host, hb_stream_t stream);
+
+/* add(ids) -> locs, src/cache/cache.h:51-88,196-206: existing id -> its slot;
+ * else the LAST empty way; else the least-recently-used way (largest counter,
+ * first on ties) unless all counters are 0, then -1.  Ids are applied in input
+ * order per set (the reference result at OMP_NUM_THREADS=1). */
+size_t hb_index_add_workspace_bytes(int64_t n);
+int hb_index_add(hb_index_t* h, const int64_t* ids, int64_t n, int64_t* locs,
+                 void* workspace, size_t workspace_bytes, hb_stream_t stream);
+
+/* lookup(ids) -> locs (and optional found mask = locs >= 0),
+ * src/cache/cache.h:90-104,213-222 and cudalookup, src/cache/lookup.cu:13-85.
+ * Does not touch the LRU counters; see hb_index_touch_lru. */
+int hb_index_lookup(hb_index_t* h, const int64_t* ids, int64_t n, int64_t* locs,
+                    uint8_t* found /* nullable */, int mode, hb_stream_t stream);
+
+/* The side effect of the reference's CPU lookup, cache_line::access_loc,
+ * src/cache/cache_line.h:80-86 via src/cache/cache.h:101: for each hit in batch
+ * order, every counter of the hit line += 1 and the hit way's counter = 0. */
+size_t hb_index_touch_lru_workspace_bytes(int64_t n);
+int hb_index_touch_lru(hb_index_t* h, const int64_t* locs, int64_t n,
+                       void* workspace, size_t workspace_bytes, hb_stream_t stream);
+
+/* reset(ids), src/cache/cache.h:106-118,208-211: a hit way becomes empty. */
+int hb_index_reset(hb_index_t* h, const int64_t* ids, int64_t n, hb_stream_t stream);
+
+/* getall(len) -> (ids, locs) in slot order, src/cache/cache.h:120-135,243-257.
+ * Writes min(len, valid) pairs; *n_written_host receives that count.
+ * Synchronises the stream. */
+int hb_index_getall(hb_index_t* h, int64_t* ids_out, int64_t* locs_out, int64_t len,
+                    int64_t* n_written_host, hb_stream_t stream);
+
+/* Rebuild the sorted (id, slot) view and its pivot levels used by
+ * HB_LOOKUP_SORTED after add/reset/import changed the index.  hb_index_lookup
+ * and hb_lookup_fetch call it themselves when the view is stale. */
+int hb_index_build_sorted(hb_index_t* h, hb_stream_t stream);
+
+/* Raw state in/out (device or host pointers): line_ids[capacity] int64,
+ * lru[capacity] int32.  For tests, checkpoints and a host mirror. */
+int hb_index_export(hb_index_t* h, int64_t* line_ids, int32_t* lru, hb_stream_t stream);
+int hb_index_import(hb_index_t* h, const int64_t* line_ids, const int32_t* lru,
+                    hb_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Row movers.  Rows are opaque byte strings of row_bytes (= dim * elem size); */
+/* index arrays are int32 (idx_bytes 4) or int64 (idx_bytes 8).  Out-of-range   */
+/* indices are undefined behaviour, as in the reference.                        */
+/* ------------------------------------------------------------------------- */
+#define HB_MOVER_AUTO 0 /* pick by row size and alignment                      */
+#define HB_MOVER_LSU 1  /* vectorised ld.global / st.global                    */
+#define HB_MOVER_BULK 2 /* cp.async.bulk through shared memory (TMA engine)    */
+
+/* dst[dst_index[i], :] = src[src_index[i], :]; dst_index NULL means i.
+ * Replaces CUDAFetch (src/cuda/uva_fetch.cu:28-45) and CUDAFetch2 (:72-106). */
+int hb_rows_gather(const void* src, const void* src_index, void* dst,
+                   const void* dst_index /* nullable */, int64_t n, int64_t row_bytes,
+                   int idx_bytes, int mover, hb_stream_t stream);
+
+/* dst[dst_index[i], :] = src[i, :] (overwrite; with duplicate indices one of
+ * the writers wins).  Replaces CUDASet (src/cuda/uva_set.cu:35-69) and
+ * CUDACombine (src/cuda/uva_fetch.cu:212-228), which compute the same thing. */
+int hb_rows_scatter(const void* src, void* dst, const void* dst_index, int64_t n,
+                    int64_t row_bytes, int idx_bytes, int mover, hb_stream_t stream);
+
+/* g = index_map[index[i]]; dst[i,:] = g != -1 ? cached_src[g,:] : backing_src[index[i],:].
+ * found (nullable) receives g != -1.  Replaces CUDAFetchWithCache2
+ * (src/cuda/uva_fetch.cu:149-192). */
+int hb_rows_gather_cached(const void* backing_src, const void* cached_src,
+                          const void* index, const void* index_map, void* dst,
+                          uint8_t* found /* nullable */, int64_t n, int64_t row_bytes,
+                          int idx_bytes, hb_stream_t stream);
+
+/* g = index_map[index[i]]; (g != -1 ? cached_dst[g,:] : backing_dst[index[i],:]) = src[i,:].
+ * Replaces CUDASetWithCache (src/cuda/uva_set.cu:112-154). */
+int hb_rows_scatter_cached(const void* src, void* backing_dst, void* cached_dst,
+                           const void* index, const void* index_map, int64_t n,
+                           int64_t row_bytes, int idx_bytes, hb_stream_t stream);
+
+/* dst[dst_index[i], :] += src[i, :] in fp32 and, when cnt is given,
+ * cnt[dst_index[i]] += 1.  Indices must be unique (the reference's assumption,
+ * python/EmbCache/server.py:547,565); duplicates go through
+ * hb_unique_segsum_f32 first.  Replaces the torch CPU indexing of
+ * _accumulate_gradients_cold_local, python/EmbCache/server.py:564-574. */
+int hb_rows_accumulate_f32(const float* src, float* dst, const void* dst_index,
+                           int32_t* cnt /* nullable */, int64_t n, int64_t dim,
+                           int idx_bytes, hb_stream_t stream);
+
+/* Fused cache lookup + cached fetch: slot = lookup(ids[i]);
+ * out_rows[i,:] = slot >= 0 ? cache_rows[slot,:] : backing_rows[ids[i],:]
+ * (a miss leaves the output row untouched when backing_rows is NULL);
+ * locs[i] = slot (nullable), found[i] = slot >= 0 (nullable).
+ * One pass for IndexCache.lookup + cudaFetch + the backing-table fetch of
+ * python/EmbCache/dist_emb.py:184-243. */
+int hb_lookup_fetch(hb_index_t* h, const int64_t* ids, int64_t n, const void* cache_rows,
+                    const void* backing_rows /* nullable */, int64_t row_bytes,
+                    void* out_rows, int64_t* locs /* nullable */,
+                    uint8_t* found /* nullable */, int mode, int mover,
+                    hb_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Hot/cold split, owner search, owner bucketing.                              */
+/* ------------------------------------------------------------------------- */
+/* Workspace of the stable multi-way partition that split_compact, bucket_pack,
+ * grad_split3 and the staging flush share. */
+size_t hb_partition_workspace_bytes(int64_t n, int num_classes);
+
+/* v = mask_table[ids[i]]: local = (v==0), hot = (v==1), cold = (v==2), one byte
+ * each.  Replaces splitCUDA / cudaSplit (src/cuda/split.cu:12-56). */
+int hb_split_masks(const int64_t* ids, int64_t n, const int8_t* mask_table,
+                   uint8_t* local_mask, uint8_t* hot_mask, uint8_t* cold_mask,
+                   hb_stream_t stream);
+
+/* hb_split_masks fused with the nonzero() calls that follow it in
+ * python/EmbCache/dist_emb.py:174-191: index_out holds the positions of the
+ * local ids, then of the hot ids, then of the cold ids, each ascending;
+ * counts (device int64[3]) their numbers.  Masks are optional (all or none). */
+int hb_split_compact(const int64_t* ids, int64_t n, const int8_t* mask_table,
+                     uint8_t* local_mask, uint8_t* hot_mask, uint8_t* cold_mask,
+                     int64_t* index_out, int64_t* counts, void* workspace,
+                     size_t workspace_bytes, hb_stream_t stream);
+
+/* out = in % g.  Replaces Reminder / cudaReminder (src/cuda/binary_search.cu:76-89). */
+int hb_owner_mod(const void* in, int64_t n, int idx_bytes, int64_t g, void* out,
+                 hb_stream_t stream);
+/* out = (upper_bound(range_partition, in) - 1) * g + in % g.  Replaces
+ * CUDABinarySearch / cudaBinarySearch (src/cuda/binary_search.cu:45-59). */
+int hb_owner_range(const void* in, int64_t n, int idx_bytes, const void* range_partition,
+                   int64_t num_part, int64_t g, void* out, hb_stream_t stream);
+/* out = upper_bound(sorted, in).  Replaces CUDABinarySearch2 / cudaBinarySearch2
+ * (src/cuda/binary_search.cu:61-74). */
+int hb_upper_bound(const void* in, int64_t n, int idx_bytes, const void* sorted, int64_t m,
+                   void* out, hb_stream_t stream);
+
+/* Bucket (ids, rows, cnt) by owner, stable inside a bucket: the owner search,
+ * torch.sort, three gathers and cudaBinarySearch2 of swap_gradients
+ * (python/EmbCache/sparse_optim.py:36-55) in one pass with the counts left on
+ * the device.  owner = id % g when range_partition is NULL, else the
+ * hb_owner_range rule.  rows and cnt are optional.  counts: device
+ * int64[num_buckets]; bucket b starts at the sum of the counts before it. */
+int hb_bucket_pack(const int64_t* ids, const void* rows, const int64_t* cnt, int64_t n,
+                   int64_t row_bytes, int num_buckets, const int64_t* range_partition,
+                   int64_t num_part, int64_t g, int64_t* out_ids, void* out_rows,
+                   int64_t* out_cnt, int64_t* counts, void* workspace,
+                   size_t workspace_bytes, hb_stream_t stream);
+
+/* The hot / cold-local / cold-remote selects of DistembSparseGradOptimizer.step
+ * (python/EmbCache/sparse_optim.py:243-259) in one pass: out holds the hot rows
+ * (hot_mask), then ~hot & local, then ~hot & ~local; counts: device int64[3]. */
+int hb_grad_split3(const int64_t* ids, const void* rows, const uint8_t* hot_mask,
+                   const uint8_t* local_mask, int64_t n, int64_t row_bytes,
+                   int64_t* out_ids, void* out_rows, int64_t* counts, void* workspace,
+                   size_t workspace_bytes, hb_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Hot-node local aggregation.                                                 */
+/* ------------------------------------------------------------------------- */
+/* Sorted unique ids with the per-id fp32 sum (mean = 0) or mean (mean = 1) of
+ * their gradient rows, deterministic.  Replaces only_unique_grads and
+ * unique_grads (python/EmbCache/sparse_optim.py:132-157).  counts (nullable):
+ * occurrences per id; when mean = 1 and cnt_in is given, 1 + sum of cnt_in,
+ * which is also the divisor (the reference starts its counts from ones,
+ * sparse_optim.py:145-148).  uniq_ids / sums / counts must hold n entries;
+ * num_unique is a device int64.  id_bits: ids are < 2^id_bits (sort passes). */
+size_t hb_unique_segsum_workspace_bytes(int64_t n, int64_t dim);
+int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* cnt_in,
+                         int64_t n, int64_t dim, int id_bits, int mean, int64_t* uniq_ids,
+                         float* sums, int64_t* counts /* nullable */, int64_t* num_unique,
+                         void* workspace, size_t workspace_bytes, hb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* HADES_B200_H_ */

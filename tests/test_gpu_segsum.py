@@ -1,0 +1,80 @@
+"""Hot-node local aggregation against the oracle's restatement of only_unique_grads /
+unique_grads: unique ids and counts bit-exact, fp32 sums within 1e-5 relative (the
+summation order differs from index_add_'s), and bitwise reproducible run to run."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+RTOL = 1e-5  # relative error bound on fp32 gradient sums
+
+
+def _close(got, want, scale):
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert err.max(initial=0.0) <= RTOL * scale, err.max()
+
+
+def _ids(rng, n, kind):
+    if kind == "zipf":
+        from hades_b200 import synth
+
+        return synth.ZipfSampler(1_000_000, 1.2).ids(rng, n)
+    if kind == "one":
+        return np.full(n, 42, dtype=np.int64)
+    if kind == "unique":
+        return rng.permutation(n * 3)[:n].astype(np.int64)
+    return rng.integers(0, max(n // 3, 1), n, dtype=np.int64)
+
+
+@pytest.mark.parametrize("kind", ["zipf", "uniform", "one", "unique"])
+@pytest.mark.parametrize("n,dim", [(1, 128), (33, 128), (5000, 128), (70_000, 64), (40_000, 3),
+                                   (30_000, 257), (9_000, 640), (524_288, 128)])
+def test_only_unique_grads(cuda_lib, oracle_mod, kind, n, dim):
+    from hades_b200 import EmbCacheLib as E
+
+    if n > 100_000 and kind not in ("zipf",):
+        pytest.skip("large case runs on the Zipf stream only")
+    rng = np.random.default_rng(n * 13 + dim)
+    ids = _ids(rng, n, kind)
+    grad = (rng.standard_normal((n, dim)) * 1e-3).astype(np.float32)
+    wu, wv, wc = oracle_mod.only_unique_grads(ids, grad)
+    gu, gv, gc = E.cudaUniqueSegSum(torch.from_numpy(ids).cuda(), torch.from_numpy(grad).cuda(), id_bits=40)
+    assert np.array_equal(gu.cpu().numpy(), wu)
+    assert np.array_equal(gc.cpu().numpy(), wc)
+    # scale: the sum of magnitudes bounds the rounding error of any summation order
+    absum = np.zeros_like(wv)
+    np.add.at(absum, np.unique(ids, return_inverse=True)[1], np.abs(grad))
+    err = np.abs(gv.cpu().numpy().astype(np.float64) - wv.astype(np.float64))
+    assert (err <= RTOL * np.maximum(absum, 1e-30)).all(), err.max()
+    # deterministic: same bits on a second run
+    gu2, gv2, gc2 = E.cudaUniqueSegSum(torch.from_numpy(ids).cuda(), torch.from_numpy(grad).cuda(), id_bits=40)
+    assert torch.equal(gv, gv2) and torch.equal(gu, gu2) and torch.equal(gc, gc2)
+
+
+@pytest.mark.parametrize("with_cnt", [False, True])
+def test_unique_grads_mean(cuda_lib, oracle_mod, with_cnt):
+    from hades_b200 import EmbCacheLib as E
+
+    rng = np.random.default_rng(21 + with_cnt)
+    n, dim = 60_000, 128
+    ids = _ids(rng, n, "zipf")
+    grad = (rng.standard_normal((n, dim)) * 1e-3).astype(np.float32)
+    cnt = rng.integers(1, 17, n, dtype=np.int64) if with_cnt else None
+    wu, wv, wc = oracle_mod.unique_grads(ids, grad, cnt)
+    gu, gv, gc = E.cudaUniqueSegSum(torch.from_numpy(ids).cuda(), torch.from_numpy(grad).cuda(),
+                                    None if cnt is None else torch.from_numpy(cnt).cuda(), mean=True, id_bits=32)
+    assert np.array_equal(gu.cpu().numpy(), wu)
+    assert np.array_equal(gc.cpu().numpy(), wc)  # 1 + sum(cnt) when cnt is given
+    absum = np.zeros_like(wv)
+    np.add.at(absum, np.unique(ids, return_inverse=True)[1], np.abs(grad))
+    err = np.abs(gv.cpu().numpy().astype(np.float64) - wv.astype(np.float64))
+    assert (err <= RTOL * np.maximum(absum / wc[:, None], 1e-30)).all()
+
+
+def test_empty(cuda_lib):
+    from hades_b200 import EmbCacheLib as E
+
+    u, v, c = E.cudaUniqueSegSum(torch.empty(0, dtype=torch.int64, device="cuda"),
+                                 torch.empty((0, 8), device="cuda"))
+    assert u.numel() == 0 and v.shape == (0, 8) and c.numel() == 0
