@@ -1,0 +1,402 @@
+#!/usr/bin/env python
+"""Benchmark of the embedding-cache / sparse-gradient hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" = one pass of the whole path over one batch of synthetic ids on every GPU:
+fused cache lookup + cached fetch (+ LRU ageing), local aggregation (sort / unique /
+segment-sum), hot/cold split, cold-cache accumulate, owner-partitioned exchange of the hot
+rows + optimiser update on the owner, and every 8th step the cold-cache flush and refill.
+The workload is configuration 2 of the baseline (20M x 128 fp32 table, 4M-entry hot cache,
+2M Zipf(1.2) ids per step and GPU); per-GPU work is fixed as N grows ("weak" scaling).
+
+Prints ONE JSON line (rank 0).  `value` is timed with the batch already in HBM; `e2e` times
+the same step with the ids arriving from pinned host memory and the found mask and slots
+read back to the host.  `--impl reference` times the reference's own CPU path (its compiled
+index + the torch CPU expressions it uses) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "embedding_rows_per_s_lookup_fetch_aggregate_sync"
+UNIT = "rows/s"
+WORKLOAD = "config2: table 20M x 128 fp32, hot cache 4M, batch 2M Zipf(1.2) per GPU, flush every 8 steps"
+CPU_SAMPLE_SCALE = 1.0 / 8.0
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload (profiling captures)")
+    ap.add_argument("--lookup", default="setassoc", choices=["setassoc", "sorted"])
+    ap.add_argument("--mover", default="auto", choices=["auto", "lsu", "bulk"])
+    ap.add_argument("--no-lru", action="store_true", help="skip the LRU ageing passes")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path).read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the reference's own CPU path
+# --------------------------------------------------------------------------------------
+def cpu_reference_run(steps: int, warmup: int, scale: float, threads: int | None = None) -> dict:
+    """The path as the reference runs it on CPU tensors: IndexCache.lookup (its compiled C++
+    index, OpenMP), torch CPU gathers for the fetch (test/test_cached_fetch.py:33-36),
+    only_unique_grads (python/EmbCache/sparse_optim.py:132-139), the server's accumulate
+    and flush (python/EmbCache/server.py:346-574) and SparseAdam.update (:590-685).
+    oracle/ is used here as the thing measured ONLY in this baseline leg."""
+    import numpy as np
+    import torch
+
+    from hades_b200 import synth
+    from oracle import oracle as om
+
+    cfg = synth.scaled(synth.CONFIG2, scale, "config2_cpu_sample")
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    use_ref = om.RefIndex.available()
+    if use_ref:
+        om.RefIndex.set_threads(threads)
+        index = om.RefIndex(cfg.cache_entries)
+    else:
+        index = om.OracleIndex(cfg.cache_entries)
+    g = torch.Generator().manual_seed(2000)
+    table = torch.empty((cfg.table_rows, cfg.dim)).normal_(0, cfg.table_sigma, generator=g)
+    hot = synth.hot_ids(cfg.table_rows, cfg.cache_entries)
+    if use_ref:
+        om.RefIndex.set_threads(1)  # add() depends on thread timing otherwise
+    locs = index.add(hot)
+    if use_ref:
+        om.RefIndex.set_threads(threads)
+    slots = index.get_capacity()
+    cache = torch.zeros((slots, cfg.dim))
+    ok = torch.from_numpy(locs >= 0)
+    cache[torch.from_numpy(locs)[ok]] = table[torch.from_numpy(hot)[ok]]
+    n_hot = max(int(cfg.table_rows * 0.01), 1)
+    cls = torch.full((cfg.table_rows,), 2, dtype=torch.int8)
+    cls[torch.from_numpy(synth.rank_to_id(np.arange(n_hot, dtype=np.int64), cfg.table_rows))] = 1
+    grad_buf = torch.zeros((slots, cfg.dim))
+    cnt_buf = torch.zeros(slots, dtype=torch.int32)
+    idx_buf = torch.full((slots,), -1, dtype=torch.int64)
+    step_s = torch.zeros(cfg.table_rows)
+    mem = torch.zeros((cfg.table_rows, cfg.dim))
+    power = torch.zeros((cfg.table_rows, cfg.dim))
+    sampler = synth.ZipfSampler(cfg.table_rows, cfg.zipf_s)
+    rng = synth.rng_for(2, 0, 1)
+    batches = [torch.from_numpy(sampler.ids(rng, cfg.batch)) for _ in range(4)]
+    grads = torch.empty((cfg.batch, cfg.dim)).normal_(0, cfg.grad_sigma, generator=g)
+
+    def adam(idx, gv):
+        t = step_s[idx] + 1
+        m = 0.9 * mem[idx] + (1.0 - 0.9) * gv
+        v = 0.999 * power[idx] + (1.0 - 0.999) * gv * gv
+        mc = m / (1.0 - torch.pow(torch.tensor(0.9), t)).unsqueeze(1)
+        vc = v / (1.0 - torch.pow(torch.tensor(0.999), t)).unsqueeze(1)
+        step_s[idx] = t
+        mem[idx] = m
+        power[idx] = v
+        table[idx] -= 0.01 * mc / (torch.sqrt(vc) + 1e-8)
+
+    def one_step(k: int):
+        ids = batches[k % len(batches)]
+        l = torch.from_numpy(index.lookup(ids.numpy()))
+        found = l >= 0
+        out = torch.empty((ids.numel(), cfg.dim))
+        out[found] = cache[l[found]]
+        out[~found] = table[ids[~found]]
+        u, inv, c = torch.unique(ids, return_inverse=True, return_counts=True)
+        s = torch.zeros((u.numel(), cfg.dim))
+        s.index_add_(0, inv, grads)
+        kind = cls[u]
+        hu, hs, hc = u[kind == 1], s[kind == 1], c[kind == 1]
+        cu, cs = u[kind == 2], s[kind == 2]
+        cl = torch.from_numpy(index.lookup(cu.numpy()))
+        hit = cl >= 0
+        sl = cl[hit]
+        idx_buf[sl] = cu[hit]
+        grad_buf[sl] += cs[hit]
+        cnt_buf[sl] += 1
+        adam(hu, hs / (1 + hc).unsqueeze(1))
+        if (k + 1) % cfg.flush_every == 0:
+            live = torch.nonzero(cnt_buf > 0).flatten()
+            fid, frow, fcnt = idx_buf[live], grad_buf[live], cnt_buf[live]
+            index.reset(fid.numpy())
+            grad_buf[live] = 0
+            cnt_buf[live] = 0
+            if live.numel():
+                adam(fid, frow / fcnt.unsqueeze(1))
+                nl = torch.from_numpy(index.add(fid.numpy()))
+                okk = nl >= 0
+                cache[nl[okk]] = table[fid[okk]]
+        return out
+
+    for k in range(warmup):
+        one_step(k)
+    t0 = time.perf_counter()
+    for k in range(warmup, warmup + steps):
+        one_step(k)
+    dt = time.perf_counter() - t0
+    return {"value": cfg.batch * steps / dt, "unit": UNIT, "cores": threads,
+            "kind": "reference" if use_ref else "port",
+            "sample": f"config2 scaled by {scale:g} (table {cfg.table_rows} x {cfg.dim}, cache "
+                      f"{cfg.cache_entries}, batch {cfg.batch}), {steps} steps after {warmup} warm-up",
+            "ms_per_step": dt / steps * 1e3}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(args.steps, 1)
+    r = cpu_reference_run(steps, max(args.warmup, 1), CPU_SAMPLE_SCALE)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": max(args.warmup, 1), "ms_per_step": r["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": r["sample"]},
+        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------------------
+def run_ours(args) -> None:
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from hades_b200 import EmbCacheLib as E
+    from hades_b200 import _lib, pipeline, synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    cfg = synth.CONFIG2 if args.scale == 1.0 else synth.scaled(synth.CONFIG2, args.scale, "config2_scaled")
+    mode = E.LOOKUP_SORTED if args.lookup == "sorted" else E.LOOKUP_SETASSOC
+    mover = {"auto": E.MOVER_AUTO, "lsu": E.MOVER_LSU, "bulk": E.MOVER_BULK}[args.mover]
+    path = pipeline.build_path(cfg, rank, world, dev, optimizer="adam", lookup_mode=mode, mover=mover,
+                               touch_lru=not args.no_lru)
+    sampler = synth.ZipfSampler(cfg.table_rows, cfg.zipf_s)
+    rng = synth.rng_for(2, rank, 1)
+    host_batches = [torch.from_numpy(sampler.ids(rng, cfg.batch)).pin_memory() for _ in range(4)]
+    dev_batches = [b.to(dev) for b in host_batches]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(2000 + rank)
+    grads = torch.empty((cfg.batch, cfg.dim), dtype=torch.float32, device=dev)
+    grads.normal_(0.0, cfg.grad_sigma, generator=gen)
+    out_rows = torch.empty((cfg.batch, cfg.dim), dtype=torch.float32, device=dev)
+    stats = synth.stream_stats(host_batches[0].numpy())
+    host_found = torch.empty(cfg.batch, dtype=torch.bool).pin_memory()
+    host_locs = torch.empty(cfg.batch, dtype=torch.int64).pin_memory()
+    ids_stage = torch.empty(cfg.batch, dtype=torch.int64, device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, first):
+        """K steps between CUDA events on the current stream, barrier + synchronize on both
+        sides; returns the max over ranks in ms."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for k in range(first, first + steps):
+            fn(k)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    last = {}
+
+    def step_resident(k):
+        rows, locs, found, st = path.step(dev_batches[k % len(dev_batches)], grads, out_rows)
+        last["found"], last["st"] = found, st
+
+    def step_e2e(k):
+        ids_stage.copy_(host_batches[k % len(host_batches)], non_blocking=True)
+        rows, locs, found, st = path.step(ids_stage, grads, out_rows)
+        host_found.copy_(found, non_blocking=True)
+        host_locs.copy_(locs, non_blocking=True)
+
+    # per-stage timing of the dominant kernels, on the launching stream
+    def stage_times(k, reps=5):
+        ids = dev_batches[k % len(dev_batches)]
+        out = {}
+        ev = lambda: torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        for name, fn in (
+            ("lookup_fetch", lambda: E.cudaLookupFetch(path.cold.index, ids, path.cold.emb, path.table,
+                                                       out_rows=out_rows, mode=mode, mover=mover)),
+            ("unique_segsum", lambda: E.cudaUniqueSegSum(ids, grads, id_bits=path.id_bits, sync=False)),
+        ):
+            fn()
+            a, b = ev(), ev()
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            out[name] = a.elapsed_time(b) / reps
+        return out
+
+    W, K = max(args.warmup, 3), max(args.steps, 1)
+    for k in range(W):
+        step_resident(k)
+    sampler_clk = ClockSampler(local_rank)
+    if rank == 0:
+        sampler_clk.start()
+    launches0 = _lib.launch_count()
+    total_ms = timed(step_resident, K, W)
+    launches = _lib.launch_count() - launches0
+    clocks = sampler_clk.stop() if rank == 0 else None
+    found_frac = float(last["found"].float().mean().item())
+    num_unique = int(last["st"].num_unique.item())
+    split_counts = last["st"].split_counts.tolist()
+
+    e2e = None
+    if not args.no_e2e:
+        for k in range(2):
+            step_e2e(k)
+        e2e_ms = timed(step_e2e, K, W + K)
+        e2e = {"value": world * cfg.batch * K / (e2e_ms * 1e-3), "unit": UNIT,
+               "h2d_bytes_per_step": cfg.batch * 8, "d2h_bytes_per_step": cfg.batch * 9,
+               "ms_per_step": e2e_ms / K,
+               "note": "ids from pinned host memory, found mask + slots read back; gradients are produced "
+                       "on the device by the backward pass and stay there"}
+
+    st_ms = stage_times(0)
+    status = _lib.device_status()
+    if status != 0:
+        raise SystemExit(f"device-side error status {status}")
+
+    if rank == 0:
+        peaks = {}
+        pk = ROOT / "MEASURED_PEAKS.json"
+        if pk.exists():
+            peaks = json.loads(pk.read_text())
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        row_bytes = cfg.dim * 4
+        lf_bytes = cfg.batch * (8 + 8 + 1) + 2 * cfg.batch * row_bytes
+        achieved = lf_bytes / (st_ms["lookup_fetch"] * 1e-3) / 1e9
+        seg_bytes = cfg.batch * (8 + row_bytes) + num_unique * (8 + 8 + row_bytes)
+        line = {
+            "metric": METRIC, "value": world * cfg.batch * K / (total_ms * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": total_ms / K,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD if args.scale == 1.0 else f"config2 scaled by {args.scale:g}",
+                       "table_rows": cfg.table_rows, "dim": cfg.dim, "cache_entries": cfg.cache_entries,
+                       "batch_per_gpu": cfg.batch, "zipf_s": cfg.zipf_s, "flush_every": cfg.flush_every,
+                       "lookup": args.lookup, "mover": args.mover, "lru_ageing": not args.no_lru,
+                       "optimizer": "SparseAdam fp32", "exchange": "local" if world == 1 else "nccl all_to_all",
+                       "l2": "inputs larger than L2: 1.0 GB of rows read and written per step, 4 id batches rotate",
+                       "stream": stats, "found_fraction": found_frac, "unique_per_batch": num_unique,
+                       "hot_cold_unique": split_counts[1:]},
+            "roofline": {"bound": "hbm", "kernel": "lookup_fetch (fused cache lookup + cached fetch)",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": "measured" if peaks else "fallback",
+                         "algorithmic_bytes": lf_bytes, "ms": st_ms["lookup_fetch"], "traffic": None,
+                         "also": {"unique_segsum_ms": st_ms["unique_segsum"],
+                                  "unique_segsum_gbs": seg_bytes / (st_ms["unique_segsum"] * 1e-3) / 1e9}},
+            "clocks": clocks, "gpu_launches": int(launches),
+        }
+        if e2e:
+            line["e2e"] = e2e
+        if world == 1 and not args.no_cpu_baseline:
+            r = cpu_reference_run(4, 1, CPU_SAMPLE_SCALE)
+            line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

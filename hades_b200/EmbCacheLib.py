@@ -431,7 +431,8 @@ def cudaSplitCompact(ids: torch.Tensor, mask: torch.Tensor, want_masks: bool = T
     return masks, index, counts
 
 
-def cudaBucketPack(ids, rows, cnt, num_buckets: int, range_partition=None, local_num_gpus: int | None = None):
+def cudaBucketPack(ids, rows, cnt, num_buckets: int, range_partition=None, local_num_gpus: int | None = None,
+                   n_dev: torch.Tensor | None = None):
     """Bucket (ids, rows, cnt) by owner, stable inside a bucket.  Returns
     (ids, rows, cnt, counts[num_buckets] on the device).  owner = id % num_buckets, or the
     cudaBinarySearch rule when range_partition is given."""
@@ -445,12 +446,46 @@ def cudaBucketPack(ids, rows, cnt, num_buckets: int, range_partition=None, local
     lib = _lib.load()
     ws = _lib.workspace(lib.hb_partition_workspace_bytes(n, num_buckets))
     _lib.check(lib.hb_bucket_pack(ids.contiguous().data_ptr(), _lib.ptr(rows), _lib.ptr(cnt), n,
+                                  _lib.ptr(n_dev),
                                   _row_bytes(rows) if rows is not None else 0, int(num_buckets),
                                   _lib.ptr(range_partition),
                                   range_partition.numel() if range_partition is not None else 0, g,
                                   out_ids.data_ptr(), _lib.ptr(out_rows), _lib.ptr(out_cnt),
                                   counts.data_ptr(), ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
     return out_ids, out_rows, out_cnt, counts
+
+
+def cudaTableSplit3(ids, rows, cnt, table, n_dev: torch.Tensor | None = None, keep=(True, True, True),
+                    caps=(None, None, None)):
+    """(ids, rows, cnt) split by class table[id] in {0, 1, 2} into one buffer set per class
+    (each compacted from entry 0, input order kept).  Returns ([ (ids, rows, cnt) | None ] * 3,
+    counts[3] on the device); keep[c] = False only counts class c.  caps[c]: an upper bound
+    the caller can prove on the size of class c (e.g. unique ids of a class with that many
+    members), to allocate less than n entries for it."""
+    _check(ids.is_cuda and ids.dtype == torch.int64, "ids is a CUDA int64 tensor")
+    _check(table.dtype == torch.int8, "table.dtype == int8")
+    n = ids.numel()
+    outs = []
+    for c in range(3):
+        if keep[c]:
+            m = n if caps[c] is None else min(n, int(caps[c]))
+            outs.append((torch.empty(m, dtype=ids.dtype, device=ids.device),
+                         torch.empty((m, rows.size(1)), dtype=rows.dtype, device=ids.device),
+                         torch.empty(m, dtype=cnt.dtype, device=ids.device) if cnt is not None else None))
+        else:
+            outs.append(None)
+    counts = torch.empty(3, dtype=torch.int64, device=ids.device)
+    arr = C.c_void_p * 3
+    p_ids = arr(*[(o[0].data_ptr() if o else None) for o in outs])
+    p_rows = arr(*[(o[1].data_ptr() if o else None) for o in outs])
+    p_cnt = arr(*[(o[2].data_ptr() if (o and o[2] is not None) else None) for o in outs])
+    lib = _lib.load()
+    ws = _lib.workspace(lib.hb_partition_workspace_bytes(n, 3))
+    _lib.check(lib.hb_table_split3(ids.contiguous().data_ptr(), rows.data_ptr(), _lib.ptr(cnt), n,
+                                   _lib.ptr(n_dev), _row_bytes(rows), table.data_ptr(), p_ids, p_rows,
+                                   p_cnt, counts.data_ptr(), ws.data_ptr(), ws.numel(),
+                                   _lib.stream_ptr()))
+    return outs, counts
 
 
 def cudaGradSplit3(ids, rows, hot_mask, local_mask):
@@ -470,7 +505,8 @@ def cudaGradSplit3(ids, rows, hot_mask, local_mask):
     return out_ids, out_rows, counts
 
 
-def cudaUniqueSegSum(ids, grads, cnt=None, mean: bool = False, id_bits: int = 64, sync: bool = True):
+def cudaUniqueSegSum(ids, grads, cnt=None, mean: bool = False, id_bits: int = 64, sync: bool = True,
+                     n_dev: torch.Tensor | None = None):
     """Sorted unique ids, per-id fp32 sum (or mean) of the rows, per-id counts;
     deterministic.  With sync=True the outputs are sliced to the number of unique ids
     (one device-to-host read, as torch.unique does); with sync=False the full-size
@@ -487,7 +523,7 @@ def cudaUniqueSegSum(ids, grads, cnt=None, mean: bool = False, id_bits: int = 64
     lib = _lib.load()
     ws = _lib.workspace(lib.hb_unique_segsum_workspace_bytes(n, dim))
     _lib.check(lib.hb_unique_segsum_f32(ids.contiguous().data_ptr(), grads.contiguous().data_ptr(),
-                                        _lib.ptr(cnt), n, dim, int(id_bits), int(mean),
+                                        _lib.ptr(cnt), n, _lib.ptr(n_dev), dim, int(id_bits), int(mean),
                                         uniq.data_ptr(), sums.data_ptr(), counts.data_ptr(),
                                         num.data_ptr(), ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
     if not sync:

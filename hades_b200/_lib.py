@@ -61,11 +61,28 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_owner_mod": (_int, [_p, _i64, _int, _i64, _p, _p]),
     "hb_owner_range": (_int, [_p, _i64, _int, _p, _i64, _i64, _p, _p]),
     "hb_upper_bound": (_int, [_p, _i64, _int, _p, _i64, _p, _p]),
-    "hb_bucket_pack": (_int, [_p, _p, _p, _i64, _i64, _int, _p, _i64, _i64, _p, _p, _p, _p, _p, _sz, _p]),
+    "hb_bucket_pack": (_int, [_p, _p, _p, _i64, _p, _i64, _int, _p, _i64, _i64, _p, _p, _p, _p, _p, _sz, _p]),
+    "hb_table_split3": (_int, [_p, _p, _p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "hb_grad_split3": (_int, [_p, _p, _p, _p, _i64, _i64, _p, _p, _p, _p, _sz, _p]),
     "hb_unique_segsum_workspace_bytes": (_sz, [_i64, _i64]),
-    "hb_unique_segsum_f32": (_int, [_p, _p, _p, _i64, _i64, _int, _int, _p, _p, _p, _p, _p, _sz, _p]),
+    "hb_unique_segsum_f32": (_int, [_p, _p, _p, _i64, _p, _i64, _int, _int, _p, _p, _p, _p, _p, _sz, _p]),
+    "hb_staging_accumulate_cached": (_int, [_p, _p, _p, _p, _i64, _p, _p, C.c_int32, _int, _p, _p, _p]),
+    "hb_staging_accumulate_direct": (_int, [_p, _p, _p, _i64, _p, _i64, _i64, _p]),
+    "hb_staging_flush_workspace_bytes": (_sz, [_i64, _int]),
+    "hb_staging_flush": (_int, [_p, _p, C.c_int32, _int, _p, _p, _p, _p, _p, _sz, _p]),
+    "hb_staging_insert_workspace_bytes": (_sz, [_i64]),
+    "hb_staging_insert": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p, _sz, _p]),
+    "hb_sparse_adam": (_int, [_p, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _int,
+                              C.c_double, C.c_double, C.c_double, C.c_double, _p]),
+    "hb_sparse_adagrad": (_int, [_p, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _p, _p, _int,
+                                 C.c_double, C.c_double, _p]),
 }
+
+
+class StagingDesc(C.Structure):
+    """hb_staging_t"""
+    _fields_ = [("grad", _p), ("cnt", _p), ("idx", _p), ("iter_count", _p),
+                ("iter_threshold", _p), ("slots", _i64), ("dim", _i64)]
 
 _LIB: C.CDLL | None = None
 

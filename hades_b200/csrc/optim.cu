@@ -1,0 +1,260 @@
+// Sparse optimiser row updates on the owning shard: Adam as the reference's
+// SparseAdam.update (python/EmbCache/sparse_optim.py:590-685) and Adagrad (the
+// reference has no Adagrad; the rule is the usual sparse Adagrad
+// sum += g*g; emb -= lr * g / (sqrt(sum) + eps)).  State, gradient and embedding
+// rows are read and written once, in one kernel; the reference moves state
+// through cached fetch/set kernels and the embedding through a CPU write.
+#include <cuda_fp16.h>
+
+#include "launch.cuh"
+
+namespace hb {
+namespace {
+
+constexpr int kBlock = 256;
+
+__device__ __forceinline__ int64_t effective_n(int64_t n, const int64_t* n_dev) {
+  if (!n_dev) return n;
+  const int64_t d = *n_dev;
+  return d < n ? d : n;
+}
+
+struct RowMap {
+  int64_t offset, stride, rows;
+  __device__ __forceinline__ int64_t operator()(int64_t id) const {
+    if (id < offset) return -1;
+    const int64_t r = (id - offset) / stride;
+    return r < rows ? r : -1;
+  }
+};
+
+template <typename E> struct EmbIO;
+template <> struct EmbIO<float> {
+  static __device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+  static __device__ __forceinline__ float load(const float* p) { return *p; }
+  static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+};
+template <> struct EmbIO<__half> {
+  static __device__ __forceinline__ float4 load4(const __half* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __half2 a = *reinterpret_cast<const __half2*>(&raw.x);
+    const __half2 b = *reinterpret_cast<const __half2*>(&raw.y);
+    const float2 fa = __half22float2(a), fb = __half22float2(b);
+    return make_float4(fa.x, fa.y, fb.x, fb.y);
+  }
+  static __device__ __forceinline__ void store4(__half* p, float4 v) {
+    const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const unsigned*>(&a);
+    raw.y = *reinterpret_cast<const unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+  static __device__ __forceinline__ float load(const __half* p) { return __half2float(*p); }
+  static __device__ __forceinline__ void store(__half* p, float v) { *p = __float2half_rn(v); }
+};
+
+struct AdamParams {
+  float lr, beta1, beta2, eps, one_minus_beta1, one_minus_beta2;
+};
+
+__device__ __forceinline__ float adam_elem(float g, float& m, float& v, float bias1, float bias2,
+                                           const AdamParams& p) {
+  // update_mem = beta1*mem + (1-beta1)*grad; update_power = beta2*power + (1-beta2)*grad^2
+  m = p.beta1 * m + p.one_minus_beta1 * g;
+  v = p.beta2 * v + p.one_minus_beta2 * (g * g);
+  const float mc = m / bias1;
+  const float vc = v / bias2;
+  return p.lr * mc / (sqrtf(vc) + p.eps);  // std_values, sparse_optim.py:654-655
+}
+
+// A group of G lanes per row; kRows rows in flight.
+template <typename E, bool VEC4>
+__global__ void __launch_bounds__(kBlock) sparse_adam_kernel(
+    const int64_t* __restrict__ ids, const float* __restrict__ grads,
+    const int64_t* __restrict__ cnt, int64_t n, const int64_t* __restrict__ n_dev, int64_t dim,
+    RowMap map, float* __restrict__ step, float* __restrict__ mem, float* __restrict__ power,
+    E* __restrict__ emb, AdamParams p, int glog2) {
+  n = effective_n(n, n_dev);
+  const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  const int64_t group = tid >> glog2;
+  const int sub = (int)(tid & ((1 << glog2) - 1));
+  const int64_t ngroups = ((int64_t)gridDim.x * blockDim.x) >> glog2;
+  const int G = 1 << glog2;
+  for (int64_t i = group; i < n; i += ngroups) {
+    const int64_t row = map(__ldg(ids + i));
+    if (row < 0) continue;
+    // state_step = state_step + 1 (per row), sparse_optim.py:624-626
+    const float t = step[row] + 1.0f;
+    const float bias1 = 1.0f - powf(p.beta1, t);
+    const float bias2 = 1.0f - powf(p.beta2, t);
+    const float inv_cnt = cnt ? (float)__ldg(cnt + i) : 1.0f;  // grad / cnt, sparse_optim.py:608-611
+    const float* g = grads + i * dim;
+    float* m = mem + row * dim;
+    float* v = power + row * dim;
+    E* e = emb + row * dim;
+    if (VEC4) {
+      for (int64_t k = sub; k < (dim >> 2); k += G) {
+        float4 gg = __ldg(reinterpret_cast<const float4*>(g) + k);
+        if (cnt) { gg.x /= inv_cnt; gg.y /= inv_cnt; gg.z /= inv_cnt; gg.w /= inv_cnt; }
+        float4 mm = reinterpret_cast<float4*>(m)[k];
+        float4 vv = reinterpret_cast<float4*>(v)[k];
+        float4 ee = EmbIO<E>::load4(e + 4 * k);
+        ee.x -= adam_elem(gg.x, mm.x, vv.x, bias1, bias2, p);
+        ee.y -= adam_elem(gg.y, mm.y, vv.y, bias1, bias2, p);
+        ee.z -= adam_elem(gg.z, mm.z, vv.z, bias1, bias2, p);
+        ee.w -= adam_elem(gg.w, mm.w, vv.w, bias1, bias2, p);
+        reinterpret_cast<float4*>(m)[k] = mm;
+        reinterpret_cast<float4*>(v)[k] = vv;
+        EmbIO<E>::store4(e + 4 * k, ee);
+      }
+    } else {
+      for (int64_t k = sub; k < dim; k += G) {
+        float gg = __ldg(g + k);
+        if (cnt) gg /= inv_cnt;
+        float mm = m[k], vv = v[k];
+        const float upd = adam_elem(gg, mm, vv, bias1, bias2, p);
+        m[k] = mm;
+        v[k] = vv;
+        EmbIO<E>::store(e + k, EmbIO<E>::load(e + k) - upd);
+      }
+    }
+  }
+}
+
+// step[row] += 1 for every updated row; a launch of its own so that no lane of
+// the update kernel can see the new step of its own row.
+__global__ void bump_step_kernel(const int64_t* __restrict__ ids, int64_t n,
+                                 const int64_t* __restrict__ n_dev, RowMap map,
+                                 float* __restrict__ step) {
+  n = effective_n(n, n_dev);
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t row = map(__ldg(ids + i));
+  if (row >= 0) step[row] += 1.0f;
+}
+
+template <typename E, bool VEC4>
+__global__ void __launch_bounds__(kBlock) sparse_adagrad_kernel(
+    const int64_t* __restrict__ ids, const float* __restrict__ grads,
+    const int64_t* __restrict__ cnt, int64_t n, const int64_t* __restrict__ n_dev, int64_t dim,
+    RowMap map, float* __restrict__ state_sum, E* __restrict__ emb, float lr, float eps, int glog2) {
+  n = effective_n(n, n_dev);
+  const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  const int64_t group = tid >> glog2;
+  const int sub = (int)(tid & ((1 << glog2) - 1));
+  const int64_t ngroups = ((int64_t)gridDim.x * blockDim.x) >> glog2;
+  const int G = 1 << glog2;
+  for (int64_t i = group; i < n; i += ngroups) {
+    const int64_t row = map(__ldg(ids + i));
+    if (row < 0) continue;
+    const float c = cnt ? (float)__ldg(cnt + i) : 1.0f;
+    const float* g = grads + i * dim;
+    float* s = state_sum + row * dim;
+    E* e = emb + row * dim;
+    if (VEC4) {
+      for (int64_t k = sub; k < (dim >> 2); k += G) {
+        float4 gg = __ldg(reinterpret_cast<const float4*>(g) + k);
+        if (cnt) { gg.x /= c; gg.y /= c; gg.z /= c; gg.w /= c; }
+        float4 ss = reinterpret_cast<float4*>(s)[k];
+        float4 ee = EmbIO<E>::load4(e + 4 * k);
+        ss.x += gg.x * gg.x; ss.y += gg.y * gg.y; ss.z += gg.z * gg.z; ss.w += gg.w * gg.w;
+        ee.x -= lr * gg.x / (sqrtf(ss.x) + eps);
+        ee.y -= lr * gg.y / (sqrtf(ss.y) + eps);
+        ee.z -= lr * gg.z / (sqrtf(ss.z) + eps);
+        ee.w -= lr * gg.w / (sqrtf(ss.w) + eps);
+        reinterpret_cast<float4*>(s)[k] = ss;
+        EmbIO<E>::store4(e + 4 * k, ee);
+      }
+    } else {
+      for (int64_t k = sub; k < dim; k += G) {
+        float gg = __ldg(g + k);
+        if (cnt) gg /= c;
+        const float ss = s[k] + gg * gg;
+        s[k] = ss;
+        EmbIO<E>::store(e + k, EmbIO<E>::load(e + k) - lr * gg / (sqrtf(ss) + eps));
+      }
+    }
+  }
+}
+
+int group_log2_for(int64_t units) {
+  int g = 0;
+  while ((1 << g) < units && g < 5) ++g;
+  return g;
+}
+
+int grid_for_groups(int64_t n, int glog2) {
+  int64_t blocks = ceil_div(n << glog2, kBlock);
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" {
+
+int hb_sparse_adam(const int64_t* ids, const float* grads, const int64_t* cnt, int64_t n,
+                   const int64_t* n_dev, int64_t dim, int64_t id_offset, int64_t id_stride,
+                   int64_t rows, float* step, float* mem, float* power, void* emb, int emb_elem_bytes,
+                   double lr, double beta1, double beta2, double eps, hb_stream_t stream) {
+  HB_CHECK_ARG(n >= 0 && dim > 0 && rows > 0 && id_stride > 0, "hb_sparse_adam: bad sizes");
+  HB_CHECK_ARG(emb_elem_bytes == 4 || emb_elem_bytes == 2,
+               "hb_sparse_adam: embedding must be fp32 (4) or fp16 (2)");
+  HB_CHECK_ARG(n == 0 || (ids && grads && step && mem && power && emb), "hb_sparse_adam: null argument");
+  if (n == 0) return HB_OK;
+  const AdamParams p{(float)lr, (float)beta1, (float)beta2, (float)eps, (float)(1.0 - beta1),
+                     (float)(1.0 - beta2)};
+  const RowMap map{id_offset, id_stride, rows};
+  const uintptr_t bits = (uintptr_t)grads | (uintptr_t)mem | (uintptr_t)power | (uintptr_t)emb;
+  const bool vec4 = dim % 4 == 0 && (bits & 15) == 0;
+  const int glog2 = group_log2_for(vec4 ? dim / 4 : dim);
+  const int grid = grid_for_groups(n, glog2);
+  cudaStream_t st = (cudaStream_t)stream;
+#define HB_ADAM(E, V)                                                                          \
+  HB_LAUNCH((sparse_adam_kernel<E, V>), grid, kBlock, 0, st, ids, grads, cnt, n, n_dev, dim, map, \
+            step, mem, power, (E*)emb, p, glog2)
+  if (emb_elem_bytes == 4) {
+    if (vec4) HB_ADAM(float, true); else HB_ADAM(float, false);
+  } else {
+    if (vec4) HB_ADAM(__half, true); else HB_ADAM(__half, false);
+  }
+#undef HB_ADAM
+  HB_LAUNCH(bump_step_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, ids, n, n_dev, map, step);
+  return HB_OK;
+}
+
+int hb_sparse_adagrad(const int64_t* ids, const float* grads, const int64_t* cnt, int64_t n,
+                      const int64_t* n_dev, int64_t dim, int64_t id_offset, int64_t id_stride,
+                      int64_t rows, float* state_sum, void* emb, int emb_elem_bytes, double lr,
+                      double eps, hb_stream_t stream) {
+  HB_CHECK_ARG(n >= 0 && dim > 0 && rows > 0 && id_stride > 0, "hb_sparse_adagrad: bad sizes");
+  HB_CHECK_ARG(emb_elem_bytes == 4 || emb_elem_bytes == 2,
+               "hb_sparse_adagrad: embedding must be fp32 (4) or fp16 (2)");
+  HB_CHECK_ARG(n == 0 || (ids && grads && state_sum && emb), "hb_sparse_adagrad: null argument");
+  if (n == 0) return HB_OK;
+  const RowMap map{id_offset, id_stride, rows};
+  const uintptr_t bits = (uintptr_t)grads | (uintptr_t)state_sum | (uintptr_t)emb;
+  // fp16 rows are read 8 bytes at a time on the vector path
+  const bool vec4 = dim % 4 == 0 && (bits & 15) == 0;
+  const int glog2 = group_log2_for(vec4 ? dim / 4 : dim);
+  const int grid = grid_for_groups(n, glog2);
+  cudaStream_t st = (cudaStream_t)stream;
+#define HB_ADAGRAD(E, V)                                                                        \
+  HB_LAUNCH((sparse_adagrad_kernel<E, V>), grid, kBlock, 0, st, ids, grads, cnt, n, n_dev, dim, \
+            map, state_sum, (E*)emb, (float)lr, (float)eps, glog2)
+  if (emb_elem_bytes == 4) {
+    if (vec4) HB_ADAGRAD(float, true); else HB_ADAGRAD(float, false);
+  } else {
+    if (vec4) HB_ADAGRAD(__half, true); else HB_ADAGRAD(__half, false);
+  }
+#undef HB_ADAGRAD
+  return HB_OK;
+}
+
+}  // extern "C"

@@ -92,6 +92,7 @@ struct OwnerFn {
 struct BucketPackPolicy {
   OwnerFn owner;
   int num_buckets;
+  const int64_t* n_dev;  // nullable device count that caps n
   const int64_t* ids;
   const char* rows;
   const int64_t* cnt;
@@ -101,6 +102,7 @@ struct BucketPackPolicy {
   char* out_rows;
   int64_t* out_cnt;
   __device__ __forceinline__ int classify(int64_t i) const {
+    if (n_dev && i >= *n_dev) return -1;
     const int64_t id = __ldg(ids + i);
     if (id < 0) return -1;
     const int o = owner(id);
@@ -138,6 +140,39 @@ struct GradSplitPolicy {
     const int64_t d = start + pos;
     if (active) out_ids[d] = ids[i];
     warp_move_rows(rows + i * row_bytes, out_rows + d * row_bytes, active, row_bytes, vb);
+  }
+};
+
+// ---- 3-way split of (ids, rows, cnt) by a per-node class table ---------------------------
+// class = table[id] in {0, 1, 2}; the split of src/cuda/split.cu applied to rows that
+// travel with their ids (gradient rows after local aggregation).
+struct TableSplitPolicy {
+  const int64_t* ids;
+  const char* rows;
+  const int64_t* cnt;
+  const int64_t* n_dev;
+  const int8_t* table;
+  int64_t row_bytes;
+  int vb;
+  int64_t* out_ids[3];   // per class, each compacted from 0; null = count only
+  char* out_rows[3];
+  int64_t* out_cnt[3];
+  __device__ __forceinline__ int classify(int64_t i) const {
+    if (n_dev && i >= *n_dev) return -1;
+    const int64_t id = __ldg(ids + i);
+    if (id < 0) return -1;
+    const int8_t v = __ldg(table + id);
+    return (v >= 0 && v <= 2) ? (int)v : -1;
+  }
+  __device__ __forceinline__ void emit(int64_t i, int c, int64_t pos, int64_t, bool active) const {
+    const bool write = active && out_ids[c] != nullptr;
+    if (write) {
+      out_ids[c][pos] = ids[i];
+      if (cnt && out_cnt[c]) out_cnt[c][pos] = cnt[i];
+    }
+    const bool move = write && out_rows[c] != nullptr;
+    warp_move_rows(rows + i * row_bytes, move ? out_rows[c] + pos * row_bytes : nullptr, move,
+                   row_bytes, vb);
   }
 };
 
@@ -227,7 +262,8 @@ int hb_upper_bound(const void* in, int64_t n, int idx_bytes, const void* sorted,
 }
 
 int hb_bucket_pack(const int64_t* ids, const void* rows, const int64_t* cnt, int64_t n,
-                   int64_t row_bytes, int num_buckets, const int64_t* range_partition,
+                   const int64_t* n_dev, int64_t row_bytes, int num_buckets,
+                   const int64_t* range_partition,
                    int64_t num_part, int64_t g, int64_t* out_ids, void* out_rows, int64_t* out_cnt,
                    int64_t* counts, void* workspace, size_t workspace_bytes, hb_stream_t stream) {
   HB_CHECK_ARG(n >= 0 && n < ((int64_t)1 << 31), "hb_bucket_pack: n out of range");
@@ -237,11 +273,38 @@ int hb_bucket_pack(const int64_t* ids, const void* rows, const int64_t* cnt, int
   HB_CHECK_ARG(!rows || (out_rows && row_bytes > 0), "hb_bucket_pack: rows without output");
   HB_CHECK_ARG(!cnt || out_cnt, "hb_bucket_pack: cnt without output");
   HB_CHECK_ARG(!range_partition || num_part > 0, "hb_bucket_pack: empty range partition");
-  BucketPackPolicy pol{{range_partition, num_part, g}, num_buckets, ids, (const char*)rows, cnt,
+  BucketPackPolicy pol{{range_partition, num_part, g}, num_buckets, n_dev, ids, (const char*)rows, cnt,
                        row_bytes, rows ? payload_vec_bytes(row_bytes, rows, out_rows) : 1,
                        out_ids, (char*)out_rows, out_cnt};
   return run_partition(pol, n, num_buckets, workspace, workspace_bytes, counts,
                        (cudaStream_t)stream);
+}
+
+int hb_table_split3(const int64_t* ids, const void* rows, const int64_t* cnt, int64_t n,
+                    const int64_t* n_dev, int64_t row_bytes, const int8_t* table,
+                    int64_t* const* out_ids, void* const* out_rows, int64_t* const* out_cnt,
+                    int64_t* counts, void* workspace, size_t workspace_bytes,
+                    hb_stream_t stream) {
+  HB_CHECK_ARG(n >= 0 && n < ((int64_t)1 << 31) && row_bytes > 0, "hb_table_split3: bad sizes");
+  HB_CHECK_ARG(counts != nullptr && table != nullptr, "hb_table_split3: null counts or table");
+  HB_CHECK_ARG(out_ids && out_rows, "hb_table_split3: null output tables");
+  HB_CHECK_ARG(n == 0 || (ids && rows), "hb_table_split3: null argument");
+  TableSplitPolicy pol;
+  pol.ids = ids;
+  pol.rows = (const char*)rows;
+  pol.cnt = cnt;
+  pol.n_dev = n_dev;
+  pol.table = table;
+  pol.row_bytes = row_bytes;
+  uintptr_t bits = (uintptr_t)row_bytes | (uintptr_t)rows;
+  for (int c = 0; c < 3; ++c) {
+    pol.out_ids[c] = out_ids[c];
+    pol.out_rows[c] = (char*)out_rows[c];
+    pol.out_cnt[c] = out_cnt ? out_cnt[c] : nullptr;
+    bits |= (uintptr_t)out_rows[c];
+  }
+  pol.vb = (bits & 15) == 0 ? 16 : ((bits & 3) == 0 ? 4 : 1);
+  return run_partition(pol, n, 3, workspace, workspace_bytes, counts, (cudaStream_t)stream);
 }
 
 int hb_grad_split3(const int64_t* ids, const void* rows, const uint8_t* hot_mask,

@@ -37,6 +37,7 @@ struct SegArgs {
   const int64_t* num_runs;    // device scalar U
   const float* grads;         // [n][dim]
   const int64_t* cnt_in;      // nullable [n]
+  const int64_t* n_dev;       // nullable device count that caps n
   int64_t n;
   int64_t dim;
   int64_t col0;               // first column of this pass
@@ -80,6 +81,12 @@ __device__ __forceinline__ float denominator(const SegArgs& a, unsigned long lon
   return (float)(a.cnt_in ? (long long)c + 1 : (long long)c);
 }
 
+__device__ __forceinline__ int64_t effective_n(const SegArgs& a) {
+  if (!a.n_dev) return a.n;
+  const int64_t d = *a.n_dev;
+  return d < a.n ? (d > 0 ? d : 0) : a.n;
+}
+
 // ---- main pass -------------------------------------------------------------------
 template <int VEC, int G, int VPL>
 __global__ void __launch_bounds__(kBlock) segsum_main_kernel(SegArgs a) {
@@ -91,10 +98,11 @@ __global__ void __launch_bounds__(kBlock) segsum_main_kernel(SegArgs a) {
   const unsigned grp_shift = grp_in_warp * G;
   const unsigned grp_mask = G == 32 ? 0xffffffffu : ((1u << G) - 1u);
   const int64_t c = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) / G;
-  const bool live = c < a.num_chunks;
+  const int64_t n_eff = effective_n(a);  // ignored entries were given the largest key
+  const bool live = c < a.num_chunks && c * a.chunk < n_eff;
   const int64_t U_runs = *a.num_runs;
   const int64_t j0 = live ? c * a.chunk : 0;
-  const int64_t j1 = live ? ((j0 + a.chunk < a.n) ? j0 + a.chunk : a.n) : 0;
+  const int64_t j1 = live ? ((j0 + a.chunk < n_eff) ? j0 + a.chunk : n_eff) : 0;
   const int vpr = a.cols / VEC;  // vectors per row in this pass
 
   int64_t u = live ? run_of(a.run_start, U_runs, j0) : 0;
@@ -184,10 +192,10 @@ __global__ void __launch_bounds__(kBlock) segsum_main_kernel(SegArgs a) {
   }
   if (live && have) {
     // does the open run go on after this chunk?
-    const bool tail = j1 < a.n && __ldg(a.keys + j1) == __ldg(a.keys + j1 - 1);
+    const bool tail = j1 < n_eff && __ldg(a.keys + j1) == __ldg(a.keys + j1 - 1);
     if (tail && !first_partial && sub == 0 && a.col0 == 0) {
       // this chunk holds the head of a crossing run: enter it in a fix-up list
-      const int64_t run_end = (u + 1 < U_runs) ? __ldg(a.run_start + u + 1) : a.n;
+      const int64_t run_end = (u + 1 < U_runs) ? __ldg(a.run_start + u + 1) : n_eff;
       const int64_t last_chunk = (run_end - 1) / a.chunk;
       const bool is_short = (last_chunk - c) <= kShortSpan;
       const int slot = atomicAdd(a.list_counts + (is_short ? 0 : 1), 1);
@@ -210,7 +218,7 @@ __global__ void __launch_bounds__(kBlock) segsum_fix_short_kernel(SegArgs a) {
   for (int64_t e = grp; e < count; e += ngrp) {
     const int2 ent = a.short_list[e];
     const int64_t c = ent.x, u = ent.y;
-    const int64_t run_end = (u + 1 < U_runs) ? __ldg(a.run_start + u + 1) : a.n;
+    const int64_t run_end = (u + 1 < U_runs) ? __ldg(a.run_start + u + 1) : effective_n(a);
     const int64_t last_chunk = (run_end - 1) / a.chunk;
     V acc[VPL];
 #pragma unroll
@@ -250,7 +258,7 @@ __global__ void __launch_bounds__(kLongBlock) segsum_fix_long_kernel(SegArgs a) 
   for (int64_t e = blockIdx.x; e < count; e += gridDim.x) {
     const int2 ent = a.long_list[e];
     const int64_t c = ent.x, u = ent.y;
-    const int64_t run_end = (u + 1 < U_runs) ? __ldg(a.run_start + u + 1) : a.n;
+    const int64_t run_end = (u + 1 < U_runs) ? __ldg(a.run_start + u + 1) : effective_n(a);
     const int64_t last_chunk = (run_end - 1) / a.chunk;
     {
       const int col = threadIdx.x % cols;
@@ -274,9 +282,16 @@ __global__ void __launch_bounds__(kLongBlock) segsum_fix_long_kernel(SegArgs a) 
 }
 
 // ---- small helpers ----------------------------------------------------------------------------
-__global__ void iota_u32_kernel(uint32_t* p, int64_t n) {
+// keys = ids (entries at and beyond the device count get the largest key of
+// id_bits bits, so they sort last), perm = 0..n-1
+__global__ void prepare_keys_kernel(const int64_t* __restrict__ ids, int64_t n,
+                                    const int64_t* __restrict__ n_dev, int64_t sentinel,
+                                    int64_t* __restrict__ keys, uint32_t* __restrict__ perm) {
   const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (i < n) p[i] = (uint32_t)i;
+  if (i >= n) return;
+  const bool keep = !n_dev || i < *n_dev;
+  keys[i] = keep ? ids[i] : sentinel;
+  perm[i] = (uint32_t)i;
 }
 
 // counts -> the denominators the reference reports (1 + sum of cnt when cnt is given)
@@ -289,9 +304,11 @@ __global__ void finish_counts_kernel(const unsigned long long* __restrict__ raw,
 
 struct RunHeadPolicy {
   const int64_t* keys;
+  const int64_t* n_dev;
   int64_t* uniq;
   int64_t* run_start;
   __device__ __forceinline__ int classify(int64_t i) const {
+    if (n_dev && i >= *n_dev) return -1;
     return (i == 0 || __ldg(keys + i - 1) != __ldg(keys + i)) ? 0 : -1;
   }
   __device__ __forceinline__ void emit(int64_t i, int, int64_t pos, int64_t, bool active) const {
@@ -410,7 +427,8 @@ size_t hb_unique_segsum_workspace_bytes(int64_t n, int64_t dim) {
 }
 
 int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* cnt_in, int64_t n,
-                         int64_t dim, int id_bits, int mean, int64_t* uniq_ids, float* sums,
+                         const int64_t* n_dev, int64_t dim, int id_bits, int mean,
+                         int64_t* uniq_ids, float* sums,
                          int64_t* counts, int64_t* num_unique, void* workspace,
                          size_t workspace_bytes, hb_stream_t stream) {
   HB_CHECK_ARG(n >= 0 && n < ((int64_t)1 << 31) && dim > 0, "hb_unique_segsum_f32: bad sizes");
@@ -429,15 +447,16 @@ int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* 
     return HB_ERR_WORKSPACE;
   }
   // 1. sort (id, position)
-  HB_CUDA(cudaMemcpyAsync(s.k0, ids, n * sizeof(int64_t), cudaMemcpyDeviceToDevice, st));
-  HB_LAUNCH(iota_u32_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, s.p0, n);
+  const int64_t sentinel = id_bits >= 63 ? INT64_MAX : (((int64_t)1 << id_bits) - 1);
+  HB_LAUNCH(prepare_keys_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, ids, n, n_dev, sentinel,
+            s.k0, s.p0);
   cub::DoubleBuffer<int64_t> keys(s.k0, s.k1);
   cub::DoubleBuffer<uint32_t> perm(s.p0, s.p1);
   HB_CUDA(cub::DeviceRadixSort::SortPairs(s.sort_temp, s.sort_temp_bytes, keys, perm, (int)n, 0,
                                           id_bits, st));
   count_library_launches(1 + (id_bits + 7) / 8);
   // 2. run heads -> unique ids, run starts, U
-  RunHeadPolicy pol{keys.Current(), uniq_ids, s.run_start};
+  RunHeadPolicy pol{keys.Current(), n_dev, uniq_ids, s.run_start};
   int rc = run_partition(pol, n, 1, s.part_ws, s.part_ws_bytes, num_unique, st);
   if (rc != HB_OK) return rc;
   // 3./4. column passes
@@ -450,6 +469,7 @@ int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* 
   a.num_runs = num_unique;
   a.grads = grads;
   a.cnt_in = cnt_in;
+  a.n_dev = n_dev;
   a.n = n;
   a.dim = dim;
   a.chunk = s.chunk;

@@ -1,0 +1,175 @@
+"""One trainer's embedding hot path on one GPU, end to end:
+
+    forward   lookup + cached fetch (+ the LRU ageing of the reference's CPU lookup)
+    backward  local aggregation -> hot/cold split -> cold-cache accumulate ->
+              owner-partitioned exchange of the hot rows -> optimiser update on the owner;
+              every ``flush_every`` steps the cold cache is flushed through the same exchange
+              and refilled
+
+It strings together what ``DistEmb.__call__`` (python/EmbCache/dist_emb.py:167-292),
+``DistembSparseGradOptimizer.step`` (python/EmbCache/sparse_optim.py:212-448) and the cache
+server loop (python/EmbCache/server.py:259-298) do across three processes in the reference.
+Everything stays on the current CUDA stream; the only host reads are the exchange sizes when
+NCCL carries the exchange (world > 1) and the flushed-row count on flush steps.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from . import EmbCacheLib as E
+from .cold_cache import ColdCache
+from .sparse_optim import ShardedEmbedding, SparseAdam, SparseAdagrad
+
+HOT, COLD = 1, 2  # classes of the per-node table (remote hot / remote cold, src/cuda/split.cu:39-43)
+
+
+@dataclass
+class StepStats:
+    """Device-side counters of one step (read them only when needed: each is a host sync)."""
+    num_unique: torch.Tensor | None = None
+    split_counts: torch.Tensor | None = None
+    sent_counts: torch.Tensor | None = None
+    flushed: int = 0
+    extra: dict = field(default_factory=dict)
+
+
+class EmbeddingPath:
+    def __init__(self, table: torch.Tensor, class_table: torch.Tensor, cold: ColdCache,
+                 optimizer, rank: int = 0, world: int = 1, flush_every: int = 8, id_bits: int = 64,
+                 lookup_mode: int = E.LOOKUP_SETASSOC, mover: int = E.MOVER_AUTO,
+                 touch_lru: bool = True, group=None):
+        """table: backing rows for cache misses, [num_nodes, dim] fp32 on this GPU.
+        class_table: int8 per node, HOT or COLD.  optimizer: SparseAdam / SparseAdagrad on this
+        rank's shard (owner = id % world)."""
+        self.table, self.class_table, self.cold, self.opt = table, class_table, cold, optimizer
+        self.rank, self.world = rank, world
+        self.flush_every, self.id_bits = flush_every, id_bits
+        self.lookup_mode, self.mover, self.touch_lru = lookup_mode, mover, touch_lru
+        self.group = group
+        self.step_no = 0
+        # unique hot ids of a batch cannot outnumber the hot ids of the table
+        self.num_hot_ids = int((class_table == HOT).sum().item())
+
+    # ---- forward -------------------------------------------------------------------------
+    def forward(self, ids: torch.Tensor, out_rows: torch.Tensor | None = None):
+        rows, locs, found = E.cudaLookupFetch(self.cold.index, ids, self.cold.emb, self.table,
+                                              out_rows=out_rows, mode=self.lookup_mode, mover=self.mover)
+        if self.touch_lru:
+            self.cold.index.cuda_touch_lru(locs)
+        return rows, locs, found
+
+    # ---- exchange ------------------------------------------------------------------------
+    def _exchange(self, ids, rows, cnt, n_dev):
+        """Bucket by owner and deliver to the owners.  Returns (ids, rows, cnt, n_dev)."""
+        p_ids, p_rows, p_cnt, counts = E.cudaBucketPack(ids, rows, cnt, self.world, n_dev=n_dev)
+        if self.world == 1:
+            return p_ids, p_rows, p_cnt, counts, counts
+        out_counts = torch.empty_like(counts)
+        dist.all_to_all_single(out_counts, counts, group=self.group)
+        in_splits, out_splits = counts.tolist(), out_counts.tolist()
+        total, sent = sum(out_splits), sum(in_splits)
+        dev = ids.device
+        r_ids = torch.empty(total, dtype=torch.int64, device=dev)
+        r_rows = torch.empty((total, rows.shape[1]), dtype=rows.dtype, device=dev)
+        r_cnt = torch.empty(total, dtype=torch.int64, device=dev)
+        dist.all_to_all_single(r_ids, p_ids[:sent], out_splits, in_splits, group=self.group)
+        dist.all_to_all_single(r_rows, p_rows[:sent], out_splits, in_splits, group=self.group)
+        dist.all_to_all_single(r_cnt, p_cnt[:sent], out_splits, in_splits, group=self.group)
+        return r_ids, r_rows, r_cnt, None, counts
+
+    # ---- backward ------------------------------------------------------------------------
+    def backward(self, ids: torch.Tensor, grads: torch.Tensor) -> StepStats:
+        st = StepStats()
+        # hot-node local aggregation (only_unique_grads, sparse_optim.py:132-139)
+        uniq, sums, counts, num = E.cudaUniqueSegSum(ids, grads, id_bits=self.id_bits, sync=False)
+        st.num_unique = num
+        # hot / cold
+        outs, split_counts = E.cudaTableSplit3(uniq, sums, counts, self.class_table, n_dev=num,
+                                               keep=(False, True, True),
+                                               caps=(None, self.num_hot_ids, None))
+        st.split_counts = split_counts
+        hot_ids, hot_rows, hot_cnt = outs[HOT]
+        cold_ids, cold_rows, _ = outs[COLD]
+        # cold rows wait in the staging table
+        self.cold.accumulate_remote(cold_ids, cold_rows, n_dev=split_counts[COLD:COLD + 1],
+                                    touch_lru=self.touch_lru)
+        # hot rows go to their owners now
+        r_ids, r_rows, r_cnt, r_n, sent = self._exchange(hot_ids, hot_rows, hot_cnt,
+                                                         split_counts[HOT:HOT + 1])
+        st.sent_counts = sent
+        if r_n is not None:
+            r_n = r_n[:1]
+        # owner: merge the senders' rows (unique_grads with counts) and update
+        self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, n_dev=r_n, id_bits=self.id_bits)
+        self.step_no += 1
+        if self.flush_every > 0 and self.step_no % self.flush_every == 0:
+            st.flushed = self.flush()
+        return st
+
+    def flush(self) -> int:
+        """Stale cold rows leave through the same exchange; their cache entries are evicted by
+        the flush (server.py:413) and come back with the current table rows, as the next
+        forward pass of the reference would re-insert them (server.py:499-544)."""
+        f_ids, f_rows, f_cnt, _ = self.cold.flush_remote(sync=True)
+        n = f_ids.numel()
+        if n == 0 and self.world == 1:
+            return 0
+        r_ids, r_rows, r_cnt, r_n, _ = self._exchange(f_ids, f_rows, f_cnt, None)
+        if r_n is not None:
+            r_n = r_n[:1]
+        if self.world == 1:
+            # one sender: rows are already unique (is_unique=True, sparse_optim.py:405-421)
+            self.opt.update(r_ids, r_rows, r_cnt, is_unique=True, n_dev=r_n)
+        else:
+            self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, n_dev=r_n, id_bits=self.id_bits)
+        if n:
+            fresh = torch.empty((n, self.table.shape[1]), dtype=self.table.dtype, device=f_ids.device)
+            E.cudaFetch2(self.table, f_ids, fresh)
+            self.cold.insert(f_ids, fresh)
+        return n
+
+    def step(self, ids: torch.Tensor, grads: torch.Tensor, out_rows: torch.Tensor | None = None):
+        rows, locs, found = self.forward(ids, out_rows)
+        st = self.backward(ids, grads)
+        return rows, locs, found, st
+
+
+def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str = "adam",
+               hot_fraction: float = 0.01, lookup_mode: int = E.LOOKUP_SETASSOC,
+               mover: int = E.MOVER_AUTO, touch_lru: bool = True, table_dtype=torch.float32,
+               seed_config: int | None = None, group=None) -> EmbeddingPath:
+    """Build the state of one trainer for a cached-fetch configuration (``synth.CacheFetchConfig``):
+    backing table, hot cache filled with the most popular ids, class table (the top
+    ``hot_fraction`` of the popularity ranking is HOT), cold cache and optimiser shard."""
+    import numpy as np
+
+    from . import synth
+
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1000 * (seed_config or cfg.config) + rank)
+    table = torch.empty((cfg.table_rows, cfg.dim), dtype=torch.float32, device=device)
+    table.normal_(0.0, cfg.table_sigma, generator=gen)
+    n_hot = max(int(cfg.table_rows * hot_fraction), 1)
+    cls = np.full(cfg.table_rows, COLD, dtype=np.int8)
+    cls[synth.rank_to_id(np.arange(n_hot, dtype=np.int64), cfg.table_rows)] = HOT
+    class_table = torch.from_numpy(cls).to(device)
+    cold = ColdCache(f"{cfg.name}_r{rank}", cfg.cache_entries, cfg.dim, threshold=None, cnt_threshold=16,
+                     default_threshold=0, num_clients=world, lookup_mode=lookup_mode, device=device)
+    hot = torch.from_numpy(synth.hot_ids(cfg.table_rows, cfg.cache_entries)).to(device)
+    rows = torch.empty((hot.numel(), cfg.dim), dtype=torch.float32, device=device)
+    E.cudaFetch2(table, hot, rows)
+    cold.insert(hot, rows)
+    del rows
+    shard = ShardedEmbedding(cfg.table_rows, cfg.dim, rank, world, dtype=table_dtype, device=device)
+    if world == 1 and table_dtype == torch.float32:
+        shard.weight = table  # one GPU: the backing table is the owner shard
+    else:
+        shard.weight.normal_(0.0, cfg.table_sigma, generator=gen)
+    opt = SparseAdam(shard, lr=0.01) if optimizer == "adam" else SparseAdagrad(shard, lr=0.01)
+    id_bits = max(int(cfg.table_rows).bit_length() + 1, 8)
+    return EmbeddingPath(table, class_table, cold, opt, rank, world, cfg.flush_every, id_bits,
+                         lookup_mode, mover, touch_lru, group)

@@ -1,0 +1,144 @@
+"""Sparse-gradient aggregation, owner-partitioned exchange and sparse optimisers, mirroring
+python/EmbCache/sparse_optim.py of the reference with the arithmetic in libhades_b200.
+
+* ``only_unique_grads`` / ``unique_grads``   sparse_optim.py:132-157
+* ``swap_gradients``                         sparse_optim.py:19-129 (owner bucketing + all-to-all)
+* ``SparseAdam.update``                      sparse_optim.py:590-685
+* ``SparseAdagrad.update``                   no counterpart in the reference (it ships only
+  SparseAdam); the usual sparse Adagrad rule.
+
+The embedding table and the optimiser state live in HBM, sharded ``owner = id % world``,
+``local row = id // world`` (the reference keeps them in DGL DistTensors on the host and
+ships rows over PCIe and RPC).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .EmbCacheLib import _check, cudaBucketPack, cudaUniqueSegSum
+
+
+def only_unique_grads(idx: torch.Tensor, grad: torch.Tensor, id_bits: int = 64):
+    """(unique ids sorted, per-id fp32 sums, per-id counts); sparse_optim.py:132-139."""
+    return cudaUniqueSegSum(idx, grad, None, mean=False, id_bits=id_bits)
+
+
+def unique_grads(idx: torch.Tensor, grad: torch.Tensor, cnt: torch.Tensor | None = None, id_bits: int = 64):
+    """(unique ids sorted, per-id mean); with cnt the divisor is 1 + sum(cnt), as in the
+    reference (sparse_optim.py:142-157, counts start from ones at :145)."""
+    ids, vals, _ = cudaUniqueSegSum(idx, grad, cnt, mean=True, id_bits=id_bits)
+    return ids, vals
+
+
+def swap_gradients(idics, grads, partition_range, num_parts, num_trainers_per_part, device,
+                   grads_cnt=None, group=None):
+    """Bucket rows by owner and exchange them: every rank receives the rows it owns.
+    owner = id % num_trainers_per_part when partition_range is None, else the range rule of
+    cudaBinarySearch.  Returns (ids, grads, cnt or None).  One fused pack kernel replaces
+    the reference's owner kernel + torch.sort + three gathers + cudaBinarySearch2
+    (sparse_optim.py:36-52); the exchange itself is NCCL all_to_all_single as there."""
+    world = int(num_parts * num_trainers_per_part)
+    ids_p, rows_p, cnt_p, counts = cudaBucketPack(idics, grads, grads_cnt, world, partition_range,
+                                                  num_trainers_per_part)
+    if world == 1 or not dist.is_initialized():
+        return ids_p, rows_p, cnt_p
+    out_counts = torch.empty_like(counts)
+    dist.all_to_all_single(out_counts, counts, group=group)
+    in_splits = counts.tolist()
+    out_splits = out_counts.tolist()
+    total = sum(out_splits)
+    out_ids = torch.empty(total, dtype=ids_p.dtype, device=device)
+    out_rows = torch.empty((total, rows_p.shape[1]), dtype=rows_p.dtype, device=device)
+    dist.all_to_all_single(out_ids, ids_p, out_splits, in_splits, group=group)
+    dist.all_to_all_single(out_rows, rows_p, out_splits, in_splits, group=group)
+    out_cnt = None
+    if cnt_p is not None:
+        out_cnt = torch.empty(total, dtype=cnt_p.dtype, device=device)
+        dist.all_to_all_single(out_cnt, cnt_p, out_splits, in_splits, group=group)
+    return out_ids, out_rows, out_cnt
+
+
+class ShardedEmbedding:
+    """The rows of a [num_embeddings, dim] table owned by this rank (owner = id % world)."""
+
+    def __init__(self, num_embeddings: int, dim: int, rank: int = 0, world: int = 1,
+                 dtype=torch.float32, device=None, init_sigma: float | None = None, seed: int = 0):
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self.num_embeddings, self.embedding_dim = int(num_embeddings), int(dim)
+        self.rank, self.world = int(rank), int(world)
+        self.rows = (self.num_embeddings - self.rank + self.world - 1) // self.world
+        self.weight = torch.zeros((self.rows, dim), dtype=dtype, device=device)
+        if init_sigma is not None:
+            g = torch.Generator(device=device)
+            g.manual_seed(seed * 1000 + rank)
+            self.weight.normal_(0.0, init_sigma, generator=g)
+
+
+class _SparseOptimizer:
+    def __init__(self, emb: ShardedEmbedding, lr: float):
+        self.emb = emb
+        self._lr = float(lr)
+
+    def _args(self, idx, grad, cnt):
+        _check(idx.is_cuda and idx.dtype == torch.int64, "idx is a CUDA int64 tensor")
+        _check(grad.dtype == torch.float32 and grad.size(1) == self.emb.embedding_dim, "grad is fp32 [n, dim]")
+        if cnt is not None:
+            _check(cnt.dtype == torch.int64, "cnt.dtype == int64")
+        return idx.contiguous(), grad.contiguous(), None if cnt is None else cnt.contiguous()
+
+
+class SparseAdam(_SparseOptimizer):
+    """SparseAdam of the reference (sparse_optim.py:531-702) on this rank's shard."""
+
+    def __init__(self, emb: ShardedEmbedding, lr: float, betas=(0.9, 0.999), eps: float = 1e-8):
+        super().__init__(emb, lr)
+        self._beta1, self._beta2, self._eps = float(betas[0]), float(betas[1]), float(eps)
+        dev = emb.weight.device
+        self.state_step = torch.zeros(emb.rows, dtype=torch.float32, device=dev)
+        self.state_mem = torch.zeros((emb.rows, emb.embedding_dim), dtype=torch.float32, device=dev)
+        self.state_power = torch.zeros((emb.rows, emb.embedding_dim), dtype=torch.float32, device=dev)
+
+    def update(self, idx, grad, cnt=None, is_unique: bool = False, n_dev: torch.Tensor | None = None,
+               id_bits: int = 64) -> None:
+        idx, grad, cnt = self._args(idx, grad, cnt)
+        if not is_unique:
+            # unique_grads (sparse_optim.py:611), without reading the unique count on the host
+            idx, grad, _, n_dev = cudaUniqueSegSum(idx, grad, cnt, mean=True, id_bits=id_bits,
+                                                   sync=False, n_dev=n_dev)
+            cnt = None
+        lib = _lib.load()
+        w = self.emb.weight
+        _lib.check(lib.hb_sparse_adam(idx.data_ptr(), grad.data_ptr(), _lib.ptr(cnt), idx.numel(),
+                                      _lib.ptr(n_dev), self.emb.embedding_dim, self.emb.rank,
+                                      self.emb.world, self.emb.rows, self.state_step.data_ptr(),
+                                      self.state_mem.data_ptr(), self.state_power.data_ptr(),
+                                      w.data_ptr(), w.element_size(), self._lr, self._beta1,
+                                      self._beta2, self._eps, _lib.stream_ptr()))
+
+
+class SparseAdagrad(_SparseOptimizer):
+    """Sparse Adagrad: sum += g*g; emb -= lr * g / (sqrt(sum) + eps)."""
+
+    def __init__(self, emb: ShardedEmbedding, lr: float, eps: float = 1e-10):
+        super().__init__(emb, lr)
+        self._eps = float(eps)
+        self.state_sum = torch.zeros((emb.rows, emb.embedding_dim), dtype=torch.float32,
+                                     device=emb.weight.device)
+
+    def update(self, idx, grad, cnt=None, is_unique: bool = False, n_dev: torch.Tensor | None = None,
+               id_bits: int = 64) -> None:
+        idx, grad, cnt = self._args(idx, grad, cnt)
+        if not is_unique:
+            # unique_grads (sparse_optim.py:611), without reading the unique count on the host
+            idx, grad, _, n_dev = cudaUniqueSegSum(idx, grad, cnt, mean=True, id_bits=id_bits,
+                                                   sync=False, n_dev=n_dev)
+            cnt = None
+        lib = _lib.load()
+        w = self.emb.weight
+        _lib.check(lib.hb_sparse_adagrad(idx.data_ptr(), grad.data_ptr(), _lib.ptr(cnt), idx.numel(),
+                                         _lib.ptr(n_dev), self.emb.embedding_dim, self.emb.rank,
+                                         self.emb.world, self.emb.rows, self.state_sum.data_ptr(),
+                                         w.data_ptr(), w.element_size(), self._lr, self._eps,
+                                         _lib.stream_ptr()))

@@ -210,10 +210,23 @@ int hb_upper_bound(const void* in, int64_t n, int idx_bytes, const void* sorted,
  * hb_owner_range rule.  rows and cnt are optional.  counts: device
  * int64[num_buckets]; bucket b starts at the sum of the counts before it. */
 int hb_bucket_pack(const int64_t* ids, const void* rows, const int64_t* cnt, int64_t n,
+                   const int64_t* n_dev /* nullable device count capping n */,
                    int64_t row_bytes, int num_buckets, const int64_t* range_partition,
                    int64_t num_part, int64_t g, int64_t* out_ids, void* out_rows,
                    int64_t* out_cnt, int64_t* counts, void* workspace,
                    size_t workspace_bytes, hb_stream_t stream);
+
+/* (ids, rows, cnt) split three ways by a per-node class table, class =
+ * table[id] in {0,1,2} (the classes of src/cuda/split.cu:34-44).  out_ids,
+ * out_rows, out_cnt are HOST arrays of three device pointers: class c is
+ * compacted, in input order, into its own buffers starting at entry 0; a NULL
+ * out_ids[c] counts the class without writing it.  counts: device int64[3].
+ * cnt / out_cnt are optional; n_dev (nullable device int64) caps n. */
+int hb_table_split3(const int64_t* ids, const void* rows, const int64_t* cnt, int64_t n,
+                    const int64_t* n_dev, int64_t row_bytes, const int8_t* table,
+                    int64_t* const* out_ids, void* const* out_rows, int64_t* const* out_cnt,
+                    int64_t* counts, void* workspace, size_t workspace_bytes,
+                    hb_stream_t stream);
 
 /* The hot / cold-local / cold-remote selects of DistembSparseGradOptimizer.step
  * (python/EmbCache/sparse_optim.py:243-259) in one pass: out holds the hot rows
@@ -232,12 +245,99 @@ int hb_grad_split3(const int64_t* ids, const void* rows, const uint8_t* hot_mask
  * occurrences per id; when mean = 1 and cnt_in is given, 1 + sum of cnt_in,
  * which is also the divisor (the reference starts its counts from ones,
  * sparse_optim.py:145-148).  uniq_ids / sums / counts must hold n entries;
- * num_unique is a device int64.  id_bits: ids are < 2^id_bits (sort passes). */
+ * num_unique is a device int64.  id_bits: ids are < 2^id_bits - 1 (sort passes).
+ * n_dev (nullable device int64) caps n: entries at and beyond it are ignored. */
 size_t hb_unique_segsum_workspace_bytes(int64_t n, int64_t dim);
 int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* cnt_in,
-                         int64_t n, int64_t dim, int id_bits, int mean, int64_t* uniq_ids,
+                         int64_t n, const int64_t* n_dev, int64_t dim, int id_bits, int mean,
+                         int64_t* uniq_ids,
                          float* sums, int64_t* counts /* nullable */, int64_t* num_unique,
                          void* workspace, size_t workspace_bytes, hb_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Cold-gradient staging table (the reference's cache-server buffers).         */
+/* ------------------------------------------------------------------------- */
+/* Caller-owned device buffers, python/EmbCache/server.py:76-160:
+ * _grad_cache_buff, _grad_cnt_cache_buff, _grad_idx_cache_buff,
+ * _grad_iter_count, _grad_iter_threshold (and their _local_ twins). */
+typedef struct hb_staging {
+  float* grad;             /* [slots][dim], zero when idle */
+  int32_t* cnt;            /* [slots] messages accumulated since the last flush */
+  int64_t* idx;            /* [slots] id staged in the slot, -1 = none */
+  int32_t* iter_count;     /* [slots] iterations since the last flush */
+  int32_t* iter_threshold; /* [slots] flush after this many iterations */
+  int64_t slots;
+  int64_t dim;
+} hb_staging_t;
+
+/* Cold remote gradients, _accumulate_gradients_cold_remote, server.py:546-562:
+ * slot = lookup(id); found: idx[slot] = id, iter_threshold[slot] =
+ * threshold_table[id] (default_threshold when the table is NULL), grad[slot] +=
+ * grads[i], cnt[slot] += 1; a miss is dropped (counted in *dropped, a device
+ * int64, when given).  ids must be unique.  n_dev (nullable device int64) caps n,
+ * so that the count left on the device by hb_unique_segsum_f32 can be used
+ * without a host read.  locs_out (nullable, n entries) receives the slots, for
+ * hb_index_touch_lru: the server's lookup is the CPU one, which ages the LRU
+ * counters.  The staging table has one slot per cache slot. */
+int hb_staging_accumulate_cached(hb_index_t* h, const hb_staging_t* s, const int64_t* ids,
+                                 const float* grads, int64_t n, const int64_t* n_dev,
+                                 const int32_t* threshold_table, int32_t default_threshold,
+                                 int mode, int64_t* dropped, int64_t* locs_out,
+                                 hb_stream_t stream);
+
+/* Cold local gradients, _accumulate_gradients_cold_local, server.py:564-574:
+ * slot = (id - id_offset) / id_stride; grad[slot] += grads[i]; cnt[slot] += 1;
+ * idx[slot] = id.  ids must be unique. */
+int hb_staging_accumulate_direct(const hb_staging_t* s, const int64_t* ids, const float* grads,
+                                 int64_t n, const int64_t* n_dev, int64_t id_offset,
+                                 int64_t id_stride, hb_stream_t stream);
+
+/* _send_staled_gradients, server.py:346-497: slots with cnt > 0 and (iter_count
+ * >= iter_threshold or cnt >= cnt_threshold) leave in slot order, bucketed by
+ * id % num_clients (counts: device int64[num_clients]); their rows are read AND
+ * zeroed, cnt and iter_count return to 0 and, when an index is given, their ids
+ * are reset in it; other slots with cnt > 0 age by one iteration.  (The
+ * reference zeroes a temporary copy of the rows, server.py:414, so its buffers
+ * are never cleared; this library implements the intended read-and-zero.)
+ * Outputs must hold `slots` entries. */
+size_t hb_staging_flush_workspace_bytes(int64_t slots, int num_clients);
+int hb_staging_flush(hb_index_t* h /* nullable */, const hb_staging_t* s, int32_t cnt_threshold,
+                     int num_clients, int64_t* out_ids, float* out_rows, int64_t* out_cnt,
+                     int64_t* counts, void* workspace, size_t workspace_bytes,
+                     hb_stream_t stream);
+
+/* _update_cache, server.py:499-544: locs = add(ids); cache_rows[locs[i]] =
+ * emb_rows[i] where locs[i] >= 0; the staging state of those slots is cleared
+ * (s may be NULL). */
+size_t hb_staging_insert_workspace_bytes(int64_t n);
+int hb_staging_insert(hb_index_t* h, const hb_staging_t* s /* nullable */, const int64_t* ids,
+                      const void* emb_rows, int64_t n, void* cache_rows, int64_t row_bytes,
+                      int64_t* locs_out, void* workspace, size_t workspace_bytes,
+                      hb_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Sparse optimiser update on the owning shard.                                */
+/* ------------------------------------------------------------------------- */
+/* Local row of an id: (id - id_offset) / id_stride, ids outside [0, rows) are
+ * skipped; ids must be unique.  grads are divided by cnt when cnt is given
+ * (the is_unique path, sparse_optim.py:608-611).  emb is fp32 (emb_elem_bytes
+ * 4) or fp16 (2); state is fp32.
+ *
+ * SparseAdam.update, python/EmbCache/sparse_optim.py:590-685: step += 1;
+ * mem = b1*mem + (1-b1)*g; power = b2*power + (1-b2)*g*g;
+ * emb -= lr * (mem/(1-b1^step)) / (sqrt(power/(1-b2^step)) + eps). */
+int hb_sparse_adam(const int64_t* ids, const float* grads, const int64_t* cnt, int64_t n,
+                   const int64_t* n_dev, int64_t dim, int64_t id_offset, int64_t id_stride,
+                   int64_t rows, float* step, float* mem, float* power, void* emb,
+                   int emb_elem_bytes, double lr, double beta1, double beta2, double eps,
+                   hb_stream_t stream);
+/* Sparse Adagrad: sum += g*g; emb -= lr * g / (sqrt(sum) + eps).  The reference
+ * ships no Adagrad (only SparseAdam); this rule has no reference counterpart to
+ * compare against. */
+int hb_sparse_adagrad(const int64_t* ids, const float* grads, const int64_t* cnt, int64_t n,
+                      const int64_t* n_dev, int64_t dim, int64_t id_offset, int64_t id_stride,
+                      int64_t rows, float* state_sum, void* emb, int emb_elem_bytes, double lr,
+                      double eps, hb_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -344,3 +344,120 @@ def unique_grads(idx, grad, cnt=None):
     np.add.at(values, inverse, grad)
     values = values / counts[:, None].astype(np.float32)
     return uniq, values.astype(np.float32), counts.astype(np.int64)
+
+
+# ---------------------------------------------------------------------------------------
+# cold-gradient staging table: python/EmbCache/server.py
+# ---------------------------------------------------------------------------------------
+def flush_thresholds(hotness):
+    """server.py:87-88: (1 / (0.001 + hotness)).ceil().int().clamp(max=100)."""
+    return np.minimum(np.ceil(1.0 / (np.float32(0.001) + hotness.astype(np.float32))), 100).astype(np.int32)
+
+
+class OracleStaging:
+    """The server's gradient buffers (server.py:76-175) and the loop steps that touch them.
+    compat_no_clear=True reproduces the reference's behaviour of never zeroing the gradient
+    rows after a flush (server.py:414,489,537 zero a temporary copy); the default is the
+    intended read-and-zero, which is what the CUDA library implements."""
+
+    def __init__(self, slots, dim, cnt_threshold=16, iter_threshold=None, compat_no_clear=False):
+        self.grad = np.zeros((slots, dim), np.float32)
+        self.cnt = np.zeros(slots, np.int32)
+        self.idx = np.full(slots, -1, np.int64)
+        self.iter_count = np.zeros(slots, np.int32)
+        self.iter_threshold = (np.zeros(slots, np.int32) if iter_threshold is None
+                               else np.asarray(iter_threshold, np.int32).copy())
+        self.cnt_threshold = cnt_threshold
+        self.compat_no_clear = compat_no_clear
+
+    def accumulate_cached(self, index: OracleIndex, ids, grads, threshold_table, default_threshold):
+        """_accumulate_gradients_cold_remote, server.py:546-562 (ids unique)."""
+        locs = index.lookup(ids, touch=True)   # the server's lookup is the CPU one (server.py:550)
+        hit = np.nonzero(locs >= 0)[0]
+        if hit.size:
+            s = locs[hit]
+            self.idx[s] = ids[hit]
+            self.iter_threshold[s] = (threshold_table[ids[hit]] if threshold_table is not None
+                                      else default_threshold)
+            self.grad[s] += grads[hit]
+            self.cnt[s] += 1
+        return int((locs < 0).sum())
+
+    def accumulate_direct(self, ids, grads, id_offset=0, id_stride=1):
+        """_accumulate_gradients_cold_local, server.py:564-574 (ids unique)."""
+        if len(ids):
+            s = (ids - id_offset) // id_stride
+            self.grad[s] += grads
+            self.cnt[s] += 1
+            self.idx[s] = ids
+
+    def flush(self, index: OracleIndex | None, num_clients):
+        """_send_staled_gradients, server.py:346-425: returns (ids, rows, cnt, counts) with
+        rows bucketed by id % num_clients, slot order inside a bucket."""
+        live = np.nonzero(self.cnt > 0)[0]
+        stale_mask = (self.iter_count[live] >= self.iter_threshold[live]) | (self.cnt[live] >= self.cnt_threshold)
+        stale = live[stale_mask]
+        ids = self.idx[stale]
+        rows = self.grad[stale].copy()
+        cnts = self.cnt[stale].astype(np.int64)
+        split = ids % num_clients
+        order = np.concatenate([np.nonzero(split == r)[0] for r in range(num_clients)]) if stale.size else np.empty(0, np.int64)
+        counts = np.bincount(split, minlength=num_clients).astype(np.int64) if stale.size else np.zeros(num_clients, np.int64)
+        if index is not None:
+            index.reset(ids)                      # server.py:413
+        if not self.compat_no_clear:
+            self.grad[stale] = 0                  # intended meaning of server.py:414
+        self.cnt[stale] = 0                       # server.py:415
+        self.iter_count[live] += 1                # server.py:418
+        self.iter_count[stale] = 0                # server.py:419
+        order = order.astype(np.int64)
+        return ids[order], rows[order], cnts[order], counts
+
+    def insert(self, index: OracleIndex, ids, embs, cache_rows):
+        """_update_cache, server.py:499-544."""
+        locs = index.add(ids)
+        ok = np.nonzero(locs >= 0)[0]
+        s = locs[ok]
+        cache_rows[s] = embs[ok]
+        if not self.compat_no_clear:
+            self.grad[s] = 0                      # intended meaning of server.py:537
+        self.cnt[s] = 0
+        self.idx[s] = -1
+        return locs
+
+
+# ---------------------------------------------------------------------------------------
+# sparse optimisers
+# ---------------------------------------------------------------------------------------
+def sparse_adam_update(idx, grad, step, mem, power, emb, lr, beta1=0.9, beta2=0.999, eps=1e-8,
+                       cnt=None, id_offset=0, id_stride=1):
+    """SparseAdam.update with is_unique=True, python/EmbCache/sparse_optim.py:606-681, in
+    float32 like the torch expressions there.  Updates step/mem/power/emb in place."""
+    f = np.float32
+    g = grad.astype(f)
+    if cnt is not None:
+        g = g / cnt.astype(f)[:, None]                                   # :609
+    rows = (idx - id_offset) // id_stride
+    t = step[rows] + f(1)                                                # :624
+    m = f(beta1) * mem[rows] + f(1.0 - beta1) * g                        # :631
+    v = f(beta2) * power[rows] + f(1.0 - beta2) * (g * g)                # :632
+    mc = m / (f(1) - np.power(f(beta1), t, dtype=f))[:, None]            # :642-643
+    vc = v / (f(1) - np.power(f(beta2), t, dtype=f))[:, None]            # :644-645
+    std = f(lr) * mc / (np.sqrt(vc) + f(eps))                            # :646-647
+    step[rows] = t
+    mem[rows] = m
+    power[rows] = v
+    emb[rows] = (emb[rows].astype(f) - std).astype(emb.dtype)            # :681
+    return std
+
+
+def sparse_adagrad_update(idx, grad, state_sum, emb, lr, eps=1e-10, cnt=None, id_offset=0, id_stride=1):
+    """Sparse Adagrad (no reference counterpart: parity unpinned by the reference)."""
+    f = np.float32
+    g = grad.astype(f)
+    if cnt is not None:
+        g = g / cnt.astype(f)[:, None]
+    rows = (idx - id_offset) // id_stride
+    s = state_sum[rows] + g * g
+    state_sum[rows] = s
+    emb[rows] = (emb[rows].astype(f) - f(lr) * g / (np.sqrt(s) + f(eps))).astype(emb.dtype)

@@ -1,0 +1,80 @@
+"""The whole per-step path (forward fetch, local aggregation, hot/cold split, cold-cache
+accumulate, owner update, periodic flush and refill) on one GPU against the same steps composed
+from the oracle's functions: index state, staging state and found masks bit-exact, optimiser
+state and table within 1e-5 relative."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _oracle_step(o, ids, grads, step_no, flush_every):
+    om = o["mod"]
+    # forward
+    out = np.zeros((ids.size, o["dim"]), np.float32)
+    locs, hit = om.lookup_fetch(o["index"], ids, o["cache"], o["table"], out)
+    o["index"].touch(locs)
+    # backward
+    u, s, c = om.only_unique_grads(ids, grads)
+    cls = o["cls"][u]
+    hot, cold = cls == 1, cls == 2
+    o["staging"].accumulate_cached(o["index"], u[cold], s[cold], None, 0)
+    hu, hm, _ = om.unique_grads(u[hot], s[hot], c[hot])
+    om.sparse_adam_update(hu, hm, o["step"], o["mem"], o["power"], o["table"], 0.01)
+    flushed = 0
+    if step_no % flush_every == 0:
+        fi, fr, fc, _ = o["staging"].flush(o["index"], 1)
+        flushed = fi.size
+        if flushed:
+            om.sparse_adam_update(fi, fr, o["step"], o["mem"], o["power"], o["table"], 0.01, cnt=fc)
+            o["staging"].insert(o["index"], fi, o["table"][fi], o["cache"])
+    return out, locs, hit, flushed
+
+
+@pytest.mark.parametrize("mode,mover", [(0, 1), (1, 2)])
+def test_pipeline_matches_oracle(cuda_lib, oracle_mod, mode, mover):
+    from hades_b200 import pipeline, synth
+
+    cfg = synth.scaled(synth.CONFIG1, 0.05, "pipe_test")
+    cfg = synth.CacheFetchConfig(cfg.name, cfg.config, cfg.table_rows, 64, cfg.cache_entries, cfg.batch,
+                                 cfg.zipf_s, flush_every=3)
+    path = pipeline.build_path(cfg, lookup_mode=mode, mover=mover, hot_fraction=0.02)
+    # oracle state from the same initial table
+    table = path.table.cpu().numpy().copy()
+    ox = oracle_mod.OracleIndex(cfg.cache_entries)
+    slots = ox.get_capacity()
+    staging = oracle_mod.OracleStaging(slots, cfg.dim, cnt_threshold=16)
+    cache = np.zeros((slots, cfg.dim), np.float32)
+    hot_ids = synth.hot_ids(cfg.table_rows, cfg.cache_entries)
+    staging.insert(ox, hot_ids, table[hot_ids], cache)
+    o = dict(mod=oracle_mod, index=ox, cache=cache, table=table, staging=staging, dim=cfg.dim,
+             cls=path.class_table.cpu().numpy(), step=np.zeros(cfg.table_rows, np.float32),
+             mem=np.zeros((cfg.table_rows, cfg.dim), np.float32),
+             power=np.zeros((cfg.table_rows, cfg.dim), np.float32))
+    assert np.array_equal(path.cold.emb.cpu().numpy(), cache)
+    rng = synth.rng_for(1, 0, 7)
+    sampler = synth.ZipfSampler(cfg.table_rows, cfg.zipf_s)
+    total_flushed = 0
+    for it in range(1, 8):
+        ids = sampler.ids(rng, cfg.batch)
+        grads = synth.normal_rows(rng, cfg.batch, cfg.dim, cfg.grad_sigma)
+        rows, locs, found, st = path.step(torch.from_numpy(ids).cuda(), torch.from_numpy(grads).cuda())
+        wout, wlocs, whit, wflushed = _oracle_step(o, ids, grads, it, cfg.flush_every)
+        assert np.array_equal(locs.cpu().numpy(), wlocs), it
+        assert np.array_equal(found.cpu().numpy(), whit), it
+        np.testing.assert_allclose(rows.cpu().numpy(), wout, rtol=1e-5, atol=1e-9)
+        assert st.flushed == wflushed, it
+        total_flushed += wflushed
+        gi, gl = path.cold.index.export_state()
+        oi, ol = ox.export()
+        assert np.array_equal(gi.cpu().numpy(), oi), it
+        assert np.array_equal(gl.cpu().numpy(), ol), it
+        assert np.array_equal(path.cold.remote.cnt.cpu().numpy(), staging.cnt), it
+        assert np.array_equal(path.cold.remote.idx.cpu().numpy(), staging.idx), it
+        np.testing.assert_allclose(path.cold.remote.grad.cpu().numpy(), staging.grad, rtol=1e-5, atol=1e-10)
+        assert np.array_equal(path.opt.state_step.cpu().numpy(), o["step"]), it
+        np.testing.assert_allclose(path.opt.state_mem.cpu().numpy(), o["mem"], rtol=1e-4, atol=1e-10)
+        np.testing.assert_allclose(path.table.cpu().numpy(), o["table"], rtol=1e-4, atol=1e-7)
+    assert total_flushed > 0
+    assert int(path.cold.dropped.item()) > 0
