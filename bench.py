@@ -38,8 +38,8 @@ CPU_SAMPLE_SCALE = 1.0 / 8.0
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=16)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload (profiling captures)")
     ap.add_argument("--lookup", default="setassoc", choices=["setassoc", "sorted"])
@@ -54,50 +54,58 @@ def parse():
 # clocks
 # --------------------------------------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and the clock-event (throttle) reasons of one GPU through NVML from a
+    background thread while the timed region runs.  Read-only."""
 
-    def __init__(self, index: int):
-        self.index, self.proc, self.path = index, None, None
+    REASONS = {
+        "hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20,
+        "hw_thermal_slowdown": 0x40, "hw_power_brake_slowdown": 0x80,
+    }
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period = index, period_s
+        self.sm, self.bits, self.max_sm, self.err = [], 0, None, None
+        self._stop = None
+        self._thread = None
 
     def start(self):
+        import threading
+
         try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
-        except Exception:
-            self.proc = None
+            import pynvml
+
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_sm = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # noqa: BLE001
+            self.err = f"nvml unavailable: {e}"
+            return
+        self._stop = threading.Event()
+
+        def loop():
+            while not self._stop.is_set():
+                try:
+                    self.sm.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                    self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+                except Exception as e:  # noqa: BLE001
+                    self.err = str(e)
+                    break
+                self._stop.wait(self.period)
+
+        self._thread = threading.Thread(target=loop, daemon=True)
+        self._thread.start()
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in open(self.path).read().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        os.unlink(self.path)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+        sm = sorted(self.sm)
+        out = {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_sm,
+               "samples": len(sm),
+               "reasons": sorted(k for k, bit in self.REASONS.items() if self.bits & bit)}
+        if self.err:
+            out["error"] = self.err
+        return out
 
 
 # --------------------------------------------------------------------------------------
@@ -211,7 +219,7 @@ def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(args.steps, 1)
+    steps = min(max(args.steps, 1), 40)  # each step is a bounded CPU sample; keep the run to minutes
     r = cpu_reference_run(steps, max(args.warmup, 1), CPU_SAMPLE_SCALE)
     line = {
         "impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
@@ -328,7 +336,6 @@ def run_ours(args) -> None:
     launches0 = _lib.launch_count()
     total_ms = timed(step_resident, K, W)
     launches = _lib.launch_count() - launches0
-    clocks = sampler_clk.stop() if rank == 0 else None
     found_frac = float(last["found"].float().mean().item())
     num_unique = int(last["st"].num_unique.item())
     split_counts = last["st"].split_counts.tolist()
@@ -344,6 +351,7 @@ def run_ours(args) -> None:
                "note": "ids from pinned host memory, found mask + slots read back; gradients are produced "
                        "on the device by the backward pass and stay there"}
 
+    clocks = sampler_clk.stop() if rank == 0 else None  # covers both timed loops
     st_ms = stage_times(0)
     status = _lib.device_status()
     if status != 0:

@@ -157,7 +157,7 @@ class IndexCache:
         locs = torch.empty_like(ids)
         need = self._lib.hb_index_add_workspace_bytes(ids.numel())
         ws = _lib.workspace(need)
-        _lib.check(self._lib.hb_index_add(self._h, ids.data_ptr(), ids.numel(), locs.data_ptr(),
+        _lib.check(self._lib.hb_index_add(self._h, ids.data_ptr(), ids.numel(), locs.data_ptr(), None,
                                           ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
         return locs
 

@@ -40,7 +40,7 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_index_lines": (_i64, [_p]),
     "hb_index_valid_entries": (_int, [_p, _p, _p]),
     "hb_index_add_workspace_bytes": (_sz, [_i64]),
-    "hb_index_add": (_int, [_p, _p, _i64, _p, _p, _sz, _p]),
+    "hb_index_add": (_int, [_p, _p, _i64, _p, _p, _p, _sz, _p]),
     "hb_index_lookup": (_int, [_p, _p, _i64, _p, _p, _int, _p]),
     "hb_index_touch_lru_workspace_bytes": (_sz, [_i64]),
     "hb_index_touch_lru": (_int, [_p, _p, _i64, _p, _sz, _p]),

@@ -44,15 +44,22 @@ __global__ void add_keys_kernel(const int64_t* __restrict__ ids, int64_t n, int6
 __global__ void add_walk_kernel(const int64_t* __restrict__ ids, int64_t n, int64_t lines,
                                 const uint32_t* __restrict__ keys,
                                 const uint32_t* __restrict__ vals, int64_t* __restrict__ line_ids,
-                                int32_t* __restrict__ lru, int64_t* __restrict__ locs) {
+                                int32_t* __restrict__ lru, int64_t* __restrict__ locs,
+                                uint8_t* __restrict__ last_writer) {
   const int64_t j = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (j >= n) return;
   const uint32_t line = keys[j];
   if (j > 0 && keys[j - 1] == line) return;  // not the head of its segment
   if ((int64_t)line >= lines) {              // unusable ids sort last
-    for (int64_t k = j; k < n; ++k) locs[vals[k]] = -1;
+    for (int64_t k = j; k < n; ++k) {
+      locs[vals[k]] = -1;
+      if (last_writer) last_writer[vals[k]] = 0;
+    }
     return;
   }
+  int64_t last_k[kWays];  // sorted position of the last id of the batch placed in each way
+#pragma unroll
+  for (int w = 0; w < kWays; ++w) last_k[w] = -1;
   int64_t lid[kWays];
   int32_t cnt[kWays];
 #pragma unroll
@@ -90,6 +97,9 @@ __global__ void add_walk_kernel(const int64_t* __restrict__ ids, int64_t n, int6
         }
       }
       locs[pos] = (int64_t)line * kWays + way;
+#pragma unroll
+      for (int w = 0; w < kWays; ++w)
+        if (w == way) last_k[w] = k;
     } else {
       locs[pos] = -1;
     }
@@ -98,6 +108,20 @@ __global__ void add_walk_kernel(const int64_t* __restrict__ ids, int64_t n, int6
   for (int w = 0; w < kWays; ++w) {
     line_ids[(int64_t)line * kWays + w] = lid[w];
     lru[(int64_t)line * kWays + w] = cnt[w];
+  }
+  if (last_writer) {
+    for (int64_t k = j; k < n && keys[k] == line; ++k) {
+      const uint32_t pos = vals[k];
+      const int64_t loc = locs[pos];
+      bool last = false;
+      if (loc >= 0) {
+        const int way = (int)(loc & (kWays - 1));
+#pragma unroll
+        for (int w = 0; w < kWays; ++w)
+          if (w == way) last = last_k[w] == k;
+      }
+      last_writer[pos] = last;
+    }
   }
 }
 
@@ -373,8 +397,9 @@ int hb_index_valid_entries(hb_index_t* h, int64_t* out_host, hb_stream_t stream)
 size_t hb_index_add_workspace_bytes(int64_t n) { return keyval_workspace_bytes(n); }
 size_t hb_index_touch_lru_workspace_bytes(int64_t n) { return keyval_workspace_bytes(n); }
 
-int hb_index_add(hb_index_t* h, const int64_t* ids, int64_t n, int64_t* locs, void* workspace,
-                 size_t workspace_bytes, hb_stream_t stream) {
+int hb_index_add(hb_index_t* h, const int64_t* ids, int64_t n, int64_t* locs,
+                 uint8_t* last_writer, void* workspace, size_t workspace_bytes,
+                 hb_stream_t stream) {
   HB_CHECK_ARG(h && (n == 0 || (ids && locs)), "hb_index_add: null argument");
   HB_CHECK_ARG(n >= 0 && n < ((int64_t)1 << 31), "hb_index_add: n out of range");
   if (n == 0) return HB_OK;
@@ -397,7 +422,7 @@ int hb_index_add(hb_index_t* h, const int64_t* ids, int64_t n, int64_t* locs, vo
                                           sort_bits(h->lines + 1), st));
   count_library_launches(3);
   HB_LAUNCH(add_walk_kernel, grid_for(n), kBlock, 0, st, ids, n, h->lines, keys.Current(),
-            vals.Current(), h->line_ids, h->lru, locs);
+            vals.Current(), h->line_ids, h->lru, locs, last_writer);
   h->sorted_stale = true;
   return HB_OK;
 }

@@ -186,14 +186,15 @@ struct FlushPolicy {
 // ---- insert (server.py:499-544): rows into the cache buffer at the slots add() gave ----------
 template <int VEC_BYTES>
 __global__ void __launch_bounds__(kBlock) staging_insert_kernel(
-    hb_staging_t s, const int64_t* __restrict__ locs, const char* __restrict__ emb_rows,
-    char* __restrict__ cache_rows, int64_t row_bytes, int64_t n) {
+    hb_staging_t s, const int64_t* __restrict__ locs, const uint8_t* __restrict__ last_writer,
+    const char* __restrict__ emb_rows, char* __restrict__ cache_rows, int64_t row_bytes, int64_t n) {
   const int lane = lane_id();
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   for (int64_t base = warp * 32; base < n; base += nwarps * 32) {
     const int64_t i = base + lane;
-    const int64_t slot = i < n ? __ldg(locs + i) : -1;
+    // of several ids that received the same slot, the last of the batch writes it
+    const int64_t slot = (i < n && last_writer[i]) ? __ldg(locs + i) : -1;
     const bool ok = slot >= 0;
     if (ok && s.cnt) {
       s.cnt[slot] = 0;   // server.py:539-541
@@ -312,7 +313,9 @@ int hb_staging_flush(hb_index_t* h, const hb_staging_t* s, int32_t cnt_threshold
   return rc;
 }
 
-size_t hb_staging_insert_workspace_bytes(int64_t n) { return hb_index_add_workspace_bytes(n); }
+size_t hb_staging_insert_workspace_bytes(int64_t n) {
+  return hb_index_add_workspace_bytes(n) + align_up((size_t)(n > 0 ? n : 1), 256);
+}
 
 int hb_staging_insert(hb_index_t* h, const hb_staging_t* s, const int64_t* ids,
                       const void* emb_rows, int64_t n, void* cache_rows, int64_t row_bytes,
@@ -324,7 +327,15 @@ int hb_staging_insert(hb_index_t* h, const hb_staging_t* s, const int64_t* ids,
   HB_CHECK_ARG(!s || s->slots == h->cache_size,
                "hb_staging_insert: the staging table must have one slot per cache slot");
   if (n == 0) return HB_OK;
-  int rc = hb_index_add(h, ids, n, locs_out, workspace, workspace_bytes, stream);
+  const size_t flag_bytes = align_up((size_t)n, 256);
+  if (!workspace || workspace_bytes < hb_staging_insert_workspace_bytes(n)) {
+    set_error("hb_staging_insert: workspace of %zu bytes needed, %zu given",
+              hb_staging_insert_workspace_bytes(n), workspace_bytes);
+    return HB_ERR_WORKSPACE;
+  }
+  uint8_t* last_writer = static_cast<uint8_t*>(workspace);
+  int rc = hb_index_add(h, ids, n, locs_out, last_writer, static_cast<char*>(workspace) + flag_bytes,
+                        workspace_bytes - flag_bytes, stream);
   if (rc) return rc;
   hb_staging_t none;
   memset(&none, 0, sizeof(none));
@@ -332,13 +343,13 @@ int hb_staging_insert(hb_index_t* h, const hb_staging_t* s, const int64_t* ids,
   const int vb = payload_vec_bytes(row_bytes, emb_rows, cache_rows);
   cudaStream_t st = (cudaStream_t)stream;
   if (vb == 16)
-    HB_LAUNCH(staging_insert_kernel<16>, warp_grid(n), kBlock, 0, st, st_desc, locs_out,
+    HB_LAUNCH(staging_insert_kernel<16>, warp_grid(n), kBlock, 0, st, st_desc, locs_out, last_writer,
               (const char*)emb_rows, (char*)cache_rows, row_bytes, n);
   else if (vb == 4)
-    HB_LAUNCH(staging_insert_kernel<4>, warp_grid(n), kBlock, 0, st, st_desc, locs_out,
+    HB_LAUNCH(staging_insert_kernel<4>, warp_grid(n), kBlock, 0, st, st_desc, locs_out, last_writer,
               (const char*)emb_rows, (char*)cache_rows, row_bytes, n);
   else
-    HB_LAUNCH(staging_insert_kernel<1>, warp_grid(n), kBlock, 0, st, st_desc, locs_out,
+    HB_LAUNCH(staging_insert_kernel<1>, warp_grid(n), kBlock, 0, st, st_desc, locs_out, last_writer,
               (const char*)emb_rows, (char*)cache_rows, row_bytes, n);
   return HB_OK;
 }

@@ -75,10 +75,15 @@ int hb_index_valid_entries(hb_index_t* h, int64_t* out_host, hb_stream_t stream)
 /* add(ids) -> locs, src/cache/cache.h:51-88,196-206: existing id -> its slot;
  * else the LAST empty way; else the least-recently-used way (largest counter,
  * first on ties) unless all counters are 0, then -1.  Ids are applied in input
- * order per set (the reference result at OMP_NUM_THREADS=1). */
+ * order per set (the reference result at OMP_NUM_THREADS=1).  Two ids of one
+ * batch can receive the same slot (a later id evicts an earlier one, or the same
+ * id repeats); last_writer (nullable, n bytes) marks for each id whether it is
+ * the last of the batch to hold its slot, i.e. whose row a sequential
+ * "rows[locs] = batch rows" leaves there. */
 size_t hb_index_add_workspace_bytes(int64_t n);
 int hb_index_add(hb_index_t* h, const int64_t* ids, int64_t n, int64_t* locs,
-                 void* workspace, size_t workspace_bytes, hb_stream_t stream);
+                 uint8_t* last_writer, void* workspace, size_t workspace_bytes,
+                 hb_stream_t stream);
 
 /* lookup(ids) -> locs (and optional found mask = locs >= 0),
  * src/cache/cache.h:90-104,213-222 and cudalookup, src/cache/lookup.cu:13-85.
