@@ -88,10 +88,10 @@ class IndexCache:
         if getattr(self, "_owner", False) and getattr(self, "_h", None):
             try:
                 self._lib.hb_index_destroy(self._h)
-            except Exception:
+                if _REGISTRY is not None and _REGISTRY.get(self._name) is self:
+                    _REGISTRY.pop(self._name, None)
+            except Exception:  # interpreter shutdown: modules may already be gone
                 pass
-            if _REGISTRY.get(self._name) is self:
-                _REGISTRY.pop(self._name, None)
             self._h = None
 
     # --- sizes -------------------------------------------------------------------------

@@ -69,27 +69,90 @@ __global__ void __launch_bounds__(kPartBlock) partition_hist_kernel(Policy pol, 
     p.block_hist[(int64_t)blockIdx.x * p.num_classes + k] = s_hist[k];
 }
 
-// One CTA: thread k walks class k's column of the block histograms.
-static __global__ void partition_scan_kernel(PartitionPlan p, int64_t* __restrict__ counts_out) {
-  for (int k = threadIdx.x; k < p.num_classes; k += blockDim.x) {
-    int64_t run = 0;
-    for (int64_t b = 0; b < p.num_blocks; ++b) {
-      int32_t* cell = p.block_hist + b * p.num_classes + k;
-      const int32_t c = *cell;
-      *cell = (int32_t)run;
-      run += c;
+// One CTA of kScanThreads turns the per-block histograms into exclusive offsets.
+// Few classes: the whole CTA scans one class at a time (each thread owns a
+// contiguous range of blocks: local sum, CTA-wide exclusive scan of the sums,
+// local write-back).  Many classes: one warp per class does the same with its
+// 32 lanes.
+constexpr int kScanThreads = 1024;
+
+__device__ __forceinline__ int64_t warp_exclusive_scan(int64_t v, int64_t& total) {
+  const int lane = threadIdx.x & 31;
+  int64_t inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int64_t t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  total = __shfl_sync(0xffffffffu, inc, 31);
+  return inc - v;
+}
+
+static __global__ void __launch_bounds__(kScanThreads) partition_scan_kernel(
+    PartitionPlan p, int64_t* __restrict__ counts_out) {
+  __shared__ int64_t s_warp[32];
+  const int K = p.num_classes;
+  const int64_t nb = p.num_blocks;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  if (K <= 8) {
+    const int64_t per = (nb + kScanThreads - 1) / kScanThreads;
+    const int64_t b0 = (int64_t)threadIdx.x * per;
+    const int64_t b1 = (b0 + per < nb) ? b0 + per : nb;
+    for (int k = 0; k < K; ++k) {
+      int64_t local = 0;
+      for (int64_t b = b0; b < b1; ++b) local += p.block_hist[b * K + k];
+      int64_t wtotal;
+      const int64_t wex = warp_exclusive_scan(local, wtotal);
+      if (lane == 31) s_warp[warp] = wtotal;
+      __syncthreads();
+      int64_t base = 0, total = 0;
+      for (int w = 0; w < kScanThreads / 32; ++w) {
+        if (w < warp) base += s_warp[w];
+        total += s_warp[w];
+      }
+      int64_t run = base + wex;
+      for (int64_t b = b0; b < b1; ++b) {
+        int32_t* cell = p.block_hist + b * K + k;
+        const int32_t c = *cell;
+        *cell = (int32_t)run;
+        run += c;
+      }
+      if (threadIdx.x == 0) {
+        p.class_total[k] = total;
+        if (counts_out) counts_out[k] = total;
+      }
+      __syncthreads();
     }
-    p.class_total[k] = run;
-    if (counts_out) counts_out[k] = run;
+  } else {
+    const int64_t per = (nb + 31) / 32;
+    const int64_t b0 = (int64_t)lane * per;
+    const int64_t b1 = (b0 + per < nb) ? b0 + per : nb;
+    for (int k = warp; k < K; k += kScanThreads / 32) {
+      int64_t local = 0;
+      for (int64_t b = b0; b < b1; ++b) local += p.block_hist[b * K + k];
+      int64_t total;
+      int64_t run = warp_exclusive_scan(local, total);
+      for (int64_t b = b0; b < b1; ++b) {
+        int32_t* cell = p.block_hist + b * K + k;
+        const int32_t c = *cell;
+        *cell = (int32_t)run;
+        run += c;
+      }
+      if (lane == 0) {
+        p.class_total[k] = total;
+        if (counts_out) counts_out[k] = total;
+      }
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     int64_t run = 0;
-    for (int k = 0; k < p.num_classes; ++k) {
+    for (int k = 0; k < K; ++k) {
       p.class_start[k] = run;
       run += p.class_total[k];
     }
-    p.class_start[p.num_classes] = run;
+    p.class_start[K] = run;
   }
 }
 
@@ -160,12 +223,12 @@ int run_partition(const Policy& pol, int64_t n, int num_classes, void* ws, size_
   if (plan_out) *plan_out = p;
   if (n <= 0) {
     HB_CUDA(cudaMemsetAsync(p.block_hist, 0, (size_t)num_classes * sizeof(int32_t), st));
-    HB_LAUNCH(partition_scan_kernel, 1, 256, 0, st, p, counts_out);
+    HB_LAUNCH(partition_scan_kernel, 1, kScanThreads, 0, st, p, counts_out);
     return HB_OK;
   }
   HB_LAUNCH(partition_hist_kernel<Policy>, (int)p.num_blocks, kPartBlock,
             (size_t)num_classes * sizeof(int), st, pol, p);
-  HB_LAUNCH(partition_scan_kernel, 1, 256, 0, st, p, counts_out);
+  HB_LAUNCH(partition_scan_kernel, 1, kScanThreads, 0, st, p, counts_out);
   HB_LAUNCH(partition_scatter_kernel<Policy>, (int)p.num_blocks, kPartBlock,
             partition_scatter_smem(num_classes), st, pol, p);
   return HB_OK;

@@ -52,6 +52,7 @@ struct SegArgs {
   int2* short_list;           // (chunk, run)
   int2* long_list;
   int* list_counts;           // [0] short, [1] long
+  float* slice_part;          // [long entries][kSlices][cols]
 };
 
 template <int VEC> struct VecF;
@@ -246,38 +247,70 @@ __global__ void __launch_bounds__(kBlock) segsum_fix_short_kernel(SegArgs a) {
   }
 }
 
-// ---- fix-up of long crossing runs: one CTA per entry ---------------------------------------
-// thread t owns float column (t % cols) of strand (t / cols); strand s adds the
-// partials c+1+s, c+1+s+S, ... in order; strand sums are then added 0,1,2,...
-__global__ void __launch_bounds__(kLongBlock) segsum_fix_long_kernel(SegArgs a) {
+// ---- fix-up of long crossing runs, two launches ----------------------------------------------
+// A long run leaves hundreds to thousands of partial rows (the hottest id of a
+// Zipf batch).  Stage A cuts the partial list of every long run into kSlices
+// contiguous slices; one CTA adds one slice (its threads form `strands` that walk
+// the slice interleaved, then the strand sums are added 0,1,2,...).  Stage B adds
+// the tail partial and the slice sums 0..kSlices-1 of a run and writes the row.
+// Shapes depend only on the run length, so the result is reproducible.
+constexpr int kSlices = 32;
+constexpr int kEntriesInFlight = 8;
+
+__global__ void __launch_bounds__(kLongBlock) segsum_fix_long_a_kernel(SegArgs a) {
   extern __shared__ float s_part[];  // [strands][cols]
   const int count = a.list_counts[1];
   const int64_t U_runs = *a.num_runs;
   const int cols = a.cols;
   const int strands = kLongBlock / cols;  // cols <= kLongBlock
-  for (int64_t e = blockIdx.x; e < count; e += gridDim.x) {
+  const int slice = blockIdx.x % kSlices;
+  const int col = threadIdx.x % cols;
+  const int strand = threadIdx.x / cols;
+  for (int64_t e = blockIdx.x / kSlices; e < count; e += kEntriesInFlight) {
     const int2 ent = a.long_list[e];
     const int64_t c = ent.x, u = ent.y;
     const int64_t run_end = (u + 1 < U_runs) ? __ldg(a.run_start + u + 1) : effective_n(a);
     const int64_t last_chunk = (run_end - 1) / a.chunk;
-    {
-      const int col = threadIdx.x % cols;
-      const int strand = threadIdx.x / cols;
-      if (strand < strands) {
-        float acc = 0.f;
-        for (int64_t cc = c + 1 + strand; cc <= last_chunk; cc += strands)
-          acc += a.head_part[cc * cols + col];
-        s_part[strand * cols + col] = acc;
+    const int64_t parts = last_chunk - c;  // head partials c+1 .. last_chunk
+    const int64_t seg = (parts + kSlices - 1) / kSlices;
+    const int64_t lo = c + 1 + slice * seg;
+    const int64_t hi = (lo + seg < last_chunk + 1) ? lo + seg : last_chunk + 1;
+    if (strand < strands) {
+      float acc = 0.f;
+      int64_t cc = lo + strand;
+      // four loads in flight, added in index order
+      for (; cc + 3 * strands < hi; cc += 4 * strands) {
+        const float x0 = a.head_part[cc * cols + col];
+        const float x1 = a.head_part[(cc + strands) * cols + col];
+        const float x2 = a.head_part[(cc + 2 * strands) * cols + col];
+        const float x3 = a.head_part[(cc + 3 * strands) * cols + col];
+        acc += x0; acc += x1; acc += x2; acc += x3;
       }
+      for (; cc < hi; cc += strands) acc += a.head_part[cc * cols + col];
+      s_part[strand * cols + col] = acc;
     }
     __syncthreads();
+    for (int k = threadIdx.x; k < cols; k += kLongBlock) {
+      float acc = 0.f;
+      for (int st = 0; st < strands; ++st) acc += s_part[st * cols + k];
+      a.slice_part[(e * kSlices + slice) * cols + k] = acc;
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(kLongBlock) segsum_fix_long_b_kernel(SegArgs a) {
+  const int count = a.list_counts[1];
+  const int cols = a.cols;
+  for (int64_t e = blockIdx.x; e < count; e += gridDim.x) {
+    const int2 ent = a.long_list[e];
+    const int64_t c = ent.x, u = ent.y;
     for (int col = threadIdx.x; col < cols; col += kLongBlock) {
       float acc = a.tail_part[c * cols + col];
-      for (int s = 0; s < strands; ++s) acc += s_part[s * cols + col];
+      for (int sl = 0; sl < kSlices; ++sl) acc += a.slice_part[(e * kSlices + sl) * cols + col];
       if (a.mean) acc /= denominator(a, a.counts[u]);
       a.sums[u * a.dim + a.col0 + col] = acc;
     }
-    __syncthreads();
   }
 }
 
@@ -341,7 +374,7 @@ struct SegPlan {
   size_t sort_temp_bytes;
   int64_t* run_start;
   unsigned long long* raw_counts;
-  float *head_part, *tail_part;
+  float *head_part, *tail_part, *slice_part;
   int2 *short_list, *long_list;
   int* list_counts;
   void* part_ws;
@@ -369,6 +402,9 @@ SegPlan make_plan(void* ws, int64_t n, int64_t dim) {
   s.cols_max = (int)(dim < 512 ? dim : 512);
   s.head_part = cv.take<float>((size_t)s.num_chunks * s.cols_max);
   s.tail_part = cv.take<float>((size_t)s.num_chunks * s.cols_max);
+  // a long run covers more than kShortSpan chunks, so there are fewer than
+  // num_chunks / kShortSpan of them; 32 slices each
+  s.slice_part = cv.take<float>((size_t)(s.num_chunks / kShortSpan + 1) * 32 * s.cols_max);
   s.short_list = cv.take<int2>(s.num_chunks);
   s.long_list = cv.take<int2>(s.num_chunks);
   s.list_counts = cv.take<int>(4);
@@ -388,7 +424,8 @@ int launch_pass(const SegArgs& a, cudaStream_t st) {
   HB_LAUNCH((segsum_fix_short_kernel<VEC, G, VPL>), fix_grid, kBlock, 0, st, a);
   const int strands = kLongBlock / a.cols > 0 ? kLongBlock / a.cols : 1;
   const size_t smem = (size_t)strands * a.cols * sizeof(float);
-  HB_LAUNCH(segsum_fix_long_kernel, sm_count(), kLongBlock, smem, st, a);
+  HB_LAUNCH(segsum_fix_long_a_kernel, kSlices * kEntriesInFlight, kLongBlock, smem, st, a);
+  HB_LAUNCH(segsum_fix_long_b_kernel, 64, kLongBlock, 0, st, a);
   return HB_OK;
 }
 
@@ -482,6 +519,7 @@ int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* 
   a.short_list = s.short_list;
   a.long_list = s.long_list;
   a.list_counts = s.list_counts;
+  a.slice_part = s.slice_part;
   const int tile = vec4 ? 512 : 128;
   for (int64_t col0 = 0; col0 < dim; col0 += tile) {
     a.col0 = col0;

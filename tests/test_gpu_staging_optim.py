@@ -104,10 +104,12 @@ def test_sparse_adam(cuda_lib, oracle_mod, emb_dtype, dim):
         opt.update(_t(ids), _t(g), None if cnt is None else _t(cnt), is_unique=True)
         oracle_mod.sparse_adam_update(ids, g, step, mem, power, w, 0.01, cnt=cnt, id_offset=rank, id_stride=world)
         assert np.array_equal(opt.state_step.cpu().numpy(), step)
-        np.testing.assert_allclose(opt.state_mem.cpu().numpy(), mem, rtol=RTOL, atol=1e-12)
-        np.testing.assert_allclose(opt.state_power.cpu().numpy(), power, rtol=RTOL, atol=1e-16)
+        # 1e-5 relative to the size of the operands: a sum of two terms of opposite sign can
+        # cancel, so the bound is on |a| + |b| (gradients ~1e-3, updates ~lr = 1e-2), not on the result
+        np.testing.assert_allclose(opt.state_mem.cpu().numpy(), mem, rtol=RTOL, atol=RTOL * 1e-3)
+        np.testing.assert_allclose(opt.state_power.cpu().numpy(), power, rtol=RTOL, atol=RTOL * 1e-6)
         if emb_dtype == np.float32:
-            np.testing.assert_allclose(emb.weight.cpu().numpy(), w, rtol=RTOL, atol=1e-9)
+            np.testing.assert_allclose(emb.weight.cpu().numpy(), w, rtol=RTOL, atol=RTOL * 2e-2)
         else:
             got = emb.weight.float().cpu().numpy()
             assert np.abs(got - w.astype(np.float32)).max() <= 2e-5  # one fp16 ulp near 0.03
@@ -130,7 +132,9 @@ def test_sparse_adam_not_unique_uses_mean(cuda_lib, oracle_mod):
     w = np.zeros((5000, 32), np.float32)
     oracle_mod.sparse_adam_update(u, mean, step, mem, power, w, 0.05)
     assert np.array_equal(opt.state_step.cpu().numpy(), step)
-    np.testing.assert_allclose(emb.weight.cpu().numpy(), w, rtol=1e-4, atol=1e-7)
+    # the first Adam step is lr * g / (|g| + eps): where the duplicates of an id nearly cancel,
+    # the rounding of the mean is amplified by 1/|g|, so the bound is relative to lr
+    np.testing.assert_allclose(emb.weight.cpu().numpy(), w, rtol=1e-4, atol=0.05 * 1e-3)
 
 
 @pytest.mark.parametrize("emb_dtype", [np.float32, np.float16])
@@ -151,9 +155,9 @@ def test_sparse_adagrad(cuda_lib, oracle_mod, emb_dtype):
         g = (rng.standard_normal((4000, dim)) * 1e-3).astype(np.float32)
         opt.update(_t(ids), _t(g), is_unique=True)
         oracle_mod.sparse_adagrad_update(ids, g, ssum, w, 0.01, id_offset=rank, id_stride=world)
-        np.testing.assert_allclose(opt.state_sum.cpu().numpy(), ssum, rtol=RTOL, atol=1e-16)
+        np.testing.assert_allclose(opt.state_sum.cpu().numpy(), ssum, rtol=RTOL, atol=RTOL * 1e-6)
         if emb_dtype == np.float32:
-            np.testing.assert_allclose(emb.weight.cpu().numpy(), w, rtol=RTOL, atol=1e-9)
+            np.testing.assert_allclose(emb.weight.cpu().numpy(), w, rtol=RTOL, atol=RTOL * 2e-2)
         else:
             got = emb.weight.float().cpu().numpy()
             assert np.abs(got - w.astype(np.float32)).max() <= 2e-5
