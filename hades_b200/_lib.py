@@ -62,6 +62,9 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_owner_range": (_int, [_p, _i64, _int, _p, _i64, _i64, _p, _p]),
     "hb_upper_bound": (_int, [_p, _i64, _int, _p, _i64, _p, _p]),
     "hb_bucket_pack": (_int, [_p, _p, _p, _i64, _p, _i64, _int, _p, _i64, _i64, _p, _p, _p, _p, _p, _sz, _p]),
+    "hb_bucket_pack_noalloc_max_items": (_i64, []),
+    "hb_bucket_pack_noalloc_max_buckets": (_int, []),
+    "hb_bucket_pack_noalloc": (_int, [_p, _p, _p, _i64, _p, _i64, _int, _p, _i64, _i64, _p, _p, _p, _p, _p]),
     "hb_table_split3": (_int, [_p, _p, _p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "hb_grad_split3": (_int, [_p, _p, _p, _p, _i64, _i64, _p, _p, _p, _p, _sz, _p]),
     "hb_unique_segsum_workspace_bytes": (_sz, [_i64, _i64]),

@@ -320,4 +320,89 @@ int hb_grad_split3(const int64_t* ids, const void* rows, const uint8_t* hot_mask
   return run_partition(pol, n, 3, workspace, workspace_bytes, counts, (cudaStream_t)stream);
 }
 
+// ---- owner bucketing for callers that must not allocate ---------------------------------
+// Some hosts of this library cannot hand it a workspace: code that runs inside a
+// region where device allocation is forbidden or unpredictable (a serving loop
+// with a frozen memory plan, a foreign runtime that owns the allocator and offers
+// no scratch hook, an interrupt-style callback that must not block in the driver).
+// For them the block histograms and offsets of the partition live in a fixed
+// array that is part of the loaded module, so the call itself creates nothing.
+//
+// The array below is DEVICE memory.  In host code its name only stands for the
+// symbol; the usable address is asked from the runtime once per device
+// (cudaGetSymbolAddress) and that address is what the kernels receive.
+constexpr int64_t kNoAllocMaxItems = (int64_t)1 << 20;  // 1,048,576 ids per call
+constexpr int kNoAllocMaxBuckets = 64;
+// partition_workspace_bytes(kNoAllocMaxItems, kNoAllocMaxBuckets) = 132,864 bytes
+constexpr size_t kNoAllocScratchBytes = 135168;  // 132 KiB, held by every GPU that loads the library
+
+static __device__ __align__(256) unsigned char g_noalloc_pack_scratch[kNoAllocScratchBytes];
+
+namespace {
+
+// Device address of the scratch array on the current device; looked up on the
+// first call per device and remembered.
+int noalloc_scratch_address(void** out) {
+  static void* addr[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    hb::set_error("hb_bucket_pack_noalloc: cannot identify the current device (%s)",
+                  cudaGetErrorString(e));
+    return HB_ERR_CUDA;
+  }
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_pack_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      hb::set_error("hb_bucket_pack_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return HB_ERR_CUDA;
+    }
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return HB_OK;
+}
+
+}  // namespace
+
+int64_t hb_bucket_pack_noalloc_max_items(void) { return kNoAllocMaxItems; }
+int hb_bucket_pack_noalloc_max_buckets(void) { return kNoAllocMaxBuckets; }
+
+int hb_bucket_pack_noalloc(const int64_t* ids, const void* rows, const int64_t* cnt, int64_t n,
+                           const int64_t* n_dev, int64_t row_bytes, int num_buckets,
+                           const int64_t* range_partition, int64_t num_part, int64_t g,
+                           int64_t* out_ids, void* out_rows, int64_t* out_cnt, int64_t* counts,
+                           hb_stream_t stream) {
+  HB_CHECK_ARG(n >= 0, "hb_bucket_pack_noalloc: negative n");
+  if (n > kNoAllocMaxItems || num_buckets > kNoAllocMaxBuckets) {
+    hb::set_error("hb_bucket_pack_noalloc: %lld ids / %d buckets exceed the built-in scratch "
+                  "(at most %lld ids and %d buckets per call); use hb_bucket_pack with a workspace",
+                  (long long)n, num_buckets, (long long)kNoAllocMaxItems, kNoAllocMaxBuckets);
+    return HB_ERR_CAPACITY;
+  }
+  HB_CHECK_ARG(g > 0 && num_buckets > 0, "hb_bucket_pack_noalloc: bad bucket parameters");
+  HB_CHECK_ARG(counts != nullptr, "hb_bucket_pack_noalloc: counts is null");
+  HB_CHECK_ARG(n == 0 || (ids && out_ids), "hb_bucket_pack_noalloc: null ids");
+  HB_CHECK_ARG(!rows || (out_rows && row_bytes > 0), "hb_bucket_pack_noalloc: rows without output");
+  HB_CHECK_ARG(!cnt || out_cnt, "hb_bucket_pack_noalloc: cnt without output");
+  HB_CHECK_ARG(!range_partition || num_part > 0, "hb_bucket_pack_noalloc: empty range partition");
+  if (partition_workspace_bytes(n, num_buckets) > kNoAllocScratchBytes) {
+    hb::set_error("hb_bucket_pack_noalloc: internal scratch too small for this request");
+    return HB_ERR_CAPACITY;
+  }
+  void* scratch = nullptr;
+  int rc = noalloc_scratch_address(&scratch);
+  if (rc != HB_OK) return rc;
+  // Nothing in the scratch has to start at zero: the histogram kernel writes
+  // every cell it later reads and the scan kernel writes the totals and starts,
+  // so whatever the previous call left behind is overwritten before use.
+  BucketPackPolicy pol{{range_partition, num_part, g}, num_buckets, n_dev, ids, (const char*)rows, cnt,
+                       row_bytes, rows ? payload_vec_bytes(row_bytes, rows, out_rows) : 1,
+                       out_ids, (char*)out_rows, out_cnt};
+  return run_partition(pol, n, num_buckets, scratch, kNoAllocScratchBytes, counts,
+                       (cudaStream_t)stream);
+}
+
+
 }  // extern "C"

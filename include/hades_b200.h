@@ -221,6 +221,31 @@ int hb_bucket_pack(const int64_t* ids, const void* rows, const int64_t* cnt, int
                    int64_t* out_cnt, int64_t* counts, void* workspace,
                    size_t workspace_bytes, hb_stream_t stream);
 
+/* hb_bucket_pack for hosts that cannot give the library scratch memory or let it
+ * allocate: a runtime that owns the device allocator and exposes no workspace
+ * hook, a serving loop whose memory plan is frozen, a callback that must not
+ * enter the driver's allocator.  No counterpart in the reference (it allocates
+ * freely through torch).  The partition's histograms and offsets live in a
+ * fixed 132 KiB device array inside the library (every GPU that loads the
+ * library holds it until the process exits), which limits one call to
+ * hb_bucket_pack_noalloc_max_items() = 1,048,576 ids and
+ * hb_bucket_pack_noalloc_max_buckets() = 64 buckets; larger requests return
+ * HB_ERR_CAPACITY.  Inputs, outputs and counts are still the caller's.  The
+ * call performs no cudaMalloc / cudaFree and calls no allocating routine.  Its
+ * FIRST call on each device also asks the runtime for the array's device
+ * address (cudaGetSymbolAddress); make that first call outside any stream
+ * capture.  All calls on a device share the one array, which keeps whatever the
+ * last call wrote: every cell is rewritten before it is read, so nothing needs
+ * clearing, but two calls that overlap on the GPU (different streams, or
+ * different threads without ordering) race on it -- order them. */
+int64_t hb_bucket_pack_noalloc_max_items(void);
+int hb_bucket_pack_noalloc_max_buckets(void);
+int hb_bucket_pack_noalloc(const int64_t* ids, const void* rows, const int64_t* cnt, int64_t n,
+                           const int64_t* n_dev, int64_t row_bytes, int num_buckets,
+                           const int64_t* range_partition, int64_t num_part, int64_t g,
+                           int64_t* out_ids, void* out_rows, int64_t* out_cnt,
+                           int64_t* counts, hb_stream_t stream);
+
 /* (ids, rows, cnt) split three ways by a per-node class table, class =
  * table[id] in {0,1,2} (the classes of src/cuda/split.cu:34-44).  out_ids,
  * out_rows, out_cnt are HOST arrays of three device pointers: class c is
