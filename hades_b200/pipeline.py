@@ -17,11 +17,10 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 
 import torch
-import torch.distributed as dist
 
 from . import EmbCacheLib as E
 from .cold_cache import ColdCache
-from .sparse_optim import ShardedEmbedding, SparseAdam, SparseAdagrad
+from .sparse_optim import ShardedEmbedding, SparseAdam, SparseAdagrad, exchange_packed
 
 HOT, COLD = 1, 2  # classes of the per-node table (remote hot / remote cold, src/cuda/split.cu:39-43)
 
@@ -67,17 +66,7 @@ class EmbeddingPath:
         p_ids, p_rows, p_cnt, counts = E.cudaBucketPack(ids, rows, cnt, self.world, n_dev=n_dev)
         if self.world == 1:
             return p_ids, p_rows, p_cnt, counts, counts
-        out_counts = torch.empty_like(counts)
-        dist.all_to_all_single(out_counts, counts, group=self.group)
-        in_splits, out_splits = counts.tolist(), out_counts.tolist()
-        total, sent = sum(out_splits), sum(in_splits)
-        dev = ids.device
-        r_ids = torch.empty(total, dtype=torch.int64, device=dev)
-        r_rows = torch.empty((total, rows.shape[1]), dtype=rows.dtype, device=dev)
-        r_cnt = torch.empty(total, dtype=torch.int64, device=dev)
-        dist.all_to_all_single(r_ids, p_ids[:sent], out_splits, in_splits, group=self.group)
-        dist.all_to_all_single(r_rows, p_rows[:sent], out_splits, in_splits, group=self.group)
-        dist.all_to_all_single(r_cnt, p_cnt[:sent], out_splits, in_splits, group=self.group)
+        r_ids, r_rows, r_cnt = exchange_packed(p_ids, p_rows, p_cnt, counts, self.group)
         return r_ids, r_rows, r_cnt, None, counts
 
     # ---- backward ------------------------------------------------------------------------

@@ -32,6 +32,30 @@ def unique_grads(idx: torch.Tensor, grad: torch.Tensor, cnt: torch.Tensor | None
     return ids, vals
 
 
+def exchange_packed(ids, rows, cnt, counts, group=None):
+    """Deliver owner-bucketed rows to their owners.  ids/rows/cnt hold the buckets back to back
+    (bucket b = rows for rank b), counts[b] their sizes (int64, on the same device).  Returns
+    (ids, rows, cnt) received by this rank, source ranks in order.  Ragged
+    ``all_to_all_single`` calls as the reference's swap_gradients makes them
+    (sparse_optim.py:73-118); the split sizes are read on the host, as there (:55,:77).
+    Works on CUDA tensors over NCCL and on CPU tensors over gloo."""
+    out_counts = torch.empty_like(counts)
+    dist.all_to_all_single(out_counts, counts, group=group)
+    in_splits, out_splits = counts.tolist(), out_counts.tolist()
+    total, sent = sum(out_splits), sum(in_splits)
+    r_ids = torch.empty(total, dtype=ids.dtype, device=ids.device)
+    dist.all_to_all_single(r_ids, ids[:sent], out_splits, in_splits, group=group)
+    r_rows = None
+    if rows is not None:
+        r_rows = torch.empty((total, rows.shape[1]), dtype=rows.dtype, device=ids.device)
+        dist.all_to_all_single(r_rows, rows[:sent], out_splits, in_splits, group=group)
+    r_cnt = None
+    if cnt is not None:
+        r_cnt = torch.empty(total, dtype=cnt.dtype, device=ids.device)
+        dist.all_to_all_single(r_cnt, cnt[:sent], out_splits, in_splits, group=group)
+    return r_ids, r_rows, r_cnt
+
+
 def swap_gradients(idics, grads, partition_range, num_parts, num_trainers_per_part, device,
                    grads_cnt=None, group=None):
     """Bucket rows by owner and exchange them: every rank receives the rows it owns.
@@ -44,20 +68,7 @@ def swap_gradients(idics, grads, partition_range, num_parts, num_trainers_per_pa
                                                   num_trainers_per_part)
     if world == 1 or not dist.is_initialized():
         return ids_p, rows_p, cnt_p
-    out_counts = torch.empty_like(counts)
-    dist.all_to_all_single(out_counts, counts, group=group)
-    in_splits = counts.tolist()
-    out_splits = out_counts.tolist()
-    total = sum(out_splits)
-    out_ids = torch.empty(total, dtype=ids_p.dtype, device=device)
-    out_rows = torch.empty((total, rows_p.shape[1]), dtype=rows_p.dtype, device=device)
-    dist.all_to_all_single(out_ids, ids_p, out_splits, in_splits, group=group)
-    dist.all_to_all_single(out_rows, rows_p, out_splits, in_splits, group=group)
-    out_cnt = None
-    if cnt_p is not None:
-        out_cnt = torch.empty(total, dtype=cnt_p.dtype, device=device)
-        dist.all_to_all_single(out_cnt, cnt_p, out_splits, in_splits, group=group)
-    return out_ids, out_rows, out_cnt
+    return exchange_packed(ids_p, rows_p, cnt_p, counts, group)
 
 
 class ShardedEmbedding:

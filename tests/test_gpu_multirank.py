@@ -1,0 +1,134 @@
+"""Two ranks on two GPUs over NCCL: the owner-partitioned exchange and the whole backward path
+against a numpy simulation of both ranks built from the oracle's functions.  Skipped when fewer
+than two GPUs are visible."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+WORLD = 2
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _cfg():
+    from hades_b200 import synth
+
+    c = synth.scaled(synth.CONFIG1, 0.05, "mr_test")
+    return synth.CacheFetchConfig(c.name, c.config, c.table_rows, 64, c.cache_entries, c.batch, c.zipf_s,
+                                  flush_every=2)
+
+
+def _batch(cfg, rank, it):
+    from hades_b200 import synth
+
+    rng = synth.rng_for(7, rank, it)
+    ids = synth.ZipfSampler(cfg.table_rows, cfg.zipf_s).ids(rng, cfg.batch)
+    grads = synth.normal_rows(rng, cfg.batch, cfg.dim, cfg.grad_sigma)
+    return ids, grads
+
+
+def _worker(rank, port):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=torch.device("cuda", rank))
+    from hades_b200 import pipeline, synth
+    from hades_b200.sparse_optim import swap_gradients
+    from oracle import oracle as om
+
+    # --- swap_gradients alone -------------------------------------------------------------
+    rng = np.random.default_rng(50 + rank)
+    n = 20_000 if rank == 0 else 7_000
+    ids = rng.integers(0, 10**7, n, dtype=np.int64)
+    rows = rng.standard_normal((n, 32)).astype(np.float32)
+    cnt = rng.integers(1, 5, n, dtype=np.int64)
+    r_ids, r_rows, r_cnt = swap_gradients(torch.from_numpy(ids).cuda(), torch.from_numpy(rows).cuda(), None, 1,
+                                          WORLD, torch.device("cuda", rank), torch.from_numpy(cnt).cuda())
+    want = []
+    for src in range(WORLD):
+        g = np.random.default_rng(50 + src)
+        m = 20_000 if src == 0 else 7_000
+        s_ids = g.integers(0, 10**7, m, dtype=np.int64)
+        s_rows = g.standard_normal((m, 32)).astype(np.float32)
+        s_cnt = g.integers(1, 5, m, dtype=np.int64)
+        mine = s_ids % WORLD == rank
+        want.append((s_ids[mine], s_rows[mine], s_cnt[mine]))
+    assert np.array_equal(r_ids.cpu().numpy(), np.concatenate([w[0] for w in want]))
+    assert np.array_equal(r_rows.cpu().numpy(), np.concatenate([w[1] for w in want]))
+    assert np.array_equal(r_cnt.cpu().numpy(), np.concatenate([w[2] for w in want]))
+
+    # --- the backward path on both ranks vs a simulation of both ----------------------------
+    cfg = _cfg()
+    path = pipeline.build_path(cfg, rank, WORLD, hot_fraction=0.02)
+    cls = path.class_table.cpu().numpy()
+    shard_rows = path.opt.emb.rows
+    w = path.opt.emb.weight.cpu().numpy().copy()
+    step = np.zeros(shard_rows, np.float32)
+    mem = np.zeros((shard_rows, cfg.dim), np.float32)
+    power = np.zeros((shard_rows, cfg.dim), np.float32)
+    # per-rank cold state (index + staging) of BOTH ranks, so that flushes can be simulated
+    sim = []
+    hot_ids = synth.hot_ids(cfg.table_rows, cfg.cache_entries)
+    for r in range(WORLD):
+        ox = om.OracleIndex(cfg.cache_entries)
+        stg = om.OracleStaging(ox.get_capacity(), cfg.dim, cnt_threshold=16)
+        ox.add(hot_ids)
+        sim.append((ox, stg))
+    for it in range(1, 5):
+        ids, grads = _batch(cfg, rank, it)
+        st = path.backward(torch.from_numpy(ids).cuda(), torch.from_numpy(grads).cuda())
+        inbox_hot, inbox_flush = [], []
+        for r in range(WORLD):
+            i_r, g_r = _batch(cfg, r, it)
+            u, s, c = om.only_unique_grads(i_r, g_r)
+            k = cls[u]
+            ox, stg = sim[r]
+            stg.accumulate_cached(ox, u[k == 2], s[k == 2], None, 0)
+            mine = (k == 1) & (u % WORLD == rank)
+            inbox_hot.append((u[mine], s[mine], c[mine]))
+        hu, hm, _ = om.unique_grads(np.concatenate([x[0] for x in inbox_hot]),
+                                    np.concatenate([x[1] for x in inbox_hot]),
+                                    np.concatenate([x[2] for x in inbox_hot]))
+        om.sparse_adam_update(hu, hm, step, mem, power, w, 0.01, id_offset=rank, id_stride=WORLD)
+        if it % cfg.flush_every == 0:
+            for r in range(WORLD):
+                ox, stg = sim[r]
+                fi, fr, fc, _ = stg.flush(ox, WORLD)
+                mine = fi % WORLD == rank
+                inbox_flush.append((fi[mine], fr[mine], fc[mine]))
+                ox.add(fi)  # refill
+            fu, fm, _ = om.unique_grads(np.concatenate([x[0] for x in inbox_flush]),
+                                        np.concatenate([x[1] for x in inbox_flush]),
+                                        np.concatenate([x[2] for x in inbox_flush]))
+            om.sparse_adam_update(fu, fm, step, mem, power, w, 0.01, id_offset=rank, id_stride=WORLD)
+        assert np.array_equal(path.opt.state_step.cpu().numpy(), step), (rank, it)
+        np.testing.assert_allclose(path.opt.state_mem.cpu().numpy(), mem, rtol=1e-4, atol=1e-9)
+        np.testing.assert_allclose(path.opt.emb.weight.cpu().numpy(), w, rtol=1e-4, atol=2e-6)
+        gi, _ = path.cold.index.export_state()
+        assert np.array_equal(gi.cpu().numpy(), sim[rank][0].export()[0]), (rank, it)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_nccl():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < WORLD:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    from oracle import build_oracle
+
+    build_oracle.build_oracle()
+    mp.spawn(_worker, args=(_free_port(),), nprocs=WORLD, join=True)
