@@ -45,6 +45,8 @@ def parse():
     ap.add_argument("--lookup", default="setassoc", choices=["setassoc", "sorted"])
     ap.add_argument("--mover", default="auto", choices=["auto", "lsu", "bulk"])
     ap.add_argument("--no-lru", action="store_true", help="skip the LRU ageing passes")
+    ap.add_argument("--exchange", default="push", choices=["push", "nccl"],
+                    help="N>1: fused pack+push over peer memory, or NCCL all_to_all_single")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -259,7 +261,7 @@ def run_ours(args) -> None:
     mode = E.LOOKUP_SORTED if args.lookup == "sorted" else E.LOOKUP_SETASSOC
     mover = {"auto": E.MOVER_AUTO, "lsu": E.MOVER_LSU, "bulk": E.MOVER_BULK}[args.mover]
     path = pipeline.build_path(cfg, rank, world, dev, optimizer="adam", lookup_mode=mode, mover=mover,
-                               touch_lru=not args.no_lru)
+                               touch_lru=not args.no_lru, exchange=args.exchange)
     sampler = synth.ZipfSampler(cfg.table_rows, cfg.zipf_s)
     rng = synth.rng_for(2, rank, 1)
     host_batches = [torch.from_numpy(sampler.ids(rng, cfg.batch)).pin_memory() for _ in range(4)]
@@ -376,7 +378,9 @@ def run_ours(args) -> None:
                        "table_rows": cfg.table_rows, "dim": cfg.dim, "cache_entries": cfg.cache_entries,
                        "batch_per_gpu": cfg.batch, "zipf_s": cfg.zipf_s, "flush_every": cfg.flush_every,
                        "lookup": args.lookup, "mover": args.mover, "lru_ageing": not args.no_lru,
-                       "optimizer": "SparseAdam fp32", "exchange": "local" if world == 1 else "nccl all_to_all",
+                       "optimizer": "SparseAdam fp32", "exchange": "local" if world == 1 else (
+                           "fused pack+push over peer memory (hot rows), nccl all_to_all (flush)"
+                           if args.exchange == "push" else "nccl all_to_all"),
                        "l2": "inputs larger than L2: 1.0 GB of rows read and written per step, 4 id batches rotate",
                        "stream": stats, "found_fraction": found_frac, "unique_per_batch": num_unique,
                        "hot_cold_unique": split_counts[1:]},

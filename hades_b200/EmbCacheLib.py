@@ -167,6 +167,20 @@ class IndexCache:
         _lib.check(self._lib.hb_index_touch_lru(self._h, locs.data_ptr(), locs.numel(),
                                                 ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
 
+    def cuda_touch_lru_runs(self, locs: torch.Tensor, runs=None, n_dev: torch.Tensor | None = None) -> None:
+        """LRU ageing for a batch grouped in runs of equal ids (no sort).  runs: the
+        ``RunsDesc`` returned by ``cudaUniqueSegSum(..., want_runs=True)`` for the ids that
+        were looked up, still valid (no other call has used the workspace since); None: the
+        batch holds each id once (every position is its own run)."""
+        n = locs.numel()
+        if runs is None:
+            _lib.check(self._lib.hb_index_touch_lru_runs(self._h, locs.data_ptr(), None, None, n, None, n,
+                                                         _lib.ptr(n_dev), _lib.stream_ptr()))
+        else:
+            _lib.check(self._lib.hb_index_touch_lru_runs(self._h, locs.data_ptr(), runs.perm, runs.run_start,
+                                                         n, runs.num_runs, n, _lib.ptr(n_dev),
+                                                         _lib.stream_ptr()))
+
     def cuda_lookup_found(self, ids: torch.Tensor, mode: int | None = None):
         """(slots, found mask) in one launch."""
         ids = ids.contiguous()
@@ -506,7 +520,8 @@ def cudaGradSplit3(ids, rows, hot_mask, local_mask):
 
 
 def cudaUniqueSegSum(ids, grads, cnt=None, mean: bool = False, id_bits: int = 64, sync: bool = True,
-                     n_dev: torch.Tensor | None = None):
+                     n_dev: torch.Tensor | None = None, want_runs: bool = False,
+                     seg_counts: torch.Tensor | None = None, seg_cap: int = 0):
     """Sorted unique ids, per-id fp32 sum (or mean) of the rows, per-id counts;
     deterministic.  With sync=True the outputs are sliced to the number of unique ids
     (one device-to-host read, as torch.unique does); with sync=False the full-size
@@ -522,10 +537,16 @@ def cudaUniqueSegSum(ids, grads, cnt=None, mean: bool = False, id_bits: int = 64
     num = torch.zeros(1, dtype=torch.int64, device=dev)
     lib = _lib.load()
     ws = _lib.workspace(lib.hb_unique_segsum_workspace_bytes(n, dim))
+    runs = _lib.RunsDesc() if want_runs else None
     _lib.check(lib.hb_unique_segsum_f32(ids.contiguous().data_ptr(), grads.contiguous().data_ptr(),
-                                        _lib.ptr(cnt), n, _lib.ptr(n_dev), dim, int(id_bits), int(mean),
+                                        _lib.ptr(cnt), n, _lib.ptr(n_dev), _lib.ptr(seg_counts),
+                                        int(seg_cap), dim, int(id_bits), int(mean),
                                         uniq.data_ptr(), sums.data_ptr(), counts.data_ptr(),
-                                        num.data_ptr(), ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
+                                        num.data_ptr(), C.byref(runs) if want_runs else None,
+                                        ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
+    if want_runs:
+        # the runs point into the shared workspace: use them before the next library call
+        return uniq, sums, counts, num, runs
     if not sync:
         return uniq, sums, counts, num
     u = int(num.item())

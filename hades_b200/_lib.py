@@ -44,6 +44,7 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_index_lookup": (_int, [_p, _p, _i64, _p, _p, _int, _p]),
     "hb_index_touch_lru_workspace_bytes": (_sz, [_i64]),
     "hb_index_touch_lru": (_int, [_p, _p, _i64, _p, _sz, _p]),
+    "hb_index_touch_lru_runs": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p]),
     "hb_index_reset": (_int, [_p, _p, _i64, _p]),
     "hb_index_getall": (_int, [_p, _p, _p, _i64, _p, _p]),
     "hb_index_build_sorted": (_int, [_p, _p]),
@@ -68,7 +69,7 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_table_split3": (_int, [_p, _p, _p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "hb_grad_split3": (_int, [_p, _p, _p, _p, _i64, _i64, _p, _p, _p, _p, _sz, _p]),
     "hb_unique_segsum_workspace_bytes": (_sz, [_i64, _i64]),
-    "hb_unique_segsum_f32": (_int, [_p, _p, _p, _i64, _p, _i64, _int, _int, _p, _p, _p, _p, _p, _sz, _p]),
+    "hb_unique_segsum_f32": (_int, [_p, _p, _p, _i64, _p, _p, _i64, _i64, _int, _int, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "hb_staging_accumulate_cached": (_int, [_p, _p, _p, _p, _i64, _p, _p, C.c_int32, _int, _p, _p, _p]),
     "hb_staging_accumulate_direct": (_int, [_p, _p, _p, _i64, _p, _i64, _i64, _p]),
     "hb_staging_flush_workspace_bytes": (_sz, [_i64, _int]),
@@ -79,7 +80,20 @@ PROTOTYPES: dict[str, tuple] = {
                               C.c_double, C.c_double, C.c_double, C.c_double, _p]),
     "hb_sparse_adagrad": (_int, [_p, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _p, _p, _int,
                                  C.c_double, C.c_double, _p]),
+    "hb_a2a_create": (_int, [_int, _int, _i64, _i64, _p]),
+    "hb_a2a_handle_bytes": (_sz, []),
+    "hb_a2a_export_handle": (_int, [_p, _p]),
+    "hb_a2a_connect": (_int, [_p, _p]),
+    "hb_a2a_destroy": (_int, [_p]),
+    "hb_a2a_push_workspace_bytes": (_sz, [_i64, _int]),
+    "hb_a2a_push": (_int, [_p, _p, _p, _p, _i64, _p, _p, _p, _p, _sz, _p]),
+    "hb_a2a_recv_view": (_int, [_p, _int, _p, _p, _p, _p, _p]),
 }
+
+
+class RunsDesc(C.Structure):
+    """hb_runs_t"""
+    _fields_ = [("perm", _p), ("run_start", _p), ("num_runs", _p), ("n", _i64)]
 
 
 class StagingDesc(C.Structure):

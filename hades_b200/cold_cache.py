@@ -121,7 +121,8 @@ class ColdCache:
             _lib.ptr(n_dev), _lib.ptr(self.threshold), self.default_threshold, self.lookup_mode,
             self.dropped.data_ptr(), _lib.ptr(locs), _lib.stream_ptr()))
         if touch_lru:
-            self.index.cuda_touch_lru(locs)
+            # ids are unique, so every position is its own run: no sort needed
+            self.index.cuda_touch_lru_runs(locs, None, n_dev)
 
     def accumulate_local(self, ids: torch.Tensor, grads: torch.Tensor, n_dev: torch.Tensor | None = None) -> None:
         _check(self.local is not None, "a local staging table was configured")

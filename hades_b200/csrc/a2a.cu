@@ -1,0 +1,206 @@
+// Owner-partitioned sparse-gradient exchange over peer memory: one fused
+// "pack + push" pass buckets (id, cnt, row) by owner and stores every bucket
+// straight into the owner GPU's receive slab over NVLink (plain st.global to
+// memory mapped with CUDA IPC; no staging copy, no host-side sizes).  Replaces
+// the sort + gathers + four all_to_all_single calls + two host reads of
+// swap_gradients (python/EmbCache/sparse_optim.py:36-118).
+//
+// Receive area of a rank (one cudaMalloc per parity, mapped by every peer):
+//   counts[world]                 rows delivered by each source
+//   ids   [world][cap]            slab s = rows sent by rank s
+//   cnt   [world][cap]
+//   rows  [world][cap][row_bytes]
+// Two parities alternate so that a fast rank's next push cannot overwrite what a
+// slow rank is still reading; one barrier per exchange (the caller's, between
+// push and consume) is then enough.  No kernel here waits on another GPU.
+#include <cstring>
+
+#include "partition_core.cuh"
+
+namespace hb {
+int* device_error_word();  // runtime.cu
+}
+
+struct hb_a2a {
+  int rank, world;
+  int64_t cap;        // rows per source slab
+  int64_t row_bytes;
+  size_t area_bytes;
+  char* local[2];            // this rank's receive areas
+  char* peer[2][64];         // peer[p][r] = rank r's area of parity p in this process
+  bool opened[64];
+  // device copy of the destination pointers for the push kernel
+  struct Dest {
+    int64_t* counts[64];
+    int64_t* ids[64];
+    int64_t* cnt[64];
+    char* rows[64];
+  };
+  Dest* dest_dev[2];
+  int parity;  // parity of the NEXT push
+};
+
+namespace hb {
+namespace {
+
+size_t off_counts() { return 0; }
+size_t off_ids(int world) { return align_up((size_t)world * sizeof(int64_t), 256); }
+size_t off_cnt(int world, int64_t cap) { return off_ids(world) + align_up((size_t)world * cap * 8, 256); }
+size_t off_rows(int world, int64_t cap) { return off_cnt(world, cap) + align_up((size_t)world * cap * 8, 256); }
+size_t area_size(int world, int64_t cap, int64_t row_bytes) {
+  return off_rows(world, cap) + align_up((size_t)world * cap * row_bytes, 256);
+}
+
+struct PushPolicy {
+  const int64_t* ids;
+  const char* rows;
+  const int64_t* cnt;
+  const int64_t* n_dev;
+  const hb_a2a::Dest* dest;
+  int world, rank;
+  int64_t cap, row_bytes;
+  int vb;
+  int* err;
+  __device__ __forceinline__ int classify(int64_t i) const {
+    if (n_dev && i >= *n_dev) return -1;
+    const int64_t id = __ldg(ids + i);
+    return id >= 0 ? (int)mod_nonneg(id, world) : -1;
+  }
+  __device__ __forceinline__ void emit(int64_t i, int c, int64_t pos, int64_t, bool active) const {
+    bool ok = active && pos < cap;
+    if (active && !ok) atomicExch(err, HB_ERR_CAPACITY);  // never write past a slab
+    const int64_t at = (int64_t)rank * cap + pos;        // my slab in the owner's area
+    if (ok) {
+      dest->ids[c][at] = ids[i];
+      dest->cnt[c][at] = cnt ? cnt[i] : 1;
+    }
+    warp_move_rows(rows + i * row_bytes, ok ? dest->rows[c] + at * row_bytes : nullptr, ok, row_bytes, vb);
+  }
+};
+
+// after the scatter: tell every owner how many rows it got from this rank
+__global__ void push_counts_kernel(PartitionPlan p, const hb_a2a::Dest* dest, int rank, int64_t cap,
+                                   int64_t* __restrict__ sent_out) {
+  const int b = threadIdx.x;
+  if (b >= p.num_classes) return;
+  int64_t c = p.class_total[b];
+  if (c > cap) c = cap;
+  dest->counts[b][rank] = c;
+  if (sent_out) sent_out[b] = c;
+  __threadfence_system();
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" {
+
+int hb_a2a_create(int rank, int world, int64_t cap_rows, int64_t row_bytes, hb_a2a_t** out) {
+  HB_CHECK_ARG(out && world >= 1 && world <= 64 && rank >= 0 && rank < world, "hb_a2a_create: bad rank/world");
+  HB_CHECK_ARG(cap_rows > 0 && row_bytes > 0, "hb_a2a_create: bad sizes");
+  hb_a2a_t* a = new hb_a2a_t();
+  memset(a, 0, sizeof(*a));
+  a->rank = rank;
+  a->world = world;
+  a->cap = cap_rows;
+  a->row_bytes = row_bytes;
+  a->area_bytes = area_size(world, cap_rows, row_bytes);
+  for (int p = 0; p < 2; ++p) {
+    HB_CUDA(cudaMalloc(&a->local[p], a->area_bytes));
+    HB_CUDA(cudaMemset(a->local[p], 0, a->area_bytes));
+    a->peer[p][rank] = a->local[p];
+    HB_CUDA(cudaMalloc(&a->dest_dev[p], sizeof(hb_a2a::Dest)));
+  }
+  *out = a;
+  return HB_OK;
+}
+
+size_t hb_a2a_handle_bytes(void) { return 2 * sizeof(cudaIpcMemHandle_t); }
+
+int hb_a2a_export_handle(hb_a2a_t* a, void* handle_out) {
+  HB_CHECK_ARG(a && handle_out, "hb_a2a_export_handle: null argument");
+  cudaIpcMemHandle_t h[2];
+  for (int p = 0; p < 2; ++p) HB_CUDA(cudaIpcGetMemHandle(&h[p], a->local[p]));
+  memcpy(handle_out, h, sizeof(h));
+  return HB_OK;
+}
+
+// handles: world entries of hb_a2a_handle_bytes() each, entry r from rank r
+int hb_a2a_connect(hb_a2a_t* a, const void* handles) {
+  HB_CHECK_ARG(a && (a->world == 1 || handles), "hb_a2a_connect: null argument");
+  const char* hp = static_cast<const char*>(handles);
+  for (int r = 0; r < a->world; ++r) {
+    if (r == a->rank) continue;
+    cudaIpcMemHandle_t h[2];
+    memcpy(h, hp + (size_t)r * sizeof(h), sizeof(h));
+    for (int p = 0; p < 2; ++p) {
+      void* ptr = nullptr;
+      HB_CUDA(cudaIpcOpenMemHandle(&ptr, h[p], cudaIpcMemLazyEnablePeerAccess));
+      a->peer[p][r] = static_cast<char*>(ptr);
+    }
+    a->opened[r] = true;
+  }
+  for (int p = 0; p < 2; ++p) {
+    hb_a2a::Dest d;
+    memset(&d, 0, sizeof(d));
+    for (int r = 0; r < a->world; ++r) {
+      char* base = a->peer[p][r];
+      d.counts[r] = reinterpret_cast<int64_t*>(base + off_counts());
+      d.ids[r] = reinterpret_cast<int64_t*>(base + off_ids(a->world));
+      d.cnt[r] = reinterpret_cast<int64_t*>(base + off_cnt(a->world, a->cap));
+      d.rows[r] = base + off_rows(a->world, a->cap);
+    }
+    HB_CUDA(cudaMemcpy(a->dest_dev[p], &d, sizeof(d), cudaMemcpyHostToDevice));
+  }
+  return HB_OK;
+}
+
+int hb_a2a_destroy(hb_a2a_t* a) {
+  if (!a) return HB_OK;
+  for (int r = 0; r < a->world; ++r)
+    if (a->opened[r])
+      for (int p = 0; p < 2; ++p) cudaIpcCloseMemHandle(a->peer[p][r]);
+  for (int p = 0; p < 2; ++p) {
+    cudaFree(a->local[p]);
+    cudaFree(a->dest_dev[p]);
+  }
+  delete a;
+  return HB_OK;
+}
+
+size_t hb_a2a_push_workspace_bytes(int64_t n, int world) { return partition_workspace_bytes(n, world, 1); }
+
+int hb_a2a_push(hb_a2a_t* a, const int64_t* ids, const void* rows, const int64_t* cnt, int64_t n,
+                const int64_t* n_dev, int64_t* sent_counts, int* parity_out, void* workspace,
+                size_t workspace_bytes, hb_stream_t stream) {
+  HB_CHECK_ARG(a && n >= 0 && n < ((int64_t)1 << 31), "hb_a2a_push: bad argument");
+  HB_CHECK_ARG(n == 0 || (ids && rows), "hb_a2a_push: null argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int p = a->parity;
+  a->parity ^= 1;
+  if (parity_out) *parity_out = p;
+  PushPolicy pol{ids, (const char*)rows, cnt, n_dev, a->dest_dev[p], a->world, a->rank, a->cap,
+                 a->row_bytes, payload_vec_bytes(a->row_bytes, rows, a->local[p] + off_rows(a->world, a->cap)),
+                 device_error_word()};
+  PartitionPlan plan;
+  int rc = run_partition(pol, n, a->world, workspace, workspace_bytes, nullptr, st, 1, &plan);
+  if (rc != HB_OK) return rc;
+  HB_LAUNCH(push_counts_kernel, 1, 64, 0, st, plan, a->dest_dev[p], a->rank, a->cap, sent_counts);
+  return HB_OK;
+}
+
+int hb_a2a_recv_view(hb_a2a_t* a, int parity, int64_t** ids, void** rows, int64_t** cnt,
+                     int64_t** counts, int64_t* cap_rows) {
+  HB_CHECK_ARG(a && (parity == 0 || parity == 1), "hb_a2a_recv_view: bad argument");
+  char* base = a->local[parity];
+  if (counts) *counts = reinterpret_cast<int64_t*>(base + off_counts());
+  if (ids) *ids = reinterpret_cast<int64_t*>(base + off_ids(a->world));
+  if (cnt) *cnt = reinterpret_cast<int64_t*>(base + off_cnt(a->world, a->cap));
+  if (rows) *rows = base + off_rows(a->world, a->cap);
+  if (cap_rows) *cap_rows = a->cap;
+  return HB_OK;
+}
+
+}  // extern "C"

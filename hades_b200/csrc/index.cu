@@ -223,6 +223,90 @@ __global__ void touch_apply_kernel(const uint32_t* __restrict__ keys,
   }
 }
 
+// ---- LRU touch from runs -------------------------------------------------------
+// The batch is given as runs of equal ids (each run = the sorted batch positions
+// of one id, ascending), so no sort is needed: a first kernel notes which run hit
+// each slot, a second computes per hit slot the same closed form as above, with
+// "hits on the line after my last hit" counted by binary search in the position
+// lists of the other hit ways of the line.
+struct RunsView {
+  const int64_t* locs;       // slot of every batch position
+  const uint32_t* perm;      // nullable: position list of the runs (identity when null)
+  const int64_t* run_start;  // nullable: run u = [run_start[u], run_start[u+1]) (run u = {u} when null)
+  const int64_t* num_runs;   // nullable device count
+  const int64_t* n_dev;      // nullable device count of positions
+  int64_t max_runs;
+  int64_t n;
+  __device__ __forceinline__ int64_t positions() const {
+    if (!n_dev) return n;
+    const int64_t d = *n_dev;
+    return d < n ? (d > 0 ? d : 0) : n;
+  }
+  __device__ __forceinline__ int64_t runs() const {
+    int64_t r = max_runs;
+    if (num_runs && *num_runs < r) r = *num_runs;
+    if (!run_start) { const int64_t p = positions(); if (p < r) r = p; }
+    return r;
+  }
+  __device__ __forceinline__ int64_t start(int64_t u) const { return run_start ? run_start[u] : u; }
+  __device__ __forceinline__ int64_t end(int64_t u, int64_t nruns, int64_t npos) const {
+    return (u + 1 < nruns) ? start(u + 1) : npos;
+  }
+  __device__ __forceinline__ int64_t pos(int64_t j) const { return perm ? (int64_t)perm[j] : j; }
+};
+
+__global__ void touch_runs_mark_kernel(RunsView v, int64_t capacity, int32_t epoch,
+                                       int32_t* __restrict__ slot_run,
+                                       int32_t* __restrict__ slot_epoch) {
+  const int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (u >= v.runs()) return;
+  const int64_t slot = v.locs[v.pos(v.start(u))];
+  if (slot < 0 || slot >= capacity) return;
+  slot_run[slot] = (int32_t)u;
+  slot_epoch[slot] = epoch;
+}
+
+__global__ void touch_runs_apply_kernel(RunsView v, int64_t capacity, int32_t epoch,
+                                        const int32_t* __restrict__ slot_run,
+                                        const int32_t* __restrict__ slot_epoch,
+                                        int32_t* __restrict__ lru) {
+  const int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  const int64_t nruns = v.runs();
+  if (u >= nruns) return;
+  const int64_t npos = v.positions();
+  const int64_t slot = v.locs[v.pos(v.start(u))];
+  if (slot < 0 || slot >= capacity) return;
+  const int64_t line = slot >> 3;
+  const int way = (int)(slot & 7);
+  const int64_t last = v.pos(v.end(u, nruns, npos) - 1);
+  int32_t total = 0, after = 0;
+  bool leader = true;
+  bool hit[kWays];
+#pragma unroll
+  for (int w = 0; w < kWays; ++w) {
+    hit[w] = slot_epoch[line * kWays + w] == epoch;
+    if (!hit[w]) continue;
+    const int64_t u2 = slot_run[line * kWays + w];
+    const int64_t s2 = v.start(u2), e2 = v.end(u2, nruns, npos);
+    total += (int32_t)(e2 - s2);
+    if (w < way) leader = false;
+    if (w != way) {
+      int64_t lo = s2, hi = e2;  // first position of the run greater than `last`
+      while (lo < hi) {
+        const int64_t mid = (lo + hi) >> 1;
+        if (v.pos(mid) <= last) lo = mid + 1; else hi = mid;
+      }
+      after += (int32_t)(e2 - lo);
+    }
+  }
+  lru[slot] = after;
+  if (leader) {
+#pragma unroll
+    for (int w = 0; w < kWays; ++w)
+      if (!hit[w]) lru[line * kWays + w] += total;
+  }
+}
+
 // ---- reset -------------------------------------------------------------------
 __global__ void reset_kernel(const int64_t* __restrict__ ids, int64_t n, int64_t lines,
                              int64_t* __restrict__ line_ids, int32_t* __restrict__ lru) {
@@ -373,6 +457,8 @@ int hb_index_destroy(hb_index_t* h) {
   cudaFree(h->pairs);
   cudaFree(h->level_store);
   cudaFree(h->scratch_count);
+  cudaFree(h->slot_run);
+  cudaFree(h->slot_epoch);
   delete h;
   return HB_OK;
 }
@@ -452,6 +538,35 @@ int hb_index_touch_lru(hb_index_t* h, const int64_t* locs, int64_t n, void* work
   count_library_launches(3);
   HB_LAUNCH(touch_apply_kernel, grid_for(n), kBlock, 0, st, keys.Current(), vals.Current(), n,
             h->cache_size, h->lru);
+  return HB_OK;
+}
+
+int hb_index_touch_lru_runs(hb_index_t* h, const int64_t* locs, const uint32_t* perm,
+                            const int64_t* run_start, int64_t max_runs, const int64_t* num_runs,
+                            int64_t n, const int64_t* n_dev, hb_stream_t stream) {
+  HB_CHECK_ARG(h && (n == 0 || locs), "hb_index_touch_lru_runs: null argument");
+  HB_CHECK_ARG(n >= 0 && n < ((int64_t)1 << 31) && max_runs >= 0 && max_runs <= n,
+               "hb_index_touch_lru_runs: sizes out of range");
+  HB_CHECK_ARG(!(perm && !run_start), "hb_index_touch_lru_runs: a position list needs run starts");
+  if (n == 0 || max_runs == 0) return HB_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t cap = h->cache_size;
+  if (!h->slot_run) {
+    HB_CUDA(cudaMalloc(&h->slot_run, cap * sizeof(int32_t)));
+    HB_CUDA(cudaMalloc(&h->slot_epoch, cap * sizeof(int32_t)));
+    HB_CUDA(cudaMemsetAsync(h->slot_epoch, 0, cap * sizeof(int32_t), st));
+    h->epoch = 0;
+  }
+  if (h->epoch == INT32_MAX) {
+    HB_CUDA(cudaMemsetAsync(h->slot_epoch, 0, cap * sizeof(int32_t), st));
+    h->epoch = 0;
+  }
+  h->epoch += 1;
+  RunsView v{locs, perm, run_start, num_runs, n_dev, max_runs, n};
+  HB_LAUNCH(touch_runs_mark_kernel, grid_for(max_runs), kBlock, 0, st, v, cap, h->epoch, h->slot_run,
+            h->slot_epoch);
+  HB_LAUNCH(touch_runs_apply_kernel, grid_for(max_runs), kBlock, 0, st, v, cap, h->epoch,
+            h->slot_run, h->slot_epoch, h->lru);
   return HB_OK;
 }
 

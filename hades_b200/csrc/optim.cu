@@ -68,7 +68,10 @@ __device__ __forceinline__ float adam_elem(float g, float& m, float& v, float bi
   return p.lr * mc / (sqrtf(vc) + p.eps);  // std_values, sparse_optim.py:654-655
 }
 
-// A group of G lanes per row; kRows rows in flight.
+// A group of G lanes per row, kOptRows rows in flight per group (their loads are
+// issued together, then the arithmetic and the stores follow).
+constexpr int kOptRows = 2;
+
 template <typename E, bool VEC4>
 __global__ void __launch_bounds__(kBlock) sparse_adam_kernel(
     const int64_t* __restrict__ ids, const float* __restrict__ grads,
@@ -81,42 +84,59 @@ __global__ void __launch_bounds__(kBlock) sparse_adam_kernel(
   const int sub = (int)(tid & ((1 << glog2) - 1));
   const int64_t ngroups = ((int64_t)gridDim.x * blockDim.x) >> glog2;
   const int G = 1 << glog2;
-  for (int64_t i = group; i < n; i += ngroups) {
-    const int64_t row = map(__ldg(ids + i));
-    if (row < 0) continue;
-    // state_step = state_step + 1 (per row), sparse_optim.py:624-626
-    const float t = step[row] + 1.0f;
-    const float bias1 = 1.0f - powf(p.beta1, t);
-    const float bias2 = 1.0f - powf(p.beta2, t);
-    const float inv_cnt = cnt ? (float)__ldg(cnt + i) : 1.0f;  // grad / cnt, sparse_optim.py:608-611
-    const float* g = grads + i * dim;
-    float* m = mem + row * dim;
-    float* v = power + row * dim;
-    E* e = emb + row * dim;
+  for (int64_t i0 = group; i0 < n; i0 += ngroups * kOptRows) {
+    int64_t row[kOptRows];
+    float bias1[kOptRows], bias2[kOptRows], c[kOptRows];
+#pragma unroll
+    for (int r = 0; r < kOptRows; ++r) {
+      const int64_t i = i0 + r * ngroups;
+      row[r] = i < n ? map(__ldg(ids + i)) : -1;
+      if (row[r] >= 0) {
+        // state_step = state_step + 1 (per row), sparse_optim.py:624-626
+        const float t = step[row[r]] + 1.0f;
+        bias1[r] = 1.0f - powf(p.beta1, t);
+        bias2[r] = 1.0f - powf(p.beta2, t);
+        c[r] = cnt ? (float)__ldg(cnt + i) : 1.0f;  // grad / cnt, sparse_optim.py:608-611
+      }
+    }
     if (VEC4) {
       for (int64_t k = sub; k < (dim >> 2); k += G) {
-        float4 gg = __ldg(reinterpret_cast<const float4*>(g) + k);
-        if (cnt) { gg.x /= inv_cnt; gg.y /= inv_cnt; gg.z /= inv_cnt; gg.w /= inv_cnt; }
-        float4 mm = reinterpret_cast<float4*>(m)[k];
-        float4 vv = reinterpret_cast<float4*>(v)[k];
-        float4 ee = EmbIO<E>::load4(e + 4 * k);
-        ee.x -= adam_elem(gg.x, mm.x, vv.x, bias1, bias2, p);
-        ee.y -= adam_elem(gg.y, mm.y, vv.y, bias1, bias2, p);
-        ee.z -= adam_elem(gg.z, mm.z, vv.z, bias1, bias2, p);
-        ee.w -= adam_elem(gg.w, mm.w, vv.w, bias1, bias2, p);
-        reinterpret_cast<float4*>(m)[k] = mm;
-        reinterpret_cast<float4*>(v)[k] = vv;
-        EmbIO<E>::store4(e + 4 * k, ee);
+        float4 gg[kOptRows], mm[kOptRows], vv[kOptRows], ee[kOptRows];
+#pragma unroll
+        for (int r = 0; r < kOptRows; ++r)
+          if (row[r] >= 0) {
+            gg[r] = __ldg(reinterpret_cast<const float4*>(grads + (i0 + r * ngroups) * dim) + k);
+            mm[r] = reinterpret_cast<const float4*>(mem + row[r] * dim)[k];
+            vv[r] = reinterpret_cast<const float4*>(power + row[r] * dim)[k];
+            ee[r] = EmbIO<E>::load4(emb + row[r] * dim + 4 * k);
+          }
+#pragma unroll
+        for (int r = 0; r < kOptRows; ++r)
+          if (row[r] >= 0) {
+            if (cnt) { gg[r].x /= c[r]; gg[r].y /= c[r]; gg[r].z /= c[r]; gg[r].w /= c[r]; }
+            ee[r].x -= adam_elem(gg[r].x, mm[r].x, vv[r].x, bias1[r], bias2[r], p);
+            ee[r].y -= adam_elem(gg[r].y, mm[r].y, vv[r].y, bias1[r], bias2[r], p);
+            ee[r].z -= adam_elem(gg[r].z, mm[r].z, vv[r].z, bias1[r], bias2[r], p);
+            ee[r].w -= adam_elem(gg[r].w, mm[r].w, vv[r].w, bias1[r], bias2[r], p);
+            reinterpret_cast<float4*>(mem + row[r] * dim)[k] = mm[r];
+            reinterpret_cast<float4*>(power + row[r] * dim)[k] = vv[r];
+            EmbIO<E>::store4(emb + row[r] * dim + 4 * k, ee[r]);
+          }
       }
     } else {
       for (int64_t k = sub; k < dim; k += G) {
-        float gg = __ldg(g + k);
-        if (cnt) gg /= inv_cnt;
-        float mm = m[k], vv = v[k];
-        const float upd = adam_elem(gg, mm, vv, bias1, bias2, p);
-        m[k] = mm;
-        v[k] = vv;
-        EmbIO<E>::store(e + k, EmbIO<E>::load(e + k) - upd);
+#pragma unroll
+        for (int r = 0; r < kOptRows; ++r)
+          if (row[r] >= 0) {
+            float gg = __ldg(grads + (i0 + r * ngroups) * dim + k);
+            if (cnt) gg /= c[r];
+            float mm = mem[row[r] * dim + k], vv = power[row[r] * dim + k];
+            const float upd = adam_elem(gg, mm, vv, bias1[r], bias2[r], p);
+            mem[row[r] * dim + k] = mm;
+            power[row[r] * dim + k] = vv;
+            E* e = emb + row[r] * dim + k;
+            EmbIO<E>::store(e, EmbIO<E>::load(e) - upd);
+          }
       }
     }
   }
@@ -185,7 +205,7 @@ int group_log2_for(int64_t units) {
 }
 
 int grid_for_groups(int64_t n, int glog2) {
-  int64_t blocks = ceil_div(n << glog2, kBlock);
+  int64_t blocks = ceil_div(ceil_div(n, kOptRows) << glog2, kBlock);
   const int64_t cap = (int64_t)sm_count() * 16;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;

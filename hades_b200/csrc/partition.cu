@@ -277,7 +277,7 @@ int hb_bucket_pack(const int64_t* ids, const void* rows, const int64_t* cnt, int
                        row_bytes, rows ? payload_vec_bytes(row_bytes, rows, out_rows) : 1,
                        out_ids, (char*)out_rows, out_cnt};
   return run_partition(pol, n, num_buckets, workspace, workspace_bytes, counts,
-                       (cudaStream_t)stream);
+                       (cudaStream_t)stream, rows ? 1 : kPartItemsMax);
 }
 
 int hb_table_split3(const int64_t* ids, const void* rows, const int64_t* cnt, int64_t n,
@@ -304,7 +304,7 @@ int hb_table_split3(const int64_t* ids, const void* rows, const int64_t* cnt, in
     bits |= (uintptr_t)out_rows[c];
   }
   pol.vb = (bits & 15) == 0 ? 16 : ((bits & 3) == 0 ? 4 : 1);
-  return run_partition(pol, n, 3, workspace, workspace_bytes, counts, (cudaStream_t)stream);
+  return run_partition(pol, n, 3, workspace, workspace_bytes, counts, (cudaStream_t)stream, 1);
 }
 
 int hb_grad_split3(const int64_t* ids, const void* rows, const uint8_t* hot_mask,
@@ -317,7 +317,7 @@ int hb_grad_split3(const int64_t* ids, const void* rows, const uint8_t* hot_mask
                "hb_grad_split3: null argument");
   GradSplitPolicy pol{ids, (const char*)rows, hot_mask, local_mask, row_bytes,
                       payload_vec_bytes(row_bytes, rows, out_rows), out_ids, (char*)out_rows};
-  return run_partition(pol, n, 3, workspace, workspace_bytes, counts, (cudaStream_t)stream);
+  return run_partition(pol, n, 3, workspace, workspace_bytes, counts, (cudaStream_t)stream, 1);
 }
 
 // ---- owner bucketing for callers that must not allocate ---------------------------------
@@ -333,7 +333,7 @@ int hb_grad_split3(const int64_t* ids, const void* rows, const uint8_t* hot_mask
 // (cudaGetSymbolAddress) and that address is what the kernels receive.
 constexpr int64_t kNoAllocMaxItems = (int64_t)1 << 20;  // 1,048,576 ids per call
 constexpr int kNoAllocMaxBuckets = 64;
-// partition_workspace_bytes(kNoAllocMaxItems, kNoAllocMaxBuckets) = 132,864 bytes
+// partition_workspace_bytes(kNoAllocMaxItems, kNoAllocMaxBuckets, 8 items per thread) = 132,864 bytes
 constexpr size_t kNoAllocScratchBytes = 135168;  // 132 KiB, held by every GPU that loads the library
 
 static __device__ __align__(256) unsigned char g_noalloc_pack_scratch[kNoAllocScratchBytes];
@@ -387,7 +387,7 @@ int hb_bucket_pack_noalloc(const int64_t* ids, const void* rows, const int64_t* 
   HB_CHECK_ARG(!rows || (out_rows && row_bytes > 0), "hb_bucket_pack_noalloc: rows without output");
   HB_CHECK_ARG(!cnt || out_cnt, "hb_bucket_pack_noalloc: cnt without output");
   HB_CHECK_ARG(!range_partition || num_part > 0, "hb_bucket_pack_noalloc: empty range partition");
-  if (partition_workspace_bytes(n, num_buckets) > kNoAllocScratchBytes) {
+  if (partition_workspace_bytes(n, num_buckets, kPartItemsMax) > kNoAllocScratchBytes) {
     hb::set_error("hb_bucket_pack_noalloc: internal scratch too small for this request");
     return HB_ERR_CAPACITY;
   }
@@ -401,7 +401,7 @@ int hb_bucket_pack_noalloc(const int64_t* ids, const void* rows, const int64_t* 
                        row_bytes, rows ? payload_vec_bytes(row_bytes, rows, out_rows) : 1,
                        out_ids, (char*)out_rows, out_cnt};
   return run_partition(pol, n, num_buckets, scratch, kNoAllocScratchBytes, counts,
-                       (cudaStream_t)stream);
+                       (cudaStream_t)stream, kPartItemsMax);
 }
 
 

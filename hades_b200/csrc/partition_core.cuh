@@ -17,30 +17,32 @@
 namespace hb {
 
 constexpr int kPartBlock = 256;
-constexpr int kPartItems = 8;                          // items per thread
-constexpr int kPartTile = kPartBlock * kPartItems;     // items per block
+constexpr int kPartItemsMax = 8;  // items per thread: 8 for id-only partitions, fewer when
+                                  // every item drags a payload row along (more CTAs in flight)
 constexpr int kPartMaxClasses = 1024;
 
 struct PartitionPlan {
   int64_t n;
   int num_classes;
+  int items;              // items per thread (1..kPartItemsMax)
   int64_t num_blocks;
   int32_t* block_hist;    // [num_blocks][K] -> exclusive offsets inside the class
   int64_t* class_total;   // [K]
   int64_t* class_start;   // [K+1]
 };
 
-static inline size_t partition_workspace_bytes(int64_t n, int num_classes) {
-  const int64_t nb = n > 0 ? ceil_div(n, kPartTile) : 1;
+static inline size_t partition_workspace_bytes(int64_t n, int num_classes, int items = 1) {
+  const int64_t nb = n > 0 ? ceil_div(n, (int64_t)kPartBlock * items) : 1;
   return align_up((size_t)nb * num_classes * sizeof(int32_t), 256) +
          2 * align_up((size_t)(num_classes + 1) * sizeof(int64_t), 256) + 256;
 }
 
-static inline PartitionPlan partition_plan(void* ws, int64_t n, int num_classes) {
+static inline PartitionPlan partition_plan(void* ws, int64_t n, int num_classes, int items) {
   PartitionPlan p;
   p.n = n;
   p.num_classes = num_classes;
-  p.num_blocks = n > 0 ? ceil_div(n, kPartTile) : 1;
+  p.items = items;
+  p.num_blocks = n > 0 ? ceil_div(n, (int64_t)kPartBlock * items) : 1;
   Carver cv(ws);
   p.block_hist = cv.take<int32_t>((size_t)p.num_blocks * num_classes);
   p.class_total = cv.take<int64_t>(num_classes + 1);
@@ -55,9 +57,8 @@ __global__ void __launch_bounds__(kPartBlock) partition_hist_kernel(Policy pol, 
   extern __shared__ int s_hist[];
   for (int k = threadIdx.x; k < p.num_classes; k += kPartBlock) s_hist[k] = 0;
   __syncthreads();
-  const int64_t base = (int64_t)blockIdx.x * kPartTile;
-#pragma unroll
-  for (int s = 0; s < kPartItems; ++s) {
+  const int64_t base = (int64_t)blockIdx.x * kPartBlock * p.items;
+  for (int s = 0; s < p.items; ++s) {
     const int64_t i = base + s * kPartBlock + threadIdx.x;
     if (i < p.n) {
       const int c = pol.classify(i);
@@ -175,8 +176,8 @@ __global__ void __launch_bounds__(kPartBlock) partition_scatter_kernel(Policy po
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const unsigned lt = (1u << lane) - 1u;
-  const int64_t base = (int64_t)blockIdx.x * kPartTile;
-  for (int s = 0; s < kPartItems; ++s) {
+  const int64_t base = (int64_t)blockIdx.x * kPartBlock * p.items;
+  for (int s = 0; s < p.items; ++s) {
     const int64_t i = base + s * kPartBlock + threadIdx.x;
     const int c = i < p.n ? pol.classify(i) : -1;
     const unsigned same = __match_any_sync(0xffffffffu, c);
@@ -206,20 +207,24 @@ static inline size_t partition_scatter_smem(int K) {
   return (size_t)((kPartBlock / 32) * K) * sizeof(int) + 2 * (size_t)K * sizeof(int64_t);
 }
 
-// Runs the three launches.  counts_out (nullable): device int64[K].
+// Runs the three launches.  counts_out (nullable): device int64[K].  items: items
+// per thread (a workspace sized for items = 1 fits every choice).
 template <typename Policy>
 int run_partition(const Policy& pol, int64_t n, int num_classes, void* ws, size_t ws_bytes,
-                  int64_t* counts_out, cudaStream_t st, PartitionPlan* plan_out = nullptr) {
+                  int64_t* counts_out, cudaStream_t st, int items = kPartItemsMax,
+                  PartitionPlan* plan_out = nullptr) {
+  if (items < 1) items = 1;
+  if (items > kPartItemsMax) items = kPartItemsMax;
   if (num_classes < 1 || num_classes > kPartMaxClasses) {
     set_error("partition: number of classes %d outside [1, %d]", num_classes, kPartMaxClasses);
     return HB_ERR_INVALID;
   }
-  if (!ws || ws_bytes < partition_workspace_bytes(n, num_classes)) {
+  if (!ws || ws_bytes < partition_workspace_bytes(n, num_classes, items)) {
     set_error("partition: workspace of %zu bytes needed, %zu given",
-              partition_workspace_bytes(n, num_classes), ws_bytes);
+              partition_workspace_bytes(n, num_classes, items), ws_bytes);
     return HB_ERR_WORKSPACE;
   }
-  PartitionPlan p = partition_plan(ws, n, num_classes);
+  PartitionPlan p = partition_plan(ws, n, num_classes, items);
   if (plan_out) *plan_out = p;
   if (n <= 0) {
     HB_CUDA(cudaMemsetAsync(p.block_hist, 0, (size_t)num_classes * sizeof(int32_t), st));

@@ -31,7 +31,7 @@ constexpr int kShortSpan = 16;   // crossing runs over at most this many chunks:
 constexpr int kLongBlock = 512;
 
 struct SegArgs {
-  const int64_t* keys;        // sorted ids [n]
+  const uint8_t* head;        // [n] 1 where a run of equal ids starts in the sorted order
   const uint32_t* perm;       // position in the input of each sorted element [n]
   const int64_t* run_start;   // [U] first sorted position of each run
   const int64_t* num_runs;    // device scalar U
@@ -89,8 +89,10 @@ __device__ __forceinline__ int64_t effective_n(const SegArgs& a) {
 }
 
 // ---- main pass -------------------------------------------------------------------
-template <int VEC, int G, int VPL>
-__global__ void __launch_bounds__(kBlock) segsum_main_kernel(SegArgs a) {
+// HAS_CNT: per-row weights are given (unique_grads with cnt); otherwise the count
+// of a run is the number of its rows and needs no per-row traffic.
+template <int VEC, int G, int VPL, bool HAS_CNT>
+__global__ void __launch_bounds__(kBlock, 3) segsum_main_kernel(SegArgs a) {
   using V = typename VecF<VEC>::T;
   constexpr int U = (8 / VPL) < G ? (8 / VPL) : G;  // rows whose loads are in flight together
   const int lane = threadIdx.x & 31;
@@ -140,12 +142,11 @@ __global__ void __launch_bounds__(kBlock) segsum_main_kernel(SegArgs a) {
     const bool valid = j < j1;
     uint32_t p = 0;
     bool head = false;
-    long long cv = 1;
+    int cv = 1;
     if (valid) {
       p = __ldg(a.perm + j);
-      const int64_t k = __ldg(a.keys + j);
-      head = j == 0 || __ldg(a.keys + j - 1) != k;
-      if (a.cnt_in) cv = __ldg(a.cnt_in + p);
+      head = __ldg(a.head + j) != 0;
+      if (HAS_CNT) cv = (int)__ldg(a.cnt_in + p);
     }
     const unsigned hb_all = __ballot_sync(0xffffffffu, head);
     const unsigned vb_all = __ballot_sync(0xffffffffu, valid);
@@ -154,11 +155,11 @@ __global__ void __launch_bounds__(kBlock) segsum_main_kernel(SegArgs a) {
 #pragma unroll 1
     for (int t0 = 0; t0 < G; t0 += U) {
       V val[U][VPL];
-      long long cvs[U];
+      int cvs[U];
 #pragma unroll
       for (int x = 0; x < U; ++x) {
         const uint32_t px = __shfl_sync(0xffffffffu, p, t0 + x, G);
-        cvs[x] = __shfl_sync(0xffffffffu, cv, t0 + x, G);
+        cvs[x] = HAS_CNT ? __shfl_sync(0xffffffffu, cv, t0 + x, G) : 1;
         if ((valids >> (t0 + x)) & 1u) {
           const V* src = reinterpret_cast<const V*>(a.grads + (int64_t)px * a.dim + a.col0);
 #pragma unroll
@@ -187,13 +188,13 @@ __global__ void __launch_bounds__(kBlock) segsum_main_kernel(SegArgs a) {
           const int k = sub + v * G;
           if (k < vpr) vadd(acc[v], val[x][v]);
         }
-        cacc += (unsigned long long)cvs[x];
+        cacc += (unsigned long long)(unsigned)cvs[x];
       }
     }
   }
   if (live && have) {
     // does the open run go on after this chunk?
-    const bool tail = j1 < n_eff && __ldg(a.keys + j1) == __ldg(a.keys + j1 - 1);
+    const bool tail = j1 < n_eff && __ldg(a.head + j1) == 0;
     if (tail && !first_partial && sub == 0 && a.col0 == 0) {
       // this chunk holds the head of a crossing run: enter it in a fix-up list
       const int64_t run_end = (u + 1 < U_runs) ? __ldg(a.run_start + u + 1) : n_eff;
@@ -317,13 +318,29 @@ __global__ void __launch_bounds__(kLongBlock) segsum_fix_long_b_kernel(SegArgs a
 // ---- small helpers ----------------------------------------------------------------------------
 // keys = ids (entries at and beyond the device count get the largest key of
 // id_bits bits, so they sort last), perm = 0..n-1
+// number of valid entries of a segmented input = sum of the segment counts
+__global__ void sum_counts_kernel(const int64_t* __restrict__ seg_counts, int64_t num_segs,
+                                  int64_t seg_cap, int64_t* __restrict__ out) {
+  if (threadIdx.x || blockIdx.x) return;
+  int64_t t = 0;
+  for (int64_t k = 0; k < num_segs; ++k) {
+    const int64_t c = seg_counts[k];
+    t += c < 0 ? 0 : (c > seg_cap ? seg_cap : c);
+  }
+  *out = t;
+}
+
+template <typename KeyT>
 __global__ void prepare_keys_kernel(const int64_t* __restrict__ ids, int64_t n,
-                                    const int64_t* __restrict__ n_dev, int64_t sentinel,
-                                    int64_t* __restrict__ keys, uint32_t* __restrict__ perm) {
+                                    const int64_t* __restrict__ n_dev,
+                                    const int64_t* __restrict__ seg_counts, int64_t seg_cap,
+                                    int64_t sentinel, KeyT* __restrict__ keys,
+                                    uint32_t* __restrict__ perm) {
   const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (i >= n) return;
-  const bool keep = !n_dev || i < *n_dev;
-  keys[i] = keep ? ids[i] : sentinel;
+  // valid entries: a prefix of the input (n_dev) or a prefix of every segment (seg_counts)
+  const bool keep = seg_counts ? (i % seg_cap) < seg_counts[i / seg_cap] : (!n_dev || i < *n_dev);
+  keys[i] = (KeyT)(keep ? ids[i] : sentinel);
   perm[i] = (uint32_t)i;
 }
 
@@ -335,18 +352,22 @@ __global__ void finish_counts_kernel(const unsigned long long* __restrict__ raw,
   if (i < n && i < *num_runs) out[i] = (int64_t)raw[i] + plus_one;
 }
 
+template <typename KeyT>
 struct RunHeadPolicy {
-  const int64_t* keys;
+  const KeyT* keys;
   const int64_t* n_dev;
+  int64_t n;
   int64_t* uniq;
   int64_t* run_start;
+  uint8_t* head;
   __device__ __forceinline__ int classify(int64_t i) const {
     if (n_dev && i >= *n_dev) return -1;
     return (i == 0 || __ldg(keys + i - 1) != __ldg(keys + i)) ? 0 : -1;
   }
   __device__ __forceinline__ void emit(int64_t i, int, int64_t pos, int64_t, bool active) const {
+    if (i < n) head[i] = active;
     if (!active) return;
-    uniq[pos] = keys[i];
+    uniq[pos] = (int64_t)keys[i];
     run_start[pos] = i;
   }
 };
@@ -360,11 +381,13 @@ int choose_chunk(int64_t n) {
 }
 
 size_t sort_temp_bytes(int64_t n) {
-  size_t bytes = 0;
+  size_t b64 = 0, b32 = 0;
   cub::DoubleBuffer<int64_t> k(nullptr, nullptr);
+  cub::DoubleBuffer<uint32_t> k32(nullptr, nullptr);
   cub::DoubleBuffer<uint32_t> v(nullptr, nullptr);
-  cub::DeviceRadixSort::SortPairs(nullptr, bytes, k, v, (int)n, 0, 64, (cudaStream_t)0);
-  return bytes;
+  cub::DeviceRadixSort::SortPairs(nullptr, b64, k, v, (int)n, 0, 64, (cudaStream_t)0);
+  cub::DeviceRadixSort::SortPairs(nullptr, b32, k32, v, (int)n, 0, 32, (cudaStream_t)0);
+  return b64 > b32 ? b64 : b32;
 }
 
 struct SegPlan {
@@ -373,6 +396,8 @@ struct SegPlan {
   void* sort_temp;
   size_t sort_temp_bytes;
   int64_t* run_start;
+  uint8_t* head;
+  int64_t* n_valid;
   unsigned long long* raw_counts;
   float *head_part, *tail_part, *slice_part;
   int2 *short_list, *long_list;
@@ -396,6 +421,8 @@ SegPlan make_plan(void* ws, int64_t n, int64_t dim) {
   s.sort_temp_bytes = sort_temp_bytes(m);
   s.sort_temp = cv.take<char>(s.sort_temp_bytes);
   s.run_start = cv.take<int64_t>(m + 1);
+  s.head = cv.take<uint8_t>(m + 1);
+  s.n_valid = cv.take<int64_t>(1);
   s.raw_counts = cv.take<unsigned long long>(m);
   s.chunk = choose_chunk(m);
   s.num_chunks = ceil_div(m, s.chunk);
@@ -417,7 +444,10 @@ SegPlan make_plan(void* ws, int64_t n, int64_t dim) {
 template <int VEC, int G, int VPL>
 int launch_pass(const SegArgs& a, cudaStream_t st) {
   const int64_t threads = a.num_chunks * G;
-  HB_LAUNCH((segsum_main_kernel<VEC, G, VPL>), (int)ceil_div(threads, kBlock), kBlock, 0, st, a);
+  if (a.cnt_in)
+    HB_LAUNCH((segsum_main_kernel<VEC, G, VPL, true>), (int)ceil_div(threads, kBlock), kBlock, 0, st, a);
+  else
+    HB_LAUNCH((segsum_main_kernel<VEC, G, VPL, false>), (int)ceil_div(threads, kBlock), kBlock, 0, st, a);
   int fix_grid = (int)ceil_div(a.num_chunks * G, kBlock);
   const int cap = sm_count() * 8;
   if (fix_grid > cap) fix_grid = cap;
@@ -464,15 +494,24 @@ size_t hb_unique_segsum_workspace_bytes(int64_t n, int64_t dim) {
 }
 
 int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* cnt_in, int64_t n,
-                         const int64_t* n_dev, int64_t dim, int id_bits, int mean,
+                         const int64_t* n_dev, const int64_t* seg_counts, int64_t seg_cap,
+                         int64_t dim, int id_bits, int mean,
                          int64_t* uniq_ids, float* sums,
-                         int64_t* counts, int64_t* num_unique, void* workspace,
-                         size_t workspace_bytes, hb_stream_t stream) {
+                         int64_t* counts, int64_t* num_unique, hb_runs_t* runs_out,
+                         void* workspace, size_t workspace_bytes, hb_stream_t stream) {
   HB_CHECK_ARG(n >= 0 && n < ((int64_t)1 << 31) && dim > 0, "hb_unique_segsum_f32: bad sizes");
   HB_CHECK_ARG(num_unique != nullptr, "hb_unique_segsum_f32: num_unique is null");
   HB_CHECK_ARG(n == 0 || (ids && grads && uniq_ids && sums), "hb_unique_segsum_f32: null argument");
   HB_CHECK_ARG(id_bits >= 1 && id_bits <= 64, "hb_unique_segsum_f32: id_bits must be in [1, 64]");
+  HB_CHECK_ARG(!seg_counts || (seg_cap > 0 && n % seg_cap == 0),
+               "hb_unique_segsum_f32: a segmented input holds whole segments of seg_cap entries");
   cudaStream_t st = (cudaStream_t)stream;
+  if (runs_out) {
+    runs_out->perm = nullptr;
+    runs_out->run_start = nullptr;
+    runs_out->num_runs = num_unique;
+    runs_out->n = n;
+  }
   if (n == 0) {
     HB_CUDA(cudaMemsetAsync(num_unique, 0, sizeof(int64_t), st));
     return HB_OK;
@@ -483,25 +522,47 @@ int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* 
               workspace_bytes);
     return HB_ERR_WORKSPACE;
   }
-  // 1. sort (id, position)
+  // 1. sort (id, position); 32-bit keys when the ids fit
   const int64_t sentinel = id_bits >= 63 ? INT64_MAX : (((int64_t)1 << id_bits) - 1);
-  HB_LAUNCH(prepare_keys_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, ids, n, n_dev, sentinel,
-            s.k0, s.p0);
-  cub::DoubleBuffer<int64_t> keys(s.k0, s.k1);
   cub::DoubleBuffer<uint32_t> perm(s.p0, s.p1);
-  HB_CUDA(cub::DeviceRadixSort::SortPairs(s.sort_temp, s.sort_temp_bytes, keys, perm, (int)n, 0,
-                                          id_bits, st));
+  int rc;
+  if (seg_counts) {
+    // valid entries are scattered over the segments; their number becomes the device count
+    HB_LAUNCH(sum_counts_kernel, 1, 32, 0, st, seg_counts, n / seg_cap, seg_cap, s.n_valid);
+    n_dev = s.n_valid;
+  }
+  if (id_bits <= 32) {
+    uint32_t* k0 = reinterpret_cast<uint32_t*>(s.k0);
+    uint32_t* k1 = reinterpret_cast<uint32_t*>(s.k1);
+    HB_LAUNCH(prepare_keys_kernel<uint32_t>, (int)ceil_div(n, kBlock), kBlock, 0, st, ids, n, n_dev,
+              seg_counts, seg_cap, sentinel, k0, s.p0);
+    cub::DoubleBuffer<uint32_t> keys(k0, k1);
+    HB_CUDA(cub::DeviceRadixSort::SortPairs(s.sort_temp, s.sort_temp_bytes, keys, perm, (int)n, 0,
+                                            id_bits, st));
+    // 2. run heads -> unique ids, run starts, head flags, U
+    RunHeadPolicy<uint32_t> pol{keys.Current(), n_dev, n, uniq_ids, s.run_start, s.head};
+    rc = run_partition(pol, n, 1, s.part_ws, s.part_ws_bytes, num_unique, st);
+  } else {
+    HB_LAUNCH(prepare_keys_kernel<int64_t>, (int)ceil_div(n, kBlock), kBlock, 0, st, ids, n, n_dev,
+              seg_counts, seg_cap, sentinel, s.k0, s.p0);
+    cub::DoubleBuffer<int64_t> keys(s.k0, s.k1);
+    HB_CUDA(cub::DeviceRadixSort::SortPairs(s.sort_temp, s.sort_temp_bytes, keys, perm, (int)n, 0,
+                                            id_bits, st));
+    RunHeadPolicy<int64_t> pol{keys.Current(), n_dev, n, uniq_ids, s.run_start, s.head};
+    rc = run_partition(pol, n, 1, s.part_ws, s.part_ws_bytes, num_unique, st);
+  }
   count_library_launches(1 + (id_bits + 7) / 8);
-  // 2. run heads -> unique ids, run starts, U
-  RunHeadPolicy pol{keys.Current(), n_dev, uniq_ids, s.run_start};
-  int rc = run_partition(pol, n, 1, s.part_ws, s.part_ws_bytes, num_unique, st);
   if (rc != HB_OK) return rc;
   // 3./4. column passes
   HB_CUDA(cudaMemsetAsync(s.raw_counts, 0, n * sizeof(unsigned long long), st));
   const bool vec4 = (dim % 4 == 0) && (((uintptr_t)grads | (uintptr_t)sums) & 15) == 0;
   SegArgs a;
-  a.keys = keys.Current();
+  a.head = s.head;
   a.perm = perm.Current();
+  if (runs_out) {
+    runs_out->perm = perm.Current();
+    runs_out->run_start = s.run_start;
+  }
   a.run_start = s.run_start;
   a.num_runs = num_unique;
   a.grads = grads;

@@ -308,7 +308,7 @@ int hb_staging_flush(hb_index_t* h, const hb_staging_t* s, int32_t cnt_threshold
                   out_ids, out_rows, out_cnt,
                   payload_vec_bytes(s->dim * (int64_t)sizeof(float), s->grad, out_rows)};
   rc = run_partition(pol, s->slots, num_clients, workspace, workspace_bytes, counts,
-                     (cudaStream_t)stream);
+                     (cudaStream_t)stream, 2);
   if (rc == HB_OK && h) h->sorted_stale = true;
   return rc;
 }

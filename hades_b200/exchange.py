@@ -1,0 +1,94 @@
+"""Owner-partitioned exchange of (id, cnt, row) over peer memory: the host side of
+``hb_a2a_*``.  One fused pack+push kernel per rank stores every bucket into its owner's receive
+slab over NVLink; one small collective orders the push before the use of what was received.
+No sizes travel through the host, so a step that uses it has no host synchronisation at all
+(the reference reads the split sizes on the host twice per exchange,
+python/EmbCache/sparse_optim.py:55,77).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+class _RawCuda:
+    """A device buffer owned by the library, exposed through __cuda_array_interface__."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+def _as_tensor(ptr: int, shape, typestr: str, device) -> torch.Tensor:
+    return torch.as_tensor(_RawCuda(ptr, shape, typestr), device=device)
+
+
+class PeerExchange:
+    def __init__(self, rank: int, world: int, cap_rows: int, dim: int, row_dtype=torch.float32,
+                 device=None, group=None):
+        self.lib = _lib.load()
+        self.rank, self.world, self.cap, self.dim, self.group = rank, world, int(cap_rows), dim, group
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self.row_dtype = row_dtype
+        elem = torch.empty(0, dtype=row_dtype).element_size()
+        h = C.c_void_p()
+        _lib.check(self.lib.hb_a2a_create(rank, world, self.cap, dim * elem, C.byref(h)))
+        self._h = h
+        nbytes = self.lib.hb_a2a_handle_bytes()
+        mine = C.create_string_buffer(nbytes)
+        _lib.check(self.lib.hb_a2a_export_handle(self._h, mine))
+        if world > 1:
+            gathered = [None] * world
+            dist.all_gather_object(gathered, bytes(mine.raw), group=group)
+            blob = b"".join(gathered)
+        else:
+            blob = bytes(mine.raw)
+        _lib.check(self.lib.hb_a2a_connect(self._h, blob))
+        self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        typestr = {torch.float32: "<f4", torch.float16: "<f2", torch.float64: "<f8"}[row_dtype]
+        self._views = []
+        for parity in (0, 1):
+            ids, rows, cnt, counts = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p()
+            cap = C.c_int64()
+            _lib.check(self.lib.hb_a2a_recv_view(self._h, parity, C.byref(ids), C.byref(rows), C.byref(cnt),
+                                                 C.byref(counts), C.byref(cap)))
+            n = world * self.cap
+            self._views.append((_as_tensor(ids.value, (n,), "<i8", self.device),
+                                _as_tensor(rows.value, (n, dim), typestr, self.device),
+                                _as_tensor(cnt.value, (n,), "<i8", self.device),
+                                _as_tensor(counts.value, (world,), "<i8", self.device)))
+        if world > 1:
+            dist.barrier(group=group)  # every rank has mapped every area before anyone pushes
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            try:
+                self.lib.hb_a2a_destroy(self._h)
+            except Exception:
+                pass
+            self._h = None
+
+    def push(self, ids, rows, cnt=None, n_dev=None, sent_counts=None) -> int:
+        """Bucket by owner and store into the owners' slabs; returns the parity to read."""
+        n = ids.numel()
+        ws = _lib.workspace(self.lib.hb_a2a_push_workspace_bytes(n, self.world))
+        parity = C.c_int(0)
+        _lib.check(self.lib.hb_a2a_push(self._h, ids.data_ptr(), rows.data_ptr(), _lib.ptr(cnt), n,
+                                        _lib.ptr(n_dev), _lib.ptr(sent_counts), C.byref(parity),
+                                        ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
+        return parity.value
+
+    def fence(self) -> None:
+        """Order every rank's push before every rank's reads: one tiny collective on the
+        current stream (no host synchronisation)."""
+        if self.world > 1:
+            dist.all_reduce(self._token, group=self.group)
+
+    def received(self, parity: int):
+        """(ids [world*cap], rows [world*cap, dim], cnt [world*cap], counts [world]) of this
+        rank's receive area: segment s holds counts[s] valid rows from rank s."""
+        return self._views[parity]

@@ -39,7 +39,7 @@ class EmbeddingPath:
     def __init__(self, table: torch.Tensor, class_table: torch.Tensor, cold: ColdCache,
                  optimizer, rank: int = 0, world: int = 1, flush_every: int = 8, id_bits: int = 64,
                  lookup_mode: int = E.LOOKUP_SETASSOC, mover: int = E.MOVER_AUTO,
-                 touch_lru: bool = True, group=None):
+                 touch_lru: bool = True, group=None, peer_exchange=None):
         """table: backing rows for cache misses, [num_nodes, dim] fp32 on this GPU.
         class_table: int8 per node, HOT or COLD.  optimizer: SparseAdam / SparseAdagrad on this
         rank's shard (owner = id % world)."""
@@ -48,15 +48,18 @@ class EmbeddingPath:
         self.flush_every, self.id_bits = flush_every, id_bits
         self.lookup_mode, self.mover, self.touch_lru = lookup_mode, mover, touch_lru
         self.group = group
+        self.px = peer_exchange  # PeerExchange for the per-step hot rows (None: NCCL all-to-all)
         self.step_no = 0
         # unique hot ids of a batch cannot outnumber the hot ids of the table
         self.num_hot_ids = int((class_table == HOT).sum().item())
 
     # ---- forward -------------------------------------------------------------------------
-    def forward(self, ids: torch.Tensor, out_rows: torch.Tensor | None = None):
+    def forward(self, ids: torch.Tensor, out_rows: torch.Tensor | None = None, defer_touch: bool = False):
+        """defer_touch: leave the LRU ageing of this lookup to ``backward(..., locs=locs)``,
+        which sorts the same ids anyway and can age the counters without a sort of its own."""
         rows, locs, found = E.cudaLookupFetch(self.cold.index, ids, self.cold.emb, self.table,
                                               out_rows=out_rows, mode=self.lookup_mode, mover=self.mover)
-        if self.touch_lru:
+        if self.touch_lru and not defer_touch:
             self.cold.index.cuda_touch_lru(locs)
         return rows, locs, found
 
@@ -70,10 +73,14 @@ class EmbeddingPath:
         return r_ids, r_rows, r_cnt, None, counts
 
     # ---- backward ------------------------------------------------------------------------
-    def backward(self, ids: torch.Tensor, grads: torch.Tensor) -> StepStats:
+    def backward(self, ids: torch.Tensor, grads: torch.Tensor, locs: torch.Tensor | None = None) -> StepStats:
+        """locs: the slots the forward pass found for `ids`, when its LRU ageing was deferred."""
         st = StepStats()
         # hot-node local aggregation (only_unique_grads, sparse_optim.py:132-139)
-        uniq, sums, counts, num = E.cudaUniqueSegSum(ids, grads, id_bits=self.id_bits, sync=False)
+        uniq, sums, counts, num, runs = E.cudaUniqueSegSum(ids, grads, id_bits=self.id_bits, sync=False,
+                                                           want_runs=True)
+        if locs is not None and self.touch_lru:
+            self.cold.index.cuda_touch_lru_runs(locs, runs)
         st.num_unique = num
         # hot / cold
         outs, split_counts = E.cudaTableSplit3(uniq, sums, counts, self.class_table, n_dev=num,
@@ -86,13 +93,20 @@ class EmbeddingPath:
         self.cold.accumulate_remote(cold_ids, cold_rows, n_dev=split_counts[COLD:COLD + 1],
                                     touch_lru=self.touch_lru)
         # hot rows go to their owners now
-        r_ids, r_rows, r_cnt, r_n, sent = self._exchange(hot_ids, hot_rows, hot_cnt,
-                                                         split_counts[HOT:HOT + 1])
-        st.sent_counts = sent
-        if r_n is not None:
-            r_n = r_n[:1]
-        # owner: merge the senders' rows (unique_grads with counts) and update
-        self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, n_dev=r_n, id_bits=self.id_bits)
+        if self.px is not None and self.world > 1:
+            parity = self.px.push(hot_ids, hot_rows, hot_cnt, split_counts[HOT:HOT + 1])
+            self.px.fence()
+            r_ids, r_rows, r_cnt, seg_counts = self.px.received(parity)
+            self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=self.id_bits,
+                            seg_counts=seg_counts, seg_cap=self.px.cap)
+        else:
+            r_ids, r_rows, r_cnt, r_n, sent = self._exchange(hot_ids, hot_rows, hot_cnt,
+                                                             split_counts[HOT:HOT + 1])
+            st.sent_counts = sent
+            if r_n is not None:
+                r_n = r_n[:1]
+            # owner: merge the senders' rows (unique_grads with counts) and update
+            self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, n_dev=r_n, id_bits=self.id_bits)
         self.step_no += 1
         if self.flush_every > 0 and self.step_no % self.flush_every == 0:
             st.flushed = self.flush()
@@ -121,15 +135,15 @@ class EmbeddingPath:
         return n
 
     def step(self, ids: torch.Tensor, grads: torch.Tensor, out_rows: torch.Tensor | None = None):
-        rows, locs, found = self.forward(ids, out_rows)
-        st = self.backward(ids, grads)
+        rows, locs, found = self.forward(ids, out_rows, defer_touch=True)
+        st = self.backward(ids, grads, locs)
         return rows, locs, found, st
 
 
 def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str = "adam",
                hot_fraction: float = 0.01, lookup_mode: int = E.LOOKUP_SETASSOC,
                mover: int = E.MOVER_AUTO, touch_lru: bool = True, table_dtype=torch.float32,
-               seed_config: int | None = None, group=None) -> EmbeddingPath:
+               seed_config: int | None = None, group=None, exchange: str = "push") -> EmbeddingPath:
     """Build the state of one trainer for a cached-fetch configuration (``synth.CacheFetchConfig``):
     backing table, hot cache filled with the most popular ids, class table (the top
     ``hot_fraction`` of the popularity ranking is HOT), cold cache and optimiser shard."""
@@ -160,5 +174,13 @@ def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str =
         shard.weight.normal_(0.0, cfg.table_sigma, generator=gen)
     opt = SparseAdam(shard, lr=0.01) if optimizer == "adam" else SparseAdagrad(shard, lr=0.01)
     id_bits = max(int(cfg.table_rows).bit_length() + 1, 8)
+    px = None
+    if world > 1 and exchange == "push":
+        from .exchange import PeerExchange
+
+        # a rank can receive from one source at most the hot ids it owns
+        hot_ranked = synth.rank_to_id(np.arange(n_hot, dtype=np.int64), cfg.table_rows)
+        cap = int(np.bincount(hot_ranked % world, minlength=world).max())
+        px = PeerExchange(rank, world, cap, cfg.dim, torch.float32, device, group)
     return EmbeddingPath(table, class_table, cold, opt, rank, world, cfg.flush_every, id_bits,
-                         lookup_mode, mover, touch_lru, group)
+                         lookup_mode, mover, touch_lru, group, px)

@@ -112,12 +112,15 @@ class SparseAdam(_SparseOptimizer):
         self.state_power = torch.zeros((emb.rows, emb.embedding_dim), dtype=torch.float32, device=dev)
 
     def update(self, idx, grad, cnt=None, is_unique: bool = False, n_dev: torch.Tensor | None = None,
-               id_bits: int = 64) -> None:
+               id_bits: int = 64, seg_counts: torch.Tensor | None = None, seg_cap: int = 0) -> None:
+        """seg_counts / seg_cap: idx, grad, cnt are the receive slabs of a peer-memory exchange
+        (segment s holds seg_counts[s] valid rows); only with is_unique=False."""
         idx, grad, cnt = self._args(idx, grad, cnt)
         if not is_unique:
             # unique_grads (sparse_optim.py:611), without reading the unique count on the host
             idx, grad, _, n_dev = cudaUniqueSegSum(idx, grad, cnt, mean=True, id_bits=id_bits,
-                                                   sync=False, n_dev=n_dev)
+                                                   sync=False, n_dev=n_dev, seg_counts=seg_counts,
+                                                   seg_cap=seg_cap)
             cnt = None
         lib = _lib.load()
         w = self.emb.weight
@@ -139,12 +142,15 @@ class SparseAdagrad(_SparseOptimizer):
                                      device=emb.weight.device)
 
     def update(self, idx, grad, cnt=None, is_unique: bool = False, n_dev: torch.Tensor | None = None,
-               id_bits: int = 64) -> None:
+               id_bits: int = 64, seg_counts: torch.Tensor | None = None, seg_cap: int = 0) -> None:
+        """seg_counts / seg_cap: idx, grad, cnt are the receive slabs of a peer-memory exchange
+        (segment s holds seg_counts[s] valid rows); only with is_unique=False."""
         idx, grad, cnt = self._args(idx, grad, cnt)
         if not is_unique:
             # unique_grads (sparse_optim.py:611), without reading the unique count on the host
             idx, grad, _, n_dev = cudaUniqueSegSum(idx, grad, cnt, mean=True, id_bits=id_bits,
-                                                   sync=False, n_dev=n_dev)
+                                                   sync=False, n_dev=n_dev, seg_counts=seg_counts,
+                                                   seg_cap=seg_cap)
             cnt = None
         lib = _lib.load()
         w = self.emb.weight

@@ -98,6 +98,20 @@ size_t hb_index_touch_lru_workspace_bytes(int64_t n);
 int hb_index_touch_lru(hb_index_t* h, const int64_t* locs, int64_t n,
                        void* workspace, size_t workspace_bytes, hb_stream_t stream);
 
+/* The same LRU effect for a batch that is already grouped: run u holds the batch
+ * positions perm[run_start[u] .. run_start[u+1]) (ascending) of ONE id, so all of
+ * them carry the same slot locs[position], and different runs carry different
+ * slots.  This is what the sort inside hb_unique_segsum_f32 leaves behind
+ * (hb_runs_t), so a step that aggregates the gradients of the ids it looked up
+ * needs no second sort for the ageing.  perm NULL = identity; run_start NULL =
+ * every position is its own run (a batch of unique ids); num_runs / n_dev:
+ * nullable device counts capping max_runs / n.  The first call allocates two
+ * int32 arrays of `capacity` entries inside the index. */
+int hb_index_touch_lru_runs(hb_index_t* h, const int64_t* locs, const uint32_t* perm,
+                            const int64_t* run_start, int64_t max_runs,
+                            const int64_t* num_runs, int64_t n, const int64_t* n_dev,
+                            hb_stream_t stream);
+
 /* reset(ids), src/cache/cache.h:106-118,208-211: a hit way becomes empty. */
 int hb_index_reset(hb_index_t* h, const int64_t* ids, int64_t n, hb_stream_t stream);
 
@@ -276,13 +290,28 @@ int hb_grad_split3(const int64_t* ids, const void* rows, const uint8_t* hot_mask
  * which is also the divisor (the reference starts its counts from ones,
  * sparse_optim.py:145-148).  uniq_ids / sums / counts must hold n entries;
  * num_unique is a device int64.  id_bits: ids are < 2^id_bits - 1 (sort passes).
- * n_dev (nullable device int64) caps n: entries at and beyond it are ignored. */
+ * n_dev (nullable device int64) caps n: entries at and beyond it are ignored.
+ * seg_counts (nullable, device int64[n / seg_cap]): the input is a sequence of
+ * segments of seg_cap entries and only the first seg_counts[s] entries of segment
+ * s are valid -- the receive slabs of hb_a2a_push, consumed in place. */
+/* The grouping that hb_unique_segsum_f32 computed, as pointers into its workspace
+ * (valid until the workspace is written again): the input positions sorted by
+ * id and the start of every run of equal ids. */
+typedef struct hb_runs {
+  const uint32_t* perm;     /* [n] input position of each sorted element */
+  const int64_t* run_start; /* [num_runs] */
+  const int64_t* num_runs;  /* device int64 (= num_unique) */
+  int64_t n;
+} hb_runs_t;
+
 size_t hb_unique_segsum_workspace_bytes(int64_t n, int64_t dim);
 int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* cnt_in,
-                         int64_t n, const int64_t* n_dev, int64_t dim, int id_bits, int mean,
+                         int64_t n, const int64_t* n_dev, const int64_t* seg_counts,
+                         int64_t seg_cap, int64_t dim, int id_bits, int mean,
                          int64_t* uniq_ids,
                          float* sums, int64_t* counts /* nullable */, int64_t* num_unique,
-                         void* workspace, size_t workspace_bytes, hb_stream_t stream);
+                         hb_runs_t* runs_out /* nullable, host */, void* workspace,
+                         size_t workspace_bytes, hb_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
 /* Cold-gradient staging table (the reference's cache-server buffers).         */
@@ -368,6 +397,38 @@ int hb_sparse_adagrad(const int64_t* ids, const float* grads, const int64_t* cnt
                       const int64_t* n_dev, int64_t dim, int64_t id_offset, int64_t id_stride,
                       int64_t rows, float* state_sum, void* emb, int emb_elem_bytes, double lr,
                       double eps, hb_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Owner-partitioned exchange over peer memory (one box, NVLink / NVSwitch).   */
+/* ------------------------------------------------------------------------- */
+/* Replaces the owner search + torch.sort + gathers + four all_to_all_single
+ * calls + two host reads of swap_gradients (python/EmbCache/sparse_optim.py:
+ * 36-118): hb_a2a_push buckets (id, cnt, row) by owner = id % world and stores
+ * every bucket straight into the owner GPU's receive slab (CUDA IPC mapping,
+ * plain stores, no multicast).  Every rank owns two receive areas that
+ * alternate from push to push; between a push and the use of what was received
+ * the caller runs ONE barrier among the ranks on the same stream (e.g. a
+ * one-element NCCL all-reduce).  A slab holds cap_rows rows per source rank;
+ * rows beyond it are dropped and HB_ERR_CAPACITY is recorded for
+ * hb_device_status.  Set-up: create on every rank, exchange the handles
+ * (hb_a2a_handle_bytes() bytes each) by any host channel, connect. */
+typedef struct hb_a2a hb_a2a_t;
+int hb_a2a_create(int rank, int world, int64_t cap_rows, int64_t row_bytes, hb_a2a_t** out);
+size_t hb_a2a_handle_bytes(void);
+int hb_a2a_export_handle(hb_a2a_t* a, void* handle_out /* host */);
+int hb_a2a_connect(hb_a2a_t* a, const void* handles /* host, world entries in rank order */);
+int hb_a2a_destroy(hb_a2a_t* a);
+size_t hb_a2a_push_workspace_bytes(int64_t n, int world);
+/* sent_counts (nullable): device int64[world], rows sent to each owner.
+ * *parity_out: which receive area this push used on every rank. */
+int hb_a2a_push(hb_a2a_t* a, const int64_t* ids, const void* rows, const int64_t* cnt /* nullable: 1 */,
+                int64_t n, const int64_t* n_dev, int64_t* sent_counts, int* parity_out,
+                void* workspace, size_t workspace_bytes, hb_stream_t stream);
+/* This rank's receive area of a parity: ids/cnt [world][cap_rows], rows
+ * [world][cap_rows][row_bytes], counts[world] (device int64: rows from each
+ * source).  Feed hb_unique_segsum_f32 with seg_counts = counts, seg_cap = cap_rows. */
+int hb_a2a_recv_view(hb_a2a_t* a, int parity, int64_t** ids, void** rows, int64_t** cnt,
+                     int64_t** counts, int64_t* cap_rows);
 
 #ifdef __cplusplus
 }

@@ -131,3 +131,37 @@ def test_open_by_name_and_empty_batches(cuda_lib):
     a.reset(torch.empty(0, dtype=torch.int64))
     with pytest.raises(RuntimeError):
         EmbCacheLib.IndexCache(64, "never_created", False, False)
+
+
+@pytest.mark.parametrize("cache_size,id_range,n", [(64, 300, 5000), (20_000, 60_000, 200_000)])
+def test_touch_lru_from_runs(cuda_lib, oracle_mod, cache_size, id_range, n):
+    """The run-based LRU ageing (grouping taken from the aggregation's sort) leaves the same
+    counters as the sequential rule, for batches with heavy duplication and for unique ids."""
+    from hades_b200 import EmbCacheLib as E
+
+    rng = np.random.default_rng(cache_size + n)
+    ix = E.IndexCache(cache_size, f"runs{cache_size}", True, False)
+    ora = oracle_mod.OracleIndex(cache_size)
+    seed_ids = rng.integers(0, id_range, cache_size * 2, dtype=np.int64)
+    assert np.array_equal(ix.add(torch.from_numpy(seed_ids)).numpy(), ora.add(seed_ids))
+    for rnd in range(3):
+        q = rng.integers(0, id_range, n, dtype=np.int64)
+        q[: n // 3] = q[0]  # one very hot id
+        rng.shuffle(q)
+        want = ora.lookup(q, touch=True)
+        qd = torch.from_numpy(q).cuda()
+        locs = ix.cudalookup(qd)
+        assert np.array_equal(locs.cpu().numpy(), want)
+        g = torch.zeros((n, 4), device="cuda")
+        *_, runs = E.cudaUniqueSegSum(qd, g, id_bits=32, sync=False, want_runs=True)
+        ix.cuda_touch_lru_runs(locs, runs)
+        assert np.array_equal(ix.export_state()[1].cpu().numpy(), ora.export()[1]), rnd
+        # unique ids: every position its own run, with a device-side count
+        uq = np.unique(rng.integers(0, id_range, n // 4, dtype=np.int64))
+        rng.shuffle(uq)
+        want = ora.lookup(uq, touch=True)
+        padded = np.concatenate([uq, np.full(100, 7, dtype=np.int64)])  # ignored tail
+        locs = ix.cudalookup(torch.from_numpy(padded).cuda())
+        ix.cuda_touch_lru_runs(locs, None, torch.tensor([uq.size], device="cuda"))
+        assert np.array_equal(locs.cpu().numpy()[: uq.size], want)
+        assert np.array_equal(ix.export_state()[1].cpu().numpy(), ora.export()[1]), rnd

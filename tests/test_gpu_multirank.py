@@ -38,7 +38,7 @@ def _batch(cfg, rank, it):
     return ids, grads
 
 
-def _worker(rank, port):
+def _worker(rank, port, exchange):
     sys.path.insert(0, str(ROOT))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -72,7 +72,8 @@ def _worker(rank, port):
 
     # --- the backward path on both ranks vs a simulation of both ----------------------------
     cfg = _cfg()
-    path = pipeline.build_path(cfg, rank, WORLD, hot_fraction=0.02)
+    path = pipeline.build_path(cfg, rank, WORLD, hot_fraction=0.02, exchange=exchange)
+    assert (path.px is not None) == (exchange == "push")
     cls = path.class_table.cpu().numpy()
     shard_rows = path.opt.emb.rows
     w = path.opt.emb.weight.cpu().numpy().copy()
@@ -123,7 +124,10 @@ def _worker(rank, port):
     dist.destroy_process_group()
 
 
-def test_two_ranks_nccl():
+@pytest.mark.parametrize("exchange", ["nccl", "push"])
+def test_two_ranks(exchange):
+    """exchange = "nccl": ragged all_to_all_single; "push": the fused pack+push kernel over
+    peer memory (plain stores, NVLS off)."""
     if not torch.cuda.is_available() or torch.cuda.device_count() < WORLD:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -131,4 +135,4 @@ def test_two_ranks_nccl():
     from oracle import build_oracle
 
     build_oracle.build_oracle()
-    mp.spawn(_worker, args=(_free_port(),), nprocs=WORLD, join=True)
+    mp.spawn(_worker, args=(_free_port(), exchange), nprocs=WORLD, join=True)
