@@ -175,6 +175,15 @@ def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str =
     opt = SparseAdam(shard, lr=0.01) if optimizer == "adam" else SparseAdagrad(shard, lr=0.01)
     id_bits = max(int(cfg.table_rows).bit_length() + 1, 8)
     px = None
+    if world > 1:
+        # NCCL sets up its send/receive connections on first use (about a second); do it now,
+        # not inside the first flush
+        import torch.distributed as dist
+
+        t = torch.zeros(world, dtype=torch.int64, device=device)
+        dist.all_to_all_single(torch.empty_like(t), t, group=group)
+        dist.all_reduce(t, group=group)
+        torch.cuda.synchronize()
     if world > 1 and exchange == "push":
         from .exchange import PeerExchange
 
