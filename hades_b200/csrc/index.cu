@@ -255,24 +255,30 @@ struct RunsView {
   __device__ __forceinline__ int64_t pos(int64_t j) const { return perm ? (int64_t)perm[j] : j; }
 };
 
-__global__ void touch_runs_mark_kernel(RunsView v, int64_t capacity, int32_t epoch,
+// The batch number lives on the device and is advanced by a kernel, so that a
+// captured CUDA graph that contains the ageing can be replayed.
+__global__ void touch_runs_next_epoch_kernel(int32_t* epoch) { *epoch += 1; }
+
+__global__ void touch_runs_mark_kernel(RunsView v, int64_t capacity, const int32_t* epoch_dev,
                                        int32_t* __restrict__ slot_run,
                                        int32_t* __restrict__ slot_epoch) {
   const int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (u >= v.runs()) return;
+  const int32_t epoch = *epoch_dev;
   const int64_t slot = v.locs[v.pos(v.start(u))];
   if (slot < 0 || slot >= capacity) return;
   slot_run[slot] = (int32_t)u;
   slot_epoch[slot] = epoch;
 }
 
-__global__ void touch_runs_apply_kernel(RunsView v, int64_t capacity, int32_t epoch,
+__global__ void touch_runs_apply_kernel(RunsView v, int64_t capacity, const int32_t* epoch_dev,
                                         const int32_t* __restrict__ slot_run,
                                         const int32_t* __restrict__ slot_epoch,
                                         int32_t* __restrict__ lru) {
   const int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   const int64_t nruns = v.runs();
   if (u >= nruns) return;
+  const int32_t epoch = *epoch_dev;
   const int64_t npos = v.positions();
   const int64_t slot = v.locs[v.pos(v.start(u))];
   if (slot < 0 || slot >= capacity) return;
@@ -552,20 +558,17 @@ int hb_index_touch_lru_runs(hb_index_t* h, const int64_t* locs, const uint32_t* 
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t cap = h->cache_size;
   if (!h->slot_run) {
+    // first use (do it outside any stream capture): marks start at batch 0, the counter at 0
     HB_CUDA(cudaMalloc(&h->slot_run, cap * sizeof(int32_t)));
-    HB_CUDA(cudaMalloc(&h->slot_epoch, cap * sizeof(int32_t)));
-    HB_CUDA(cudaMemsetAsync(h->slot_epoch, 0, cap * sizeof(int32_t), st));
-    h->epoch = 0;
+    HB_CUDA(cudaMalloc(&h->slot_epoch, (cap + 1) * sizeof(int32_t)));
+    HB_CUDA(cudaMemsetAsync(h->slot_epoch, 0, (cap + 1) * sizeof(int32_t), st));
   }
-  if (h->epoch == INT32_MAX) {
-    HB_CUDA(cudaMemsetAsync(h->slot_epoch, 0, cap * sizeof(int32_t), st));
-    h->epoch = 0;
-  }
-  h->epoch += 1;
+  int32_t* epoch_dev = h->slot_epoch + cap;  // the batch counter sits after the marks
   RunsView v{locs, perm, run_start, num_runs, n_dev, max_runs, n};
-  HB_LAUNCH(touch_runs_mark_kernel, grid_for(max_runs), kBlock, 0, st, v, cap, h->epoch, h->slot_run,
+  HB_LAUNCH(touch_runs_next_epoch_kernel, 1, 1, 0, st, epoch_dev);
+  HB_LAUNCH(touch_runs_mark_kernel, grid_for(max_runs), kBlock, 0, st, v, cap, epoch_dev, h->slot_run,
             h->slot_epoch);
-  HB_LAUNCH(touch_runs_apply_kernel, grid_for(max_runs), kBlock, 0, st, v, cap, h->epoch,
+  HB_LAUNCH(touch_runs_apply_kernel, grid_for(max_runs), kBlock, 0, st, v, cap, epoch_dev,
             h->slot_run, h->slot_epoch, h->lru);
   return HB_OK;
 }

@@ -49,10 +49,10 @@ struct hb_index {
   int64_t level_cap[hb::kMaxLevels];
   int64_t* scratch_count;      // device int64[4] for small reductions
   // run-based LRU ageing: which run of the current batch hit a slot (valid when
-  // slot_epoch[slot] == epoch); allocated on first use
+  // slot_epoch[slot] == the batch counter kept at slot_epoch[capacity]); allocated
+  // on first use.  The counter is 32 bits: 2^31 batches per index.
   int32_t* slot_run;
   int32_t* slot_epoch;
-  int32_t epoch;
   hb::IndexView view;
 };
 

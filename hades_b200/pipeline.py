@@ -50,6 +50,7 @@ class EmbeddingPath:
         self.group = group
         self.px = peer_exchange  # PeerExchange for the per-step hot rows (None: NCCL all-to-all)
         self.step_no = 0
+        self._graphs, self._g_ids, self._g_grads, self._g_out, self._g_next = [], None, None, None, 0
         # unique hot ids of a batch cannot outnumber the hot ids of the table
         self.num_hot_ids = int((class_table == HOT).sum().item())
 
@@ -75,6 +76,18 @@ class EmbeddingPath:
     # ---- backward ------------------------------------------------------------------------
     def backward(self, ids: torch.Tensor, grads: torch.Tensor, locs: torch.Tensor | None = None) -> StepStats:
         """locs: the slots the forward pass found for `ids`, when its LRU ageing was deferred."""
+        st = self._backward_core(ids, grads, locs)
+        self._after_step(st)
+        return st
+
+    def _after_step(self, st: StepStats) -> None:
+        self.step_no += 1
+        if self.flush_every > 0 and self.step_no % self.flush_every == 0:
+            st.flushed = self.flush()
+
+    def _backward_core(self, ids, grads, locs) -> StepStats:
+        """Everything of the backward path that runs every step, with no host read (so that it
+        can be captured in a CUDA graph)."""
         st = StepStats()
         # hot-node local aggregation (only_unique_grads, sparse_optim.py:132-139)
         uniq, sums, counts, num, runs = E.cudaUniqueSegSum(ids, grads, id_bits=self.id_bits, sync=False,
@@ -107,9 +120,6 @@ class EmbeddingPath:
                 r_n = r_n[:1]
             # owner: merge the senders' rows (unique_grads with counts) and update
             self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, n_dev=r_n, id_bits=self.id_bits)
-        self.step_no += 1
-        if self.flush_every > 0 and self.step_no % self.flush_every == 0:
-            st.flushed = self.flush()
         return st
 
     def flush(self) -> int:
@@ -135,9 +145,37 @@ class EmbeddingPath:
         return n
 
     def step(self, ids: torch.Tensor, grads: torch.Tensor, out_rows: torch.Tensor | None = None):
+        if self._graphs and grads is self._g_grads and out_rows is self._g_out:
+            if ids is not self._g_ids:
+                self._g_ids.copy_(ids, non_blocking=True)
+            graph, (rows, locs, found, st) = self._graphs[self._g_next]
+            self._g_next = (self._g_next + 1) % len(self._graphs)
+            graph.replay()
+            st.flushed = 0
+            self._after_step(st)
+            return rows, locs, found, st
         rows, locs, found = self.forward(ids, out_rows, defer_touch=True)
         st = self.backward(ids, grads, locs)
         return rows, locs, found, st
+
+    def capture(self, ids_buf: torch.Tensor, grads: torch.Tensor, out_rows: torch.Tensor) -> None:
+        """Capture the per-step part of ``step`` (forward + backward without the periodic flush)
+        in a CUDA graph over the caller's buffers; later ``step(ids, grads, out_rows)`` calls
+        with the same ``grads`` and ``out_rows`` replay it (``ids`` is copied into ``ids_buf``
+        unless it is that tensor).  Call it after a few eager steps: every lazy allocation of
+        the library has to have happened.  With the peer-memory exchange two graphs are
+        captured, one per receive-area parity, and replayed alternately.  Not available with
+        the NCCL all-to-all exchange, which reads sizes on the host."""
+        if self.world > 1 and self.px is None:
+            raise RuntimeError("the NCCL all-to-all exchange cannot be captured; use exchange='push'")
+        graphs = []
+        for _ in range(2 if (self.px is not None and self.world > 1) else 1):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                rows, locs, found = self.forward(ids_buf, out_rows, defer_touch=True)
+                st = self._backward_core(ids_buf, grads, locs)
+            graphs.append((g, (rows, locs, found, st)))
+        self._graphs, self._g_ids, self._g_grads, self._g_out, self._g_next = graphs, ids_buf, grads, out_rows, 0
 
 
 def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str = "adam",

@@ -78,3 +78,38 @@ def test_pipeline_matches_oracle(cuda_lib, oracle_mod, mode, mover):
         np.testing.assert_allclose(path.table.cpu().numpy(), o["table"], rtol=1e-4, atol=1e-7)
     assert total_flushed > 0
     assert int(path.cold.dropped.item()) > 0
+
+
+def test_graph_replay_equals_eager(cuda_lib):
+    """The captured CUDA graph of the per-step path leaves exactly the bytes the eager launches
+    leave (same kernels, same order), across flush steps."""
+    from hades_b200 import pipeline, synth
+
+    base = synth.scaled(synth.CONFIG1, 0.05, "graph_test")
+    cfg = synth.CacheFetchConfig(base.name, base.config, base.table_rows, 128, base.cache_entries, base.batch,
+                                 base.zipf_s, flush_every=3)
+    paths = [pipeline.build_path(synth.CacheFetchConfig(cfg.name + str(i), *list(cfg.__dict__.values())[1:]))
+             for i in range(2)]
+    sampler = synth.ZipfSampler(cfg.table_rows, cfg.zipf_s)
+    rng = synth.rng_for(1, 0, 11)
+    batches = [torch.from_numpy(sampler.ids(rng, cfg.batch)).cuda() for _ in range(9)]
+    grads = torch.from_numpy(synth.normal_rows(rng, cfg.batch, cfg.dim, cfg.grad_sigma)).cuda()
+    outs = [torch.empty((cfg.batch, cfg.dim), device="cuda") for _ in range(2)]
+    ids_buf = torch.empty(cfg.batch, dtype=torch.int64, device="cuda")
+    for k in range(2):
+        for p, o in zip(paths, outs):
+            p.step(batches[k], grads, o)
+    torch.cuda.synchronize()
+    paths[1].capture(ids_buf, grads, outs[1])
+    for k in range(2, 9):
+        r0 = paths[0].step(batches[k], grads, outs[0])
+        r1 = paths[1].step(batches[k], grads, outs[1])
+        assert torch.equal(r0[0], r1[0]) and torch.equal(r0[1], r1[1]) and torch.equal(r0[2], r1[2]), k
+        assert r0[3].flushed == r1[3].flushed
+        assert int(r0[3].num_unique.item()) == int(r1[3].num_unique.item())
+    assert len(paths[1]._graphs) == 1
+    assert torch.equal(paths[0].table, paths[1].table)
+    assert torch.equal(paths[0].opt.state_mem, paths[1].opt.state_mem)
+    assert torch.equal(paths[0].cold.remote.grad, paths[1].cold.remote.grad)
+    for a, b in zip(paths[0].cold.index.export_state(), paths[1].cold.index.export_state()):
+        assert torch.equal(a, b)
