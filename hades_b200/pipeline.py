@@ -163,18 +163,17 @@ class EmbeddingPath:
         in a CUDA graph over the caller's buffers; later ``step(ids, grads, out_rows)`` calls
         with the same ``grads`` and ``out_rows`` replay it (``ids`` is copied into ``ids_buf``
         unless it is that tensor).  Call it after a few eager steps: every lazy allocation of
-        the library has to have happened.  With the peer-memory exchange two graphs are
-        captured, one per receive-area parity, and replayed alternately.  Not available with
-        the NCCL all-to-all exchange, which reads sizes on the host."""
-        if self.world > 1 and self.px is None:
-            raise RuntimeError("the NCCL all-to-all exchange cannot be captured; use exchange='push'")
+        the library has to have happened.  One GPU only: with more ranks the step contains a
+        collective (the NCCL all-to-all reads sizes on the host; the peer-memory exchange is
+        ordered by an NCCL all-reduce and alternates two receive areas chosen on the host)."""
+        if self.world > 1:
+            raise RuntimeError("graph capture of the step is available on one GPU only")
         graphs = []
-        for _ in range(2 if (self.px is not None and self.world > 1) else 1):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                rows, locs, found = self.forward(ids_buf, out_rows, defer_touch=True)
-                st = self._backward_core(ids_buf, grads, locs)
-            graphs.append((g, (rows, locs, found, st)))
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            rows, locs, found = self.forward(ids_buf, out_rows, defer_touch=True)
+            st = self._backward_core(ids_buf, grads, locs)
+        graphs.append((g, (rows, locs, found, st)))
         self._graphs, self._g_ids, self._g_grads, self._g_out, self._g_next = graphs, ids_buf, grads, out_rows, 0
 
 
