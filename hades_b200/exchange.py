@@ -36,18 +36,40 @@ class PeerExchange:
         self.row_dtype = row_dtype
         elem = torch.empty(0, dtype=row_dtype).element_size()
         h = C.c_void_p()
-        _lib.check(self.lib.hb_a2a_create(rank, world, self.cap, dim * elem, C.byref(h)))
-        self._h = h
         nbytes = self.lib.hb_a2a_handle_bytes()
         mine = C.create_string_buffer(nbytes)
-        _lib.check(self.lib.hb_a2a_export_handle(self._h, mine))
+        err = None
+        try:
+            _lib.check(self.lib.hb_a2a_create(rank, world, self.cap, dim * elem, C.byref(h)))
+            self._h = h
+            _lib.check(self.lib.hb_a2a_export_handle(self._h, mine))
+        except Exception as e:  # noqa: BLE001
+            err = str(e)
+        if world > 1:
+            # collectives are entered by every rank, whether or not its local set-up worked
+            gathered = [None] * world
+            dist.all_gather_object(gathered, (err, bytes(mine.raw)), group=group)
+            errs = [g[0] for g in gathered if g[0]]
+            if errs:
+                raise RuntimeError("peer exchange set-up failed on a rank: " + errs[0])
+            blob = b"".join(g[1] for g in gathered)
+        else:
+            if err:
+                raise RuntimeError(err)
+            blob = bytes(mine.raw)
+        try:
+            _lib.check(self.lib.hb_a2a_connect(self._h, blob))
+            err = None
+        except Exception as e:  # noqa: BLE001
+            err = str(e)
         if world > 1:
             gathered = [None] * world
-            dist.all_gather_object(gathered, bytes(mine.raw), group=group)
-            blob = b"".join(gathered)
-        else:
-            blob = bytes(mine.raw)
-        _lib.check(self.lib.hb_a2a_connect(self._h, blob))
+            dist.all_gather_object(gathered, err, group=group)
+            errs = [g for g in gathered if g]
+            if errs:
+                raise RuntimeError("peer exchange could not map a peer's memory: " + errs[0])
+        elif err:
+            raise RuntimeError(err)
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
         typestr = {torch.float32: "<f4", torch.float16: "<f2", torch.float64: "<f8"}[row_dtype]
         self._views = []

@@ -227,6 +227,18 @@ def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str =
         # a rank can receive from one source at most the hot ids it owns
         hot_ranked = synth.rank_to_id(np.arange(n_hot, dtype=np.int64), cfg.table_rows)
         cap = int(np.bincount(hot_ranked % world, minlength=world).max())
-        px = PeerExchange(rank, world, cap, cfg.dim, torch.float32, device, group)
+        try:
+            px = PeerExchange(rank, world, cap, cfg.dim, torch.float32, device, group)
+            ok = 1
+        except Exception as e:  # noqa: BLE001  (e.g. CUDA IPC not permitted between these processes)
+            import warnings
+
+            warnings.warn(f"peer-memory exchange unavailable ({e}); using the NCCL all-to-all")
+            px, ok = None, 0
+        # every rank must use the same exchange
+        agree = torch.tensor([ok], dtype=torch.int32, device=device)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN, group=group)
+        if int(agree.item()) == 0:
+            px = None
     return EmbeddingPath(table, class_table, cold, opt, rank, world, cfg.flush_every, id_bits,
                          lookup_mode, mover, touch_lru, group, px)
