@@ -248,7 +248,35 @@ __device__ __forceinline__ void warp_move_rows(const char* src_row, char* dst_ro
   if (act == 0u) return;
   const unsigned long long sb = (unsigned long long)src_row;
   const unsigned long long db = (unsigned long long)dst_row;
-  if (vb == 16) {
+  if (vb == 16 && row_bytes <= 256) {
+    // narrow rows: G = 2..16 lanes per row, 32/G rows per pass, 4 passes in flight
+    const int vpr = (int)(row_bytes >> 4);
+    int G = 16;
+    while ((G >> 1) >= vpr && G > 1) G >>= 1;
+    const int rpp = 32 / G;
+    const int sub = lane & (G - 1);
+    const int which = lane / G;
+    for (int q0 = 0; q0 < 32; q0 += 4 * rpp) {
+      const uint4* s[4];
+      uint4* d[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int q = q0 + u * rpp + which;
+        const unsigned long long a = __shfl_sync(0xffffffffu, sb, q & 31);
+        const unsigned long long b = __shfl_sync(0xffffffffu, db, q & 31);
+        const bool on = q < 32 && ((act >> q) & 1u) && sub < vpr;
+        s[u] = on ? reinterpret_cast<const uint4*>(a) : nullptr;
+        d[u] = reinterpret_cast<uint4*>(b);
+      }
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (s[u]) v[u] = __ldg(s[u] + sub);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (s[u]) d[u][sub] = v[u];
+    }
+  } else if (vb == 16) {
     const int64_t vpr = row_bytes >> 4;
     for (int q0 = 0; q0 < 32; q0 += 4) {
       if (((act >> q0) & 0xfu) == 0u) continue;
