@@ -251,6 +251,82 @@ def cudaUnpinPtr(ptr: int) -> None:
 
 
 # ---------------------------------------------------------------------------------------
+# named host shared memory: src/shm/shared_memory.h:14-64 (bound in src/pybind.cc:37-45)
+# Host plumbing of the reference's socket/shm control plane; kept so that code which creates
+# shared tensors through this module still runs.  No GPU work happens here.
+# ---------------------------------------------------------------------------------------
+_SHM: dict[int, tuple] = {}
+
+
+def _shm_path(name: str) -> str:
+    return "/dev/shm/" + name.lstrip("/")
+
+
+def _map_shared(name: str, size: int, create: bool, pin_memory: bool):
+    import mmap
+    import os
+
+    flags = os.O_RDWR | (os.O_CREAT if create else 0)
+    try:
+        fd = os.open(_shm_path(name), flags, 0o600)
+    except OSError as e:
+        raise RuntimeError(f"fail to open {name}: {e.strerror}") from e
+    if create:
+        os.ftruncate(fd, int(size))
+    mm = mmap.mmap(fd, int(size), mmap.MAP_SHARED, mmap.PROT_READ | mmap.PROT_WRITE)
+    buf = (C.c_char * int(size)).from_buffer(mm)
+    ptr_ = C.addressof(buf)
+    _SHM[ptr_] = (mm, buf, fd, name)
+    if pin_memory:
+        cudaPinPtr(ptr_, int(size))
+    return ptr_, fd
+
+
+def create_shared_mem(name: str, size: int, pin_memory: bool = True):
+    """(ptr, fd) of a new named segment; src/shm/shared_memory.h:14-32."""
+    return _map_shared(name, size, True, pin_memory)
+
+
+def open_shared_mem(name: str, size: int, pin_memory: bool = True):
+    """(ptr, fd) of an existing named segment; src/shm/shared_memory.h:34-48."""
+    return _map_shared(name, size, False, pin_memory)
+
+
+def release_shared_mem(name: str, size: int, ptr: int, fd: int, pin_memory: bool = True) -> None:
+    """Unpin, unmap, close and unlink; src/shm/shared_memory.h:50-57."""
+    import os
+
+    if pin_memory:
+        cudaUnpinPtr(ptr)
+    ent = _SHM.pop(ptr, None)
+    if ent is not None:
+        mm, buf, _, _ = ent
+        del buf
+        try:
+            mm.close()
+        except BufferError:
+            pass  # a tensor still views the mapping; it is released with that tensor
+    try:
+        os.close(fd)
+    except OSError:
+        pass
+    try:
+        os.unlink(_shm_path(name))
+    except FileNotFoundError:
+        pass
+
+
+def open_shared_tensor(ptr: int, dtype, shape):
+    """A tensor over shared memory (torch::from_blob); src/shm/shared_memory.h:59-64."""
+    numel = 1
+    for d in shape:
+        numel *= int(d)
+    nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+    raw = (C.c_char * nbytes).from_address(ptr)
+    return torch.frombuffer(raw, dtype=dtype, count=numel).view(*shape) if numel else torch.empty(shape, dtype=dtype)
+
+
+# ---------------------------------------------------------------------------------------
 # row movers: src/cuda/ops.h:15-31
 # ---------------------------------------------------------------------------------------
 def cudaFetch(src, src_index, dst, dst_index, mover: int = MOVER_AUTO) -> None:
