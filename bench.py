@@ -45,9 +45,13 @@ def parse():
     ap.add_argument("--lookup", default="setassoc", choices=["setassoc", "sorted"])
     ap.add_argument("--mover", default="auto", choices=["auto", "lsu", "bulk"])
     ap.add_argument("--no-lru", action="store_true", help="skip the LRU ageing passes")
-    ap.add_argument("--workload", default="config2", choices=["config2", "c4_exchange"],
+    ap.add_argument("--workload", default="config2", choices=["config2", "c4_exchange", "c5"],
                     help="config2: the whole path (default); c4_exchange: only the owner-partitioned "
-                         "exchange at configuration-4 shapes (1,048,576 unique ids x 64 fp32 per rank)")
+                         "exchange at configuration-4 shapes (1,048,576 unique ids x 64 fp32 per rank); "
+                         "c5: the whole path on the frontier of a sampled 2-layer GraphSAGE step over a "
+                         "synthetic R-MAT graph (1e8 nodes, 1,024 seeds, fanout [25, 10], per GPU)")
+    ap.add_argument("--optimizer", default="adam", choices=["adam", "adagrad"])
+    ap.add_argument("--rmat-bits", type=int, default=0, help="c5 on a smaller graph of 2**bits vertices")
     ap.add_argument("--exchange", default="push", choices=["push", "nccl"],
                     help="N>1: fused pack+push over peer memory, or NCCL all_to_all_single")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -261,14 +265,22 @@ def run_ours(args) -> None:
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
 
-    cfg = synth.CONFIG2 if args.scale == 1.0 else synth.scaled(synth.CONFIG2, args.scale, "config2_scaled")
     mode = E.LOOKUP_SORTED if args.lookup == "sorted" else E.LOOKUP_SETASSOC
     mover = {"auto": E.MOVER_AUTO, "lsu": E.MOVER_LSU, "bulk": E.MOVER_BULK}[args.mover]
-    path = pipeline.build_path(cfg, rank, world, dev, optimizer="adam", lookup_mode=mode, mover=mover,
-                               touch_lru=not args.no_lru, exchange=args.exchange)
-    sampler = synth.ZipfSampler(cfg.table_rows, cfg.zipf_s)
-    rng = synth.rng_for(2, rank, 1)
-    host_batches = [torch.from_numpy(sampler.ids(rng, cfg.batch)).pin_memory() for _ in range(4)]
+    c5 = args.workload == "c5"
+    if c5:
+        cfg = synth.CONFIG5 if not args.rmat_bits else synth.scaled_rmat(synth.CONFIG5, args.rmat_bits)
+        path = pipeline.build_rmat_path(cfg, rank, world, dev, optimizer=args.optimizer, lookup_mode=mode,
+                                        mover=mover, touch_lru=not args.no_lru, exchange=args.exchange)
+        rng = synth.rng_for(5, rank, 1)
+        host_batches = [torch.from_numpy(synth.rmat_frontier(cfg, rng)).pin_memory() for _ in range(4)]
+    else:
+        cfg = synth.CONFIG2 if args.scale == 1.0 else synth.scaled(synth.CONFIG2, args.scale, "config2_scaled")
+        path = pipeline.build_path(cfg, rank, world, dev, optimizer=args.optimizer, lookup_mode=mode, mover=mover,
+                                   touch_lru=not args.no_lru, exchange=args.exchange)
+        sampler = synth.ZipfSampler(cfg.table_rows, cfg.zipf_s)
+        rng = synth.rng_for(2, rank, 1)
+        host_batches = [torch.from_numpy(sampler.ids(rng, cfg.batch)).pin_memory() for _ in range(4)]
     dev_batches = [b.to(dev) for b in host_batches]
     gen = torch.Generator(device=dev)
     gen.manual_seed(2000 + rank)
@@ -424,7 +436,7 @@ def run_ours(args) -> None:
         row_bytes = cfg.dim * 4
         # dram__bytes_read.sum + dram__bytes_write.sum of one lookup_fetch launch at full size
         # (one-pass ncu capture, profiles/lookup_fetch512_kernel_config2.md); only for that workload
-        traffic = 1.136e9 if (args.scale == 1.0 and args.lookup == "setassoc" and cfg.dim == 128) else None
+        traffic = 1.136e9 if (not c5 and args.scale == 1.0 and args.lookup == "setassoc" and cfg.dim == 128) else None
         lf_bytes = cfg.batch * (8 + 8 + 1) + 2 * cfg.batch * row_bytes
         achieved = lf_bytes / (st_ms["lookup_fetch"] * 1e-3) / 1e9
         seg_bytes = cfg.batch * (8 + row_bytes) + num_unique * (8 + 8 + row_bytes)
@@ -433,15 +445,21 @@ def run_ours(args) -> None:
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": total_ms / K,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD if args.scale == 1.0 else f"config2 scaled by {args.scale:g}",
+            "config": {"workload": (f"config5: R-MAT(0.57,0.19,0.19) 2^{cfg.bits} ({cfg.num_nodes} nodes), "
+                                    f"{cfg.seeds} seeds x fanout {list(cfg.fanout)} per GPU, dim {cfg.dim} fp32") if c5
+                       else (WORKLOAD if args.scale == 1.0 else f"config2 scaled by {args.scale:g}"),
                        "table_rows": cfg.table_rows, "dim": cfg.dim, "cache_entries": cfg.cache_entries,
-                       "batch_per_gpu": cfg.batch, "zipf_s": cfg.zipf_s, "flush_every": cfg.flush_every,
+                       "batch_per_gpu": cfg.batch, "zipf_s": None if c5 else cfg.zipf_s,
+                       "flush_every": cfg.flush_every,
                        "lookup": args.lookup, "mover": args.mover, "lru_ageing": not args.no_lru,
                        "cuda_graph": use_graph,
-                       "optimizer": "SparseAdam fp32", "exchange": "local" if world == 1 else (
+                       "optimizer": "SparseAdam fp32" if args.optimizer == "adam" else "SparseAdagrad fp32",
+                       "exchange": "local" if world == 1 else (
                            "fused pack+push over peer memory (hot rows), nccl all_to_all (flush)"
                            if args.exchange == "push" else "nccl all_to_all"),
-                       "l2": "inputs larger than L2: 1.0 GB of rows read and written per step, 4 id batches rotate",
+                       "l2": ("145 MB of rows read and written per step (just above L2), 4 frontier batches rotate"
+                              if c5 else
+                              "inputs larger than L2: 1.0 GB of rows read and written per step, 4 id batches rotate"),
                        "stream": stats, "found_fraction": found_frac, "unique_per_batch": num_unique,
                        "hot_cold_unique": split_counts[1:]},
             "roofline": {"bound": "hbm", "kernel": "lookup_fetch (fused cache lookup + cached fetch)",
@@ -457,7 +475,7 @@ def run_ours(args) -> None:
         }
         if e2e:
             line["e2e"] = e2e
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not c5:
             r = cpu_reference_run(4, 1, CPU_SAMPLE_SCALE)
             line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line))

@@ -5,7 +5,7 @@
 Row movers (LSU vs bulk-copy path), the two lookup algorithms, the fused lookup+fetch on a
 Zipf(1.2) stream (91 % duplicates, reads mostly served by L2) and on uniform ids (no reuse),
 local aggregation, and the two LRU ageing forms.  CUDA events, 20 repetitions after a warm-up
-call; algorithmic bytes as defined in include/hades_b200.h and DESIGN.md.
+call; algorithmic bytes as defined in include/hades_b200.h.
 """
 from __future__ import annotations
 

@@ -177,6 +177,67 @@ class EmbeddingPath:
         self._graphs, self._g_ids, self._g_grads, self._g_out, self._g_next = graphs, ids_buf, grads, out_rows, 0
 
 
+def _warm_collectives(world: int, device, group) -> None:
+    """NCCL sets up its send/receive connections on first use (about a second); do it at
+    set-up, not inside the first flush."""
+    if world > 1:
+        import torch.distributed as dist
+
+        t = torch.zeros(world, dtype=torch.int64, device=device)
+        dist.all_to_all_single(torch.empty_like(t), t, group=group)
+        dist.all_reduce(t, group=group)
+        torch.cuda.synchronize()
+
+
+def _peer_exchange(rank, world, cap, dim, device, group):
+    """The peer-memory exchange, or None when it cannot be set up on every rank."""
+    import torch.distributed as dist
+
+    from .exchange import PeerExchange
+
+    try:
+        px = PeerExchange(rank, world, cap, dim, torch.float32, device, group)
+        ok = 1
+    except Exception as e:  # noqa: BLE001  (e.g. CUDA IPC not permitted between these processes)
+        import warnings
+
+        warnings.warn(f"peer-memory exchange unavailable ({e}); using the NCCL all-to-all")
+        px, ok = None, 0
+    agree = torch.tensor([ok], dtype=torch.int32, device=device)  # every rank must use the same exchange
+    dist.all_reduce(agree, op=dist.ReduceOp.MIN, group=group)
+    return px if int(agree.item()) == 1 else None
+
+
+def assemble_path(name: str, table: torch.Tensor, class_table: torch.Tensor, cache_ids: torch.Tensor,
+                  hot_per_owner_max: int, rank: int, world: int, device, optimizer: str, flush_every: int,
+                  lookup_mode: int, mover: int, touch_lru: bool, group, exchange: str,
+                  cache_entries: int, table_dtype=torch.float32, table_sigma: float = 0.01,
+                  generator=None) -> EmbeddingPath:
+    """Cold cache filled with `cache_ids` (rows from `table`), optimiser shard, exchange."""
+    rows_total, dim = table.shape
+    cold = ColdCache(f"{name}_r{rank}", cache_entries, dim, threshold=None, cnt_threshold=16,
+                     default_threshold=0, num_clients=world, lookup_mode=lookup_mode, device=device)
+    rows = torch.empty((cache_ids.numel(), dim), dtype=torch.float32, device=device)
+    E.cudaFetch2(table, cache_ids, rows)
+    cold.insert(cache_ids, rows)
+    del rows
+    shard = ShardedEmbedding(rows_total, dim, rank, world, dtype=table_dtype, device=device)
+    if world == 1 and table_dtype == torch.float32:
+        shard.weight = table  # one GPU: the backing table is the owner shard
+    else:
+        shard.weight.normal_(0.0, table_sigma, generator=generator)
+    opt = SparseAdam(shard, lr=0.01) if optimizer == "adam" else SparseAdagrad(shard, lr=0.01)
+    id_bits = max(int(rows_total).bit_length() + 1, 8)
+    _warm_collectives(world, device, group)
+    px = None
+    if world > 1 and exchange == "push":
+        px = _peer_exchange(rank, world, hot_per_owner_max, dim, device, group)
+    path = EmbeddingPath(table, class_table, cold, opt, rank, world, flush_every, id_bits,
+                         lookup_mode, mover, touch_lru, group, px)
+    path.cache_fill_ids = cache_ids  # what the cold cache was filled with, in insertion order
+    return path
+
+
 def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str = "adam",
                hot_fraction: float = 0.01, lookup_mode: int = E.LOOKUP_SETASSOC,
                mover: int = E.MOVER_AUTO, touch_lru: bool = True, table_dtype=torch.float32,
@@ -194,51 +255,55 @@ def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str =
     table = torch.empty((cfg.table_rows, cfg.dim), dtype=torch.float32, device=device)
     table.normal_(0.0, cfg.table_sigma, generator=gen)
     n_hot = max(int(cfg.table_rows * hot_fraction), 1)
+    hot_ranked = synth.rank_to_id(np.arange(n_hot, dtype=np.int64), cfg.table_rows)
     cls = np.full(cfg.table_rows, COLD, dtype=np.int8)
-    cls[synth.rank_to_id(np.arange(n_hot, dtype=np.int64), cfg.table_rows)] = HOT
+    cls[hot_ranked] = HOT
     class_table = torch.from_numpy(cls).to(device)
-    cold = ColdCache(f"{cfg.name}_r{rank}", cfg.cache_entries, cfg.dim, threshold=None, cnt_threshold=16,
-                     default_threshold=0, num_clients=world, lookup_mode=lookup_mode, device=device)
-    hot = torch.from_numpy(synth.hot_ids(cfg.table_rows, cfg.cache_entries)).to(device)
-    rows = torch.empty((hot.numel(), cfg.dim), dtype=torch.float32, device=device)
-    E.cudaFetch2(table, hot, rows)
-    cold.insert(hot, rows)
-    del rows
-    shard = ShardedEmbedding(cfg.table_rows, cfg.dim, rank, world, dtype=table_dtype, device=device)
-    if world == 1 and table_dtype == torch.float32:
-        shard.weight = table  # one GPU: the backing table is the owner shard
-    else:
-        shard.weight.normal_(0.0, cfg.table_sigma, generator=gen)
-    opt = SparseAdam(shard, lr=0.01) if optimizer == "adam" else SparseAdagrad(shard, lr=0.01)
-    id_bits = max(int(cfg.table_rows).bit_length() + 1, 8)
-    px = None
-    if world > 1:
-        # NCCL sets up its send/receive connections on first use (about a second); do it now,
-        # not inside the first flush
-        import torch.distributed as dist
+    cache_ids = torch.from_numpy(synth.hot_ids(cfg.table_rows, cfg.cache_entries)).to(device)
+    # a rank can receive from one source at most the hot ids it owns
+    cap = int(np.bincount(hot_ranked % world, minlength=world).max())
+    return assemble_path(cfg.name, table, class_table, cache_ids, cap, rank, world, device, optimizer,
+                         cfg.flush_every, lookup_mode, mover, touch_lru, group, exchange,
+                         cfg.cache_entries, table_dtype, cfg.table_sigma, gen)
 
-        t = torch.zeros(world, dtype=torch.int64, device=device)
-        dist.all_to_all_single(torch.empty_like(t), t, group=group)
-        dist.all_reduce(t, group=group)
-        torch.cuda.synchronize()
-    if world > 1 and exchange == "push":
-        from .exchange import PeerExchange
 
-        # a rank can receive from one source at most the hot ids it owns
-        hot_ranked = synth.rank_to_id(np.arange(n_hot, dtype=np.int64), cfg.table_rows)
-        cap = int(np.bincount(hot_ranked % world, minlength=world).max())
-        try:
-            px = PeerExchange(rank, world, cap, cfg.dim, torch.float32, device, group)
-            ok = 1
-        except Exception as e:  # noqa: BLE001  (e.g. CUDA IPC not permitted between these processes)
-            import warnings
-
-            warnings.warn(f"peer-memory exchange unavailable ({e}); using the NCCL all-to-all")
-            px, ok = None, 0
-        # every rank must use the same exchange
-        agree = torch.tensor([ok], dtype=torch.int32, device=device)
-        dist.all_reduce(agree, op=dist.ReduceOp.MIN, group=group)
-        if int(agree.item()) == 0:
-            px = None
-    return EmbeddingPath(table, class_table, cold, opt, rank, world, cfg.flush_every, id_bits,
-                         lookup_mode, mover, touch_lru, group, px)
+def build_rmat_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str = "adam",
+                    lookup_mode: int = E.LOOKUP_SETASSOC, mover: int = E.MOVER_AUTO,
+                    touch_lru: bool = True, group=None, exchange: str = "push") -> EmbeddingPath:
+    """State of one trainer for the sampled-GraphSAGE configuration (``synth.RmatConfig``).
+    Under R-MAT a vertex is the more popular the fewer one-bits its id has, so the HOT class
+    is ``popcount(id) <= cfg.hot_popcount`` and the cold cache starts with the most popular
+    cold vertices (popcount hot_popcount+1, +2, ... in id order)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    n, dim = cfg.num_nodes, cfg.dim
+    need = n * dim * 4 * (1 if world > 1 else 0) + (n // world + 1) * dim * 4 * (3 if optimizer == "adam" else 2)
+    need += 2 * (cfg.cache_entries + 8) * dim * 4 + n * 2
+    total = torch.cuda.get_device_properties(device).total_memory
+    if need > 0.9 * total:
+        raise RuntimeError(f"configuration {cfg.name} needs about {need / 2**30:.0f} GiB per GPU with "
+                           f"{world} rank(s) and optimizer={optimizer}; this GPU has {total / 2**30:.0f} GiB")
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1000 * cfg.config + rank)
+    table = torch.empty((n, dim), dtype=torch.float32, device=device)
+    table.normal_(0.0, cfg.table_sigma, generator=gen)
+    ids = torch.arange(n, dtype=torch.int32, device=device)
+    x = ids - ((ids >> 1) & 0x55555555)                      # popcount of a 32-bit word
+    x = (x & 0x33333333) + ((x >> 2) & 0x33333333)
+    x = (x + (x >> 4)) & 0x0F0F0F0F
+    pc = ((x * 0x01010101) >> 24).to(torch.int8)
+    del ids, x
+    class_table = torch.where(pc <= cfg.hot_popcount, torch.tensor(HOT, dtype=torch.int8, device=device),
+                              torch.tensor(COLD, dtype=torch.int8, device=device))
+    picked, have, k = [], 0, cfg.hot_popcount + 1
+    while have < cfg.cache_entries and k <= cfg.bits:
+        level = torch.nonzero(pc == k).flatten()[: cfg.cache_entries - have]
+        picked.append(level)
+        have += level.numel()
+        k += 1
+    cache_ids = torch.cat(picked).to(torch.int64)
+    hot = torch.nonzero(pc <= cfg.hot_popcount).flatten()
+    cap = int(torch.bincount(hot % world, minlength=world).max().item())
+    del pc, hot
+    return assemble_path(cfg.name, table, class_table, cache_ids, cap, rank, world, device, optimizer,
+                         cfg.flush_every, lookup_mode, mover, touch_lru, group, exchange,
+                         cfg.cache_entries, torch.float32, cfg.table_sigma, gen)

@@ -118,3 +118,83 @@ def stream_stats(ids: np.ndarray) -> dict:
     assumption)."""
     u = np.unique(ids).size
     return {"n": int(ids.size), "unique": int(u), "duplicate_fraction": float(1.0 - u / max(ids.size, 1))}
+
+
+# ---------------------------------------------------------------------------------------
+# configuration 5: sampled 2-layer GraphSAGE frontier on a synthetic R-MAT graph
+# ---------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class RmatConfig:
+    """R-MAT(a, b, c, d) over 2**bits >= num_nodes vertices; the edge list is never
+    materialised: a neighbour of u is drawn bit by bit from the conditional quadrant
+    probabilities given u's bits (source bit 0: P(dest bit 0) = a/(a+b); source bit 1:
+    c/(c+d)), redrawn while it falls outside [0, num_nodes)."""
+    name: str = "c5_graphsage_rmat"
+    config: int = 5
+    num_nodes: int = 100_000_000
+    bits: int = 27
+    a: float = 0.57
+    b: float = 0.19
+    c: float = 0.19
+    seeds: int = 1024
+    fanout: tuple = (25, 10)
+    dim: int = 128
+    cache_entries: int = 4_000_000
+    hot_popcount: int = 7       # ids with at most this many one-bits are "hot" (about 1 % of the ids)
+    table_sigma: float = 0.01
+    grad_sigma: float = 1e-3
+    flush_every: int = 8
+
+    @property
+    def table_rows(self) -> int:
+        return self.num_nodes
+
+    @property
+    def batch(self) -> int:
+        n, total = self.seeds, self.seeds
+        for f in self.fanout:
+            n *= f
+            total += n
+        return total
+
+
+CONFIG5 = RmatConfig()
+
+
+def scaled_rmat(cfg: RmatConfig, bits: int, seeds: int | None = None, name: str | None = None) -> RmatConfig:
+    """The same sampler on a smaller graph (tests, captures): 2**bits vertices, 3/4 of them used."""
+    return RmatConfig(name or f"{cfg.name}_b{bits}", cfg.config, (3 << bits) // 4, bits, cfg.a, cfg.b, cfg.c,
+                      seeds or cfg.seeds, cfg.fanout, cfg.dim, max((3 << bits) // 100, 64),
+                      max(bits // 4, 1), cfg.table_sigma, cfg.grad_sigma, cfg.flush_every)
+
+
+def rmat_neighbors(cfg: RmatConfig, src: np.ndarray, fanout: int, rng: np.random.Generator) -> np.ndarray:
+    """fanout sampled neighbours of every vertex in src, shape [len(src) * fanout]."""
+    u = np.repeat(np.asarray(src, dtype=np.int64), fanout)
+    d = 1.0 - cfg.a - cfg.b - cfg.c
+    p0_s0 = cfg.a / (cfg.a + cfg.b)
+    p0_s1 = cfg.c / (cfg.c + d)
+    out = np.empty_like(u)
+    todo = np.arange(u.size)
+    while todo.size:
+        v = np.zeros(todo.size, dtype=np.int64)
+        uu = u[todo]
+        for level in range(cfg.bits - 1, -1, -1):
+            sbit = (uu >> level) & 1
+            p0 = np.where(sbit == 0, p0_s0, p0_s1)
+            v |= (rng.random(todo.size) >= p0).astype(np.int64) << level
+        ok = v < cfg.num_nodes
+        out[todo[ok]] = v[ok]
+        todo = todo[~ok]
+    return out
+
+
+def rmat_frontier(cfg: RmatConfig, rng: np.random.Generator) -> np.ndarray:
+    """All vertices whose embeddings one step fetches: the seeds and their sampled 1-hop and
+    2-hop neighbours, duplicates kept (the embedding layer de-duplicates gradients, not ids)."""
+    layer = rng.integers(0, cfg.num_nodes, cfg.seeds, dtype=np.int64)
+    parts = [layer]
+    for f in cfg.fanout:
+        layer = rmat_neighbors(cfg, layer, f, rng)
+        parts.append(layer)
+    return np.concatenate(parts)

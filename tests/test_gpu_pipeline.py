@@ -113,3 +113,43 @@ def test_graph_replay_equals_eager(cuda_lib):
     assert torch.equal(paths[0].cold.remote.grad, paths[1].cold.remote.grad)
     for a, b in zip(paths[0].cold.index.export_state(), paths[1].cold.index.export_state()):
         assert torch.equal(a, b)
+
+
+def test_rmat_frontier_path_matches_oracle(cuda_lib, oracle_mod):
+    """Configuration-5 shapes scaled down: frontier ids of a sampled 2-hop expansion on a small
+    R-MAT graph, hot class by popcount, through the same step as above."""
+    from hades_b200 import pipeline, synth
+
+    cfg = synth.scaled_rmat(synth.CONFIG5, 16, seeds=64)
+    cfg = synth.RmatConfig(**{**cfg.__dict__, "dim": 32, "flush_every": 2})
+    path = pipeline.build_rmat_path(cfg)
+    table = path.table.cpu().numpy().copy()
+    cls = path.class_table.cpu().numpy()
+    ids_all = np.arange(cfg.num_nodes)
+    pop = np.array([bin(int(i)).count("1") for i in ids_all])
+    assert np.array_equal(cls == 1, pop <= cfg.hot_popcount)
+    fill = path.cache_fill_ids.cpu().numpy()
+    assert (pop[fill] > cfg.hot_popcount).all() and fill.size == min(cfg.cache_entries, (pop > cfg.hot_popcount).sum())
+    ox = oracle_mod.OracleIndex(cfg.cache_entries)
+    slots = ox.get_capacity()
+    staging = oracle_mod.OracleStaging(slots, cfg.dim, cnt_threshold=16)
+    cache = np.zeros((slots, cfg.dim), np.float32)
+    staging.insert(ox, fill, table[fill], cache)
+    o = dict(mod=oracle_mod, index=ox, cache=cache, table=table, staging=staging, dim=cfg.dim, cls=cls,
+             step=np.zeros(cfg.table_rows, np.float32), mem=np.zeros((cfg.table_rows, cfg.dim), np.float32),
+             power=np.zeros((cfg.table_rows, cfg.dim), np.float32))
+    rng = synth.rng_for(5, 0, 1)
+    for it in range(1, 5):
+        ids = synth.rmat_frontier(cfg, rng)
+        assert ids.size == cfg.batch
+        grads = synth.normal_rows(rng, ids.size, cfg.dim, cfg.grad_sigma)
+        rows, locs, found, st = path.step(torch.from_numpy(ids).cuda(), torch.from_numpy(grads).cuda())
+        wout, wlocs, whit, wflushed = _oracle_step(o, ids, grads, it, cfg.flush_every)
+        assert np.array_equal(locs.cpu().numpy(), wlocs) and np.array_equal(found.cpu().numpy(), whit), it
+        assert st.flushed == wflushed, it
+        np.testing.assert_allclose(rows.cpu().numpy(), wout, rtol=1e-5, atol=1e-9)
+        assert np.array_equal(path.opt.state_step.cpu().numpy(), o["step"]), it
+        np.testing.assert_allclose(path.table.cpu().numpy(), o["table"], rtol=1e-4, atol=1e-6)
+        gi, gl = path.cold.index.export_state()
+        oi, ol = ox.export()
+        assert np.array_equal(gi.cpu().numpy(), oi) and np.array_equal(gl.cpu().numpy(), ol), it
