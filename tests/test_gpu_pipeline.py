@@ -147,7 +147,9 @@ def test_rmat_frontier_path_matches_oracle(cuda_lib, oracle_mod):
         wout, wlocs, whit, wflushed = _oracle_step(o, ids, grads, it, cfg.flush_every)
         assert np.array_equal(locs.cpu().numpy(), wlocs) and np.array_equal(found.cpu().numpy(), whit), it
         assert st.flushed == wflushed, it
-        np.testing.assert_allclose(rows.cpu().numpy(), wout, rtol=1e-5, atol=1e-9)
+        # fetched rows carry earlier Adam updates (lr = 1e-2), whose first step lr*g/(|g|+eps)
+        # amplifies the rounding of a nearly cancelling mean: bound relative to lr
+        np.testing.assert_allclose(rows.cpu().numpy(), wout, rtol=1e-4, atol=1e-6)
         assert np.array_equal(path.opt.state_step.cpu().numpy(), o["step"]), it
         np.testing.assert_allclose(path.table.cpu().numpy(), o["table"], rtol=1e-4, atol=1e-6)
         gi, gl = path.cold.index.export_state()
