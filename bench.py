@@ -387,7 +387,8 @@ def run_ours(args) -> None:
     for k in range(W):
         step_resident(k)
     launches_per_step = (_lib.launch_count() - launches_eager0) / W
-    use_graph = not args.no_graph and world == 1  # the multi-GPU step holds a collective: eager
+    # N > 1: graphs around the exchange, the push and its fence stay eager (see EmbeddingPath.capture)
+    use_graph = not args.no_graph and (world == 1 or path.px is not None)
     if use_graph:
         torch.cuda.synchronize()
         path.capture(ids_stage, grads, out_rows)

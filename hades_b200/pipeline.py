@@ -85,9 +85,9 @@ class EmbeddingPath:
         if self.flush_every > 0 and self.step_no % self.flush_every == 0:
             st.flushed = self.flush()
 
-    def _backward_core(self, ids, grads, locs) -> StepStats:
-        """Everything of the backward path that runs every step, with no host read (so that it
-        can be captured in a CUDA graph)."""
+    def _backward_local(self, ids, grads, locs):
+        """Backward up to the exchange: aggregation, LRU ageing, hot/cold split, cold
+        accumulate.  No host read and no collective.  Returns (stats, hot ids, rows, cnt)."""
         st = StepStats()
         # hot-node local aggregation (only_unique_grads, sparse_optim.py:132-139)
         uniq, sums, counts, num, runs = E.cudaUniqueSegSum(ids, grads, id_bits=self.id_bits, sync=False,
@@ -105,16 +105,26 @@ class EmbeddingPath:
         # cold rows wait in the staging table
         self.cold.accumulate_remote(cold_ids, cold_rows, n_dev=split_counts[COLD:COLD + 1],
                                     touch_lru=self.touch_lru)
+        return st, hot_ids, hot_rows, hot_cnt
+
+    def _owner_update_from_slabs(self, parity: int) -> None:
+        """Owner side after a peer-memory push: merge the senders' slabs and update."""
+        r_ids, r_rows, r_cnt, seg_counts = self.px.received(parity)
+        self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=self.id_bits,
+                        seg_counts=seg_counts, seg_cap=self.px.cap)
+
+    def _backward_core(self, ids, grads, locs) -> StepStats:
+        """Everything of the backward path that runs every step (no host read unless NCCL
+        carries the exchange)."""
+        st, hot_ids, hot_rows, hot_cnt = self._backward_local(ids, grads, locs)
+        n_hot = st.split_counts[HOT:HOT + 1]
         # hot rows go to their owners now
         if self.px is not None and self.world > 1:
-            parity = self.px.push(hot_ids, hot_rows, hot_cnt, split_counts[HOT:HOT + 1])
+            parity = self.px.push(hot_ids, hot_rows, hot_cnt, n_hot)
             self.px.fence()
-            r_ids, r_rows, r_cnt, seg_counts = self.px.received(parity)
-            self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=self.id_bits,
-                            seg_counts=seg_counts, seg_cap=self.px.cap)
+            self._owner_update_from_slabs(parity)
         else:
-            r_ids, r_rows, r_cnt, r_n, sent = self._exchange(hot_ids, hot_rows, hot_cnt,
-                                                             split_counts[HOT:HOT + 1])
+            r_ids, r_rows, r_cnt, r_n, sent = self._exchange(hot_ids, hot_rows, hot_cnt, n_hot)
             st.sent_counts = sent
             if r_n is not None:
                 r_n = r_n[:1]
@@ -148,9 +158,18 @@ class EmbeddingPath:
         if self._graphs and grads is self._g_grads and out_rows is self._g_out:
             if ids is not self._g_ids:
                 self._g_ids.copy_(ids, non_blocking=True)
-            graph, (rows, locs, found, st) = self._graphs[self._g_next]
-            self._g_next = (self._g_next + 1) % len(self._graphs)
-            graph.replay()
+            if self.world == 1:
+                graph, (rows, locs, found, st) = self._graphs[0]
+                graph.replay()
+            else:
+                # local part from the graph, the push and its fence launched eagerly (they hold
+                # the collective and the host-chosen receive area), owner update from the graph
+                # captured for that receive area
+                graph, (rows, locs, found, st, hot_ids, hot_rows, hot_cnt) = self._graphs[0]
+                graph.replay()
+                parity = self.px.push(hot_ids, hot_rows, hot_cnt, st.split_counts[HOT:HOT + 1])
+                self.px.fence()
+                self._graphs[1 + parity][0].replay()
             st.flushed = 0
             self._after_step(st)
             return rows, locs, found, st
@@ -159,21 +178,35 @@ class EmbeddingPath:
         return rows, locs, found, st
 
     def capture(self, ids_buf: torch.Tensor, grads: torch.Tensor, out_rows: torch.Tensor) -> None:
-        """Capture the per-step part of ``step`` (forward + backward without the periodic flush)
-        in a CUDA graph over the caller's buffers; later ``step(ids, grads, out_rows)`` calls
-        with the same ``grads`` and ``out_rows`` replay it (``ids`` is copied into ``ids_buf``
-        unless it is that tensor).  Call it after a few eager steps: every lazy allocation of
-        the library has to have happened.  One GPU only: with more ranks the step contains a
-        collective (the NCCL all-to-all reads sizes on the host; the peer-memory exchange is
-        ordered by an NCCL all-reduce and alternates two receive areas chosen on the host)."""
-        if self.world > 1:
-            raise RuntimeError("graph capture of the step is available on one GPU only")
+        """Capture the per-step work of ``step`` in CUDA graphs over the caller's buffers; later
+        ``step(ids, grads, out_rows)`` calls with the same ``grads`` and ``out_rows`` replay them
+        (``ids`` is copied into ``ids_buf`` unless it is that tensor).  Call it after a few eager
+        steps: every lazy allocation of the library has to have happened.
+
+        One GPU: one graph holds the whole step (the periodic flush stays eager).  Several GPUs
+        with the peer-memory exchange: one graph for everything before the exchange and one per
+        receive area for the owner update; the push and its fence are launched eagerly between
+        them, so no collective is ever captured.  Not available with the NCCL all-to-all, which
+        reads sizes on the host."""
+        if self.world > 1 and self.px is None:
+            raise RuntimeError("the NCCL all-to-all exchange reads sizes on the host and cannot be captured")
         graphs = []
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            rows, locs, found = self.forward(ids_buf, out_rows, defer_touch=True)
-            st = self._backward_core(ids_buf, grads, locs)
-        graphs.append((g, (rows, locs, found, st)))
+        if self.world == 1:
+            with torch.cuda.graph(g):
+                rows, locs, found = self.forward(ids_buf, out_rows, defer_touch=True)
+                st = self._backward_core(ids_buf, grads, locs)
+            graphs.append((g, (rows, locs, found, st)))
+        else:
+            with torch.cuda.graph(g):
+                rows, locs, found = self.forward(ids_buf, out_rows, defer_touch=True)
+                st, hot_ids, hot_rows, hot_cnt = self._backward_local(ids_buf, grads, locs)
+            graphs.append((g, (rows, locs, found, st, hot_ids, hot_rows, hot_cnt)))
+            for parity in (0, 1):
+                gp = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gp):
+                    self._owner_update_from_slabs(parity)
+                graphs.append((gp, None))
         self._graphs, self._g_ids, self._g_grads, self._g_out, self._g_next = graphs, ids_buf, grads, out_rows, 0
 
 

@@ -72,8 +72,9 @@ def _worker(rank, port, exchange):
 
     # --- the backward path on both ranks vs a simulation of both ----------------------------
     cfg = _cfg()
-    path = pipeline.build_path(cfg, rank, WORLD, hot_fraction=0.02, exchange=exchange)
-    assert (path.px is not None) == (exchange == "push")
+    path = pipeline.build_path(cfg, rank, WORLD, hot_fraction=0.02,
+                               exchange="push" if exchange.startswith("push") else "nccl")
+    assert (path.px is not None) == exchange.startswith("push")
     cls = path.class_table.cpu().numpy()
     shard_rows = path.opt.emb.rows
     w = path.opt.emb.weight.cpu().numpy().copy()
@@ -88,9 +89,21 @@ def _worker(rank, port, exchange):
         stg = om.OracleStaging(ox.get_capacity(), cfg.dim, cnt_threshold=16)
         ox.add(hot_ids)
         sim.append((ox, stg))
+    use_graph = exchange == "push_graph"
+    if use_graph:
+        g_ids = torch.empty(cfg.batch, dtype=torch.int64, device="cuda")
+        g_grads = torch.empty((cfg.batch, cfg.dim), device="cuda")
+        g_out = torch.empty((cfg.batch, cfg.dim), device="cuda")
     for it in range(1, 5):
         ids, grads = _batch(cfg, rank, it)
-        st = path.backward(torch.from_numpy(ids).cuda(), torch.from_numpy(grads).cuda())
+        if use_graph:
+            if it == 2:  # one eager step first, then the captured graphs
+                torch.cuda.synchronize()
+                path.capture(g_ids, g_grads, g_out)
+            g_grads.copy_(torch.from_numpy(grads))
+            st = path.step(torch.from_numpy(ids).cuda(), g_grads, g_out)[3]
+        else:
+            st = path.backward(torch.from_numpy(ids).cuda(), torch.from_numpy(grads).cuda())
         inbox_hot, inbox_flush = [], []
         for r in range(WORLD):
             i_r, g_r = _batch(cfg, r, it)
@@ -124,10 +137,11 @@ def _worker(rank, port, exchange):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["nccl", "push"])
+@pytest.mark.parametrize("exchange", ["nccl", "push", "push_graph"])
 def test_two_ranks(exchange):
     """exchange = "nccl": ragged all_to_all_single; "push": the fused pack+push kernel over
-    peer memory (plain stores, NVLS off)."""
+    peer memory (plain stores, NVLS off); "push_graph": the same with the local part and the
+    owner update replayed from CUDA graphs."""
     if not torch.cuda.is_available() or torch.cuda.device_count() < WORLD:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp

@@ -63,7 +63,7 @@ def test_pipeline_matches_oracle(cuda_lib, oracle_mod, mode, mover):
         wout, wlocs, whit, wflushed = _oracle_step(o, ids, grads, it, cfg.flush_every)
         assert np.array_equal(locs.cpu().numpy(), wlocs), it
         assert np.array_equal(found.cpu().numpy(), whit), it
-        np.testing.assert_allclose(rows.cpu().numpy(), wout, rtol=1e-5, atol=1e-9)
+        np.testing.assert_allclose(rows.cpu().numpy(), wout, rtol=1e-4, atol=1e-6)  # rows carry Adam updates
         assert st.flushed == wflushed, it
         total_flushed += wflushed
         gi, gl = path.cold.index.export_state()
