@@ -595,6 +595,47 @@ def cudaGradSplit3(ids, rows, hot_mask, local_mask):
     return out_ids, out_rows, counts
 
 
+def cudaUniqueSegSumSplit(ids, grads, table, keep=(True, True, True), caps=(None, None, None),
+                          id_bits: int = 64, want_runs: bool = False):
+    """only_unique_grads fused with the hot/cold selects that follow it: the per-id sums,
+    ids and counts of class table[id] go straight into that class's buffers.  Returns
+    ([(ids, rows, cnt) | None] * 3, class_counts[3] on the device, num_unique on the device
+    [, runs]).  caps[c]: a proven upper bound on the unique ids of class c (allocation)."""
+    _check(ids.is_cuda and ids.dtype == torch.int64, "ids is a CUDA int64 tensor")
+    _check(grads.dtype == torch.float32 and grads.dim() == 2, "grads is a 2-D fp32 tensor")
+    _check(table.dtype == torch.int8, "table.dtype == int8")
+    n, dim = ids.numel(), grads.size(1)
+    dev = ids.device
+    outs = []
+    for c in range(3):
+        if keep[c]:
+            m = n if caps[c] is None else min(n, int(caps[c]))
+            outs.append((torch.empty(m, dtype=torch.int64, device=dev),
+                         torch.empty((m, dim), dtype=torch.float32, device=dev),
+                         torch.empty(m, dtype=torch.int64, device=dev)))
+        else:
+            outs.append(None)
+    class_counts = torch.empty(3, dtype=torch.int64, device=dev)
+    num = torch.zeros(1, dtype=torch.int64, device=dev)
+    desc = _lib.ClassSplitDesc()
+    desc.table = table.data_ptr()
+    for c in range(3):
+        desc.out_ids[c] = outs[c][0].data_ptr() if outs[c] else None
+        desc.out_rows[c] = outs[c][1].data_ptr() if outs[c] else None
+        desc.out_cnt[c] = outs[c][2].data_ptr() if outs[c] else None
+    desc.class_counts = class_counts.data_ptr()
+    lib = _lib.load()
+    ws = _lib.workspace(lib.hb_unique_segsum_workspace_bytes(n, dim))
+    runs = _lib.RunsDesc() if want_runs else None
+    _lib.check(lib.hb_unique_segsum_f32(ids.contiguous().data_ptr(), grads.contiguous().data_ptr(), None, n,
+                                        None, None, 0, dim, int(id_bits), 0, None, None, None,
+                                        num.data_ptr(), C.byref(runs) if want_runs else None,
+                                        C.byref(desc), ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
+    if want_runs:
+        return outs, class_counts, num, runs
+    return outs, class_counts, num
+
+
 def cudaUniqueSegSum(ids, grads, cnt=None, mean: bool = False, id_bits: int = 64, sync: bool = True,
                      n_dev: torch.Tensor | None = None, want_runs: bool = False,
                      seg_counts: torch.Tensor | None = None, seg_cap: int = 0):
@@ -618,7 +659,7 @@ def cudaUniqueSegSum(ids, grads, cnt=None, mean: bool = False, id_bits: int = 64
                                         _lib.ptr(cnt), n, _lib.ptr(n_dev), _lib.ptr(seg_counts),
                                         int(seg_cap), dim, int(id_bits), int(mean),
                                         uniq.data_ptr(), sums.data_ptr(), counts.data_ptr(),
-                                        num.data_ptr(), C.byref(runs) if want_runs else None,
+                                        num.data_ptr(), C.byref(runs) if want_runs else None, None,
                                         ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
     if want_runs:
         # the runs point into the shared workspace: use them before the next library call

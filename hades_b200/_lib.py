@@ -69,7 +69,7 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_table_split3": (_int, [_p, _p, _p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "hb_grad_split3": (_int, [_p, _p, _p, _p, _i64, _i64, _p, _p, _p, _p, _sz, _p]),
     "hb_unique_segsum_workspace_bytes": (_sz, [_i64, _i64]),
-    "hb_unique_segsum_f32": (_int, [_p, _p, _p, _i64, _p, _p, _i64, _i64, _int, _int, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "hb_unique_segsum_f32": (_int, [_p, _p, _p, _i64, _p, _p, _i64, _i64, _int, _int, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "hb_staging_accumulate_cached": (_int, [_p, _p, _p, _p, _i64, _p, _p, C.c_int32, _int, _p, _p, _p]),
     "hb_staging_accumulate_direct": (_int, [_p, _p, _p, _i64, _p, _i64, _i64, _p]),
     "hb_staging_flush_workspace_bytes": (_sz, [_i64, _int]),
@@ -94,6 +94,12 @@ PROTOTYPES: dict[str, tuple] = {
 class RunsDesc(C.Structure):
     """hb_runs_t"""
     _fields_ = [("perm", _p), ("run_start", _p), ("num_runs", _p), ("n", _i64)]
+
+
+class ClassSplitDesc(C.Structure):
+    """hb_class_split_t"""
+    _fields_ = [("table", _p), ("out_ids", _p * 3), ("out_rows", _p * 3), ("out_cnt", _p * 3),
+                ("class_counts", _p)]
 
 
 class StagingDesc(C.Structure):

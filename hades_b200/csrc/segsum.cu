@@ -45,7 +45,12 @@ struct SegArgs {
   int chunk;                  // R
   int64_t num_chunks;
   int mean;                   // divide by the count
-  float* sums;                // [U][dim]
+  float* sums;                // [U][dim] (null when the rows go to class buffers)
+  // optional split of the output by a per-id class (hot / cold): run u goes to
+  // row dpos[u] of class_rows[dclass[u]] (a null buffer drops the class)
+  const int8_t* dclass;       // [U], null = no split
+  const int32_t* dpos;        // [U]
+  float* class_rows[3];
   unsigned long long* counts; // [U], zeroed before the main pass
   float* head_part;           // [num_chunks][cols]
   float* tail_part;           // [num_chunks][cols]
@@ -75,6 +80,14 @@ __device__ __forceinline__ int64_t run_of(const int64_t* run_start, int64_t U, i
     if (__ldg(run_start + mid) <= pos) lo = mid + 1; else hi = mid;
   }
   return lo - 1;
+}
+
+// where the finished row of run u goes (null = nowhere)
+__device__ __forceinline__ float* out_row(const SegArgs& a, int64_t u) {
+  if (!a.dclass) return a.sums + u * a.dim + a.col0;
+  const int c = a.dclass[u];
+  float* base = (c >= 0 && c < 3) ? a.class_rows[c] : nullptr;
+  return base ? base + (int64_t)a.dpos[u] * a.dim + a.col0 : nullptr;
 }
 
 __device__ __forceinline__ float denominator(const SegArgs& a, unsigned long long c) {
@@ -120,7 +133,7 @@ __global__ void __launch_bounds__(kBlock, 3) segsum_main_kernel(SegArgs a) {
     // write the open run: complete -> output row; crossing -> partial row
     float* dst;
     bool complete = !first_partial && !tail;
-    if (complete) dst = a.sums + u * a.dim + a.col0;
+    if (complete) dst = out_row(a, u);
     else if (first_partial) dst = a.head_part + c * a.cols;
     else dst = a.tail_part + c * a.cols;
     if (complete && a.mean) {
@@ -128,10 +141,12 @@ __global__ void __launch_bounds__(kBlock, 3) segsum_main_kernel(SegArgs a) {
 #pragma unroll
       for (int v = 0; v < VPL; ++v) vdiv(acc[v], d);
     }
+    if (dst) {
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-      const int k = sub + v * G;
-      if (k < vpr) reinterpret_cast<V*>(dst)[k] = acc[v];
+      for (int v = 0; v < VPL; ++v) {
+        const int k = sub + v * G;
+        if (k < vpr) reinterpret_cast<V*>(dst)[k] = acc[v];
+      }
     }
     if (sub == 0 && a.col0 == 0 && cacc) atomicAdd(a.counts + u, cacc);
   };
@@ -240,10 +255,13 @@ __global__ void __launch_bounds__(kBlock) segsum_fix_short_kernel(SegArgs a) {
 #pragma unroll
       for (int v = 0; v < VPL; ++v) vdiv(acc[v], d);
     }
+    float* dst = out_row(a, u);
+    if (dst) {
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-      const int k = sub + v * G;
-      if (k < vpr) reinterpret_cast<V*>(a.sums + u * a.dim + a.col0)[k] = acc[v];
+      for (int v = 0; v < VPL; ++v) {
+        const int k = sub + v * G;
+        if (k < vpr) reinterpret_cast<V*>(dst)[k] = acc[v];
+      }
     }
   }
 }
@@ -310,7 +328,8 @@ __global__ void __launch_bounds__(kLongBlock) segsum_fix_long_b_kernel(SegArgs a
       float acc = a.tail_part[c * cols + col];
       for (int sl = 0; sl < kSlices; ++sl) acc += a.slice_part[(e * kSlices + sl) * cols + col];
       if (a.mean) acc /= denominator(a, a.counts[u]);
-      a.sums[u * a.dim + a.col0 + col] = acc;
+      float* dst = out_row(a, u);
+      if (dst) dst[col] = acc;
     }
   }
 }
@@ -351,6 +370,42 @@ __global__ void finish_counts_kernel(const unsigned long long* __restrict__ raw,
   const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (i < n && i < *num_runs) out[i] = (int64_t)raw[i] + plus_one;
 }
+
+// with a split: counts go to the class buffers too
+__global__ void finish_counts_split_kernel(const unsigned long long* __restrict__ raw,
+                                           const int64_t* __restrict__ num_runs, int plus_one,
+                                           const int8_t* __restrict__ dclass,
+                                           const int32_t* __restrict__ dpos, int64_t* c0, int64_t* c1,
+                                           int64_t* c2, int64_t n) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= n || i >= *num_runs) return;
+  const int c = dclass[i];
+  int64_t* out = c == 0 ? c0 : (c == 1 ? c1 : (c == 2 ? c2 : nullptr));
+  if (out) out[dpos[i]] = (int64_t)raw[i] + plus_one;
+}
+
+// unique ids -> class by a per-node table, position inside the class, compacted ids
+struct ClassOfRunPolicy {
+  const int64_t* uniq;
+  const int64_t* num_runs;
+  const int8_t* table;
+  int8_t* dclass;
+  int32_t* dpos;
+  int64_t n;
+  int64_t* out_ids[3];
+  __device__ __forceinline__ int classify(int64_t u) const {
+    if (u >= *num_runs) return -1;
+    const int8_t v = __ldg(table + __ldg(uniq + u));
+    return (v >= 0 && v <= 2) ? (int)v : -1;
+  }
+  __device__ __forceinline__ void emit(int64_t u, int c, int64_t pos, int64_t, bool active) const {
+    if (u < n) {
+      dclass[u] = (int8_t)c;
+      dpos[u] = (int32_t)pos;
+    }
+    if (active && out_ids[c]) out_ids[c][pos] = uniq[u];
+  }
+};
 
 template <typename KeyT>
 struct RunHeadPolicy {
@@ -398,6 +453,11 @@ struct SegPlan {
   int64_t* run_start;
   uint8_t* head;
   int64_t* n_valid;
+  int8_t* dclass;
+  int32_t* dpos;
+  int64_t* uniq_tmp;
+  void* class_ws;
+  size_t class_ws_bytes;
   unsigned long long* raw_counts;
   float *head_part, *tail_part, *slice_part;
   int2 *short_list, *long_list;
@@ -423,6 +483,11 @@ SegPlan make_plan(void* ws, int64_t n, int64_t dim) {
   s.run_start = cv.take<int64_t>(m + 1);
   s.head = cv.take<uint8_t>(m + 1);
   s.n_valid = cv.take<int64_t>(1);
+  s.dclass = cv.take<int8_t>(m + 1);
+  s.dpos = cv.take<int32_t>(m + 1);
+  s.uniq_tmp = cv.take<int64_t>(m + 1);
+  s.class_ws_bytes = partition_workspace_bytes(m, 3, kPartItemsMax);
+  s.class_ws = cv.take<char>(s.class_ws_bytes);
   s.raw_counts = cv.take<unsigned long long>(m);
   s.chunk = choose_chunk(m);
   s.num_chunks = ceil_div(m, s.chunk);
@@ -498,10 +563,14 @@ int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* 
                          int64_t dim, int id_bits, int mean,
                          int64_t* uniq_ids, float* sums,
                          int64_t* counts, int64_t* num_unique, hb_runs_t* runs_out,
-                         void* workspace, size_t workspace_bytes, hb_stream_t stream) {
+                         const hb_class_split_t* split, void* workspace, size_t workspace_bytes,
+                         hb_stream_t stream) {
   HB_CHECK_ARG(n >= 0 && n < ((int64_t)1 << 31) && dim > 0, "hb_unique_segsum_f32: bad sizes");
   HB_CHECK_ARG(num_unique != nullptr, "hb_unique_segsum_f32: num_unique is null");
-  HB_CHECK_ARG(n == 0 || (ids && grads && uniq_ids && sums), "hb_unique_segsum_f32: null argument");
+  HB_CHECK_ARG(n == 0 || (ids && grads), "hb_unique_segsum_f32: null argument");
+  HB_CHECK_ARG(n == 0 || split || (uniq_ids && sums), "hb_unique_segsum_f32: null output");
+  HB_CHECK_ARG(!split || (split->table && split->class_counts),
+               "hb_unique_segsum_f32: a split needs the class table and class_counts");
   HB_CHECK_ARG(id_bits >= 1 && id_bits <= 64, "hb_unique_segsum_f32: id_bits must be in [1, 64]");
   HB_CHECK_ARG(!seg_counts || (seg_cap > 0 && n % seg_cap == 0),
                "hb_unique_segsum_f32: a segmented input holds whole segments of seg_cap entries");
@@ -514,9 +583,11 @@ int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* 
   }
   if (n == 0) {
     HB_CUDA(cudaMemsetAsync(num_unique, 0, sizeof(int64_t), st));
+    if (split) HB_CUDA(cudaMemsetAsync(split->class_counts, 0, 3 * sizeof(int64_t), st));
     return HB_OK;
   }
   SegPlan s = make_plan(workspace, n, dim);
+  if (!uniq_ids) uniq_ids = s.uniq_tmp;
   if (!workspace || workspace_bytes < s.total) {
     set_error("hb_unique_segsum_f32: workspace of %zu bytes needed, %zu given", s.total,
               workspace_bytes);
@@ -553,9 +624,19 @@ int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* 
   }
   count_library_launches(1 + (id_bits + 7) / 8);
   if (rc != HB_OK) return rc;
+  // 2b. optional split: class and position of every unique id
+  if (split) {
+    ClassOfRunPolicy cp{uniq_ids, num_unique, split->table, s.dclass, s.dpos, n,
+                        {split->out_ids[0], split->out_ids[1], split->out_ids[2]}};
+    rc = run_partition(cp, n, 3, s.class_ws, s.class_ws_bytes, split->class_counts, st, kPartItemsMax);
+    if (rc != HB_OK) return rc;
+  }
   // 3./4. column passes
   HB_CUDA(cudaMemsetAsync(s.raw_counts, 0, n * sizeof(unsigned long long), st));
-  const bool vec4 = (dim % 4 == 0) && (((uintptr_t)grads | (uintptr_t)sums) & 15) == 0;
+  uintptr_t align_bits = (uintptr_t)grads | (uintptr_t)sums;
+  if (split)
+    for (int c = 0; c < 3; ++c) align_bits |= (uintptr_t)split->out_rows[c];
+  const bool vec4 = (dim % 4 == 0) && (align_bits & 15) == 0;
   SegArgs a;
   a.head = s.head;
   a.perm = perm.Current();
@@ -574,6 +655,9 @@ int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* 
   a.num_chunks = s.num_chunks;
   a.mean = mean;
   a.sums = sums;
+  a.dclass = split ? s.dclass : nullptr;
+  a.dpos = s.dpos;
+  for (int c = 0; c < 3; ++c) a.class_rows[c] = split ? split->out_rows[c] : nullptr;
   a.counts = s.raw_counts;
   a.head_part = s.head_part;
   a.tail_part = s.tail_part;
@@ -592,6 +676,11 @@ int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* 
   if (counts) {
     HB_LAUNCH(finish_counts_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, s.raw_counts,
               num_unique, (cnt_in && mean) ? 1 : 0, counts, n);
+  }
+  if (split && (split->out_cnt[0] || split->out_cnt[1] || split->out_cnt[2])) {
+    HB_LAUNCH(finish_counts_split_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, s.raw_counts,
+              num_unique, (cnt_in && mean) ? 1 : 0, s.dclass, s.dpos, split->out_cnt[0],
+              split->out_cnt[1], split->out_cnt[2], n);
   }
   return HB_OK;
 }

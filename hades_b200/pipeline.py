@@ -89,16 +89,14 @@ class EmbeddingPath:
         """Backward up to the exchange: aggregation, LRU ageing, hot/cold split, cold
         accumulate.  No host read and no collective.  Returns (stats, hot ids, rows, cnt)."""
         st = StepStats()
-        # hot-node local aggregation (only_unique_grads, sparse_optim.py:132-139)
-        uniq, sums, counts, num, runs = E.cudaUniqueSegSum(ids, grads, id_bits=self.id_bits, sync=False,
-                                                           want_runs=True)
+        # hot-node local aggregation (only_unique_grads, sparse_optim.py:132-139) with the hot /
+        # cold selects (sparse_optim.py:243-259) fused into its output
+        outs, split_counts, num, runs = E.cudaUniqueSegSumSplit(
+            ids, grads, self.class_table, keep=(False, True, True), caps=(None, self.num_hot_ids, None),
+            id_bits=self.id_bits, want_runs=True)
         if locs is not None and self.touch_lru:
             self.cold.index.cuda_touch_lru_runs(locs, runs)
         st.num_unique = num
-        # hot / cold
-        outs, split_counts = E.cudaTableSplit3(uniq, sums, counts, self.class_table, n_dev=num,
-                                               keep=(False, True, True),
-                                               caps=(None, self.num_hot_ids, None))
         st.split_counts = split_counts
         hot_ids, hot_rows, hot_cnt = outs[HOT]
         cold_ids, cold_rows, _ = outs[COLD]

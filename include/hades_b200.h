@@ -304,14 +304,31 @@ typedef struct hb_runs {
   int64_t n;
 } hb_runs_t;
 
+/* Optional split of the aggregated rows by a per-node class table (class =
+ * table[id] in {0,1,2}, the classes of src/cuda/split.cu:34-44): the row, id and
+ * count of every unique id go straight to the buffers of its class, compacted
+ * from entry 0 in id order, instead of to uniq_ids / sums / counts -- the hot /
+ * cold selects of python/EmbCache/sparse_optim.py:243-259 without a second pass
+ * over the rows.  A NULL out_rows[c] / out_ids[c] / out_cnt[c] drops that part of
+ * class c.  class_counts: device int64[3]. */
+typedef struct hb_class_split {
+  const int8_t* table;
+  int64_t* out_ids[3];
+  float* out_rows[3];
+  int64_t* out_cnt[3];
+  int64_t* class_counts;
+} hb_class_split_t;
+
 size_t hb_unique_segsum_workspace_bytes(int64_t n, int64_t dim);
 int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* cnt_in,
                          int64_t n, const int64_t* n_dev, const int64_t* seg_counts,
                          int64_t seg_cap, int64_t dim, int id_bits, int mean,
                          int64_t* uniq_ids,
                          float* sums, int64_t* counts /* nullable */, int64_t* num_unique,
-                         hb_runs_t* runs_out /* nullable, host */, void* workspace,
-                         size_t workspace_bytes, hb_stream_t stream);
+                         hb_runs_t* runs_out /* nullable, host */,
+                         const hb_class_split_t* split /* nullable, host; then uniq_ids, sums,
+                         counts may be NULL */, void* workspace, size_t workspace_bytes,
+                         hb_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
 /* Cold-gradient staging table (the reference's cache-server buffers).         */

@@ -78,3 +78,33 @@ def test_empty(cuda_lib):
     u, v, c = E.cudaUniqueSegSum(torch.empty(0, dtype=torch.int64, device="cuda"),
                                  torch.empty((0, 8), device="cuda"))
     assert u.numel() == 0 and v.shape == (0, 8) and c.numel() == 0
+
+
+@pytest.mark.parametrize("n,dim", [(1, 8), (5000, 128), (200_000, 64), (60_000, 257)])
+def test_unique_segsum_with_class_split(cuda_lib, oracle_mod, n, dim):
+    """Aggregation with the hot/cold selects fused into its output: every class buffer holds
+    the ids (ascending), counts and sums that selecting from only_unique_grads' output gives;
+    a dropped class is only counted; ids whose table value is outside {0,1,2} vanish."""
+    from hades_b200 import EmbCacheLib as E
+
+    rng = np.random.default_rng(n + dim)
+    nodes = 50_000
+    table = rng.integers(0, 3, nodes).astype(np.int8)
+    table[::53] = 7
+    ids = _ids(rng, n, "uniform") % nodes
+    grad = (rng.standard_normal((n, dim)) * 1e-3).astype(np.float32)
+    u, s, c = oracle_mod.only_unique_grads(ids, grad)
+    outs, class_counts, num = E.cudaUniqueSegSumSplit(torch.from_numpy(ids).cuda(), torch.from_numpy(grad).cuda(),
+                                                      torch.from_numpy(table).cuda(), keep=(True, False, True),
+                                                      id_bits=20)
+    assert int(num.item()) == u.size
+    cc = class_counts.cpu().numpy()
+    for k in range(3):
+        sel = table[u] == k
+        assert cc[k] == sel.sum()
+        if k == 1:
+            assert outs[k] is None
+            continue
+        gi, gr, gc = (t[: cc[k]].cpu().numpy() for t in outs[k])
+        assert np.array_equal(gi, u[sel]) and np.array_equal(gc, c[sel])
+        np.testing.assert_allclose(gr, s[sel], rtol=1e-4, atol=1e-8)
