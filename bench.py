@@ -52,8 +52,9 @@ def parse():
                          "synthetic R-MAT graph (1e8 nodes, 1,024 seeds, fanout [25, 10], per GPU)")
     ap.add_argument("--optimizer", default="adam", choices=["adam", "adagrad"])
     ap.add_argument("--rmat-bits", type=int, default=0, help="c5 on a smaller graph of 2**bits vertices")
-    ap.add_argument("--exchange", default="push", choices=["push", "nccl"],
-                    help="N>1: fused pack+push over peer memory, or NCCL all_to_all_single")
+    ap.add_argument("--exchange", default="push", choices=["push", "push_nccl_fence", "nccl"],
+                    help="N>1: fused pack+push over peer memory with the device-side fence (default) or "
+                         "with an NCCL all-reduce as the fence, or NCCL all_to_all_single")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly (no CUDA graph)")
@@ -456,8 +457,9 @@ def run_ours(args) -> None:
                        "cuda_graph": use_graph,
                        "optimizer": "SparseAdam fp32" if args.optimizer == "adam" else "SparseAdagrad fp32",
                        "exchange": "local" if world == 1 else (
-                           "fused pack+push over peer memory (hot rows), nccl all_to_all (flush)"
-                           if args.exchange == "push" else "nccl all_to_all"),
+                           "nccl all_to_all" if path.px is None else
+                           f"fused pack+push over peer memory, {path.px.fence_kind} fence (hot rows); "
+                           "nccl all_to_all (flush)"),
                        "l2": ("145 MB of rows read and written per step (just above L2), 4 frontier batches rotate"
                               if c5 else
                               "inputs larger than L2: 1.0 GB of rows read and written per step, 4 id batches rotate"),
@@ -511,7 +513,8 @@ def run_exchange(args) -> None:
     sent_to_others = int((ids_np % world != rank).sum())
     bytes_out = sent_to_others * (8 + 8 + dim * 4)
     cap = int(np.bincount(ids_np % world, minlength=world).max() * 1.05) + 16
-    px = PeerExchange(rank, world, cap, dim, torch.float32, dev)
+    px = PeerExchange(rank, world, cap, dim, torch.float32, dev)                    # device-side fence
+    px_nf = PeerExchange(rank, world, cap, dim, torch.float32, dev, fence="nccl")   # all-reduce as the fence
 
     def ev():
         return torch.cuda.Event(enable_timing=True)
@@ -537,12 +540,16 @@ def run_exchange(args) -> None:
         px.push(ids, rows, cnt)
         px.fence()
 
+    def do_push_nccl_fence():
+        px_nf.push(ids, rows, cnt)
+        px_nf.fence()
+
     def do_nccl():
         swap_gradients(ids, rows, None, 1, world, dev, cnt)
 
     W, K = max(args.warmup, 3), max(args.steps, 1)
     out = {}
-    for name, fn in (("push", do_push), ("nccl", do_nccl)):
+    for name, fn in (("push", do_push), ("push_nccl_fence", do_push_nccl_fence), ("nccl", do_nccl)):
         for _ in range(W):
             fn()
         out[name] = timed(fn, K)
@@ -552,7 +559,8 @@ def run_exchange(args) -> None:
                 "steps": K, "warmup": W, "higher_is_better": True, "data": "synthetic", "dtype": "f32",
                 "config": {"workload": "config4 exchange: 1,048,576 unique ids x 64 fp32 (+8 B id, 8 B cnt) per rank",
                            "rows_per_rank": n, "bytes_leaving_each_gpu": bytes_out},
-                "push_ms": out["push"], "nccl_ms": out["nccl"], "device_status": status}
+                "push_ms": out["push"], "push_nccl_fence_ms": out["push_nccl_fence"], "nccl_ms": out["nccl"],
+                "device_status": status}
         if world > 1:
             line["value"] = bytes_out / (out["push"] * 1e-3) / 1e9
             line["nccl_value"] = bytes_out / (out["nccl"] * 1e-3) / 1e9

@@ -7,12 +7,17 @@
 //
 // Receive area of a rank (one cudaMalloc per parity, mapped by every peer):
 //   counts[world]                 rows delivered by each source
+//   flags [world]                 (parity 0 only) last exchange each source has finished pushing
 //   ids   [world][cap]            slab s = rows sent by rank s
 //   cnt   [world][cap]
 //   rows  [world][cap][row_bytes]
 // Two parities alternate so that a fast rank's next push cannot overwrite what a
 // slow rank is still reading; one barrier per exchange (the caller's, between
-// push and consume) is then enough.  No kernel here waits on another GPU.
+// push and consume) is then enough.  The barrier is either the caller's collective or
+// hb_a2a_fence: every rank stores its exchange number into every peer's flag array
+// and waits, WITH AN ITERATION LIMIT, until all peers have done the same; a rank
+// that gives up records HB_ERR_TIMEOUT and returns.  (The ranks run on different
+// GPUs, so the waiting kernels do run at the same time.)
 #include <cstring>
 
 #include "partition_core.cuh"
@@ -31,12 +36,14 @@ struct hb_a2a {
   bool opened[64];
   // device copy of the destination pointers for the push kernel
   struct Dest {
+    unsigned long long* flags[64];  // parity-0 area of every rank
     int64_t* counts[64];
     int64_t* ids[64];
     int64_t* cnt[64];
     char* rows[64];
   };
   Dest* dest_dev[2];
+  unsigned long long* epoch_dev;  // number of fences done, on the device (graph replay safe)
   int parity;  // parity of the NEXT push
 };
 
@@ -44,7 +51,8 @@ namespace hb {
 namespace {
 
 size_t off_counts() { return 0; }
-size_t off_ids(int world) { return align_up((size_t)world * sizeof(int64_t), 256); }
+size_t off_flags() { return 1024; }  // world <= 64: counts end at 512
+size_t off_ids(int) { return 2048; }
 size_t off_cnt(int world, int64_t cap) { return off_ids(world) + align_up((size_t)world * cap * 8, 256); }
 size_t off_rows(int world, int64_t cap) { return off_cnt(world, cap) + align_up((size_t)world * cap * 8, 256); }
 size_t area_size(int world, int64_t cap, int64_t row_bytes) {
@@ -90,6 +98,28 @@ __global__ void push_counts_kernel(PartitionPlan p, const hb_a2a::Dest* dest, in
   __threadfence_system();
 }
 
+// One CTA per rank.  Thread t: tell rank t that this rank has finished pushing exchange
+// number e (everything before this kernel in the stream), then wait until rank t says the
+// same.  Bounded: about a second of polling, then HB_ERR_TIMEOUT and return.
+__global__ void a2a_fence_kernel(const hb_a2a::Dest* dest, const unsigned long long* local_flags,
+                                 unsigned long long* epoch, int rank, int world, int* err) {
+  __shared__ unsigned long long e;
+  if (threadIdx.x == 0) e = ++(*epoch);
+  __syncthreads();
+  const int t = threadIdx.x;
+  if (t >= world) return;
+  __threadfence_system();  // my rows and counts are visible before my flag
+  *reinterpret_cast<volatile unsigned long long*>(dest->flags[t] + rank) = e;
+  const volatile unsigned long long* mine = local_flags + t;
+  bool ok = false;
+  for (int it = 0; it < (1 << 20); ++it) {
+    if (*mine >= e) { ok = true; break; }
+    __nanosleep(it < 64 ? 100 : 1000);
+  }
+  if (!ok) atomicExch(err, HB_ERR_TIMEOUT);
+  __threadfence_system();  // reads of the slabs stay after the flag
+}
+
 }  // namespace
 }  // namespace hb
 
@@ -113,6 +143,8 @@ int hb_a2a_create(int rank, int world, int64_t cap_rows, int64_t row_bytes, hb_a
     a->peer[p][rank] = a->local[p];
     HB_CUDA(cudaMalloc(&a->dest_dev[p], sizeof(hb_a2a::Dest)));
   }
+  HB_CUDA(cudaMalloc(&a->epoch_dev, sizeof(unsigned long long)));
+  HB_CUDA(cudaMemset(a->epoch_dev, 0, sizeof(unsigned long long)));
   *out = a;
   return HB_OK;
 }
@@ -147,6 +179,7 @@ int hb_a2a_connect(hb_a2a_t* a, const void* handles) {
     memset(&d, 0, sizeof(d));
     for (int r = 0; r < a->world; ++r) {
       char* base = a->peer[p][r];
+      d.flags[r] = reinterpret_cast<unsigned long long*>(a->peer[0][r] + off_flags());
       d.counts[r] = reinterpret_cast<int64_t*>(base + off_counts());
       d.ids[r] = reinterpret_cast<int64_t*>(base + off_ids(a->world));
       d.cnt[r] = reinterpret_cast<int64_t*>(base + off_cnt(a->world, a->cap));
@@ -166,6 +199,7 @@ int hb_a2a_destroy(hb_a2a_t* a) {
     cudaFree(a->local[p]);
     cudaFree(a->dest_dev[p]);
   }
+  cudaFree(a->epoch_dev);
   delete a;
   return HB_OK;
 }
@@ -188,6 +222,15 @@ int hb_a2a_push(hb_a2a_t* a, const int64_t* ids, const void* rows, const int64_t
   int rc = run_partition(pol, n, a->world, workspace, workspace_bytes, nullptr, st, 1, &plan);
   if (rc != HB_OK) return rc;
   HB_LAUNCH(push_counts_kernel, 1, 64, 0, st, plan, a->dest_dev[p], a->rank, a->cap, sent_counts);
+  return HB_OK;
+}
+
+int hb_a2a_fence(hb_a2a_t* a, hb_stream_t stream) {
+  HB_CHECK_ARG(a != nullptr, "hb_a2a_fence: null exchange");
+  if (a->world == 1) return HB_OK;
+  HB_LAUNCH(a2a_fence_kernel, 1, 64, 0, (cudaStream_t)stream, a->dest_dev[0],
+            reinterpret_cast<const unsigned long long*>(a->local[0] + off_flags()), a->epoch_dev,
+            a->rank, a->world, device_error_word());
   return HB_OK;
 }
 

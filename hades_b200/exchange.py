@@ -29,7 +29,10 @@ def _as_tensor(ptr: int, shape, typestr: str, device) -> torch.Tensor:
 
 class PeerExchange:
     def __init__(self, rank: int, world: int, cap_rows: int, dim: int, row_dtype=torch.float32,
-                 device=None, group=None):
+                 device=None, group=None, fence: str = "device"):
+        """fence: "device" = hb_a2a_fence (flags in peer memory, bounded wait, no collective
+        library); "nccl" = a 4-byte all-reduce."""
+        self.fence_kind = fence
         self.lib = _lib.load()
         self.rank, self.world, self.cap, self.dim, self.group = rank, world, int(cap_rows), dim, group
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
@@ -108,7 +111,10 @@ class PeerExchange:
         """Order every rank's push before every rank's reads: one tiny collective on the
         current stream (no host synchronisation)."""
         if self.world > 1:
-            dist.all_reduce(self._token, group=self.group)
+            if self.fence_kind == "device":
+                _lib.check(self.lib.hb_a2a_fence(self._h, _lib.stream_ptr()))
+            else:
+                dist.all_reduce(self._token, group=self.group)
 
     def received(self, parity: int):
         """(ids [world*cap], rows [world*cap, dim], cnt [world*cap], counts [world]) of this

@@ -51,6 +51,7 @@ class EmbeddingPath:
         self.px = peer_exchange  # PeerExchange for the per-step hot rows (None: NCCL all-to-all)
         self.step_no = 0
         self._graphs, self._g_ids, self._g_grads, self._g_out, self._g_next = [], None, None, None, 0
+        self._whole_step_graphs = True
         # unique hot ids of a batch cannot outnumber the hot ids of the table
         self.num_hot_ids = int((class_table == HOT).sum().item())
 
@@ -156,13 +157,15 @@ class EmbeddingPath:
         if self._graphs and grads is self._g_grads and out_rows is self._g_out:
             if ids is not self._g_ids:
                 self._g_ids.copy_(ids, non_blocking=True)
-            if self.world == 1:
-                graph, (rows, locs, found, st) = self._graphs[0]
+            if self._whole_step_graphs:
+                # one graph per receive area, each holding the whole step (push and device
+                # fence included); they alternate like the areas do
+                graph, (rows, locs, found, st) = self._graphs[self._g_next]
+                self._g_next = (self._g_next + 1) % len(self._graphs)
                 graph.replay()
             else:
-                # local part from the graph, the push and its fence launched eagerly (they hold
-                # the collective and the host-chosen receive area), owner update from the graph
-                # captured for that receive area
+                # local part from the graph, the push and its fence launched eagerly (the NCCL
+                # fence is a collective), owner update from the graph captured for that area
                 graph, (rows, locs, found, st, hot_ids, hot_rows, hot_cnt) = self._graphs[0]
                 graph.replay()
                 parity = self.px.push(hot_ids, hot_rows, hot_cnt, st.split_counts[HOT:HOT + 1])
@@ -182,20 +185,24 @@ class EmbeddingPath:
         steps: every lazy allocation of the library has to have happened.
 
         One GPU: one graph holds the whole step (the periodic flush stays eager).  Several GPUs
-        with the peer-memory exchange: one graph for everything before the exchange and one per
-        receive area for the owner update; the push and its fence are launched eagerly between
-        them, so no collective is ever captured.  Not available with the NCCL all-to-all, which
-        reads sizes on the host."""
+        with the peer-memory exchange and its device-side fence: two graphs, one per receive
+        area, each holding the whole step; they are replayed alternately.  With the NCCL fence
+        the collective is not captured: one graph for everything before the exchange and one
+        per receive area for the owner update, push and fence launched eagerly between them.
+        Not available with the NCCL all-to-all, which reads sizes on the host."""
         if self.world > 1 and self.px is None:
             raise RuntimeError("the NCCL all-to-all exchange reads sizes on the host and cannot be captured")
         graphs = []
-        g = torch.cuda.CUDAGraph()
-        if self.world == 1:
-            with torch.cuda.graph(g):
-                rows, locs, found = self.forward(ids_buf, out_rows, defer_touch=True)
-                st = self._backward_core(ids_buf, grads, locs)
-            graphs.append((g, (rows, locs, found, st)))
+        self._whole_step_graphs = self.world == 1 or self.px.fence_kind == "device"
+        if self._whole_step_graphs:
+            for _ in range(1 if self.world == 1 else 2):  # the push picks the areas in turn
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    rows, locs, found = self.forward(ids_buf, out_rows, defer_touch=True)
+                    st = self._backward_core(ids_buf, grads, locs)
+                graphs.append((g, (rows, locs, found, st)))
         else:
+            g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 rows, locs, found = self.forward(ids_buf, out_rows, defer_touch=True)
                 st, hot_ids, hot_rows, hot_cnt = self._backward_local(ids_buf, grads, locs)
@@ -220,14 +227,14 @@ def _warm_collectives(world: int, device, group) -> None:
         torch.cuda.synchronize()
 
 
-def _peer_exchange(rank, world, cap, dim, device, group):
+def _peer_exchange(rank, world, cap, dim, device, group, fence="device"):
     """The peer-memory exchange, or None when it cannot be set up on every rank."""
     import torch.distributed as dist
 
     from .exchange import PeerExchange
 
     try:
-        px = PeerExchange(rank, world, cap, dim, torch.float32, device, group)
+        px = PeerExchange(rank, world, cap, dim, torch.float32, device, group, fence)
         ok = 1
     except Exception as e:  # noqa: BLE001  (e.g. CUDA IPC not permitted between these processes)
         import warnings
@@ -261,8 +268,9 @@ def assemble_path(name: str, table: torch.Tensor, class_table: torch.Tensor, cac
     id_bits = max(int(rows_total).bit_length() + 1, 8)
     _warm_collectives(world, device, group)
     px = None
-    if world > 1 and exchange == "push":
-        px = _peer_exchange(rank, world, hot_per_owner_max, dim, device, group)
+    if world > 1 and exchange in ("push", "push_nccl_fence"):
+        px = _peer_exchange(rank, world, hot_per_owner_max, dim, device, group,
+                            "device" if exchange == "push" else "nccl")
     path = EmbeddingPath(table, class_table, cold, opt, rank, world, flush_every, id_bits,
                          lookup_mode, mover, touch_lru, group, px)
     path.cache_fill_ids = cache_ids  # what the cold cache was filled with, in insertion order

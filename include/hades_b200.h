@@ -441,6 +441,14 @@ size_t hb_a2a_push_workspace_bytes(int64_t n, int world);
 int hb_a2a_push(hb_a2a_t* a, const int64_t* ids, const void* rows, const int64_t* cnt /* nullable: 1 */,
                 int64_t n, const int64_t* n_dev, int64_t* sent_counts, int* parity_out,
                 void* workspace, size_t workspace_bytes, hb_stream_t stream);
+/* The barrier between a push and the use of what was received, without a
+ * collective library: every rank stores its exchange number into every peer's
+ * flag array and polls its own until all peers have done so.  The wait has an
+ * iteration limit (about a second); a rank that gives up records HB_ERR_TIMEOUT
+ * for hb_device_status and returns.  Every rank must call it once per push, and
+ * the ranks must be on different GPUs.  The exchange number lives on the device,
+ * so a captured graph holding push + fence can be replayed. */
+int hb_a2a_fence(hb_a2a_t* a, hb_stream_t stream);
 /* This rank's receive area of a parity: ids/cnt [world][cap_rows], rows
  * [world][cap_rows][row_bytes], counts[world] (device int64: rows from each
  * source).  Feed hb_unique_segsum_f32 with seg_counts = counts, seg_cap = cap_rows. */

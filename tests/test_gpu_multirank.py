@@ -73,7 +73,8 @@ def _worker(rank, port, exchange):
     # --- the backward path on both ranks vs a simulation of both ----------------------------
     cfg = _cfg()
     path = pipeline.build_path(cfg, rank, WORLD, hot_fraction=0.02,
-                               exchange="push" if exchange.startswith("push") else "nccl")
+                               exchange={"nccl": "nccl", "push": "push", "push_graph": "push",
+                                         "push_nccl_fence_graph": "push_nccl_fence"}[exchange])
     assert (path.px is not None) == exchange.startswith("push")
     cls = path.class_table.cpu().numpy()
     shard_rows = path.opt.emb.rows
@@ -89,7 +90,7 @@ def _worker(rank, port, exchange):
         stg = om.OracleStaging(ox.get_capacity(), cfg.dim, cnt_threshold=16)
         ox.add(hot_ids)
         sim.append((ox, stg))
-    use_graph = exchange == "push_graph"
+    use_graph = exchange.endswith("_graph")
     if use_graph:
         g_ids = torch.empty(cfg.batch, dtype=torch.int64, device="cuda")
         g_grads = torch.empty((cfg.batch, cfg.dim), device="cuda")
@@ -137,11 +138,12 @@ def _worker(rank, port, exchange):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["nccl", "push", "push_graph"])
+@pytest.mark.parametrize("exchange", ["nccl", "push", "push_graph", "push_nccl_fence_graph"])
 def test_two_ranks(exchange):
     """exchange = "nccl": ragged all_to_all_single; "push": the fused pack+push kernel over
-    peer memory (plain stores, NVLS off); "push_graph": the same with the local part and the
-    owner update replayed from CUDA graphs."""
+    peer memory with the device-side fence (plain stores, NVLS off); "push_graph": the same
+    replayed from two whole-step CUDA graphs; "push_nccl_fence_graph": NCCL all-reduce as the
+    fence, graphs around the eagerly launched exchange."""
     if not torch.cuda.is_available() or torch.cuda.device_count() < WORLD:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
