@@ -88,6 +88,7 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_a2a_push_workspace_bytes": (_sz, [_i64, _int]),
     "hb_a2a_push": (_int, [_p, _p, _p, _p, _i64, _p, _p, _p, _p, _sz, _p]),
     "hb_a2a_fence": (_int, [_p, _p]),
+    "hb_wait_flag": (_int, [_p, C.c_uint64, _p]),
     "hb_a2a_recv_view": (_int, [_p, _int, _p, _p, _p, _p, _p]),
 }
 

@@ -98,6 +98,20 @@ __global__ void push_counts_kernel(PartitionPlan p, const hb_a2a::Dest* dest, in
   __threadfence_system();
 }
 
+// Poll a flag until it reaches `value`, at most about a second; false = gave up.
+__device__ __forceinline__ bool wait_flag_bounded(const volatile unsigned long long* flag,
+                                                  unsigned long long value) {
+  for (int it = 0; it < (1 << 20); ++it) {
+    if (*flag >= value) return true;
+    __nanosleep(it < 64 ? 100 : 1000);
+  }
+  return false;
+}
+
+__global__ void wait_flag_kernel(const unsigned long long* flag, unsigned long long value, int* err) {
+  if (!wait_flag_bounded(flag, value)) atomicExch(err, HB_ERR_TIMEOUT);
+}
+
 // One CTA per rank.  Thread t: tell rank t that this rank has finished pushing exchange
 // number e (everything before this kernel in the stream), then wait until rank t says the
 // same.  Bounded: about a second of polling, then HB_ERR_TIMEOUT and return.
@@ -110,13 +124,7 @@ __global__ void a2a_fence_kernel(const hb_a2a::Dest* dest, const unsigned long l
   if (t >= world) return;
   __threadfence_system();  // my rows and counts are visible before my flag
   *reinterpret_cast<volatile unsigned long long*>(dest->flags[t] + rank) = e;
-  const volatile unsigned long long* mine = local_flags + t;
-  bool ok = false;
-  for (int it = 0; it < (1 << 20); ++it) {
-    if (*mine >= e) { ok = true; break; }
-    __nanosleep(it < 64 ? 100 : 1000);
-  }
-  if (!ok) atomicExch(err, HB_ERR_TIMEOUT);
+  if (!wait_flag_bounded(local_flags + t, e)) atomicExch(err, HB_ERR_TIMEOUT);
   __threadfence_system();  // reads of the slabs stay after the flag
 }
 
@@ -231,6 +239,14 @@ int hb_a2a_fence(hb_a2a_t* a, hb_stream_t stream) {
   HB_LAUNCH(a2a_fence_kernel, 1, 64, 0, (cudaStream_t)stream, a->dest_dev[0],
             reinterpret_cast<const unsigned long long*>(a->local[0] + off_flags()), a->epoch_dev,
             a->rank, a->world, device_error_word());
+  return HB_OK;
+}
+
+int hb_wait_flag(const uint64_t* flag, uint64_t value, hb_stream_t stream) {
+  HB_CHECK_ARG(flag != nullptr, "hb_wait_flag: null flag");
+  HB_LAUNCH(wait_flag_kernel, 1, 1, 0, (cudaStream_t)stream,
+            reinterpret_cast<const unsigned long long*>(flag), (unsigned long long)value,
+            device_error_word());
   return HB_OK;
 }
 

@@ -449,6 +449,12 @@ int hb_a2a_push(hb_a2a_t* a, const int64_t* ids, const void* rows, const int64_t
  * the ranks must be on different GPUs.  The exchange number lives on the device,
  * so a captured graph holding push + fence can be replayed. */
 int hb_a2a_fence(hb_a2a_t* a, hb_stream_t stream);
+/* The bounded wait that hb_a2a_fence uses, on its own: a one-thread kernel polls
+ * the device word *flag until it is >= value, for at most about a second; if it
+ * gives up it records HB_ERR_TIMEOUT for hb_device_status and returns, and the
+ * context stays usable.  (Failure detection is built on this: a peer that never
+ * arrives shows up as a status code, never as a hung or trapped GPU.) */
+int hb_wait_flag(const uint64_t* flag, uint64_t value, hb_stream_t stream);
 /* This rank's receive area of a parity: ids/cnt [world][cap_rows], rows
  * [world][cap_rows][row_bytes], counts[world] (device int64: rows from each
  * source).  Feed hb_unique_segsum_f32 with seg_counts = counts, seg_cap = cap_rows. */
