@@ -8,8 +8,8 @@
  * mapped into the device address space also works for the row movers, as it
  * does for the reference's UVA kernels), every call is asynchronous on the
  * given stream (a cudaStream_t passed as void*), and the caller owns all
- * buffers.  Kernels need "workspace" scratch are given it by the caller:
- * hb_xxx_workspace_bytes() tells how much.
+ * buffers.  Kernels that need scratch memory are given it by the caller as a
+ * workspace: hb_xxx_workspace_bytes() tells how much.
  *
  * Each declaration cites the reference interface (HADES, path inside the
  * reference project) that it replaces.
