@@ -43,9 +43,11 @@ def parse():
     ap.add_argument("--lookup", default="setassoc", choices=["setassoc", "sorted"])
     ap.add_argument("--mover", default="auto", choices=["auto", "lsu", "bulk"])
     ap.add_argument("--no-lru", action="store_true", help="skip the LRU ageing passes")
-    ap.add_argument("--workload", default="config2", choices=["config2", "c4_exchange", "c5"],
-                    help="config2: the whole path (default); c4_exchange: only the owner-partitioned "
-                         "exchange at configuration-4 shapes (1,048,576 unique ids x 64 fp32 per rank); "
+    ap.add_argument("--workload", default="config2", choices=["config2", "c3", "c4_exchange", "c5"],
+                    help="config2: the whole path (default); c3: hot-node local aggregation + reduction of "
+                         "the hot ids across GPUs (524,288 ids per GPU, Zipf(1.2) over 1e8); c4_exchange: the "
+                         "owner-partitioned sync at configuration-4 shapes (1,048,576 unique ids x 64 fp32 per "
+                         "rank) and the Adagrad update on the fp16 shard; "
                          "c5: the whole path on the frontier of a sampled 2-layer GraphSAGE step over a "
                          "synthetic R-MAT graph (1e8 nodes, 1,024 seeds, fanout [25, 10], per GPU)")
     ap.add_argument("--optimizer", default="adam", choices=["adam", "adagrad"])
@@ -484,16 +486,9 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
-def run_exchange(args) -> None:
-    """The sparse-gradient all-to-all alone, configuration-4 shapes, against the NVLink roofline:
-    bytes that leave a GPU / (770 GB/s measured peer copy on this pool; 900 GB/s nominal)."""
-    import numpy as np
+def _dist_setup():
     import torch
     import torch.distributed as dist
-
-    from hades_b200 import _lib, synth
-    from hades_b200.exchange import PeerExchange
-    from hades_b200.sparse_optim import swap_gradients
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -502,26 +497,12 @@ def run_exchange(args) -> None:
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    n, dim = int(1_048_576 * args.scale), 64
-    rng = synth.rng_for(4, rank, 0)
-    ids_np = synth.ZipfSampler(240_000_000 // 16, 1.1).unique_ids(rng, n)  # distinct ids, Zipf(1.1) ranks
-    ids = torch.from_numpy(ids_np).to(dev)
-    rows = torch.empty((n, dim), device=dev).normal_(0, 1e-3)
-    cnt = torch.ones(n, dtype=torch.int64, device=dev)
-    sent_to_others = int((ids_np % world != rank).sum())
-    bytes_out = sent_to_others * (8 + 8 + dim * 4)
-    cap = int(np.bincount(ids_np % world, minlength=world).max() * 1.05) + 16
-    px = PeerExchange(rank, world, cap, dim, torch.float32, dev)                    # device-side fence
-    px_nf = PeerExchange(rank, world, cap, dim, torch.float32, dev, fence="nccl")   # all-reduce as the fence
-
-    def ev():
-        return torch.cuda.Event(enable_timing=True)
 
     def timed(fn, steps):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-        a, b = ev(), ev()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(steps):
             fn()
@@ -534,6 +515,39 @@ def run_exchange(args) -> None:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    return rank, world, dev, timed
+
+
+def run_exchange(args) -> None:
+    """Configuration 4: owner-partitioned sparse-gradient sync + sparse Adagrad on an fp16 table
+    sharded by id % world.  Times the all-to-all alone against the NVLink roofline (bytes that
+    leave a GPU / 770 GB/s measured peer copy on this pool; 900 GB/s nominal), three ways, and
+    the whole sync (exchange + owner-side merge + Adagrad update on the owning shard)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from hades_b200 import _lib, synth
+    from hades_b200.exchange import PeerExchange
+    from hades_b200.sparse_optim import ShardedEmbedding, SparseAdagrad, swap_gradients
+
+    rank, world, dev, timed = _dist_setup()
+    n, dim = int(1_048_576 * args.scale), 64
+    table_rows = int(240_000_000 * args.scale)
+    rng = synth.rng_for(4, rank, 0)
+    ids_np = synth.ZipfSampler(table_rows, 1.1).unique_ids(rng, n)  # distinct ids, Zipf(1.1) without replacement
+    ids = torch.from_numpy(ids_np).to(dev)
+    rows = torch.empty((n, dim), device=dev).normal_(0, 1e-3)
+    cnt = torch.ones(n, dtype=torch.int64, device=dev)
+    sent_to_others = int((ids_np % world != rank).sum())
+    bytes_out = sent_to_others * (8 + 8 + dim * 4)
+    cap = int(np.bincount(ids_np % world, minlength=world).max() * 1.05) + 16
+    px = PeerExchange(rank, world, cap, dim, torch.float32, dev)                    # device-side fence
+    px_nf = PeerExchange(rank, world, cap, dim, torch.float32, dev, fence="nccl")   # all-reduce as the fence
+    shard = ShardedEmbedding(table_rows, dim, rank, world, dtype=torch.float16, device=dev, init_sigma=0.01, seed=4)
+    opt = SparseAdagrad(shard, lr=0.01)
+    id_bits = max(table_rows.bit_length() + 1, 8)
+
     def do_push():
         px.push(ids, rows, cnt)
         px.fence()
@@ -545,9 +559,16 @@ def run_exchange(args) -> None:
     def do_nccl():
         swap_gradients(ids, rows, None, 1, world, dev, cnt)
 
+    def do_sync_update():
+        parity = px.push(ids, rows, cnt)
+        px.fence()
+        r_ids, r_rows, r_cnt, seg = px.received(parity)
+        opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=id_bits, seg_counts=seg, seg_cap=px.cap)
+
     W, K = max(args.warmup, 3), max(args.steps, 1)
     out = {}
-    for name, fn in (("push", do_push), ("push_nccl_fence", do_push_nccl_fence), ("nccl", do_nccl)):
+    for name, fn in (("push", do_push), ("push_nccl_fence", do_push_nccl_fence), ("nccl", do_nccl),
+                     ("sync_update", do_sync_update)):
         for _ in range(W):
             fn()
         out[name] = timed(fn, K)
@@ -555,10 +576,12 @@ def run_exchange(args) -> None:
     if rank == 0:
         line = {"metric": "sparse_grad_all_to_all_GBps_per_gpu_out", "unit": "GB/s", "n_gpus": world,
                 "steps": K, "warmup": W, "higher_is_better": True, "data": "synthetic", "dtype": "f32",
-                "config": {"workload": "config4 exchange: 1,048,576 unique ids x 64 fp32 (+8 B id, 8 B cnt) per rank",
+                "config": {"workload": "config4: 1,048,576 unique ids x 64 fp32 (+8 B id, 8 B cnt) per rank, "
+                                       f"fp16 table of {table_rows} x 64 sharded id % world, sparse Adagrad fp32 state",
                            "rows_per_rank": n, "bytes_leaving_each_gpu": bytes_out},
                 "push_ms": out["push"], "push_nccl_fence_ms": out["push_nccl_fence"], "nccl_ms": out["nccl"],
-                "device_status": status}
+                "sync_update_ms": out["sync_update"],
+                "sync_update_rows_per_s": world * n / (out["sync_update"] * 1e-3), "device_status": status}
         if world > 1:
             line["value"] = bytes_out / (out["push"] * 1e-3) / 1e9
             line["nccl_value"] = bytes_out / (out["nccl"] * 1e-3) / 1e9
@@ -570,12 +593,100 @@ def run_exchange(args) -> None:
         dist.destroy_process_group()
 
 
+def run_hot_aggregation(args) -> None:
+    """Configuration 3: hot-node local aggregation.  Every GPU holds 524,288 gradient ids,
+    Zipf(1.2) over [0, 1e8), with 128-dim fp32 gradients; per GPU sort / unique / segment-sum;
+    the rows of the hot ids (top 1 % of the popularity ranking) then go to their owners
+    (id % world), which merge what the ranks sent (unique_grads with counts)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from hades_b200 import EmbCacheLib as E
+    from hades_b200 import _lib, synth
+    from hades_b200.exchange import PeerExchange
+
+    rank, world, dev, timed = _dist_setup()
+    nodes = int(100_000_000 * args.scale)
+    n, dim = int(524_288 * args.scale), 128
+    sampler = synth.ZipfSampler(nodes, 1.2)
+    rng = synth.rng_for(3, rank, 0)
+    batches = [torch.from_numpy(sampler.ids(rng, n)).to(dev) for _ in range(4)]
+    stats = synth.stream_stats(batches[0].cpu().numpy())
+    grads = torch.empty((n, dim), device=dev).normal_(0, 1e-3)
+    n_hot = max(nodes // 100, 1)
+    hot_ranked = synth.rank_to_id(np.arange(n_hot, dtype=np.int64), nodes)
+    cls = np.full(nodes, 2, dtype=np.int8)
+    cls[hot_ranked] = 1
+    table = torch.from_numpy(cls).to(dev)
+    cap = int(np.bincount(hot_ranked % world, minlength=world).max())
+    cap = min(cap, n)
+    px = PeerExchange(rank, world, cap, dim, torch.float32, dev) if world > 1 else None
+    id_bits = max(nodes.bit_length() + 1, 8)
+    state = {"k": 0, "u": None, "hot": None, "merged": None}
+
+    def local_only():
+        ids = batches[state["k"] % 4]
+        state["k"] += 1
+        outs, cc, num = E.cudaUniqueSegSumSplit(ids, grads, table, keep=(False, True, False),
+                                                caps=(None, min(n_hot, n), None), id_bits=id_bits)
+        state["u"], state["hot"], state["cc"] = num, outs[1], cc
+
+    def with_reduction():
+        local_only()
+        h_ids, h_rows, h_cnt = state["hot"]
+        if px is None:
+            state["merged"] = E.cudaUniqueSegSum(h_ids, h_rows, h_cnt, mean=True, id_bits=id_bits, sync=False,
+                                                 n_dev=state["cc"][1:2])
+        else:
+            parity = px.push(h_ids, h_rows, h_cnt, state["cc"][1:2])
+            px.fence()
+            r_ids, r_rows, r_cnt, seg = px.received(parity)
+            state["merged"] = E.cudaUniqueSegSum(r_ids, r_rows, r_cnt, mean=True, id_bits=id_bits, sync=False,
+                                                 seg_counts=seg, seg_cap=px.cap)
+
+    W, K = max(args.warmup, 3), max(args.steps, 1)
+    out = {}
+    for name, fn in (("local", local_only), ("local_plus_hot_reduction", with_reduction)):
+        for _ in range(W):
+            fn()
+        out[name] = timed(fn, K)
+    uniq = int(state["u"].item())
+    hot_u = int(state["cc"][1].item())
+    merged = int(state["merged"][3].item())
+    status = _lib.device_status()
+    if rank == 0:
+        peaks = {}
+        pk = ROOT / "MEASURED_PEAKS.json"
+        if pk.exists():
+            peaks = json.loads(pk.read_text())
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        alg = n * (8 + dim * 4) + uniq * 16 + hot_u * dim * 4
+        line = {"metric": "gradient_rows_per_s_local_aggregation_plus_hot_reduction", "unit": "rows/s",
+                "value": world * n / (out["local_plus_hot_reduction"] * 1e-3), "n_gpus": world, "steps": K,
+                "warmup": W, "higher_is_better": True, "scaling": "weak", "data": "synthetic", "dtype": "f32",
+                "ms_per_step": out["local_plus_hot_reduction"], "local_aggregation_ms": out["local"],
+                "config": {"workload": f"config3: {n} ids per GPU, Zipf(1.2) over {nodes}, dim 128 fp32, hot = top 1 %",
+                           "stream": stats, "unique": uniq, "hot_unique": hot_u, "owned_after_reduction": merged,
+                           "exchange": "local" if world == 1 else "fused pack+push over peer memory, device fence"},
+                "roofline": {"bound": "hbm", "kernel": "local aggregation (sort + run heads + segment-sum, hot rows kept)",
+                             "achieved": alg / (out["local"] * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                             "frac": alg / (out["local"] * 1e-3) / 1e9 / peak,
+                             "peak_source": "measured" if peaks else "fallback", "traffic": None},
+                "device_status": status}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "c4_exchange":
         run_exchange(args)
+    elif args.workload == "c3":
+        run_hot_aggregation(args)
     else:
         run_ours(args)
 
