@@ -215,6 +215,77 @@ class EmbeddingPath:
         self._graphs, self._g_ids, self._g_grads, self._g_out, self._g_next = graphs, ids_buf, grads, out_rows, 0
 
 
+    # ---- forward and backward as separate graphs (a model runs between them) -------------------
+    def capture_split(self, ids_buf: torch.Tensor, grads_buf: torch.Tensor, out_rows: torch.Tensor) -> None:
+        """Capture the forward fetch and the backward path as separate CUDA graphs over the
+        caller's buffers, for use with a model between them (``forward_replay`` /
+        ``backward_replay``).  Same conditions as ``capture``; several GPUs need the peer-memory
+        exchange with the device-side fence (one backward graph per receive area)."""
+        if self.world > 1 and (self.px is None or self.px.fence_kind != "device"):
+            raise RuntimeError("split capture on several GPUs needs the peer-memory exchange with the device fence")
+        fg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(fg):
+            rows, locs, found = self.forward(ids_buf, out_rows, defer_touch=True)
+        back = []
+        for _ in range(1 if self.world == 1 else 2):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                st = self._backward_core(ids_buf, grads_buf, locs)
+            back.append((g, st))
+        self._split = dict(fwd=fg, back=back, next=0, ids=ids_buf, grads=grads_buf, out=(rows, locs, found))
+
+    def forward_replay(self, ids: torch.Tensor):
+        sp = self._split
+        if ids is not sp["ids"]:
+            sp["ids"].copy_(ids, non_blocking=True)
+        sp["fwd"].replay()
+        return sp["out"]
+
+    def backward_replay(self, grads: torch.Tensor) -> StepStats:
+        """Backward for the ids of the last ``forward_replay``."""
+        sp = self._split
+        if grads is not sp["grads"]:
+            sp["grads"].copy_(grads, non_blocking=True)
+        g, st = sp["back"][sp["next"]]
+        sp["next"] = (sp["next"] + 1) % len(sp["back"])
+        g.replay()
+        st.flushed = 0
+        self._after_step(st)
+        return st
+
+    # ---- save / resume ---------------------------------------------------------------------------
+    def state_dict(self) -> dict:
+        """Everything a resumed run needs to continue bit for bit: index lines and LRU counters,
+        cached rows, staging buffers, optimiser state, table / owner shard, step counter.  (The
+        reference keeps all of this in server shared memory and DGL DistTensors and has no
+        save path; python/EmbCache/server.py:76-175.)"""
+        line_ids, lru = self.cold.index.export_state()
+        r = self.cold.remote
+        opt = {k: v.clone() for k, v in vars(self.opt).items() if isinstance(v, torch.Tensor)}
+        sd = {"step_no": self.step_no, "index_ids": line_ids, "index_lru": lru, "cache_emb": self.cold.emb.clone(),
+              "staging": {"grad": r.grad.clone(), "cnt": r.cnt.clone(), "idx": r.idx.clone(),
+                          "iter_count": r.iter_count.clone(), "iter_threshold": r.iter_threshold.clone()},
+              "dropped": self.cold.dropped.clone(), "optimizer": opt, "weight": self.opt.emb.weight.clone()}
+        if self.opt.emb.weight is not self.table:
+            sd["table"] = self.table.clone()
+        return sd
+
+    def load_state_dict(self, sd: dict) -> None:
+        """In place (buffer addresses are kept, so captured graphs stay valid)."""
+        self.step_no = int(sd["step_no"])
+        self.cold.index.import_state(sd["index_ids"], sd["index_lru"])
+        self.cold.emb.copy_(sd["cache_emb"])
+        r = self.cold.remote
+        for k, v in sd["staging"].items():
+            getattr(r, k).copy_(v)
+        self.cold.dropped.copy_(sd["dropped"])
+        for k, v in sd["optimizer"].items():
+            getattr(self.opt, k).copy_(v)
+        self.opt.emb.weight.copy_(sd["weight"])
+        if "table" in sd:
+            self.table.copy_(sd["table"])
+
+
 def _warm_collectives(world: int, device, group) -> None:
     """NCCL sets up its send/receive connections on first use (about a second); do it at
     set-up, not inside the first flush."""
