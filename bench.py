@@ -369,8 +369,10 @@ def run_ours(args) -> None:
         ev = lambda: torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         for name, fn in (
-            ("lookup_fetch", lambda: E.cudaLookupFetch(path.cold.index, ids, path.cold.emb, path.table,
-                                                       out_rows=out_rows, mode=mode, mover=mover)),
+            ("lookup_fetch", (lambda: path.shared.lookup_fetch(path.cold.index, ids, path.cold.emb, out_rows, mode))
+             if path.shared is not None else
+             (lambda: E.cudaLookupFetch(path.cold.index, ids, path.cold.emb, path.table,
+                                        out_rows=out_rows, mode=mode, mover=mover))),
             ("unique_segsum", lambda: E.cudaUniqueSegSum(ids, grads, id_bits=path.id_bits, sync=False)),
         ):
             fn()

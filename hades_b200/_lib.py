@@ -90,6 +90,15 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_a2a_fence": (_int, [_p, _p]),
     "hb_wait_flag": (_int, [_p, C.c_uint64, _p]),
     "hb_a2a_recv_view": (_int, [_p, _int, _p, _p, _p, _p, _p]),
+    "hb_peer_table_create": (_int, [_int, _int, _i64, _i64, _p]),
+    "hb_peer_table_handle_bytes": (_sz, []),
+    "hb_peer_table_export_handle": (_int, [_p, _p]),
+    "hb_peer_table_connect": (_int, [_p, _p]),
+    "hb_peer_table_set_peer": (_int, [_p, _int, _p]),
+    "hb_peer_table_local": (_int, [_p, _p, _p]),
+    "hb_peer_table_destroy": (_int, [_p]),
+    "hb_peer_table_gather": (_int, [_p, _p, _i64, _p, _p, _p]),
+    "hb_lookup_fetch_sharded": (_int, [_p, _p, _i64, _p, _p, _p, _p, _p, _int, _p]),
 }
 
 

@@ -31,7 +31,7 @@ class DistEmbeddingTensor:
     def __init__(self, path: EmbeddingPath, name: str = "emb"):
         self.path = path
         self.name = name
-        self.num_embeddings, self.embedding_dim = path.table.shape
+        self.num_embeddings, self.embedding_dim = path.num_nodes, path.dim
         self.enable_cache = True
         self.trace: list[tuple] = []
         self._captured_batch = 0
@@ -42,10 +42,10 @@ class DistEmbeddingTensor:
         ``batch`` ids (other sizes keep running eagerly).  Call after a few eager steps.  The rows
         a replayed call returns live in the graph's output buffer: the next such call overwrites
         them."""
-        dev = self.path.table.device
+        dev = self.path.device
         ids = torch.zeros(batch, dtype=torch.int64, device=dev)
         grads = torch.zeros((batch, self.embedding_dim), dtype=torch.float32, device=dev)
-        out = torch.empty((batch, self.embedding_dim), dtype=self.path.table.dtype, device=dev)
+        out = torch.empty((batch, self.embedding_dim), dtype=self.path.row_dtype, device=dev)
         self.path.capture_split(ids, grads, out)
         self._captured_batch = batch
 
@@ -53,31 +53,14 @@ class DistEmbeddingTensor:
         """Current table rows (no cache), the reference's ``self.tensor[ids]``
         (dist_emb.py:168-169): from the owners' shards when the table is sharded."""
         p = self.path
-        w = p.opt.emb.weight
-        out = torch.empty((ids.numel(), self.embedding_dim), dtype=w.dtype, device=ids.device)
-        if p.world == 1:
-            E.cudaFetch2(w, ids, out)
-            return out
-        import torch.distributed as dist
-
-        owner = ids % p.world
-        order = torch.argsort(owner, stable=True)
-        send_ids = ids[order]
-        counts = torch.bincount(owner, minlength=p.world)
-        recv_counts = torch.empty_like(counts)
-        dist.all_to_all_single(recv_counts, counts, group=p.group)
-        sc, rc = counts.tolist(), recv_counts.tolist()
-        asked = torch.empty(sum(rc), dtype=torch.int64, device=ids.device)
-        dist.all_to_all_single(asked, send_ids, rc, sc, group=p.group)
-        mine = torch.empty((asked.numel(), self.embedding_dim), dtype=w.dtype, device=ids.device)
-        E.cudaFetch2(w, asked // p.world, mine)
-        back = torch.empty((ids.numel(), self.embedding_dim), dtype=w.dtype, device=ids.device)
-        dist.all_to_all_single(back, mine, sc, rc, group=p.group)
-        E.cudaCombine(back, out, order)
+        if p.shared is not None:
+            return p.shared.gather(ids)
+        out = torch.empty((ids.numel(), self.embedding_dim), dtype=p.table.dtype, device=ids.device)
+        E.cudaFetch2(p.table, ids, out)
         return out
 
     def __call__(self, ids: torch.Tensor, device=None, is_training: bool = True) -> torch.Tensor:
-        dev = self.path.table.device
+        dev = self.path.device
         ids = ids.to(dev, non_blocking=True)
         if not is_training:
             rows = self.authoritative_rows(ids)
@@ -103,7 +86,7 @@ class DistEmb(nn.Module):
 
     def __init__(self, path: EmbeddingPath, name: str = "emb_layer"):
         super().__init__()
-        self.emb_dim = path.table.shape[1]
+        self.emb_dim = path.dim
         self.sparse_emb = DistEmbeddingTensor(path, name)
 
     def forward(self, idx: torch.Tensor) -> torch.Tensor:

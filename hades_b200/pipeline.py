@@ -54,16 +54,38 @@ class EmbeddingPath:
         self._whole_step_graphs = True
         # unique hot ids of a batch cannot outnumber the hot ids of the table
         self.num_hot_ids = int((class_table == HOT).sum().item())
+        self.num_nodes, self.dim, self.row_dtype = class_table.numel(), cold.dim, cold.emb.dtype
+        self.device = class_table.device
+        # owner shards that every GPU can read: cache misses fetch the authoritative row from the
+        # owner (table is then None); otherwise misses read `table` on this GPU
+        self.shared = getattr(optimizer.emb, "peer_table", None)
+        self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     # ---- forward -------------------------------------------------------------------------
     def forward(self, ids: torch.Tensor, out_rows: torch.Tensor | None = None, defer_touch: bool = False):
         """defer_touch: leave the LRU ageing of this lookup to ``backward(..., locs=locs)``,
         which sorts the same ids anyway and can age the counters without a sort of its own."""
-        rows, locs, found = E.cudaLookupFetch(self.cold.index, ids, self.cold.emb, self.table,
-                                              out_rows=out_rows, mode=self.lookup_mode, mover=self.mover)
+        if self.shared is not None:
+            rows, locs, found = self.shared.lookup_fetch(self.cold.index, ids, self.cold.emb, out_rows,
+                                                         self.lookup_mode)
+        else:
+            rows, locs, found = E.cudaLookupFetch(self.cold.index, ids, self.cold.emb, self.table,
+                                                  out_rows=out_rows, mode=self.lookup_mode, mover=self.mover)
         if self.touch_lru and not defer_touch:
             self.cold.index.cuda_touch_lru(locs)
         return rows, locs, found
+
+    def _fence_shards(self) -> None:
+        """All ranks' optimiser updates before anyone's next read of a shard (and the other way
+        round at the next exchange): the exchange's device-side fence, else a 4-byte all-reduce."""
+        if self.shared is None or self.world == 1:
+            return
+        if self.px is not None and self.px.fence_kind == "device":
+            self.px.fence()
+        else:
+            import torch.distributed as dist
+
+            dist.all_reduce(self._token, group=self.group)
 
     # ---- exchange ------------------------------------------------------------------------
     def _exchange(self, ids, rows, cnt, n_dev):
@@ -129,6 +151,7 @@ class EmbeddingPath:
                 r_n = r_n[:1]
             # owner: merge the senders' rows (unique_grads with counts) and update
             self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, n_dev=r_n, id_bits=self.id_bits)
+        self._fence_shards()
         return st
 
     def flush(self) -> int:
@@ -147,9 +170,13 @@ class EmbeddingPath:
             self.opt.update(r_ids, r_rows, r_cnt, is_unique=True, n_dev=r_n)
         else:
             self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, n_dev=r_n, id_bits=self.id_bits)
+        self._fence_shards()  # the refill reads what every owner has just written
         if n:
-            fresh = torch.empty((n, self.table.shape[1]), dtype=self.table.dtype, device=f_ids.device)
-            E.cudaFetch2(self.table, f_ids, fresh)
+            if self.shared is not None:
+                fresh = self.shared.gather(f_ids)
+            else:
+                fresh = torch.empty((n, self.dim), dtype=self.table.dtype, device=f_ids.device)
+                E.cudaFetch2(self.table, f_ids, fresh)
             self.cold.insert(f_ids, fresh)
         return n
 
@@ -171,6 +198,7 @@ class EmbeddingPath:
                 parity = self.px.push(hot_ids, hot_rows, hot_cnt, st.split_counts[HOT:HOT + 1])
                 self.px.fence()
                 self._graphs[1 + parity][0].replay()
+                self._fence_shards()
             st.flushed = 0
             self._after_step(st)
             return rows, locs, found, st
@@ -266,7 +294,7 @@ class EmbeddingPath:
               "staging": {"grad": r.grad.clone(), "cnt": r.cnt.clone(), "idx": r.idx.clone(),
                           "iter_count": r.iter_count.clone(), "iter_threshold": r.iter_threshold.clone()},
               "dropped": self.cold.dropped.clone(), "optimizer": opt, "weight": self.opt.emb.weight.clone()}
-        if self.opt.emb.weight is not self.table:
+        if self.table is not None and self.opt.emb.weight is not self.table:
             sd["table"] = self.table.clone()
         return sd
 
@@ -330,11 +358,20 @@ def assemble_path(name: str, table: torch.Tensor, class_table: torch.Tensor, cac
     E.cudaFetch2(table, cache_ids, rows)
     cold.insert(cache_ids, rows)
     del rows
-    shard = ShardedEmbedding(rows_total, dim, rank, world, dtype=table_dtype, device=device)
+    share = world > 1 and table_dtype == torch.float32
+    shard = ShardedEmbedding(rows_total, dim, rank, world, dtype=table_dtype, device=device, shared=share,
+                             group=group)
     if world == 1 and table_dtype == torch.float32:
         shard.weight = table  # one GPU: the backing table is the owner shard
     else:
-        shard.weight.normal_(0.0, table_sigma, generator=generator)
+        # every rank generated the same table; it keeps the rows it owns
+        shard.weight.copy_(table[rank::world])
+        if share:
+            table = None  # cache misses read the owners' shards
+            import torch.distributed as dist
+
+            torch.cuda.synchronize()
+            dist.barrier(group=group)  # every shard is filled before anyone reads it
     opt = SparseAdam(shard, lr=0.01) if optimizer == "adam" else SparseAdagrad(shard, lr=0.01)
     id_bits = max(int(rows_total).bit_length() + 1, 8)
     _warm_collectives(world, device, group)
@@ -361,7 +398,7 @@ def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str =
 
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
     gen = torch.Generator(device=device)
-    gen.manual_seed(1000 * (seed_config or cfg.config) + rank)
+    gen.manual_seed(1000 * (seed_config or cfg.config))  # the same table on every rank
     table = torch.empty((cfg.table_rows, cfg.dim), dtype=torch.float32, device=device)
     table.normal_(0.0, cfg.table_sigma, generator=gen)
     n_hot = max(int(cfg.table_rows * hot_fraction), 1)
@@ -393,7 +430,7 @@ def build_rmat_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: 
         raise RuntimeError(f"configuration {cfg.name} needs about {need / 2**30:.0f} GiB per GPU with "
                            f"{world} rank(s) and optimizer={optimizer}; this GPU has {total / 2**30:.0f} GiB")
     gen = torch.Generator(device=device)
-    gen.manual_seed(1000 * cfg.config + rank)
+    gen.manual_seed(1000 * cfg.config)  # the same table on every rank
     table = torch.empty((n, dim), dtype=torch.float32, device=device)
     table.normal_(0.0, cfg.table_sigma, generator=gen)
     ids = torch.arange(n, dtype=torch.int32, device=device)

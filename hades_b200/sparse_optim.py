@@ -75,12 +75,24 @@ class ShardedEmbedding:
     """The rows of a [num_embeddings, dim] table owned by this rank (owner = id % world)."""
 
     def __init__(self, num_embeddings: int, dim: int, rank: int = 0, world: int = 1,
-                 dtype=torch.float32, device=None, init_sigma: float | None = None, seed: int = 0):
+                 dtype=torch.float32, device=None, init_sigma: float | None = None, seed: int = 0,
+                 shared: bool = False, group=None):
+        """shared: keep the shard in memory that every GPU of the box can read
+        (``peer_table.PeerTable``), so that forward passes on other ranks fetch the authoritative
+        rows; a collective call (every rank constructs it)."""
         device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.num_embeddings, self.embedding_dim = int(num_embeddings), int(dim)
         self.rank, self.world = int(rank), int(world)
         self.rows = (self.num_embeddings - self.rank + self.world - 1) // self.world
-        self.weight = torch.zeros((self.rows, dim), dtype=dtype, device=device)
+        self.peer_table = None
+        if shared:
+            from .peer_table import PeerTable
+
+            self.peer_table = PeerTable(num_embeddings, dim, rank, world, dtype, device, group)
+            self.weight = self.peer_table.weight
+            self.weight.zero_()
+        else:
+            self.weight = torch.zeros((self.rows, dim), dtype=dtype, device=device)
         if init_sigma is not None:
             g = torch.Generator(device=device)
             g.manual_seed(seed * 1000 + rank)

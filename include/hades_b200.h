@@ -461,6 +461,44 @@ int hb_wait_flag(const uint64_t* flag, uint64_t value, hb_stream_t stream);
 int hb_a2a_recv_view(hb_a2a_t* a, int parity, int64_t** ids, void** rows, int64_t** cnt,
                      int64_t** counts, int64_t* cap_rows);
 
+/* ------------------------------------------------------------------------- */
+/* Table sharded over the GPUs of one box, readable from every GPU.            */
+/* ------------------------------------------------------------------------- */
+/* The forward direction of the owner partitioning.  The row of id lives on rank
+ * id % world at local row id / world (python/EmbCache/sparse_optim.py:38,
+ * cache.py:149-150); every shard is mapped into every process (CUDA IPC), and
+ * the kernels below read the authoritative row of any id with plain loads over
+ * NVLink.  Replaces the pull of remote rows from DGL's DistTensor through the
+ * host, `self.tensor[remote_ids.cpu()]` (python/EmbCache/dist_emb.py:241-243),
+ * in the manner of the reference's own unified-addressing reads of pinned host
+ * memory (src/cuda/uva_fetch.cu:72-106).  Rows are multiples of 16 bytes.
+ * Set-up as hb_a2a_*: create on every rank, exchange the handles, connect.  A
+ * single process that drives several GPUs itself passes the shard pointers with
+ * hb_peer_table_set_peer instead (peer access enabled by the caller).
+ * Ordering is the caller's: all ranks pass a fence (hb_a2a_fence or a
+ * collective on the stream) between an owner's update of its shard and the
+ * next read by anyone. */
+typedef struct hb_peer_table hb_peer_table_t;
+int hb_peer_table_create(int rank, int world, int64_t num_rows /* whole table */, int64_t row_bytes,
+                         hb_peer_table_t** out);
+size_t hb_peer_table_handle_bytes(void);
+int hb_peer_table_export_handle(hb_peer_table_t* t, void* handle_out /* host */);
+int hb_peer_table_connect(hb_peer_table_t* t, const void* handles /* host, world entries in rank order */);
+int hb_peer_table_set_peer(hb_peer_table_t* t, int rank, const void* shard_rows);
+/* This rank's shard: rows_local = ceil((num_rows - rank) / world) rows. */
+int hb_peer_table_local(hb_peer_table_t* t, void** rows, int64_t* rows_local);
+int hb_peer_table_destroy(hb_peer_table_t* t);
+/* dst[i, :] = row of ids[i] from its owner's shard, i < min(n, *n_dev). */
+int hb_peer_table_gather(hb_peer_table_t* t, const int64_t* ids, int64_t n,
+                         const int64_t* n_dev /* nullable */, void* dst, hb_stream_t stream);
+/* hb_lookup_fetch whose misses read the owner's shard: out_rows[i] = cached row
+ * when the index holds ids[i], else the authoritative row.  The one pass that
+ * python/EmbCache/dist_emb.py:184-243 makes of lookup, cache fetch and the
+ * DistTensor pull. */
+int hb_lookup_fetch_sharded(hb_index_t* h, const int64_t* ids, int64_t n, const void* cache_rows,
+                            hb_peer_table_t* table, void* out_rows, int64_t* locs /* nullable */,
+                            uint8_t* found /* nullable */, int mode, hb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -70,70 +70,86 @@ def _worker(rank, port, exchange):
     assert np.array_equal(r_rows.cpu().numpy(), np.concatenate([w[1] for w in want]))
     assert np.array_equal(r_cnt.cpu().numpy(), np.concatenate([w[2] for w in want]))
 
-    # --- the backward path on both ranks vs a simulation of both ----------------------------
+    # --- the whole step on both ranks vs a simulation of both -------------------------------
+    # The table is sharded by owner and every GPU reads every shard: cache misses of the
+    # forward fetch and the refill after a flush see the owners' current rows.
     cfg = _cfg()
     path = pipeline.build_path(cfg, rank, WORLD, hot_fraction=0.02,
                                exchange={"nccl": "nccl", "push": "push", "push_graph": "push",
                                          "push_nccl_fence_graph": "push_nccl_fence"}[exchange])
     assert (path.px is not None) == exchange.startswith("push")
+    assert path.shared is not None and path.table is None
     cls = path.class_table.cpu().numpy()
-    shard_rows = path.opt.emb.rows
-    w = path.opt.emb.weight.cpu().numpy().copy()
-    step = np.zeros(shard_rows, np.float32)
-    mem = np.zeros((shard_rows, cfg.dim), np.float32)
-    power = np.zeros((shard_rows, cfg.dim), np.float32)
-    # per-rank cold state (index + staging) of BOTH ranks, so that flushes can be simulated
+    # the whole table from the shards, through the same reads the kernels do
+    all_ids = torch.arange(cfg.table_rows, dtype=torch.int64, device="cuda")
+    w = path.shared.gather(all_ids).cpu().numpy()
+    assert np.array_equal(w[rank::WORLD], path.opt.emb.weight.cpu().numpy())
+    step = np.zeros(cfg.table_rows, np.float32)
+    mem = np.zeros((cfg.table_rows, cfg.dim), np.float32)
+    power = np.zeros((cfg.table_rows, cfg.dim), np.float32)
+    # cold state (index, cached rows, staging) of BOTH ranks
     sim = []
     hot_ids = synth.hot_ids(cfg.table_rows, cfg.cache_entries)
     for r in range(WORLD):
         ox = om.OracleIndex(cfg.cache_entries)
         stg = om.OracleStaging(ox.get_capacity(), cfg.dim, cnt_threshold=16)
-        ox.add(hot_ids)
-        sim.append((ox, stg))
+        cache = np.zeros((ox.get_capacity(), cfg.dim), np.float32)
+        stg.insert(ox, hot_ids, w[hot_ids], cache)
+        sim.append((ox, stg, cache))
     use_graph = exchange.endswith("_graph")
-    if use_graph:
-        g_ids = torch.empty(cfg.batch, dtype=torch.int64, device="cuda")
-        g_grads = torch.empty((cfg.batch, cfg.dim), device="cuda")
-        g_out = torch.empty((cfg.batch, cfg.dim), device="cuda")
-    for it in range(1, 5):
+    g_ids = torch.empty(cfg.batch, dtype=torch.int64, device="cuda")
+    g_grads = torch.empty((cfg.batch, cfg.dim), device="cuda")
+    g_out = torch.empty((cfg.batch, cfg.dim), device="cuda")
+    for it in range(1, 6):
         ids, grads = _batch(cfg, rank, it)
-        if use_graph:
-            if it == 2:  # one eager step first, then the captured graphs
-                torch.cuda.synchronize()
-                path.capture(g_ids, g_grads, g_out)
-            g_grads.copy_(torch.from_numpy(grads))
-            st = path.step(torch.from_numpy(ids).cuda(), g_grads, g_out)[3]
-        else:
-            st = path.backward(torch.from_numpy(ids).cuda(), torch.from_numpy(grads).cuda())
-        inbox_hot, inbox_flush = [], []
+        if use_graph and it == 2:  # one eager step first, then the captured graphs
+            torch.cuda.synchronize()
+            path.capture(g_ids, g_grads, g_out)
+        g_grads.copy_(torch.from_numpy(grads))
+        rows, locs, found, st = path.step(torch.from_numpy(ids).cuda(), g_grads, g_out)
+        rows, locs, found = rows.cpu().numpy(), locs.cpu().numpy(), found.cpu().numpy()
+        # every rank's forward reads the table as the previous step left it
+        uniq = []
         for r in range(WORLD):
             i_r, g_r = _batch(cfg, r, it)
+            ox, stg, cache = sim[r]
+            out = np.zeros((i_r.size, cfg.dim), np.float32)
+            l_r, hit_r = om.lookup_fetch(ox, i_r, cache, w, out)
+            ox.touch(l_r)
+            if r == rank:
+                assert np.array_equal(locs, l_r) and np.array_equal(found, hit_r), (rank, it)
+                np.testing.assert_allclose(rows, out, rtol=1e-4, atol=2e-6)
             u, s, c = om.only_unique_grads(i_r, g_r)
             k = cls[u]
-            ox, stg = sim[r]
             stg.accumulate_cached(ox, u[k == 2], s[k == 2], None, 0)
-            mine = (k == 1) & (u % WORLD == rank)
-            inbox_hot.append((u[mine], s[mine], c[mine]))
-        hu, hm, _ = om.unique_grads(np.concatenate([x[0] for x in inbox_hot]),
-                                    np.concatenate([x[1] for x in inbox_hot]),
-                                    np.concatenate([x[2] for x in inbox_hot]))
-        om.sparse_adam_update(hu, hm, step, mem, power, w, 0.01, id_offset=rank, id_stride=WORLD)
+            uniq.append((u[k == 1], s[k == 1], c[k == 1]))
+        for owner in range(WORLD):
+            inbox = [(u[u % WORLD == owner], s[u % WORLD == owner], c[u % WORLD == owner]) for u, s, c in uniq]
+            hu, hm, _ = om.unique_grads(*[np.concatenate([x[j] for x in inbox]) for j in range(3)])
+            om.sparse_adam_update(hu, hm, step, mem, power, w, 0.01)
         if it % cfg.flush_every == 0:
+            flushed = []
             for r in range(WORLD):
-                ox, stg = sim[r]
+                ox, stg, cache = sim[r]
                 fi, fr, fc, _ = stg.flush(ox, WORLD)
-                mine = fi % WORLD == rank
-                inbox_flush.append((fi[mine], fr[mine], fc[mine]))
-                ox.add(fi)  # refill
-            fu, fm, _ = om.unique_grads(np.concatenate([x[0] for x in inbox_flush]),
-                                        np.concatenate([x[1] for x in inbox_flush]),
-                                        np.concatenate([x[2] for x in inbox_flush]))
-            om.sparse_adam_update(fu, fm, step, mem, power, w, 0.01, id_offset=rank, id_stride=WORLD)
-        assert np.array_equal(path.opt.state_step.cpu().numpy(), step), (rank, it)
-        np.testing.assert_allclose(path.opt.state_mem.cpu().numpy(), mem, rtol=1e-4, atol=1e-9)
-        np.testing.assert_allclose(path.opt.emb.weight.cpu().numpy(), w, rtol=1e-4, atol=2e-6)
-        gi, _ = path.cold.index.export_state()
-        assert np.array_equal(gi.cpu().numpy(), sim[rank][0].export()[0]), (rank, it)
+                flushed.append((fi, fr, fc))
+            for owner in range(WORLD):
+                inbox = [(fi[fi % WORLD == owner], fr[fi % WORLD == owner], fc[fi % WORLD == owner])
+                         for fi, fr, fc in flushed]
+                fu, fm, _ = om.unique_grads(*[np.concatenate([x[j] for x in inbox]) for j in range(3)])
+                om.sparse_adam_update(fu, fm, step, mem, power, w, 0.01)
+            for r in range(WORLD):  # refill with the rows every owner has just written
+                ox, stg, cache = sim[r]
+                stg.insert(ox, flushed[r][0], w[flushed[r][0]], cache)
+        assert np.array_equal(path.opt.state_step.cpu().numpy(), step[rank::WORLD]), (rank, it)
+        np.testing.assert_allclose(path.opt.state_mem.cpu().numpy(), mem[rank::WORLD], rtol=1e-4, atol=1e-9)
+        np.testing.assert_allclose(path.opt.emb.weight.cpu().numpy(), w[rank::WORLD], rtol=1e-4, atol=2e-6)
+        gi, gl = path.cold.index.export_state()
+        oi, ol = sim[rank][0].export()
+        assert np.array_equal(gi.cpu().numpy(), oi) and np.array_equal(gl.cpu().numpy(), ol), (rank, it)
+        np.testing.assert_allclose(path.cold.emb.cpu().numpy(), sim[rank][2], rtol=1e-4, atol=2e-6)
+    assert path.step_no == 5
+    torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()
 
