@@ -4,6 +4,8 @@
 // :346-497, _update_cache :499-544), which does it with torch CPU indexing on
 // shared-memory tensors behind sockets.
 #include "index.cuh"
+#include <type_traits>
+
 #include "partition_core.cuh"
 
 namespace hb {
@@ -130,6 +132,12 @@ __global__ void __launch_bounds__(kBlock) staging_accumulate_direct_kernel(
 // iter_threshold or cnt >= cnt_threshold); stale rows leave in slot order,
 // bucketed by id % num_clients, and the slot is cleared; live slots with cnt > 0
 // age by one iteration.
+//
+// Two passes.  The partition selects: it writes the id of every stale slot to its place in
+// the output (slot order within a bucket), leaves the slot number where the count will go,
+// resets the cache entry and ages the live slots; no row moves there, because with a few
+// per cent of the slots stale a warp of the partition would move one or two rows at a time.
+// The second pass runs over the stale entries only: count out and cleared, row out and zeroed.
 struct FlushPolicy {
   hb_staging_t s;
   int32_t cnt_threshold;
@@ -137,9 +145,7 @@ struct FlushPolicy {
   int64_t* line_ids;  // nullable: the cache index entries of flushed ids are reset
   int32_t* lru;
   int64_t* out_ids;
-  float* out_rows;
-  int64_t* out_cnt;
-  int vb;
+  int64_t* out_cnt;   // holds the slot number until the second pass
   __device__ __forceinline__ int classify(int64_t i) const {
     const int32_t c = s.cnt[i];
     if (c <= 0) return -1;
@@ -150,38 +156,70 @@ struct FlushPolicy {
   __device__ __forceinline__ void emit(int64_t i, int, int64_t pos, int64_t start,
                                        bool active) const {
     const int64_t d = start + pos;
-    const bool in_range = i < s.slots;
     if (active) {
       const int64_t id = s.idx[i];
       out_ids[d] = id;
-      out_cnt[d] = (int64_t)s.cnt[i];
+      out_cnt[d] = i;
       if (line_ids && line_ids[i] == id) {  // _idx_cache.reset(ids), server.py:413
         line_ids[i] = -1;
         lru[i] = 0;
       }
-    } else if (in_range && s.cnt[i] > 0) {
+    } else if (i < s.slots && s.cnt[i] > 0) {
       s.iter_count[i] += 1;  // server.py:418
-    }
-    const size_t row_bytes = (size_t)s.dim * sizeof(float);
-    warp_move_rows(reinterpret_cast<const char*>(s.grad + (in_range ? i : 0) * s.dim),
-                   reinterpret_cast<char*>(out_rows + (active ? d : 0) * s.dim), active,
-                   (int64_t)row_bytes, vb);
-    // read-and-zero: the row, its count and its age start again
-    if (active) {
-      s.cnt[i] = 0;
-      s.iter_count[i] = 0;  // server.py:419
-    }
-    __syncwarp();
-    const unsigned act = __ballot_sync(0xffffffffu, active);
-    const int lane = threadIdx.x & 31;
-    for (int q = 0; q < 32; ++q) {
-      if (!((act >> q) & 1u)) continue;
-      const int64_t slot = __shfl_sync(0xffffffffu, i, q);
-      float* row = s.grad + slot * s.dim;
-      for (int64_t k = lane; k < s.dim; k += 32) row[k] = 0.f;
     }
   }
 };
+
+// Second pass of the flush: entry d < sum(counts) left slot out_cnt[d]; its count goes out
+// and starts again (server.py:419), its row goes out and is zeroed.  VB: bytes per vector.
+template <int VB>
+__global__ void __launch_bounds__(kBlock) staging_flush_move_kernel(
+    hb_staging_t s, const int64_t* __restrict__ counts, int num_clients,
+    int64_t* __restrict__ out_cnt, float* __restrict__ out_rows) {
+  using V = typename std::conditional<VB == 16, uint4, uint32_t>::type;
+  int64_t total = 0;
+  for (int c = 0; c < num_clients; ++c) total += counts[c];
+  const int lane = lane_id();
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t vpr = (int64_t)s.dim * 4 / VB;
+  V zero;
+  memset(&zero, 0, sizeof(zero));
+  for (int64_t base = warp * 32; base < total; base += nwarps * 32) {
+    const int64_t d = base + lane;
+    int64_t slot = -1;
+    if (d < total) {
+      slot = out_cnt[d];
+      out_cnt[d] = (int64_t)s.cnt[slot];
+      s.cnt[slot] = 0;
+      s.iter_count[slot] = 0;
+    }
+    const int rows_here = (int)((total - base) < 32 ? (total - base) : 32);
+    for (int q0 = 0; q0 < rows_here; q0 += 4) {
+      V* src[4];
+      V* dst[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t sl = __shfl_sync(0xffffffffu, slot, (q0 + u) & 31);
+        const bool on = q0 + u < rows_here;
+        src[u] = on ? reinterpret_cast<V*>(s.grad + sl * s.dim) : nullptr;
+        dst[u] = reinterpret_cast<V*>(out_rows + (base + q0 + u) * s.dim);
+      }
+      for (int64_t k = lane; k < vpr; k += 32) {
+        V v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (src[u]) v[u] = src[u][k];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (src[u]) {
+            __stcs(dst[u] + k, v[u]);
+            src[u][k] = zero;
+          }
+      }
+    }
+  }
+}
 
 // ---- insert (server.py:499-544): rows into the cache buffer at the slots add() gave ----------
 template <int VEC_BYTES>
@@ -305,12 +343,20 @@ int hb_staging_flush(hb_index_t* h, const hb_staging_t* s, int32_t cnt_threshold
   HB_CHECK_ARG(!h || h->cache_size == s->slots,
                "hb_staging_flush: the staging table must have one slot per cache slot");
   FlushPolicy pol{*s, cnt_threshold, num_clients, h ? h->line_ids : nullptr, h ? h->lru : nullptr,
-                  out_ids, out_rows, out_cnt,
-                  payload_vec_bytes(s->dim * (int64_t)sizeof(float), s->grad, out_rows)};
+                  out_ids, out_cnt};
   rc = run_partition(pol, s->slots, num_clients, workspace, workspace_bytes, counts,
-                     (cudaStream_t)stream, 2);
-  if (rc == HB_OK && h) h->sorted_stale = true;
-  return rc;
+                     (cudaStream_t)stream, 8);
+  if (rc != HB_OK) return rc;
+  if (h) h->sorted_stale = true;
+  // the number of stale rows is only known on the device: size the grid for a full table
+  const int grid = warp_grid(s->slots < (int64_t)sm_count() * 16 * 256 ? s->slots : (int64_t)sm_count() * 16 * 256);
+  if (payload_vec_bytes(s->dim * (int64_t)sizeof(float), s->grad, out_rows) == 16)
+    HB_LAUNCH(staging_flush_move_kernel<16>, grid, kBlock, 0, (cudaStream_t)stream, *s, counts, num_clients,
+              out_cnt, out_rows);
+  else
+    HB_LAUNCH(staging_flush_move_kernel<4>, grid, kBlock, 0, (cudaStream_t)stream, *s, counts, num_clients,
+              out_cnt, out_rows);
+  return HB_OK;
 }
 
 size_t hb_staging_insert_workspace_bytes(int64_t n) {

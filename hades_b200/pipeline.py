@@ -60,6 +60,7 @@ class EmbeddingPath:
         # owner (table is then None); otherwise misses read `table` on this GPU
         self.shared = getattr(optimizer.emb, "peer_table", None)
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._side, self._cold_done, self._cold_refs = None, None, None
 
     # ---- forward -------------------------------------------------------------------------
     def forward(self, ids: torch.Tensor, out_rows: torch.Tensor | None = None, defer_touch: bool = False):
@@ -108,9 +109,13 @@ class EmbeddingPath:
         if self.flush_every > 0 and self.step_no % self.flush_every == 0:
             st.flushed = self.flush()
 
-    def _backward_local(self, ids, grads, locs):
+    def _backward_local(self, ids, grads, locs, join: bool = True):
         """Backward up to the exchange: aggregation, LRU ageing, hot/cold split, cold
-        accumulate.  No host read and no collective.  Returns (stats, hot ids, rows, cnt)."""
+        accumulate.  No host read and no collective.  Returns (stats, hot ids, rows, cnt).
+
+        The cold accumulate touches only the staging table and the index, the hot rows' way to
+        their owners only the exchange buffers and the optimiser state, so the former runs on a
+        side stream; join=False leaves the join to the caller (``_join_cold``)."""
         st = StepStats()
         # hot-node local aggregation (only_unique_grads, sparse_optim.py:132-139) with the hot /
         # cold selects (sparse_optim.py:243-259) fused into its output
@@ -124,9 +129,28 @@ class EmbeddingPath:
         hot_ids, hot_rows, hot_cnt = outs[HOT]
         cold_ids, cold_rows, _ = outs[COLD]
         # cold rows wait in the staging table
-        self.cold.accumulate_remote(cold_ids, cold_rows, n_dev=split_counts[COLD:COLD + 1],
-                                    touch_lru=self.touch_lru)
+        main = torch.cuda.current_stream()
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        forked = torch.cuda.Event()
+        forked.record(main)
+        with torch.cuda.stream(self._side):
+            self._side.wait_event(forked)
+            self.cold.accumulate_remote(cold_ids, cold_rows, n_dev=split_counts[COLD:COLD + 1],
+                                        touch_lru=self.touch_lru)
+            self._cold_done = torch.cuda.Event()
+            self._cold_done.record(self._side)
+        # the side stream reads buffers that belong to this stream's allocator: keep them
+        # until the join is enqueued, so that nothing allocated in between can reuse them
+        self._cold_refs = (outs, split_counts)
+        if join:
+            self._join_cold()
         return st, hot_ids, hot_rows, hot_cnt
+
+    def _join_cold(self) -> None:
+        if self._cold_done is not None:
+            torch.cuda.current_stream().wait_event(self._cold_done)
+            self._cold_done, self._cold_refs = None, None
 
     def _owner_update_from_slabs(self, parity: int) -> None:
         """Owner side after a peer-memory push: merge the senders' slabs and update."""
@@ -137,10 +161,16 @@ class EmbeddingPath:
     def _backward_core(self, ids, grads, locs) -> StepStats:
         """Everything of the backward path that runs every step (no host read unless NCCL
         carries the exchange)."""
-        st, hot_ids, hot_rows, hot_cnt = self._backward_local(ids, grads, locs)
+        st, hot_ids, hot_rows, hot_cnt = self._backward_local(ids, grads, locs, join=False)
         n_hot = st.split_counts[HOT:HOT + 1]
         # hot rows go to their owners now
-        if self.px is not None and self.world > 1:
+        if self.world == 1:
+            # One trainer: bucketing by owner is the identity (the reference skips the exchange
+            # too, sparse_optim.py:263,320), and the hot ids are already unique and ascending, so
+            # unique_grads (sparse_optim.py:142-157) reduces to its division by 1 + cnt.
+            st.sent_counts = n_hot
+            self.opt.update(hot_ids, hot_rows, hot_cnt + 1, is_unique=True, n_dev=n_hot)
+        elif self.px is not None:
             parity = self.px.push(hot_ids, hot_rows, hot_cnt, n_hot)
             self.px.fence()
             self._owner_update_from_slabs(parity)
@@ -151,6 +181,7 @@ class EmbeddingPath:
                 r_n = r_n[:1]
             # owner: merge the senders' rows (unique_grads with counts) and update
             self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, n_dev=r_n, id_bits=self.id_bits)
+        self._join_cold()
         self._fence_shards()
         return st
 
@@ -162,14 +193,13 @@ class EmbeddingPath:
         n = f_ids.numel()
         if n == 0 and self.world == 1:
             return 0
-        r_ids, r_rows, r_cnt, r_n, _ = self._exchange(f_ids, f_rows, f_cnt, None)
-        if r_n is not None:
-            r_n = r_n[:1]
         if self.world == 1:
-            # one sender: rows are already unique (is_unique=True, sparse_optim.py:405-421)
-            self.opt.update(r_ids, r_rows, r_cnt, is_unique=True, n_dev=r_n)
+            # one trainer: every flushed row is its own (is_unique=True, sparse_optim.py:405-421)
+            self.opt.update(f_ids, f_rows, f_cnt, is_unique=True)
         else:
-            self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, n_dev=r_n, id_bits=self.id_bits)
+            r_ids, r_rows, r_cnt, r_n, _ = self._exchange(f_ids, f_rows, f_cnt, None)
+            self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, n_dev=None if r_n is None else r_n[:1],
+                            id_bits=self.id_bits)
         self._fence_shards()  # the refill reads what every owner has just written
         if n:
             if self.shared is not None:
