@@ -73,7 +73,7 @@ __device__ __forceinline__ float adam_elem(float g, float& m, float& v, float bi
 constexpr int kOptRows = 2;
 
 template <typename E, bool VEC4>
-__global__ void __launch_bounds__(kBlock) sparse_adam_kernel(
+__global__ void __launch_bounds__(kBlock, 4) sparse_adam_kernel(
     const int64_t* __restrict__ ids, const float* __restrict__ grads,
     const int64_t* __restrict__ cnt, int64_t n, const int64_t* __restrict__ n_dev, int64_t dim,
     RowMap map, float* __restrict__ step, float* __restrict__ mem, float* __restrict__ power,
@@ -84,20 +84,28 @@ __global__ void __launch_bounds__(kBlock) sparse_adam_kernel(
   const int sub = (int)(tid & ((1 << glog2) - 1));
   const int64_t ngroups = ((int64_t)gridDim.x * blockDim.x) >> glog2;
   const int G = 1 << glog2;
-  for (int64_t i0 = group; i0 < n; i0 += ngroups * kOptRows) {
+  const int lane = threadIdx.x & 31;
+  const int leader = lane & ~(G - 1);       // first lane of this row group
+  const int64_t warp_first = group - (lane >> glog2);  // the loop bound is the same for the whole warp
+  for (int64_t w0 = warp_first, i0 = group; w0 < n; w0 += ngroups * kOptRows, i0 += ngroups * kOptRows) {
     int64_t row[kOptRows];
     float bias1[kOptRows], bias2[kOptRows], c[kOptRows];
 #pragma unroll
     for (int r = 0; r < kOptRows; ++r) {
       const int64_t i = i0 + r * ngroups;
       row[r] = i < n ? map(__ldg(ids + i)) : -1;
-      if (row[r] >= 0) {
+      // the per-row scalars are worked out by the group's first lane and handed round
+      float b1 = 1.0f, b2 = 1.0f, cc = 1.0f;
+      if (row[r] >= 0 && sub == 0) {
         // state_step = state_step + 1 (per row), sparse_optim.py:624-626
         const float t = step[row[r]] + 1.0f;
-        bias1[r] = 1.0f - powf(p.beta1, t);
-        bias2[r] = 1.0f - powf(p.beta2, t);
-        c[r] = cnt ? (float)__ldg(cnt + i) : 1.0f;  // grad / cnt, sparse_optim.py:608-611
+        b1 = 1.0f - powf(p.beta1, t);
+        b2 = 1.0f - powf(p.beta2, t);
+        cc = cnt ? (float)__ldg(cnt + i) : 1.0f;  // grad / cnt, sparse_optim.py:608-611
       }
+      bias1[r] = __shfl_sync(0xffffffffu, b1, leader);
+      bias2[r] = __shfl_sync(0xffffffffu, b2, leader);
+      c[r] = __shfl_sync(0xffffffffu, cc, leader);
     }
     if (VEC4) {
       for (int64_t k = sub; k < (dim >> 2); k += G) {
@@ -140,6 +148,98 @@ __global__ void __launch_bounds__(kBlock) sparse_adam_kernel(
       }
     }
   }
+}
+
+// The vector path of both update rules (dim % 4 == 0, 16-byte aligned rows).  A warp takes 32
+// rows per round: lane l works out the per-row scalars of row l once (for Adam the two bias
+// corrections, whose powf would otherwise be issued for every 16 bytes of the row), then the
+// warp walks the rows, G lanes per row and kOptRows rows in flight, taking the scalars by
+// shuffle.  Divisions by per-row scalars are multiplications by their reciprocals (one ulp,
+// far inside the 1e-5 the parity tests allow); the element-wise division and the square root
+// are IEEE.
+template <typename E, bool ADAM>
+__global__ void __launch_bounds__(kBlock, 3) sparse_update_vec_kernel(
+    const int64_t* __restrict__ ids, const float* __restrict__ grads,
+    const int64_t* __restrict__ cnt, int64_t n, const int64_t* __restrict__ n_dev, int64_t dim,
+    RowMap map, const float* __restrict__ step, float* __restrict__ s0, float* __restrict__ s1,
+    E* __restrict__ emb, AdamParams p, int glog2) {
+  n = effective_n(n, n_dev);
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int G = 1 << glog2, rpp = 32 >> glog2;
+  const int sub = lane & (G - 1), which = lane >> glog2;
+  const int64_t vpr = dim >> 2;
+  for (int64_t base = warp * 32; base < n; base += nwarps * 32) {
+    const int64_t i = base + lane;
+    const int64_t row = i < n ? map(__ldg(ids + i)) : -1;
+    float ra = 1.0f, rb = 1.0f, rc = 1.0f;
+    if (row >= 0) {
+      if (ADAM) {
+        // state_step = state_step + 1 (per row), sparse_optim.py:624-626
+        const float t = step[row] + 1.0f;
+        ra = 1.0f / (1.0f - powf(p.beta1, t));
+        rb = 1.0f / (1.0f - powf(p.beta2, t));
+      }
+      if (cnt) rc = 1.0f / (float)__ldg(cnt + i);  // grad / cnt, sparse_optim.py:608-611
+    }
+    for (int pass = 0; pass < G; pass += kOptRows) {
+      int64_t rw[kOptRows];
+      float a[kOptRows], b[kOptRows], c[kOptRows];
+      const float4* gp[kOptRows];
+#pragma unroll
+      for (int u = 0; u < kOptRows; ++u) {
+        const int q = ((pass + u) * rpp + which) & 31;
+        rw[u] = __shfl_sync(0xffffffffu, row, q);
+        a[u] = __shfl_sync(0xffffffffu, ra, q);
+        b[u] = __shfl_sync(0xffffffffu, rb, q);
+        c[u] = __shfl_sync(0xffffffffu, rc, q);
+        if (pass + u >= G) rw[u] = -1;
+        gp[u] = reinterpret_cast<const float4*>(grads + (base + q) * dim);
+      }
+      for (int64_t k = sub; k < vpr; k += G) {
+        float4 gg[kOptRows], mm[kOptRows], vv[kOptRows], ee[kOptRows];
+#pragma unroll
+        for (int u = 0; u < kOptRows; ++u)
+          if (rw[u] >= 0) {
+            gg[u] = __ldg(gp[u] + k);
+            mm[u] = reinterpret_cast<const float4*>(s0 + rw[u] * dim)[k];
+            if (ADAM) vv[u] = reinterpret_cast<const float4*>(s1 + rw[u] * dim)[k];
+            ee[u] = EmbIO<E>::load4(emb + rw[u] * dim + 4 * k);
+          }
+#pragma unroll
+        for (int u = 0; u < kOptRows; ++u)
+          if (rw[u] >= 0) {
+            float* g4 = reinterpret_cast<float*>(&gg[u]);
+            float* m4 = reinterpret_cast<float*>(&mm[u]);
+            float* v4 = reinterpret_cast<float*>(&vv[u]);
+            float* e4 = reinterpret_cast<float*>(&ee[u]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float g = cnt ? g4[j] * c[u] : g4[j];
+              if (ADAM) {
+                m4[j] = p.beta1 * m4[j] + p.one_minus_beta1 * g;
+                v4[j] = p.beta2 * v4[j] + p.one_minus_beta2 * (g * g);
+                e4[j] -= p.lr * (m4[j] * a[u]) / (sqrtf(v4[j] * b[u]) + p.eps);  // sparse_optim.py:654-655
+              } else {
+                m4[j] += g * g;
+                e4[j] -= p.lr * g / (sqrtf(m4[j]) + p.eps);
+              }
+            }
+            reinterpret_cast<float4*>(s0 + rw[u] * dim)[k] = mm[u];
+            if (ADAM) reinterpret_cast<float4*>(s1 + rw[u] * dim)[k] = vv[u];
+            EmbIO<E>::store4(emb + rw[u] * dim + 4 * k, ee[u]);
+          }
+      }
+    }
+  }
+}
+
+int grid_for_warps(int64_t n) {
+  int64_t blocks = ceil_div(ceil_div(n, 32) * 32, kBlock);
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  return blocks < 1 ? 1 : (int)blocks;
 }
 
 // step[row] += 1 for every updated row; a launch of its own so that no lane of
@@ -239,11 +339,15 @@ int hb_sparse_adam(const int64_t* ids, const float* grads, const int64_t* cnt, i
 #define HB_ADAM(E, V)                                                                          \
   HB_LAUNCH((sparse_adam_kernel<E, V>), grid, kBlock, 0, st, ids, grads, cnt, n, n_dev, dim, map, \
             step, mem, power, (E*)emb, p, glog2)
+#define HB_ADAM_VEC(E)                                                                         \
+  HB_LAUNCH((sparse_update_vec_kernel<E, true>), grid_for_warps(n), kBlock, 0, st, ids, grads, cnt, n, \
+            n_dev, dim, map, step, mem, power, (E*)emb, p, glog2)
   if (emb_elem_bytes == 4) {
-    if (vec4) HB_ADAM(float, true); else HB_ADAM(float, false);
+    if (vec4) HB_ADAM_VEC(float); else HB_ADAM(float, false);
   } else {
-    if (vec4) HB_ADAM(__half, true); else HB_ADAM(__half, false);
+    if (vec4) HB_ADAM_VEC(__half); else HB_ADAM(__half, false);
   }
+#undef HB_ADAM_VEC
 #undef HB_ADAM
   HB_LAUNCH(bump_step_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, ids, n, n_dev, map, step);
   return HB_OK;
@@ -268,11 +372,16 @@ int hb_sparse_adagrad(const int64_t* ids, const float* grads, const int64_t* cnt
 #define HB_ADAGRAD(E, V)                                                                        \
   HB_LAUNCH((sparse_adagrad_kernel<E, V>), grid, kBlock, 0, st, ids, grads, cnt, n, n_dev, dim, \
             map, state_sum, (E*)emb, (float)lr, (float)eps, glog2)
+  const AdamParams p{(float)lr, 0.f, 0.f, (float)eps, 0.f, 0.f};
+#define HB_ADAGRAD_VEC(E)                                                                       \
+  HB_LAUNCH((sparse_update_vec_kernel<E, false>), grid_for_warps(n), kBlock, 0, st, ids, grads, cnt, n, \
+            n_dev, dim, map, nullptr, state_sum, nullptr, (E*)emb, p, glog2)
   if (emb_elem_bytes == 4) {
-    if (vec4) HB_ADAGRAD(float, true); else HB_ADAGRAD(float, false);
+    if (vec4) HB_ADAGRAD_VEC(float); else HB_ADAGRAD(float, false);
   } else {
-    if (vec4) HB_ADAGRAD(__half, true); else HB_ADAGRAD(__half, false);
+    if (vec4) HB_ADAGRAD_VEC(__half); else HB_ADAGRAD(__half, false);
   }
+#undef HB_ADAGRAD_VEC
 #undef HB_ADAGRAD
   return HB_OK;
 }
