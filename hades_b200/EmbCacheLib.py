@@ -668,3 +668,28 @@ def cudaUniqueSegSum(ids, grads, cnt=None, mean: bool = False, id_bits: int = 64
         return uniq, sums, counts, num
     u = int(num.item())
     return uniq[:u], sums[:u], counts[:u]
+
+
+def cudaMergeSortedSlabs(ids, rows, cnt, seg_counts, seg_cap: int, mean: bool = True):
+    """unique_grads over receive slabs whose segments each hold strictly ascending ids (what the
+    peer-memory push delivers): (unique ids, rows, counts, num_unique on the device), full-size
+    buffers, no host read.  Same results as ``cudaUniqueSegSum(..., seg_counts=...)`` without
+    its sort."""
+    _check(ids.is_cuda and ids.dtype == torch.int64, "ids is a CUDA int64 tensor")
+    _check(rows.dtype == torch.float32 and rows.dim() == 2 and rows.size(0) == ids.numel(),
+           "rows is fp32 [len(ids), dim]")
+    _check(seg_cap > 0 and ids.numel() % seg_cap == 0, "ids holds whole segments of seg_cap entries")
+    n, dim = ids.numel(), rows.size(1)
+    num_seg = n // seg_cap
+    dev = ids.device
+    uniq = torch.empty(n, dtype=torch.int64, device=dev)
+    out = torch.empty((n, dim), dtype=torch.float32, device=dev)
+    counts = torch.empty(n, dtype=torch.int64, device=dev)
+    num = torch.zeros(1, dtype=torch.int64, device=dev)
+    lib = _lib.load()
+    ws = _lib.workspace(lib.hb_merge_sorted_slabs_workspace_bytes(num_seg, seg_cap))
+    _lib.check(lib.hb_merge_sorted_slabs_f32(ids.contiguous().data_ptr(), rows.contiguous().data_ptr(),
+                                             _lib.ptr(cnt), seg_counts.data_ptr(), num_seg, int(seg_cap), dim,
+                                             int(mean), uniq.data_ptr(), out.data_ptr(), counts.data_ptr(),
+                                             num.data_ptr(), ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
+    return uniq, out, counts, num

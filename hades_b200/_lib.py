@@ -90,6 +90,8 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_a2a_fence": (_int, [_p, _p]),
     "hb_wait_flag": (_int, [_p, C.c_uint64, _p]),
     "hb_a2a_recv_view": (_int, [_p, _int, _p, _p, _p, _p, _p]),
+    "hb_merge_sorted_slabs_workspace_bytes": (_sz, [_i64, _i64]),
+    "hb_merge_sorted_slabs_f32": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _int, _p, _p, _p, _p, _p, _sz, _p]),
     "hb_peer_table_create": (_int, [_int, _int, _i64, _i64, _p]),
     "hb_peer_table_handle_bytes": (_sz, []),
     "hb_peer_table_export_handle": (_int, [_p, _p]),

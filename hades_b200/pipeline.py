@@ -155,8 +155,9 @@ class EmbeddingPath:
     def _owner_update_from_slabs(self, parity: int) -> None:
         """Owner side after a peer-memory push: merge the senders' slabs and update."""
         r_ids, r_rows, r_cnt, seg_counts = self.px.received(parity)
+        # every slab holds the sorted unique hot ids of its sender (stable bucketing): a merge
         self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=self.id_bits,
-                        seg_counts=seg_counts, seg_cap=self.px.cap)
+                        seg_counts=seg_counts, seg_cap=self.px.cap, sorted_segments=True)
 
     def _backward_core(self, ids, grads, locs) -> StepStats:
         """Everything of the backward path that runs every step (no host read unless NCCL

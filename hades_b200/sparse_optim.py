@@ -17,7 +17,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .EmbCacheLib import _check, cudaBucketPack, cudaUniqueSegSum
+from .EmbCacheLib import _check, cudaBucketPack, cudaMergeSortedSlabs, cudaUniqueSegSum
 
 
 def only_unique_grads(idx: torch.Tensor, grad: torch.Tensor, id_bits: int = 64):
@@ -69,6 +69,16 @@ def swap_gradients(idics, grads, partition_range, num_parts, num_trainers_per_pa
     if world == 1 or not dist.is_initialized():
         return ids_p, rows_p, cnt_p
     return exchange_packed(ids_p, rows_p, cnt_p, counts, group)
+
+
+def _merge_duplicates(idx, grad, cnt, n_dev, id_bits, seg_counts, seg_cap, sorted_segments):
+    """unique_grads (sparse_optim.py:611) without reading the unique count on the host."""
+    if sorted_segments and seg_counts is not None:
+        idx, grad, _, n_dev = cudaMergeSortedSlabs(idx, grad, cnt, seg_counts, seg_cap, mean=True)
+    else:
+        idx, grad, _, n_dev = cudaUniqueSegSum(idx, grad, cnt, mean=True, id_bits=id_bits, sync=False,
+                                               n_dev=n_dev, seg_counts=seg_counts, seg_cap=seg_cap)
+    return idx, grad, n_dev
 
 
 class ShardedEmbedding:
@@ -124,15 +134,14 @@ class SparseAdam(_SparseOptimizer):
         self.state_power = torch.zeros((emb.rows, emb.embedding_dim), dtype=torch.float32, device=dev)
 
     def update(self, idx, grad, cnt=None, is_unique: bool = False, n_dev: torch.Tensor | None = None,
-               id_bits: int = 64, seg_counts: torch.Tensor | None = None, seg_cap: int = 0) -> None:
+               id_bits: int = 64, seg_counts: torch.Tensor | None = None, seg_cap: int = 0,
+               sorted_segments: bool = False) -> None:
         """seg_counts / seg_cap: idx, grad, cnt are the receive slabs of a peer-memory exchange
-        (segment s holds seg_counts[s] valid rows); only with is_unique=False."""
+        (segment s holds seg_counts[s] valid rows); only with is_unique=False.  sorted_segments:
+        every segment holds strictly ascending ids (merge instead of sort)."""
         idx, grad, cnt = self._args(idx, grad, cnt)
         if not is_unique:
-            # unique_grads (sparse_optim.py:611), without reading the unique count on the host
-            idx, grad, _, n_dev = cudaUniqueSegSum(idx, grad, cnt, mean=True, id_bits=id_bits,
-                                                   sync=False, n_dev=n_dev, seg_counts=seg_counts,
-                                                   seg_cap=seg_cap)
+            idx, grad, n_dev = _merge_duplicates(idx, grad, cnt, n_dev, id_bits, seg_counts, seg_cap, sorted_segments)
             cnt = None
         lib = _lib.load()
         w = self.emb.weight
@@ -154,15 +163,14 @@ class SparseAdagrad(_SparseOptimizer):
                                      device=emb.weight.device)
 
     def update(self, idx, grad, cnt=None, is_unique: bool = False, n_dev: torch.Tensor | None = None,
-               id_bits: int = 64, seg_counts: torch.Tensor | None = None, seg_cap: int = 0) -> None:
+               id_bits: int = 64, seg_counts: torch.Tensor | None = None, seg_cap: int = 0,
+               sorted_segments: bool = False) -> None:
         """seg_counts / seg_cap: idx, grad, cnt are the receive slabs of a peer-memory exchange
-        (segment s holds seg_counts[s] valid rows); only with is_unique=False."""
+        (segment s holds seg_counts[s] valid rows); only with is_unique=False.  sorted_segments:
+        every segment holds strictly ascending ids (merge instead of sort)."""
         idx, grad, cnt = self._args(idx, grad, cnt)
         if not is_unique:
-            # unique_grads (sparse_optim.py:611), without reading the unique count on the host
-            idx, grad, _, n_dev = cudaUniqueSegSum(idx, grad, cnt, mean=True, id_bits=id_bits,
-                                                   sync=False, n_dev=n_dev, seg_counts=seg_counts,
-                                                   seg_cap=seg_cap)
+            idx, grad, n_dev = _merge_duplicates(idx, grad, cnt, n_dev, id_bits, seg_counts, seg_cap, sorted_segments)
             cnt = None
         lib = _lib.load()
         w = self.emb.weight

@@ -461,6 +461,21 @@ int hb_wait_flag(const uint64_t* flag, uint64_t value, hb_stream_t stream);
 int hb_a2a_recv_view(hb_a2a_t* a, int parity, int64_t** ids, void** rows, int64_t** cnt,
                      int64_t** counts, int64_t* cap_rows);
 
+/* unique_grads (python/EmbCache/sparse_optim.py:142-157) on the owner for slabs whose
+ * ids are strictly ascending within each segment, which is what hb_a2a_push delivers
+ * when every rank sends the sorted unique ids of its own aggregation: a merge of
+ * num_seg sorted lists instead of a sort.  Layout and results as hb_unique_segsum_f32
+ * with seg_counts (ids/cnt [num_seg][seg_cap], rows [num_seg][seg_cap][dim]; unique ids
+ * ascending, rows added in segment order, mean != 0 divides by the count, which starts
+ * from one when cnt is given; out_counts nullable).  Segments that are not ascending
+ * give undefined results. */
+size_t hb_merge_sorted_slabs_workspace_bytes(int64_t num_seg, int64_t seg_cap);
+int hb_merge_sorted_slabs_f32(const int64_t* ids, const float* rows, const int64_t* cnt /* nullable */,
+                              const int64_t* seg_counts, int64_t num_seg, int64_t seg_cap, int64_t dim,
+                              int mean, int64_t* uniq_ids, float* out_rows,
+                              int64_t* out_counts /* nullable */, int64_t* num_unique,
+                              void* workspace, size_t workspace_bytes, hb_stream_t stream);
+
 /* ------------------------------------------------------------------------- */
 /* Table sharded over the GPUs of one box, readable from every GPU.            */
 /* ------------------------------------------------------------------------- */

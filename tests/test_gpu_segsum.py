@@ -108,3 +108,41 @@ def test_unique_segsum_with_class_split(cuda_lib, oracle_mod, n, dim):
         gi, gr, gc = (t[: cc[k]].cpu().numpy() for t in outs[k])
         assert np.array_equal(gi, u[sel]) and np.array_equal(gc, c[sel])
         np.testing.assert_allclose(gr, s[sel], rtol=1e-4, atol=1e-8)
+
+
+@pytest.mark.parametrize("num_seg,cap,dim,universe", [(1, 500, 128, 2000), (2, 3000, 128, 5000), (3, 1000, 20, 1500),
+                                                       (8, 2000, 64, 6000), (8, 40, 7, 60), (40, 64, 32, 300)])
+@pytest.mark.parametrize("with_cnt,mean", [(True, True), (False, True), (False, False)])
+def test_merge_sorted_slabs_equals_sorting_path(cuda_lib, oracle_mod, num_seg, cap, dim, universe, with_cnt, mean):
+    """Slabs of ascending unique ids (ragged, one of them empty): the merge gives what the
+    sorting path gives on the same slabs, and what the oracle's unique_grads gives."""
+    from hades_b200 import EmbCacheLib as E
+
+    rng = np.random.default_rng(num_seg * 1000 + cap)
+    ids = np.full((num_seg, cap), -1, np.int64)
+    rows = rng.standard_normal((num_seg, cap, dim)).astype(np.float32)
+    cnt = rng.integers(1, 6, (num_seg, cap)).astype(np.int64)
+    counts = rng.integers(0, cap + 1, num_seg).astype(np.int64)
+    counts[rng.integers(0, num_seg)] = 0 if num_seg > 1 else cap
+    counts = np.minimum(counts, universe)
+    if num_seg > 2:
+        counts[1] = min(cap, universe)  # one full slab
+    for s in range(num_seg):
+        ids[s, :counts[s]] = np.sort(rng.choice(universe, counts[s], replace=False))
+    d_ids, d_rows = torch.from_numpy(ids.reshape(-1)).cuda(), torch.from_numpy(rows.reshape(-1, dim)).cuda()
+    d_cnt = torch.from_numpy(cnt.reshape(-1)).cuda() if with_cnt else None
+    d_counts = torch.from_numpy(counts).cuda()
+    u, r, c, num = E.cudaMergeSortedSlabs(d_ids, d_rows, d_cnt, d_counts, cap, mean=mean)
+    u2, r2, c2, num2 = E.cudaUniqueSegSum(d_ids, d_rows, d_cnt, mean=mean, id_bits=20, sync=False,
+                                          seg_counts=d_counts, seg_cap=cap)
+    k = int(num.item())
+    assert k == int(num2.item())
+    assert torch.equal(u[:k], u2[:k]) and torch.equal(c[:k], c2[:k])
+    # the sorting path may add a long run in another order
+    torch.testing.assert_close(r[:k], r2[:k], rtol=1e-5, atol=1e-5)
+    valid = np.concatenate([np.arange(s * cap, s * cap + counts[s]) for s in range(num_seg)]).astype(np.int64)
+    if valid.size and mean:
+        wu, wm, _ = oracle_mod.unique_grads(ids.reshape(-1)[valid], rows.reshape(-1, dim)[valid],
+                                            cnt.reshape(-1)[valid] if with_cnt else None)
+        assert np.array_equal(u[:k].cpu().numpy(), wu)
+        np.testing.assert_allclose(r[:k].cpu().numpy(), wm, rtol=1e-5, atol=1e-6)
