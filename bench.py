@@ -537,7 +537,8 @@ def run_exchange(args) -> None:
     n, dim = int(1_048_576 * args.scale), 64
     table_rows = int(240_000_000 * args.scale)
     rng = synth.rng_for(4, rank, 0)
-    ids_np = synth.ZipfSampler(table_rows, 1.1).unique_ids(rng, n)  # distinct ids, Zipf(1.1) without replacement
+    # distinct ids, Zipf(1.1) without replacement, ascending as a rank's local aggregation emits them
+    ids_np = np.sort(synth.ZipfSampler(table_rows, 1.1).unique_ids(rng, n))
     ids = torch.from_numpy(ids_np).to(dev)
     rows = torch.empty((n, dim), device=dev).normal_(0, 1e-3)
     cnt = torch.ones(n, dtype=torch.int64, device=dev)
@@ -565,7 +566,8 @@ def run_exchange(args) -> None:
         parity = px.push(ids, rows, cnt)
         px.fence()
         r_ids, r_rows, r_cnt, seg = px.received(parity)
-        opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=id_bits, seg_counts=seg, seg_cap=px.cap)
+        opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=id_bits, seg_counts=seg, seg_cap=px.cap,
+                   sorted_segments=True)
 
     W, K = max(args.warmup, 3), max(args.steps, 1)
     out = {}

@@ -118,26 +118,34 @@ __global__ void __launch_bounds__(kBlock) merge_sum_kernel(
     }
     const float denom = (float)(cnt ? csum + 1 : csum);  // counts start from ones when cnt is given
     const int len = (int)(p1 - p0);
+    // the k loops are uniform across the warp (k0), so that every lane takes part in the shuffles
     if (VEC4) {
-      for (int64_t k = lane; k < (dim >> 2); k += 32) {
+      const int64_t vpr = dim >> 2;
+      for (int64_t k0 = 0; k0 < vpr; k0 += 32) {
+        const int64_t k = k0 + lane;
+        const bool on = k < vpr;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int q = 0; q < len; ++q) {
           const int64_t eq = __shfl_sync(0xffffffffu, q < 32 ? e : e2, q & 31);
-          const float4 v = __ldg(reinterpret_cast<const float4*>(rows + eq * dim) + k);
-          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          if (on) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(rows + eq * dim) + k);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          }
         }
         if (mean) { acc.x /= denom; acc.y /= denom; acc.z /= denom; acc.w /= denom; }
-        reinterpret_cast<float4*>(out_rows + r * dim)[k] = acc;
+        if (on) reinterpret_cast<float4*>(out_rows + r * dim)[k] = acc;
       }
     } else {
-      for (int64_t k = lane; k < dim; k += 32) {
+      for (int64_t k0 = 0; k0 < dim; k0 += 32) {
+        const int64_t k = k0 + lane;
+        const bool on = k < dim;
         float acc = 0.f;
         for (int q = 0; q < len; ++q) {
           const int64_t eq = __shfl_sync(0xffffffffu, q < 32 ? e : e2, q & 31);
-          acc += __ldg(rows + eq * dim + k);
+          if (on) acc += __ldg(rows + eq * dim + k);
         }
         if (mean) acc /= denom;
-        out_rows[r * dim + k] = acc;
+        if (on) out_rows[r * dim + k] = acc;
       }
     }
     if (lane == 0) {
