@@ -646,8 +646,8 @@ def run_hot_aggregation(args) -> None:
             parity = px.push(h_ids, h_rows, h_cnt, state["cc"][1:2])
             px.fence()
             r_ids, r_rows, r_cnt, seg = px.received(parity)
-            state["merged"] = E.cudaUniqueSegSum(r_ids, r_rows, r_cnt, mean=True, id_bits=id_bits, sync=False,
-                                                 seg_counts=seg, seg_cap=px.cap)
+            # every slab holds its sender's ascending unique hot ids: a merge, not a sort
+            state["merged"] = E.cudaMergeSortedSlabs(r_ids, r_rows, r_cnt, seg, px.cap, mean=True)
 
     W, K = max(args.warmup, 3), max(args.steps, 1)
     out = {}
