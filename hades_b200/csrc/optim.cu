@@ -162,7 +162,8 @@ __global__ void __launch_bounds__(kBlock, 3) sparse_update_vec_kernel(
     const int64_t* __restrict__ ids, const float* __restrict__ grads,
     const int64_t* __restrict__ cnt, int64_t n, const int64_t* __restrict__ n_dev, int64_t dim,
     RowMap map, const float* __restrict__ step, float* __restrict__ s0, float* __restrict__ s1,
-    E* __restrict__ emb, AdamParams p, int glog2) {
+    E* __restrict__ emb, AdamParams p, int glog2, int rpw) {
+  // rpw: rows a warp takes per round (32, or fewer so that a short list still fills the GPU)
   n = effective_n(n, n_dev);
   const int lane = threadIdx.x & 31;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
@@ -170,9 +171,9 @@ __global__ void __launch_bounds__(kBlock, 3) sparse_update_vec_kernel(
   const int G = 1 << glog2, rpp = 32 >> glog2;
   const int sub = lane & (G - 1), which = lane >> glog2;
   const int64_t vpr = dim >> 2;
-  for (int64_t base = warp * 32; base < n; base += nwarps * 32) {
+  for (int64_t base = warp * rpw; base < n; base += nwarps * rpw) {
     const int64_t i = base + lane;
-    const int64_t row = i < n ? map(__ldg(ids + i)) : -1;
+    const int64_t row = (lane < rpw && i < n) ? map(__ldg(ids + i)) : -1;
     float ra = 1.0f, rb = 1.0f, rc = 1.0f;
     if (row >= 0) {
       if (ADAM) {
@@ -183,7 +184,7 @@ __global__ void __launch_bounds__(kBlock, 3) sparse_update_vec_kernel(
       }
       if (cnt) rc = 1.0f / (float)__ldg(cnt + i);  // grad / cnt, sparse_optim.py:608-611
     }
-    for (int pass = 0; pass < G; pass += kOptRows) {
+    for (int pass = 0; pass * rpp < rpw; pass += kOptRows) {
       int64_t rw[kOptRows];
       float a[kOptRows], b[kOptRows], c[kOptRows];
       const float4* gp[kOptRows];
@@ -194,7 +195,7 @@ __global__ void __launch_bounds__(kBlock, 3) sparse_update_vec_kernel(
         a[u] = __shfl_sync(0xffffffffu, ra, q);
         b[u] = __shfl_sync(0xffffffffu, rb, q);
         c[u] = __shfl_sync(0xffffffffu, rc, q);
-        if (pass + u >= G) rw[u] = -1;
+        if ((pass + u) * rpp + which >= rpw) rw[u] = -1;
         gp[u] = reinterpret_cast<const float4*>(grads + (base + q) * dim);
       }
       for (int64_t k = sub; k < vpr; k += G) {
@@ -235,8 +236,17 @@ __global__ void __launch_bounds__(kBlock, 3) sparse_update_vec_kernel(
   }
 }
 
-int grid_for_warps(int64_t n) {
-  int64_t blocks = ceil_div(ceil_div(n, 32) * 32, kBlock);
+// rows per warp and round: 32 unless that leaves the GPU short of warps (a list of 84k rows is
+// only 2.6k rounds of 32)
+int rows_per_warp_for(int64_t n, int glog2) {
+  const int min_rows = 32 >> glog2 > 4 ? 32 >> glog2 : 4;  // at least one pass of whole row groups
+  int rpw = 32;
+  while (rpw > min_rows && ceil_div(n, rpw) < (int64_t)sm_count() * 48) rpw >>= 1;
+  return rpw;
+}
+
+int grid_for_warps(int64_t n, int rpw) {
+  int64_t blocks = ceil_div(ceil_div(n, rpw) * 32, kBlock);
   const int64_t cap = (int64_t)sm_count() * 16;
   if (blocks > cap) blocks = cap;
   return blocks < 1 ? 1 : (int)blocks;
@@ -335,13 +345,14 @@ int hb_sparse_adam(const int64_t* ids, const float* grads, const int64_t* cnt, i
   const bool vec4 = dim % 4 == 0 && (bits & 15) == 0;
   const int glog2 = group_log2_for(vec4 ? dim / 4 : dim);
   const int grid = grid_for_groups(n, glog2);
+  const int rpw = rows_per_warp_for(n, glog2);
   cudaStream_t st = (cudaStream_t)stream;
 #define HB_ADAM(E, V)                                                                          \
   HB_LAUNCH((sparse_adam_kernel<E, V>), grid, kBlock, 0, st, ids, grads, cnt, n, n_dev, dim, map, \
             step, mem, power, (E*)emb, p, glog2)
 #define HB_ADAM_VEC(E)                                                                         \
-  HB_LAUNCH((sparse_update_vec_kernel<E, true>), grid_for_warps(n), kBlock, 0, st, ids, grads, cnt, n, \
-            n_dev, dim, map, step, mem, power, (E*)emb, p, glog2)
+  HB_LAUNCH((sparse_update_vec_kernel<E, true>), grid_for_warps(n, rpw), kBlock, 0, st, ids, grads, cnt, n, \
+            n_dev, dim, map, step, mem, power, (E*)emb, p, glog2, rpw)
   if (emb_elem_bytes == 4) {
     if (vec4) HB_ADAM_VEC(float); else HB_ADAM(float, false);
   } else {
@@ -368,14 +379,15 @@ int hb_sparse_adagrad(const int64_t* ids, const float* grads, const int64_t* cnt
   const bool vec4 = dim % 4 == 0 && (bits & 15) == 0;
   const int glog2 = group_log2_for(vec4 ? dim / 4 : dim);
   const int grid = grid_for_groups(n, glog2);
+  const int rpw = rows_per_warp_for(n, glog2);
   cudaStream_t st = (cudaStream_t)stream;
 #define HB_ADAGRAD(E, V)                                                                        \
   HB_LAUNCH((sparse_adagrad_kernel<E, V>), grid, kBlock, 0, st, ids, grads, cnt, n, n_dev, dim, \
             map, state_sum, (E*)emb, (float)lr, (float)eps, glog2)
   const AdamParams p{(float)lr, 0.f, 0.f, (float)eps, 0.f, 0.f};
 #define HB_ADAGRAD_VEC(E)                                                                       \
-  HB_LAUNCH((sparse_update_vec_kernel<E, false>), grid_for_warps(n), kBlock, 0, st, ids, grads, cnt, n, \
-            n_dev, dim, map, nullptr, state_sum, nullptr, (E*)emb, p, glog2)
+  HB_LAUNCH((sparse_update_vec_kernel<E, false>), grid_for_warps(n, rpw), kBlock, 0, st, ids, grads, cnt, n, \
+            n_dev, dim, map, nullptr, state_sum, nullptr, (E*)emb, p, glog2, rpw)
   if (emb_elem_bytes == 4) {
     if (vec4) HB_ADAGRAD_VEC(float); else HB_ADAGRAD(float, false);
   } else {
