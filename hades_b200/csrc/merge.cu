@@ -79,80 +79,90 @@ __global__ void __launch_bounds__(kBlock) merge_rank_kernel(
   src[p] = (int32_t)e;
 }
 
-// one warp per distinct id: add its rows in slab order, divide, write id / row / count
-template <bool VEC4>
+// A warp takes 32 distinct ids per round.  Lane l reads the extent of run l, adds its counts and
+// writes id and count; then the warp walks the 32 runs, G lanes per row and kRuns runs in flight,
+// adding each run's rows in slab order.  (A warp per run would spend its time waiting: nearly all
+// runs hold one or two rows.)
+constexpr int kRuns = 4;
+
+template <typename V>
+__device__ __forceinline__ void vadd(V& a, const V& b);
+template <>
+__device__ __forceinline__ void vadd<float4>(float4& a, const float4& b) {
+  a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+}
+template <>
+__device__ __forceinline__ void vadd<float>(float& a, const float& b) { a += b; }
+__device__ __forceinline__ void vdiv(float4& a, float d) { a.x /= d; a.y /= d; a.z /= d; a.w /= d; }
+__device__ __forceinline__ void vdiv(float& a, float d) { a /= d; }
+
+template <typename V>
 __global__ void __launch_bounds__(kBlock) merge_sum_kernel(
     const int64_t* __restrict__ ids, const float* __restrict__ rows, const int64_t* __restrict__ cnt,
     const int64_t* __restrict__ seg_counts, int num_seg, int64_t cap, int64_t dim, int mean,
     const int32_t* __restrict__ src, const int32_t* __restrict__ run_start,
     const int64_t* __restrict__ num_unique, int64_t* __restrict__ uniq_ids,
-    float* __restrict__ out_rows, int64_t* __restrict__ out_counts) {
+    float* __restrict__ out_rows, int64_t* __restrict__ out_counts, int glog2) {
   int64_t total = 0;
   for (int s = 0; s < num_seg; ++s) total += seg_len(seg_counts, s, cap);
   const int64_t u = *num_unique;
   const int lane = threadIdx.x & 31;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  for (int64_t r = warp; r < u; r += nwarps) {
-    const int64_t p0 = run_start[r];
-    const int64_t p1 = r + 1 < u ? (int64_t)run_start[r + 1] : total;
-    // at most num_seg (<= 64) entries: lane l holds entry p0 + l
-    int64_t e = -1, c = 0;
-    if (p0 + lane < p1) {
-      e = src[p0 + lane];
-      c = cnt ? __ldg(cnt + e) : 1;
-    }
-    int64_t csum = c;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) csum += __shfl_xor_sync(0xffffffffu, csum, o);
-    int64_t e2 = -1;  // entries 32..63 of a run (more than 32 sources)
-    if (p1 - p0 > 32) {
-      int64_t c2 = 0;
-      if (p0 + 32 + lane < p1) {
-        e2 = src[p0 + 32 + lane];
-        c2 = cnt ? __ldg(cnt + e2) : 1;
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) c2 += __shfl_xor_sync(0xffffffffu, c2, o);
-      csum += c2;
-    }
-    const float denom = (float)(cnt ? csum + 1 : csum);  // counts start from ones when cnt is given
-    const int len = (int)(p1 - p0);
-    // the k loops are uniform across the warp (k0), so that every lane takes part in the shuffles
-    if (VEC4) {
-      const int64_t vpr = dim >> 2;
-      for (int64_t k0 = 0; k0 < vpr; k0 += 32) {
-        const int64_t k = k0 + lane;
-        const bool on = k < vpr;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int q = 0; q < len; ++q) {
-          const int64_t eq = __shfl_sync(0xffffffffu, q < 32 ? e : e2, q & 31);
-          if (on) {
-            const float4 v = __ldg(reinterpret_cast<const float4*>(rows + eq * dim) + k);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-          }
-        }
-        if (mean) { acc.x /= denom; acc.y /= denom; acc.z /= denom; acc.w /= denom; }
-        if (on) reinterpret_cast<float4*>(out_rows + r * dim)[k] = acc;
-      }
-    } else {
-      for (int64_t k0 = 0; k0 < dim; k0 += 32) {
-        const int64_t k = k0 + lane;
-        const bool on = k < dim;
-        float acc = 0.f;
-        for (int q = 0; q < len; ++q) {
-          const int64_t eq = __shfl_sync(0xffffffffu, q < 32 ? e : e2, q & 31);
-          if (on) acc += __ldg(rows + eq * dim + k);
-        }
-        if (mean) acc /= denom;
-        if (on) out_rows[r * dim + k] = acc;
-      }
-    }
-    if (lane == 0) {
-      uniq_ids[r] = __ldg(ids + e);
+  const int G = 1 << glog2, rpp = 32 >> glog2;
+  const int sub = lane & (G - 1), which = lane >> glog2;
+  const int64_t vpr = dim * 4 / (int64_t)sizeof(V);  // vectors per row
+  const V* vrows = reinterpret_cast<const V*>(rows);
+  V* vout = reinterpret_cast<V*>(out_rows);
+  for (int64_t r0 = warp * 32; r0 < u; r0 += nwarps * 32) {
+    const int64_t r = r0 + lane;
+    int p0 = 0, len = 0;
+    float denom = 1.0f;
+    if (r < u) {
+      p0 = run_start[r];
+      len = (int)((r + 1 < u ? (int64_t)run_start[r + 1] : total) - p0);
+      int64_t csum = 0;
+      for (int j = 0; j < len; ++j) csum += cnt ? __ldg(cnt + src[p0 + j]) : 1;
+      denom = (float)(cnt ? csum + 1 : csum);  // counts start from ones when cnt is given
+      uniq_ids[r] = __ldg(ids + src[p0]);
       if (out_counts) out_counts[r] = csum + ((cnt && mean) ? 1 : 0);
     }
+    for (int pass = 0; pass < G; pass += kRuns) {
+      int P0[kRuns], L[kRuns];
+      float D[kRuns];
+      int64_t R[kRuns];
+#pragma unroll
+      for (int t = 0; t < kRuns; ++t) {
+        const int q = ((pass + t) * rpp + which) & 31;
+        P0[t] = __shfl_sync(0xffffffffu, p0, q);
+        L[t] = __shfl_sync(0xffffffffu, len, q);
+        D[t] = __shfl_sync(0xffffffffu, denom, q);
+        if (pass + t >= G) L[t] = 0;
+        R[t] = r0 + q;
+      }
+      for (int64_t k = sub; k < vpr; k += G) {
+        V acc[kRuns];
+#pragma unroll
+        for (int t = 0; t < kRuns; ++t)
+          if (L[t] > 0) acc[t] = __ldg(vrows + (int64_t)src[P0[t]] * vpr + k);
+#pragma unroll
+        for (int t = 0; t < kRuns; ++t)
+          for (int j = 1; j < L[t]; ++j) vadd(acc[t], __ldg(vrows + (int64_t)src[P0[t] + j] * vpr + k));
+#pragma unroll
+        for (int t = 0; t < kRuns; ++t)
+          if (L[t] > 0) {
+            if (mean) vdiv(acc[t], D[t]);
+            vout[R[t] * vpr + k] = acc[t];
+          }
+      }
+    }
   }
+}
+
+int group_log2_for(int64_t units) {
+  int g = 0;
+  while ((1 << g) < units && g < 5) ++g;
+  return g;
 }
 
 }  // namespace
@@ -190,16 +200,17 @@ int hb_merge_sorted_slabs_f32(const int64_t* ids, const float* rows, const int64
   HB_CUDA(cub::DeviceSelect::Flagged(p.select_temp, p.select_temp_bytes, thrust::counting_iterator<int32_t>(0),
                                      p.flag, p.run_start, num_unique, (int)n, st));
   count_library_launches(2);
-  int64_t blocks = ceil_div(n * 32, kBlock);
+  int64_t blocks = ceil_div(n, kBlock);
   const int64_t cap_blocks = (int64_t)sm_count() * 8;
   if (blocks > cap_blocks) blocks = cap_blocks;
   const bool vec4 = dim % 4 == 0 && ((((uintptr_t)rows | (uintptr_t)out_rows)) & 15) == 0;
+  const int glog2 = group_log2_for(vec4 ? dim / 4 : dim);
   if (vec4)
-    HB_LAUNCH(merge_sum_kernel<true>, (int)blocks, kBlock, 0, st, ids, rows, cnt, seg_counts, (int)num_seg, seg_cap,
-              dim, mean, p.src, p.run_start, num_unique, uniq_ids, out_rows, out_counts);
+    HB_LAUNCH(merge_sum_kernel<float4>, (int)blocks, kBlock, 0, st, ids, rows, cnt, seg_counts, (int)num_seg,
+              seg_cap, dim, mean, p.src, p.run_start, num_unique, uniq_ids, out_rows, out_counts, glog2);
   else
-    HB_LAUNCH(merge_sum_kernel<false>, (int)blocks, kBlock, 0, st, ids, rows, cnt, seg_counts, (int)num_seg, seg_cap,
-              dim, mean, p.src, p.run_start, num_unique, uniq_ids, out_rows, out_counts);
+    HB_LAUNCH(merge_sum_kernel<float>, (int)blocks, kBlock, 0, st, ids, rows, cnt, seg_counts, (int)num_seg,
+              seg_cap, dim, mean, p.src, p.run_start, num_unique, uniq_ids, out_rows, out_counts, glog2);
   return HB_OK;
 }
 
