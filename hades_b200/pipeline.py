@@ -197,17 +197,32 @@ class EmbeddingPath:
         if self.world == 1:
             # one trainer: every flushed row is its own (is_unique=True, sparse_optim.py:405-421)
             self.opt.update(f_ids, f_rows, f_cnt, is_unique=True)
-        else:
-            r_ids, r_rows, r_cnt, r_n, _ = self._exchange(f_ids, f_rows, f_cnt, None)
-            self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, n_dev=None if r_n is None else r_n[:1],
-                            id_bits=self.id_bits)
-        self._fence_shards()  # the refill reads what every owner has just written
-        if n:
-            if self.shared is not None:
-                fresh = self.shared.gather(f_ids)
-            else:
+            if n:
                 fresh = torch.empty((n, self.dim), dtype=self.table.dtype, device=f_ids.device)
                 E.cudaFetch2(self.table, f_ids, fresh)
+                self.cold.insert(f_ids, fresh)
+            return n
+        import torch.distributed as dist
+
+        p_ids, p_rows, p_cnt, counts = E.cudaBucketPack(f_ids, f_rows, f_cnt, self.world)
+        r_ids, r_rows, r_cnt, (sent, received) = exchange_packed(p_ids, p_rows, p_cnt, counts, self.group,
+                                                                 return_splits=True)
+        self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=self.id_bits)
+        if self.shared is not None:
+            # The exchange in reverse: every owner returns the rows it now holds, in the order
+            # the ids arrived, so the refill costs one local gather and one all-to-all instead of
+            # row-by-row reads over NVLink.  A rank has all its rows back only after every
+            # owner's update, so this is also the fence before the next read of a shard.
+            w = self.opt.emb.weight
+            back = torch.empty((r_ids.numel(), self.dim), dtype=w.dtype, device=w.device)
+            E.cudaFetch2(w, r_ids // self.world, back)
+            fresh = torch.empty((sum(sent), self.dim), dtype=w.dtype, device=w.device)
+            dist.all_to_all_single(fresh, back, sent, received, group=self.group)
+            if n:
+                self.cold.insert(p_ids[:n], fresh)
+        elif n:
+            fresh = torch.empty((n, self.dim), dtype=self.table.dtype, device=f_ids.device)
+            E.cudaFetch2(self.table, f_ids, fresh)
             self.cold.insert(f_ids, fresh)
         return n
 

@@ -32,13 +32,14 @@ def unique_grads(idx: torch.Tensor, grad: torch.Tensor, cnt: torch.Tensor | None
     return ids, vals
 
 
-def exchange_packed(ids, rows, cnt, counts, group=None):
+def exchange_packed(ids, rows, cnt, counts, group=None, return_splits: bool = False):
     """Deliver owner-bucketed rows to their owners.  ids/rows/cnt hold the buckets back to back
     (bucket b = rows for rank b), counts[b] their sizes (int64, on the same device).  Returns
     (ids, rows, cnt) received by this rank, source ranks in order.  Ragged
     ``all_to_all_single`` calls as the reference's swap_gradients makes them
     (sparse_optim.py:73-118); the split sizes are read on the host, as there (:55,:77).
-    Works on CUDA tensors over NCCL and on CPU tensors over gloo."""
+    Works on CUDA tensors over NCCL and on CPU tensors over gloo.  return_splits: also return
+    (rows sent to each rank, rows received from each rank), for an exchange in reverse."""
     out_counts = torch.empty_like(counts)
     dist.all_to_all_single(out_counts, counts, group=group)
     in_splits, out_splits = counts.tolist(), out_counts.tolist()
@@ -53,6 +54,8 @@ def exchange_packed(ids, rows, cnt, counts, group=None):
     if cnt is not None:
         r_cnt = torch.empty(total, dtype=cnt.dtype, device=ids.device)
         dist.all_to_all_single(r_cnt, cnt[:sent], out_splits, in_splits, group=group)
+    if return_splits:
+        return r_ids, r_rows, r_cnt, (in_splits, out_splits)
     return r_ids, r_rows, r_cnt
 
 
