@@ -60,7 +60,8 @@ class StagingTable:
                                         ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
         if not sync:
             return out_ids, out_rows, out_cnt, counts
-        total = int(counts.sum().item())
+        self.last_counts_host = counts.tolist()  # the one host read of a flush
+        total = sum(self.last_counts_host)
         return out_ids[:total], out_rows[:total], out_cnt[:total], counts
 
 

@@ -190,7 +190,7 @@ class EmbeddingPath:
         """Stale cold rows leave through the same exchange; their cache entries are evicted by
         the flush (server.py:413) and come back with the current table rows, as the next
         forward pass of the reference would re-insert them (server.py:499-544)."""
-        f_ids, f_rows, f_cnt, _ = self.cold.flush_remote(sync=True)
+        f_ids, f_rows, f_cnt, counts = self.cold.flush_remote(sync=True)
         n = f_ids.numel()
         if n == 0 and self.world == 1:
             return 0
@@ -204,9 +204,10 @@ class EmbeddingPath:
             return n
         import torch.distributed as dist
 
-        p_ids, p_rows, p_cnt, counts = E.cudaBucketPack(f_ids, f_rows, f_cnt, self.world)
-        r_ids, r_rows, r_cnt, (sent, received) = exchange_packed(p_ids, p_rows, p_cnt, counts, self.group,
-                                                                 return_splits=True)
+        # the flush already leaves its rows bucketed by owner (num_clients = world)
+        r_ids, r_rows, r_cnt, (sent, received) = exchange_packed(
+            f_ids, f_rows, f_cnt, counts, self.group, return_splits=True,
+            counts_host=self.cold.remote.last_counts_host)
         self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=self.id_bits)
         if self.shared is not None:
             # The exchange in reverse: every owner returns the rows it now holds, in the order
@@ -219,7 +220,7 @@ class EmbeddingPath:
             fresh = torch.empty((sum(sent), self.dim), dtype=w.dtype, device=w.device)
             dist.all_to_all_single(fresh, back, sent, received, group=self.group)
             if n:
-                self.cold.insert(p_ids[:n], fresh)
+                self.cold.insert(f_ids, fresh)
         elif n:
             fresh = torch.empty((n, self.dim), dtype=self.table.dtype, device=f_ids.device)
             E.cudaFetch2(self.table, f_ids, fresh)

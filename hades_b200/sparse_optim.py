@@ -32,7 +32,8 @@ def unique_grads(idx: torch.Tensor, grad: torch.Tensor, cnt: torch.Tensor | None
     return ids, vals
 
 
-def exchange_packed(ids, rows, cnt, counts, group=None, return_splits: bool = False):
+def exchange_packed(ids, rows, cnt, counts, group=None, return_splits: bool = False,
+                    counts_host: list | None = None):
     """Deliver owner-bucketed rows to their owners.  ids/rows/cnt hold the buckets back to back
     (bucket b = rows for rank b), counts[b] their sizes (int64, on the same device).  Returns
     (ids, rows, cnt) received by this rank, source ranks in order.  Ragged
@@ -42,7 +43,8 @@ def exchange_packed(ids, rows, cnt, counts, group=None, return_splits: bool = Fa
     (rows sent to each rank, rows received from each rank), for an exchange in reverse."""
     out_counts = torch.empty_like(counts)
     dist.all_to_all_single(out_counts, counts, group=group)
-    in_splits, out_splits = counts.tolist(), out_counts.tolist()
+    in_splits = counts.tolist() if counts_host is None else list(counts_host)  # sizes the caller already read
+    out_splits = out_counts.tolist()
     total, sent = sum(out_splits), sum(in_splits)
     r_ids = torch.empty(total, dtype=ids.dtype, device=ids.device)
     dist.all_to_all_single(r_ids, ids[:sent], out_splits, in_splits, group=group)
