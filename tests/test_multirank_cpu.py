@@ -53,6 +53,18 @@ def _worker(rank, world, port, empty_rank):
     assert np.array_equal(r_rows.numpy(), np.concatenate(want_rows))
     assert np.array_equal(r_cnt.numpy(), np.concatenate(want_cnt))
     assert (r_ids.numpy() % world == rank).all()
+    # the exchange in reverse (refill after a flush): every owner answers each id it received
+    # with a row; the answers come back in the order the ids were sent
+    again = exchange_packed(torch.from_numpy(p_ids), torch.from_numpy(p_rows), torch.from_numpy(p_cnt),
+                            torch.from_numpy(counts), return_splits=True, counts_host=counts.tolist())
+    assert np.array_equal(again[0].numpy(), r_ids.numpy())
+    sent, received = again[3]
+    assert sent == counts.tolist() and sum(received) == r_ids.numel()
+    answer = (again[0].double() * 3 + rank).reshape(-1, 1).repeat(1, 2)      # a function of (id, owner)
+    back = torch.empty((sum(sent), 2), dtype=torch.float64)
+    dist.all_to_all_single(back, answer, sent, received)
+    want_back = np.stack([p_ids * 3.0 + p_ids % world] * 2, axis=1)
+    assert np.array_equal(back.numpy(), want_back[:sum(sent)])
     dist.barrier()
     dist.destroy_process_group()
 
