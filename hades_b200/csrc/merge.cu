@@ -116,25 +116,27 @@ __global__ void __launch_bounds__(kBlock) merge_sum_kernel(
   V* vout = reinterpret_cast<V*>(out_rows);
   for (int64_t r0 = warp * 32; r0 < u; r0 += nwarps * 32) {
     const int64_t r = r0 + lane;
-    int p0 = 0, len = 0;
+    int p0 = 0, len = 0, first = 0;
     float denom = 1.0f;
     if (r < u) {
       p0 = run_start[r];
       len = (int)((r + 1 < u ? (int64_t)run_start[r + 1] : total) - p0);
+      first = src[p0];  // handed to the row loop by shuffle: its loads then wait for nothing
       int64_t csum = 0;
       for (int j = 0; j < len; ++j) csum += cnt ? __ldg(cnt + src[p0 + j]) : 1;
       denom = (float)(cnt ? csum + 1 : csum);  // counts start from ones when cnt is given
-      uniq_ids[r] = __ldg(ids + src[p0]);
+      uniq_ids[r] = __ldg(ids + first);
       if (out_counts) out_counts[r] = csum + ((cnt && mean) ? 1 : 0);
     }
     for (int pass = 0; pass < G; pass += kRuns) {
-      int P0[kRuns], L[kRuns];
+      int P0[kRuns], L[kRuns], F[kRuns];
       float D[kRuns];
       int64_t R[kRuns];
 #pragma unroll
       for (int t = 0; t < kRuns; ++t) {
         const int q = ((pass + t) * rpp + which) & 31;
         P0[t] = __shfl_sync(0xffffffffu, p0, q);
+        F[t] = __shfl_sync(0xffffffffu, first, q);
         L[t] = __shfl_sync(0xffffffffu, len, q);
         D[t] = __shfl_sync(0xffffffffu, denom, q);
         if (pass + t >= G) L[t] = 0;
@@ -144,7 +146,7 @@ __global__ void __launch_bounds__(kBlock) merge_sum_kernel(
         V acc[kRuns];
 #pragma unroll
         for (int t = 0; t < kRuns; ++t)
-          if (L[t] > 0) acc[t] = __ldg(vrows + (int64_t)src[P0[t]] * vpr + k);
+          if (L[t] > 0) acc[t] = __ldg(vrows + (int64_t)F[t] * vpr + k);
 #pragma unroll
         for (int t = 0; t < kRuns; ++t)
           for (int j = 1; j < L[t]; ++j) vadd(acc[t], __ldg(vrows + (int64_t)src[P0[t] + j] * vpr + k));
