@@ -62,18 +62,21 @@ class ZipfSampler:
     def ids(self, rng: np.random.Generator, n: int) -> np.ndarray:
         return rank_to_id(self.ranks(rng, n), self.num_ids)
 
-    def unique_ids(self, rng: np.random.Generator, n: int) -> np.ndarray:
-        """n distinct ids, Zipf-weighted without replacement (draw, de-duplicate in draw
-        order, top up)."""
-        seen: list[np.ndarray] = []
+    def unique_ranks(self, rng: np.random.Generator, n: int) -> np.ndarray:
+        """n distinct popularity ranks, Zipf-weighted without replacement (draw, de-duplicate
+        in draw order, top up)."""
         have = np.empty(0, dtype=np.int64)
         while have.size < n:
             draw = self.ranks(rng, int((n - have.size) * 1.5) + 16)
             cat = np.concatenate([have, draw])
             _, first = np.unique(cat, return_index=True)
             have = cat[np.sort(first)]
-        del seen
-        return rank_to_id(have[:n], self.num_ids)
+        return have[:n]
+
+    def unique_ids(self, rng: np.random.Generator, n: int, id_space: int | None = None) -> np.ndarray:
+        """n distinct ids; id_space: spread the ranks over a larger id space than the ranking
+        (a ranking truncated to its head keeps the CDF small for very large tables)."""
+        return rank_to_id(self.unique_ranks(rng, n), self.num_ids if id_space is None else id_space)
 
 
 def hot_ids(num_ids: int, count: int) -> np.ndarray:
