@@ -9,8 +9,11 @@
 It strings together what ``DistEmb.__call__`` (python/EmbCache/dist_emb.py:167-292),
 ``DistembSparseGradOptimizer.step`` (python/EmbCache/sparse_optim.py:212-448) and the cache
 server loop (python/EmbCache/server.py:259-298) do across three processes in the reference.
-Everything stays on the current CUDA stream; the only host reads are the exchange sizes when
-NCCL carries the exchange (world > 1) and the flushed-row count on flush steps.
+Everything is ordered on the current CUDA stream (the cold accumulate forks to a side stream and
+joins before the step ends); the only host reads are the exchange sizes when NCCL carries the
+exchange (world > 1) and the flushed-row counts on flush steps.  With several GPUs the table
+exists once, sharded by owner and readable from every GPU (``peer_table.PeerTable``): cache misses
+read the owner's current row.
 """
 from __future__ import annotations
 
@@ -40,7 +43,8 @@ class EmbeddingPath:
                  optimizer, rank: int = 0, world: int = 1, flush_every: int = 8, id_bits: int = 64,
                  lookup_mode: int = E.LOOKUP_SETASSOC, mover: int = E.MOVER_AUTO,
                  touch_lru: bool = True, group=None, peer_exchange=None):
-        """table: backing rows for cache misses, [num_nodes, dim] fp32 on this GPU.
+        """table: backing rows for cache misses, [num_nodes, dim] fp32 on this GPU; None when the
+        optimiser's shard is a ``PeerTable`` (misses then read the owners' shards).
         class_table: int8 per node, HOT or COLD.  optimizer: SparseAdam / SparseAdagrad on this
         rank's shard (owner = id % world)."""
         self.table, self.class_table, self.cold, self.opt = table, class_table, cold, optimizer
