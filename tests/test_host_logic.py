@@ -71,3 +71,55 @@ def test_synthetic_generators_are_seeded_and_sane():
     assert rows.dtype == np.float32 and abs(float(rows.std()) - 0.01) < 1e-3
     small = synth.scaled(synth.CONFIG2, 0.01)
     assert small.table_rows == 200_000 and small.batch == 20_000 and small.dim == 128
+
+
+class _FakePath:
+    """Stands in for EmbeddingPath: records what the layer and the optimiser hand over."""
+
+    def __init__(self, nodes=50, dim=4):
+        self.table = torch.arange(nodes * dim, dtype=torch.float32).reshape(nodes, dim)
+        self.num_nodes, self.dim, self.row_dtype, self.device = nodes, dim, torch.float32, torch.device("cpu")
+        self.shared, self.calls = None, []
+
+    def forward(self, ids, out_rows=None, defer_touch=False):
+        assert defer_touch
+        return self.table[ids].clone(), ids * 10, torch.ones_like(ids, dtype=torch.bool)
+
+    def backward(self, ids, grads, locs):
+        self.calls.append((ids.clone(), grads.clone(), locs.clone()))
+        return "stats"
+
+
+def test_layer_trace_and_optimizer_step_follow_the_reference_protocol():
+    """zero_grad only arms the clearing of the trace at the next step (sparse_optim.py:350-354,
+    468-470); a step hands the concatenated (ids, grads, slots) of every traced call to the path."""
+    from hades_b200.dist_emb import DistEmb, DistembSparseGradOptimizer
+
+    path = _FakePath()
+    layer = DistEmb(path)
+    opt = DistembSparseGradOptimizer([layer.sparse_emb])
+    a, b = torch.tensor([3, 5, 3]), torch.tensor([7])
+    ha, hb = layer(a), layer(b)
+    assert ha.requires_grad and ha.is_leaf and torch.equal(ha.detach(), path.table[a])
+    opt.zero_grad()
+    (ha.sum() * 2 + hb.sum() * 3).backward()
+    opt.step()
+    ids, grads, locs = path.calls[-1]
+    assert torch.equal(ids, torch.tensor([3, 5, 3, 7])) and torch.equal(locs, ids * 10)
+    assert torch.equal(grads, torch.cat([torch.full((3, 4), 2.0), torch.full((1, 4), 3.0)]))
+    assert layer.sparse_emb.trace == [] and opt.last_stats[layer.sparse_emb.name] == "stats"
+    # without zero_grad the trace stays and the next step applies it again, as in the reference
+    hc = layer(torch.tensor([1]))
+    hc.sum().backward()
+    opt.step()
+    opt.step()
+    assert len(path.calls) == 3 and torch.equal(path.calls[1][0], path.calls[2][0])
+    # calls whose rows received no gradient are left out; no_grad calls are not traced
+    opt.zero_grad()
+    opt.step()
+    with torch.no_grad():
+        layer(torch.tensor([2]))
+    assert layer.sparse_emb.trace == []
+    layer(torch.tensor([4]))
+    opt.step()
+    assert len(path.calls) == 4
