@@ -445,6 +445,11 @@ size_t sort_temp_bytes(int64_t n) {
   return b64 > b32 ? b64 : b32;
 }
 
+// Items per thread of the class/position partition.  Only the first U of the n positions hold a
+// unique id, so few of its CTAs have work: small tiles spread that work over more of them (each
+// item of a tile costs a dependent table read and three barriers in turn).
+constexpr int kClassItems = 2;
+
 struct SegPlan {
   int64_t *k0, *k1;
   uint32_t *p0, *p1;
@@ -486,7 +491,7 @@ SegPlan make_plan(void* ws, int64_t n, int64_t dim) {
   s.dclass = cv.take<int8_t>(m + 1);
   s.dpos = cv.take<int32_t>(m + 1);
   s.uniq_tmp = cv.take<int64_t>(m + 1);
-  s.class_ws_bytes = partition_workspace_bytes(m, 3, kPartItemsMax);
+  s.class_ws_bytes = partition_workspace_bytes(m, 3, kClassItems);
   s.class_ws = cv.take<char>(s.class_ws_bytes);
   s.raw_counts = cv.take<unsigned long long>(m);
   s.chunk = choose_chunk(m);
@@ -628,7 +633,7 @@ int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* 
   if (split) {
     ClassOfRunPolicy cp{uniq_ids, num_unique, split->table, s.dclass, s.dpos, n,
                         {split->out_ids[0], split->out_ids[1], split->out_ids[2]}};
-    rc = run_partition(cp, n, 3, s.class_ws, s.class_ws_bytes, split->class_counts, st, kPartItemsMax);
+    rc = run_partition(cp, n, 3, s.class_ws, s.class_ws_bytes, split->class_counts, st, kClassItems);
     if (rc != HB_OK) return rc;
   }
   // 3./4. column passes
