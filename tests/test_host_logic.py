@@ -71,6 +71,17 @@ def test_synthetic_generators_are_seeded_and_sane():
     assert rows.dtype == np.float32 and abs(float(rows.std()) - 0.01) < 1e-3
     small = synth.scaled(synth.CONFIG2, 0.01)
     assert small.table_rows == 200_000 and small.batch == 20_000 and small.dim == 128
+    # a ranking cut to its head, spread over a larger id space (configuration 4's 2.4e8 ids)
+    w = synth.ZipfSampler(5000, 1.1).unique_ids(synth.rng_for(4, 1), 2000, id_space=10**7)
+    assert np.unique(w).size == 2000 and w.max() >= 5000 and w.max() < 10**7
+    # the sampled 2-hop frontier of configuration 5, on a small R-MAT graph
+    cfg = synth.scaled_rmat(synth.CONFIG5, 14, seeds=16)
+    f1, f2 = synth.rmat_frontier(cfg, synth.rng_for(5, 0)), synth.rmat_frontier(cfg, synth.rng_for(5, 0))
+    assert np.array_equal(f1, f2) and f1.size == cfg.batch == 16 * (1 + 25 + 250)
+    assert f1.min() >= 0 and f1.max() < cfg.num_nodes
+    # R-MAT favours vertices with few one-bits: the sampled neighbours have fewer than uniform ids would
+    pop = np.array([bin(int(v)).count("1") for v in f1[16:]])
+    assert pop.mean() < 0.5 * cfg.bits - 1.0
 
 
 class _FakePath:
