@@ -134,3 +134,24 @@ def test_layer_trace_and_optimizer_step_follow_the_reference_protocol():
     layer(torch.tensor([4]))
     opt.step()
     assert len(path.calls) == 4
+
+
+def test_presampled_hotness_class_table_and_cache_fill():
+    from hades_b200 import hotness as H
+
+    batches = [torch.tensor([1, 2, 2, 7]), torch.tensor([2, 7, 9]), torch.tensor([7]), torch.tensor([0, 7])]
+    heat = H.presampling(batches, 12)
+    want = torch.zeros(12)
+    want[[0, 1, 9]] = 0.25
+    want[2] = 0.5   # twice in the first batch still counts once for that batch
+    want[7] = 1.0
+    assert torch.equal(heat, want)
+    local = torch.zeros(12, dtype=torch.bool)
+    local[[0, 7]] = True
+    table = H.class_table(heat, 0.5, local)
+    assert table.dtype == torch.int8
+    assert table.tolist() == [0, 2, 1, 2, 2, 2, 2, 0, 2, 2, 2, 2]
+    assert H.class_table(heat, 0.5).tolist() == [2, 2, 1, 2, 2, 2, 2, 1, 2, 2, 2, 2]
+    assert H.hottest_ids(heat, table == 2, 3).tolist() == [1, 9, 3]     # ties by ascending id
+    thr = H.flush_thresholds(heat)                                       # ceil(1 / (0.001 + heat)) capped at 100
+    assert thr[7].item() == 1 and thr[2].item() == 2 and thr[1].item() == 4 and thr[3].item() == 100

@@ -65,6 +65,15 @@ def _worker(rank, world, port, empty_rank):
     dist.all_to_all_single(back, answer, sent, received)
     want_back = np.stack([p_ids * 3.0 + p_ids % world] * 2, axis=1)
     assert np.array_equal(back.numpy(), want_back[:sum(sent)])
+    # presampled hotness: heats and batch counts are summed over the ranks
+    from hades_b200 import hotness as H
+
+    mine = [torch.tensor([rank, 5]), torch.tensor([5, 6 + rank])] + ([torch.tensor([9])] if rank == 0 else [])
+    heat = H.presampling(mine, 10)
+    want = torch.zeros(10)
+    want[0] = want[1] = want[6] = want[7] = want[9] = 1.0   # 5 batches in all
+    want[5] = 4.0
+    assert torch.allclose(heat, want / 5.0)
     dist.barrier()
     dist.destroy_process_group()
 
