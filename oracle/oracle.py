@@ -347,6 +347,131 @@ def unique_grads(idx, grad, cnt=None):
 
 
 # ---------------------------------------------------------------------------------------
+# the reference's own CUDA operators (GPU box only)
+# ---------------------------------------------------------------------------------------
+class RefCuda:
+    """The reference's CUDA operators (src/cuda/ops.h:9-41), compiled from its own .cu files into
+    oracle/_ref/libhades_ref_cuda.so by oracle/build_oracle.py.  Arguments are torch CUDA tensors;
+    the kernels run on the legacy default stream like in the reference, so every call here
+    synchronises the device before and after.  ``available()`` is False when the library did not
+    build or did not travel, or when there is no CUDA device."""
+
+    _lib = None
+
+    @classmethod
+    def _load(cls):
+        if cls._lib is None:
+            so = HERE / "_ref" / "libhades_ref_cuda.so"
+            if not so.exists():
+                return None
+            import torch
+
+            if not torch.cuda.is_available():
+                return None
+            cls._lib = C.CDLL(str(so))
+            for name in ("fetch", "fetch2", "fetch_with_cache2", "set", "set_with_cache", "combine", "split",
+                         "reminder", "binary_search", "binary_search2"):
+                getattr(cls._lib, f"ref_cuda_{name}").restype = None
+        return cls._lib
+
+    @classmethod
+    def available(cls) -> bool:
+        try:
+            return cls._load() is not None
+        except OSError:
+            return False
+
+    @staticmethod
+    def _p(t):
+        return C.c_void_p(t.data_ptr())
+
+    @staticmethod
+    def _dim(t):
+        return C.c_int64(t.size(1) if t.dim() == 2 else 0)
+
+    @classmethod
+    def _call(cls, name, *args):
+        import torch
+
+        torch.cuda.synchronize()
+        getattr(cls._load(), f"ref_cuda_{name}")(*args)
+        torch.cuda.synchronize()
+
+    @classmethod
+    def fetch(cls, src, src_index, dst, dst_index):
+        cls._call("fetch", cls._p(src), C.c_int64(src.size(0)), cls._p(src_index), cls._p(dst),
+                  C.c_int64(dst.size(0)), cls._p(dst_index), C.c_int64(src_index.numel()), cls._dim(src),
+                  C.c_int(src.element_size()), C.c_int(src_index.element_size()))
+
+    @classmethod
+    def fetch2(cls, src, src_index, dst):
+        cls._call("fetch2", cls._p(src), C.c_int64(src.size(0)), cls._p(src_index), cls._p(dst),
+                  C.c_int64(src_index.numel()), cls._dim(src), C.c_int(src.element_size()),
+                  C.c_int(src_index.element_size()))
+
+    @classmethod
+    def fetch_with_cache2(cls, backing, cached, src_index, index_map, dst):
+        cls._call("fetch_with_cache2", cls._p(backing), C.c_int64(backing.size(0)), cls._p(cached),
+                  C.c_int64(cached.size(0)), cls._p(src_index), cls._p(index_map), cls._p(dst),
+                  C.c_int64(src_index.numel()), cls._dim(backing), C.c_int(backing.element_size()),
+                  C.c_int(src_index.element_size()))
+
+    @classmethod
+    def set(cls, src, dst, dst_index):
+        cls._call("set", cls._p(src), cls._p(dst), C.c_int64(dst.size(0)), cls._p(dst_index),
+                  C.c_int64(dst_index.numel()), cls._dim(src), C.c_int(src.element_size()),
+                  C.c_int(dst_index.element_size()))
+
+    @classmethod
+    def set_with_cache(cls, src, backing, cached, dst_index, index_map):
+        cls._call("set_with_cache", cls._p(src), cls._p(backing), C.c_int64(backing.size(0)), cls._p(cached),
+                  C.c_int64(cached.size(0)), cls._p(dst_index), cls._p(index_map), C.c_int64(dst_index.numel()),
+                  cls._dim(src), C.c_int(src.element_size()), C.c_int(dst_index.element_size()))
+
+    @classmethod
+    def combine(cls, src, dst, dst_index):
+        cls._call("combine", cls._p(src), cls._p(dst), C.c_int64(dst.size(0)), cls._p(dst_index),
+                  C.c_int64(dst_index.numel()), cls._dim(src), C.c_int(src.element_size()),
+                  C.c_int(dst_index.element_size()))
+
+    @classmethod
+    def split(cls, ids, mask):
+        import torch
+
+        outs = [torch.zeros(ids.numel(), dtype=torch.bool, device=ids.device) for _ in range(3)]
+        cls._call("split", cls._p(ids), C.c_int64(ids.numel()), cls._p(mask), C.c_int64(mask.numel()),
+                  cls._p(outs[0]), cls._p(outs[1]), cls._p(outs[2]))
+        return outs
+
+    @classmethod
+    def reminder(cls, ids, g):
+        import torch
+
+        out = torch.empty_like(ids)
+        cls._call("reminder", cls._p(ids), C.c_int64(ids.numel()), C.c_int64(g), cls._p(out),
+                  C.c_int(ids.element_size()))
+        return out
+
+    @classmethod
+    def binary_search(cls, ids, range_partition, g):
+        import torch
+
+        out = torch.empty_like(ids)
+        cls._call("binary_search", cls._p(ids), C.c_int64(ids.numel()), cls._p(range_partition),
+                  C.c_int64(range_partition.numel()), C.c_int64(g), cls._p(out), C.c_int(ids.element_size()))
+        return out
+
+    @classmethod
+    def binary_search2(cls, values, sorted_range):
+        import torch
+
+        out = torch.empty_like(values)
+        cls._call("binary_search2", cls._p(values), C.c_int64(values.numel()), cls._p(sorted_range),
+                  C.c_int64(sorted_range.numel()), cls._p(out), C.c_int(values.element_size()))
+        return out
+
+
+# ---------------------------------------------------------------------------------------
 # cold-gradient staging table: python/EmbCache/server.py
 # ---------------------------------------------------------------------------------------
 def flush_thresholds(hotness):

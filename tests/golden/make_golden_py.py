@@ -4,7 +4,8 @@ on CPU tensors.  The reference package imports DGL and its compiled extension at
 neither is needed by these two functions, so DGL is stubbed and ``EmbCacheLib`` is served by this
 repository's mirror (which is not called on this path).
 
-Run where the reference checkout is present:  python tests/golden/make_golden_py.py
+Run where the reference checkout is present:
+    HADES_REFERENCE_ROOT=<checkout> python tests/golden/make_golden_py.py
 """
 from __future__ import annotations
 
@@ -17,7 +18,15 @@ import numpy as np
 import torch
 
 ROOT = Path(__file__).resolve().parents[2]
-REFERENCE = Path(os.environ.get("HADES_REFERENCE_ROOT", "/root/reference"))
+sys.path.insert(0, str(ROOT))
+
+from oracle.build_oracle import reference_root  # noqa: E402
+
+# the reference checkout: first argument, else $HADES_REFERENCE_ROOT, else a checkout named
+# `reference` beside this repository
+REFERENCE = reference_root(sys.argv[1] if len(sys.argv) > 1 else None)
+if REFERENCE is None:
+    raise SystemExit("set HADES_REFERENCE_ROOT (or pass the checkout as the first argument)")
 OUT = Path(__file__).resolve().parent / "aggregation_golden.npz"
 
 
