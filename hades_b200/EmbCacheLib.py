@@ -169,17 +169,19 @@ class IndexCache:
 
     def cuda_touch_lru_runs(self, locs: torch.Tensor, runs=None, n_dev: torch.Tensor | None = None) -> None:
         """LRU ageing for a batch grouped in runs of equal ids (no sort).  runs: the
-        ``RunsDesc`` returned by ``cudaUniqueSegSum(..., want_runs=True)`` for the ids that
-        were looked up, still valid (no other call has used the workspace since); None: the
-        batch holds each id once (every position is its own run)."""
+        ``BatchRuns`` of ``cudaRunsBuild`` (or the ``RunsDesc`` returned by
+        ``cudaUniqueSegSum(..., want_runs=True)``, valid until another call uses the shared
+        workspace) for the ids that were looked up; None: the batch holds each id once (every
+        position is its own run)."""
         n = locs.numel()
         if runs is None:
             _lib.check(self._lib.hb_index_touch_lru_runs(self._h, locs.data_ptr(), None, None, n, None, n,
                                                          _lib.ptr(n_dev), _lib.stream_ptr()))
         else:
+            runs = getattr(runs, "desc", runs)  # a BatchRuns or its RunsDesc
+            cap = _lib.ptr(n_dev) if n_dev is not None else runs.n_dev
             _lib.check(self._lib.hb_index_touch_lru_runs(self._h, locs.data_ptr(), runs.perm, runs.run_start,
-                                                         n, runs.num_runs, n, _lib.ptr(n_dev),
-                                                         _lib.stream_ptr()))
+                                                         n, runs.num_runs, n, cap, _lib.stream_ptr()))
 
     def cuda_lookup_found(self, ids: torch.Tensor, mode: int | None = None):
         """(slots, found mask) in one launch."""
@@ -619,6 +621,7 @@ def cudaUniqueSegSumSplit(ids, grads, table, keep=(True, True, True), caps=(None
     num = torch.zeros(1, dtype=torch.int64, device=dev)
     desc = _lib.ClassSplitDesc()
     desc.table = table.data_ptr()
+    desc.table_len = table.numel()
     for c in range(3):
         desc.out_ids[c] = outs[c][0].data_ptr() if outs[c] else None
         desc.out_rows[c] = outs[c][1].data_ptr() if outs[c] else None
@@ -634,6 +637,145 @@ def cudaUniqueSegSumSplit(ids, grads, table, keep=(True, True, True), caps=(None
     if want_runs:
         return outs, class_counts, num, runs
     return outs, class_counts, num
+
+
+class BatchRuns:
+    """A batch of ids grouped into runs of equal ids (``hb_runs_t``): the sort of a step, done
+    once and used by the forward fetch, the LRU ageing, the miss list and the backward
+    aggregation.  Keeps its own workspace (the grouping must outlive other library calls).
+
+    desc: the ``RunsDesc`` for C calls; num_unique: device int64[1]; class_counts: device
+    int64[3] and class_ids[c]: the distinct ids of class c, ascending (None when that class is
+    not kept or no class table was given)."""
+
+    def __init__(self, ids, desc, ws, num_unique, class_counts, class_ids, uniq_ids):
+        self.ids, self.desc, self.ws = ids, desc, ws
+        self.num_unique, self.class_counts, self.class_ids, self.uniq_ids = num_unique, class_counts, class_ids, uniq_ids
+        self.n = ids.numel()
+        self._version = ids._version
+
+    def matches(self, ids: torch.Tensor) -> bool:
+        """True when `ids` is the tensor these runs were built from, unchanged since."""
+        return (ids.data_ptr() == self.ids.data_ptr() and ids.numel() == self.n
+                and ids._version == self._version)
+
+
+def cudaRunsBuild(ids, id_bits: int = 64, table=None, keep=(True, True, True), caps=(None, None, None),
+                  n_dev: torch.Tensor | None = None, seg_counts: torch.Tensor | None = None, seg_cap: int = 0,
+                  ws: torch.Tensor | None = None, want_uniq: bool = False) -> BatchRuns:
+    """Sort (id, position) once and number the runs of equal ids (torch.unique of
+    python/EmbCache/sparse_optim.py:133).  table: int8 class per node; then the distinct ids of
+    every kept class are compacted into ``class_ids[c]`` (caps[c]: a proven bound on their
+    number).  ws: a uint8 CUDA tensor to hold the grouping (allocated when None or too small)."""
+    _check(ids.is_cuda and ids.dtype == torch.int64, "ids is a CUDA int64 tensor")
+    ids = ids.contiguous()
+    n, dev = ids.numel(), ids.device
+    lib = _lib.load()
+    need = lib.hb_runs_workspace_bytes(n)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+    class_ids, class_counts = [None, None, None], None
+    arr = None
+    if table is not None:
+        _check(table.dtype == torch.int8, "table.dtype == int8")
+        for c in range(3):
+            if keep[c]:
+                m = n if caps[c] is None else min(n, int(caps[c]))
+                class_ids[c] = torch.empty(max(m, 1), dtype=torch.int64, device=dev)
+        class_counts = torch.zeros(3, dtype=torch.int64, device=dev)
+        arr = (C.c_void_p * 3)(*[(t.data_ptr() if t is not None else None) for t in class_ids])
+    num = torch.zeros(1, dtype=torch.int64, device=dev)
+    uniq = torch.empty(max(n, 1), dtype=torch.int64, device=dev) if want_uniq else None
+    desc = _lib.RunsDesc()
+    _lib.check(lib.hb_runs_build(ids.data_ptr(), n, _lib.ptr(n_dev), _lib.ptr(seg_counts), int(seg_cap),
+                                 int(id_bits), _lib.ptr(table), table.numel() if table is not None else 0,
+                                 arr, _lib.ptr(class_counts), _lib.ptr(uniq), num.data_ptr(), ws.data_ptr(),
+                                 ws.numel(), C.byref(desc), _lib.stream_ptr()))
+    return BatchRuns(ids, desc, ws, num, class_counts, class_ids, uniq)
+
+
+def cudaLookupFetchRuns(index: IndexCache, runs: BatchRuns, cache_rows, backing_rows=None, peer_table=None,
+                        out_rows=None, mode: int | None = None):
+    """``cudaLookupFetch`` over a batch that ``cudaRunsBuild`` sorted: (out_rows, locs, found) at
+    the batch positions, every distinct id read once per warp that meets it.  Misses read
+    backing_rows on this GPU, or the owners' shards of peer_table (``peer_table.PeerTable``)."""
+    n = runs.n
+    dev = runs.ids.device
+    if out_rows is None:
+        out_rows = torch.empty((n, cache_rows.size(1)), dtype=cache_rows.dtype, device=dev)
+    _check(out_rows.size(1) == cache_rows.size(1), "out_rows.size(1) == cache_rows.size(1)")
+    if backing_rows is not None:
+        _check(backing_rows.size(1) == cache_rows.size(1), "backing_rows.size(1) == cache_rows.size(1)")
+    locs = torch.empty(n, dtype=torch.int64, device=dev)
+    found = torch.empty(n, dtype=torch.bool, device=dev)
+    lib = _lib.load()
+    _lib.check(lib.hb_lookup_fetch_runs(index.handle, C.byref(runs.desc), _dev_ptr(cache_rows, "cache_rows"),
+                                        None if backing_rows is None else _dev_ptr(backing_rows, "backing_rows"),
+                                        0 if backing_rows is None else backing_rows.size(0),
+                                        None if peer_table is None else peer_table.handle,
+                                        _row_bytes(cache_rows), out_rows.data_ptr(), locs.data_ptr(),
+                                        found.data_ptr(), index.lookup_mode if mode is None else mode,
+                                        _lib.stream_ptr()))
+    return out_rows, locs, found
+
+
+def cudaSegSumRuns(runs: BatchRuns, grads, cnt=None, mean: bool = False, split_keep=None, caps=(None, None, None),
+                   ws: torch.Tensor | None = None):
+    """The aggregation of ``cudaUniqueSegSum`` over existing runs (the ids of ``grads`` are the ids
+    the runs were built from).  split_keep=None: returns (sums [n, dim], counts [n]) in the order
+    of ``runs.uniq_ids``.  split_keep=(k0, k1, k2) (runs built with a class table): returns
+    [(rows, cnt) | None] * 3, the per-id sums and counts of class c at the positions of
+    ``runs.class_ids[c]``."""
+    _check(grads.dtype == torch.float32 and grads.dim() == 2 and grads.size(0) == runs.n,
+           "grads is fp32 [len(ids), dim]")
+    n, dim, dev = runs.n, grads.size(1), grads.device
+    lib = _lib.load()
+    need = lib.hb_segsum_runs_workspace_bytes(n, dim)
+    if ws is None:
+        ws = _lib.workspace(need)
+    _check(ws.numel() >= need, "workspace holds hb_segsum_runs_workspace_bytes")
+    grads = grads.contiguous()
+    if split_keep is None:
+        sums = torch.empty((max(n, 1), dim), dtype=torch.float32, device=dev)
+        counts = torch.empty(max(n, 1), dtype=torch.int64, device=dev)
+        _lib.check(lib.hb_segsum_runs_f32(C.byref(runs.desc), grads.data_ptr(), _lib.ptr(cnt), dim, int(mean),
+                                          sums.data_ptr(), counts.data_ptr(), None, ws.data_ptr(), ws.numel(),
+                                          _lib.stream_ptr()))
+        return sums, counts
+    outs = []
+    desc = _lib.ClassSplitDesc()
+    for c in range(3):
+        if split_keep[c]:
+            m = runs.class_ids[c].numel() if runs.class_ids[c] is not None else (
+                n if caps[c] is None else min(n, int(caps[c])))
+            outs.append((torch.empty((max(m, 1), dim), dtype=torch.float32, device=dev),
+                         torch.empty(max(m, 1), dtype=torch.int64, device=dev)))
+            desc.out_rows[c], desc.out_cnt[c] = outs[c][0].data_ptr(), outs[c][1].data_ptr()
+        else:
+            outs.append(None)
+    _lib.check(lib.hb_segsum_runs_f32(C.byref(runs.desc), grads.data_ptr(), _lib.ptr(cnt), dim, int(mean), None,
+                                      None, C.byref(desc), ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
+    return outs
+
+
+def cudaRunsMissList(runs: BatchRuns, locs, want_class: int, cap: int, ws: torch.Tensor | None = None):
+    """The distinct ids of class want_class (< 0: any) whose lookup missed, ascending, at most
+    cap: (miss_ids [cap] padded with -1, miss_src [cap] = a batch position of the id,
+    miss_count on the device).  What DistEmbeddingTensor.__call__ ships to the cache server,
+    python/EmbCache/dist_emb.py:218-259."""
+    dev = locs.device
+    lib = _lib.load()
+    need = lib.hb_runs_miss_list_workspace_bytes(runs.n)
+    if ws is None:
+        ws = _lib.workspace(need)
+    _check(ws.numel() >= need, "workspace holds hb_runs_miss_list_workspace_bytes")
+    miss_ids = torch.empty(cap, dtype=torch.int64, device=dev)
+    miss_src = torch.zeros(cap, dtype=torch.int64, device=dev)
+    count = torch.zeros(1, dtype=torch.int64, device=dev)
+    _lib.check(lib.hb_runs_miss_list(C.byref(runs.desc), locs.data_ptr(), int(want_class), int(cap),
+                                     miss_ids.data_ptr(), miss_src.data_ptr(), count.data_ptr(), ws.data_ptr(),
+                                     ws.numel(), _lib.stream_ptr()))
+    return miss_ids, miss_src, count
 
 
 def cudaUniqueSegSum(ids, grads, cnt=None, mean: bool = False, id_bits: int = 64, sync: bool = True,

@@ -70,12 +70,20 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_grad_split3": (_int, [_p, _p, _p, _p, _i64, _i64, _p, _p, _p, _p, _sz, _p]),
     "hb_unique_segsum_workspace_bytes": (_sz, [_i64, _i64]),
     "hb_unique_segsum_f32": (_int, [_p, _p, _p, _i64, _p, _p, _i64, _i64, _int, _int, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "hb_runs_workspace_bytes": (_sz, [_i64]),
+    "hb_runs_build": (_int, [_p, _i64, _p, _p, _i64, _int, _p, _i64, _p, _p, _p, _p, _p, _sz, _p, _p]),
+    "hb_segsum_runs_workspace_bytes": (_sz, [_i64, _i64]),
+    "hb_segsum_runs_f32": (_int, [_p, _p, _p, _i64, _int, _p, _p, _p, _p, _sz, _p]),
+    "hb_lookup_fetch_runs": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p, _p, _int, _p]),
+    "hb_runs_miss_list_workspace_bytes": (_sz, [_i64]),
+    "hb_runs_miss_list": (_int, [_p, _p, _int, _i64, _p, _p, _p, _p, _sz, _p]),
     "hb_staging_accumulate_cached": (_int, [_p, _p, _p, _p, _i64, _p, _p, C.c_int32, _int, _p, _p, _p]),
     "hb_staging_accumulate_direct": (_int, [_p, _p, _p, _i64, _p, _i64, _i64, _p]),
     "hb_staging_flush_workspace_bytes": (_sz, [_i64, _int]),
-    "hb_staging_flush": (_int, [_p, _p, C.c_int32, _int, _p, _p, _p, _p, _p, _sz, _p]),
+    "hb_staging_flush": (_int, [_p, _p, C.c_int32, _int, _i64, _p, _p, _p, _p, _p, _sz, _p]),
     "hb_staging_insert_workspace_bytes": (_sz, [_i64]),
     "hb_staging_insert": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p, _sz, _p]),
+    "hb_staging_insert_gather": (_int, [_p, _p, _p, _p, _p, _i64, _p, _i64, _p, _p, _sz, _p]),
     "hb_sparse_adam": (_int, [_p, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _int,
                               C.c_double, C.c_double, C.c_double, C.c_double, _p]),
     "hb_sparse_adagrad": (_int, [_p, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _p, _p, _int,
@@ -88,6 +96,7 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_a2a_push_workspace_bytes": (_sz, [_i64, _int]),
     "hb_a2a_push": (_int, [_p, _p, _p, _p, _i64, _p, _p, _p, _p, _sz, _p]),
     "hb_a2a_fence": (_int, [_p, _p]),
+    "hb_a2a_reset": (_int, [_p, _p]),
     "hb_wait_flag": (_int, [_p, C.c_uint64, _p]),
     "hb_a2a_recv_view": (_int, [_p, _int, _p, _p, _p, _p, _p]),
     "hb_merge_sorted_slabs_workspace_bytes": (_sz, [_i64, _i64]),
@@ -106,13 +115,15 @@ PROTOTYPES: dict[str, tuple] = {
 
 class RunsDesc(C.Structure):
     """hb_runs_t"""
-    _fields_ = [("perm", _p), ("run_start", _p), ("num_runs", _p), ("n", _i64)]
+    _fields_ = [("perm", _p), ("run_start", _p), ("num_runs", _p), ("n", _i64), ("keys", _p),
+                ("key_bytes", _int), ("head", _p), ("uniq_ids", _p), ("dclass", _p), ("dpos", _p),
+                ("class_counts", _p), ("n_dev", _p)]
 
 
 class ClassSplitDesc(C.Structure):
     """hb_class_split_t"""
-    _fields_ = [("table", _p), ("out_ids", _p * 3), ("out_rows", _p * 3), ("out_cnt", _p * 3),
-                ("class_counts", _p)]
+    _fields_ = [("table", _p), ("table_len", _i64), ("out_ids", _p * 3), ("out_rows", _p * 3),
+                ("out_cnt", _p * 3), ("class_counts", _p)]
 
 
 class StagingDesc(C.Structure):

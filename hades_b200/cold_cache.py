@@ -46,22 +46,28 @@ class StagingTable:
                                      self.iter_count.data_ptr(), self.iter_threshold.data_ptr(),
                                      self.slots, self.dim)
 
-    def flush(self, index: IndexCache | None, cnt_threshold: int, num_clients: int, sync: bool = True):
+    def flush(self, index: IndexCache | None, cnt_threshold: int, num_clients: int, sync: bool = True,
+              out_cap: int = 0):
+        """sync=True: one host read of the counts, outputs sliced to the rows that left.
+        sync=False: no host read; the outputs hold out_cap entries (0: one per slot) of which
+        the first min(counts.sum(), out_cap) are valid.  out_cap < slots needs num_clients == 1:
+        stale rows beyond it stay staged until the next flush."""
         lib = _lib.load()
         dev = self.grad.device
-        out_ids = torch.empty(self.slots, dtype=torch.int64, device=dev)
-        out_rows = torch.empty((self.slots, self.dim), dtype=torch.float32, device=dev)
-        out_cnt = torch.empty(self.slots, dtype=torch.int64, device=dev)
+        cap = self.slots if out_cap <= 0 else min(int(out_cap), self.slots)
+        out_ids = torch.empty(cap, dtype=torch.int64, device=dev)
+        out_rows = torch.empty((cap, self.dim), dtype=torch.float32, device=dev)
+        out_cnt = torch.empty(cap, dtype=torch.int64, device=dev)
         counts = torch.empty(num_clients, dtype=torch.int64, device=dev)
         ws = _lib.workspace(lib.hb_staging_flush_workspace_bytes(self.slots, num_clients))
         _lib.check(lib.hb_staging_flush(index.handle if index is not None else None, C.byref(self.desc),
-                                        int(cnt_threshold), int(num_clients), out_ids.data_ptr(),
+                                        int(cnt_threshold), int(num_clients), cap, out_ids.data_ptr(),
                                         out_rows.data_ptr(), out_cnt.data_ptr(), counts.data_ptr(),
                                         ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
         if not sync:
             return out_ids, out_rows, out_cnt, counts
         self.last_counts_host = counts.tolist()  # the one host read of a flush
-        total = sum(self.last_counts_host)
+        total = min(sum(self.last_counts_host), cap)
         return out_ids[:total], out_rows[:total], out_cnt[:total], counts
 
 
@@ -109,6 +115,26 @@ class ColdCache:
                                          ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
         return locs
 
+    def insert_gather(self, ids: torch.Tensor, rows: torch.Tensor, row_index: torch.Tensor,
+                      ws: torch.Tensor | None = None) -> torch.Tensor:
+        """``insert`` with the embedding of ids[i] at rows[row_index[i]]; negative ids (padding
+        of a fixed-size miss list) are ignored.  ws: scratch of at least
+        hb_staging_insert_workspace_bytes(len(ids)) bytes (the shared one when None)."""
+        _check(ids.is_cuda and ids.dtype == torch.int64 and row_index.dtype == torch.int64, "int64 CUDA tensors")
+        _check(rows.size(1) == self.dim, "rows matches dim")
+        lib = _lib.load()
+        n = ids.numel()
+        locs = torch.empty(n, dtype=torch.int64, device=ids.device)
+        need = lib.hb_staging_insert_workspace_bytes(n)
+        if ws is None:
+            ws = _lib.workspace(need)
+        _check(ws.numel() >= need, "workspace holds hb_staging_insert_workspace_bytes")
+        _lib.check(lib.hb_staging_insert_gather(self.index.handle, C.byref(self.remote.desc), ids.data_ptr(),
+                                                rows.data_ptr(), row_index.data_ptr(), n, self.emb.data_ptr(),
+                                                self.dim * self.emb.element_size(), locs.data_ptr(),
+                                                ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
+        return locs
+
     # -- server step 3 -------------------------------------------------------------------
     def accumulate_remote(self, ids: torch.Tensor, grads: torch.Tensor, n_dev: torch.Tensor | None = None,
                           touch_lru: bool = True) -> None:
@@ -133,9 +159,9 @@ class ColdCache:
                                                     _lib.stream_ptr()))
 
     # -- server step 0 -------------------------------------------------------------------
-    def flush_remote(self, sync: bool = True):
-        return self.remote.flush(self.index, self.cnt_threshold, self.num_clients, sync)
+    def flush_remote(self, sync: bool = True, out_cap: int = 0):
+        return self.remote.flush(self.index, self.cnt_threshold, self.num_clients, sync, out_cap)
 
-    def flush_local(self, sync: bool = True):
+    def flush_local(self, sync: bool = True, out_cap: int = 0):
         _check(self.local is not None, "a local staging table was configured")
-        return self.local.flush(None, self.cnt_threshold, self.num_clients, sync)
+        return self.local.flush(None, self.cnt_threshold, self.num_clients, sync, out_cap)

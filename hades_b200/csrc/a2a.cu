@@ -145,15 +145,37 @@ int hb_a2a_create(int rank, int world, int64_t cap_rows, int64_t row_bytes, hb_a
   a->cap = cap_rows;
   a->row_bytes = row_bytes;
   a->area_bytes = area_size(world, cap_rows, row_bytes);
-  for (int p = 0; p < 2; ++p) {
-    HB_CUDA(cudaMalloc(&a->local[p], a->area_bytes));
-    HB_CUDA(cudaMemset(a->local[p], 0, a->area_bytes));
+  // a failed allocation releases what the earlier ones took
+  cudaError_t e = cudaSuccess;
+  for (int p = 0; p < 2 && e == cudaSuccess; ++p) {
+    e = cudaMalloc(&a->local[p], a->area_bytes);
+    if (e == cudaSuccess) e = cudaMemset(a->local[p], 0, a->area_bytes);
     a->peer[p][rank] = a->local[p];
-    HB_CUDA(cudaMalloc(&a->dest_dev[p], sizeof(hb_a2a::Dest)));
+    if (e == cudaSuccess) e = cudaMalloc(&a->dest_dev[p], sizeof(hb_a2a::Dest));
   }
-  HB_CUDA(cudaMalloc(&a->epoch_dev, sizeof(unsigned long long)));
-  HB_CUDA(cudaMemset(a->epoch_dev, 0, sizeof(unsigned long long)));
+  if (e == cudaSuccess) e = cudaMalloc(&a->epoch_dev, sizeof(unsigned long long));
+  if (e == cudaSuccess) e = cudaMemset(a->epoch_dev, 0, sizeof(unsigned long long));
+  if (e != cudaSuccess) {
+    set_error("hb_a2a_create: allocating the receive areas (%zu bytes each) failed: %s", a->area_bytes,
+              cudaGetErrorString(e));
+    hb_a2a_destroy(a);
+    return HB_ERR_CUDA;
+  }
   *out = a;
+  return HB_OK;
+}
+
+// Back to the state after hb_a2a_connect: exchange number 0, no flag set, next push into
+// area 0.  After a fence gave up (HB_ERR_TIMEOUT: a peer never arrived) the ranks' exchange
+// numbers differ for good; once the host side has agreed that every rank is alive again,
+// all ranks call this -- with a host barrier before it (nobody is still pushing or polling)
+// and after it (nobody pushes into an area that is about to be cleared) -- and go on.
+int hb_a2a_reset(hb_a2a_t* a, hb_stream_t stream) {
+  HB_CHECK_ARG(a != nullptr, "hb_a2a_reset: null exchange");
+  cudaStream_t st = (cudaStream_t)stream;
+  HB_CUDA(cudaMemsetAsync(a->epoch_dev, 0, sizeof(unsigned long long), st));
+  for (int p = 0; p < 2; ++p) HB_CUDA(cudaMemsetAsync(a->local[p], 0, off_ids(a->world), st));  // counts and flags
+  a->parity = 0;
   return HB_OK;
 }
 

@@ -49,14 +49,12 @@ __global__ void add_walk_kernel(const int64_t* __restrict__ ids, int64_t n, int6
   const int64_t j = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (j >= n) return;
   const uint32_t line = keys[j];
-  if (j > 0 && keys[j - 1] == line) return;  // not the head of its segment
-  if ((int64_t)line >= lines) {              // unusable ids sort last
-    for (int64_t k = j; k < n; ++k) {
-      locs[vals[k]] = -1;
-      if (last_writer) last_writer[vals[k]] = 0;
-    }
+  if ((int64_t)line >= lines) {              // unusable ids (negative: padding) sort last
+    locs[vals[j]] = -1;                      // every thread answers for its own entry
+    if (last_writer) last_writer[vals[j]] = 0;
     return;
   }
+  if (j > 0 && keys[j - 1] == line) return;  // not the head of its segment
   int64_t last_k[kWays];  // sorted position of the last id of the batch placed in each way
 #pragma unroll
   for (int w = 0; w < kWays; ++w) last_k[w] = -1;

@@ -13,32 +13,28 @@
 
 #include "index.cuh"
 #include "launch.cuh"
-
-struct hb_peer_table {
-  int rank, world;
-  int64_t num_rows;    // rows of the whole table
-  int64_t rows_local;  // rows of this rank's shard
-  int64_t row_bytes;
-  char* local;
-  char* peer[64];
-  bool opened[64];
-};
+#include "shard.cuh"
 
 namespace hb {
+int* device_error_word();  // runtime.cu
+
+int make_shard_view(const hb_peer_table* t, ShardView* out) {
+  memset(out, 0, sizeof(*out));
+  out->world = t->world;
+  out->num_rows = t->num_rows;
+  for (int r = 0; r < t->world; ++r) {
+    if (!t->peer[r]) {
+      set_error("hb_peer_table: shard of rank %d is not mapped (connect or set_peer first)", r);
+      return HB_ERR_INVALID;
+    }
+    out->p[r] = t->peer[r];
+  }
+  return HB_OK;
+}
+
 namespace {
 
 constexpr int kBlock = 256;
-
-struct ShardView {
-  const char* p[64];
-  int world;
-};
-
-__device__ __forceinline__ const char* shard_row(const ShardView& s, int64_t id, int64_t row_bytes) {
-  if (s.world == 1) return s.p[0] + id * row_bytes;
-  const int64_t owner = mod_nonneg(id, s.world);
-  return s.p[owner] + ((id - owner) / s.world) * row_bytes;
-}
 
 // Copy the rows whose sources the 32 lanes hold (nullptr = none) to out rows base .. base+31,
 // 16 bytes per lane and instruction, four rows in flight.
@@ -75,7 +71,7 @@ template <int MODE>
 __global__ void __launch_bounds__(kBlock, MODE == HB_LOOKUP_SORTED ? 2 : 3) sharded_lookup_fetch_kernel(
     IndexView v, ShardView sh, const int64_t* __restrict__ ids, int64_t n,
     const char* __restrict__ cache_rows, int64_t row_bytes, char* __restrict__ out,
-    int64_t* __restrict__ locs, uint8_t* __restrict__ found) {
+    int64_t* __restrict__ locs, uint8_t* __restrict__ found, int* __restrict__ err) {
   __shared__ int64_t s_top[MODE == HB_LOOKUP_SORTED ? kTopMax : 1];
   if (MODE == HB_LOOKUP_SORTED) {
     stage_top_level(v, s_top);
@@ -94,7 +90,8 @@ __global__ void __launch_bounds__(kBlock, MODE == HB_LOOKUP_SORTED ? 2 : 3) shar
     }
     const char* src = nullptr;
     if (slot >= 0) src = cache_rows + slot * row_bytes;
-    else if (id >= 0) src = shard_row(sh, id, row_bytes);
+    else if (id >= 0 && id < sh.num_rows) src = shard_row(sh, id, row_bytes);
+    else if (id >= sh.num_rows) atomicExch(err, HB_ERR_INVALID);  // no such row: the output row stays as it was
     warp_copy_rows16(src, out + base * row_bytes, row_bytes);
   }
 }
@@ -102,7 +99,7 @@ __global__ void __launch_bounds__(kBlock, MODE == HB_LOOKUP_SORTED ? 2 : 3) shar
 // out[i] = authoritative row of ids[i] for i < min(n, *n_dev)
 __global__ void __launch_bounds__(kBlock) sharded_gather_kernel(
     ShardView sh, const int64_t* __restrict__ ids, int64_t n, const int64_t* __restrict__ n_dev,
-    int64_t row_bytes, char* __restrict__ out) {
+    int64_t row_bytes, char* __restrict__ out, int* __restrict__ err) {
   if (n_dev && *n_dev < n) n = *n_dev;
   const int lane = lane_id();
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
@@ -110,21 +107,10 @@ __global__ void __launch_bounds__(kBlock) sharded_gather_kernel(
   for (int64_t base = warp * 32; base < n; base += nwarps * 32) {
     const int64_t i = base + lane;
     const int64_t id = i < n ? __ldg(ids + i) : -1;
-    warp_copy_rows16(id >= 0 ? shard_row(sh, id, row_bytes) : nullptr, out + base * row_bytes, row_bytes);
+    if (id >= sh.num_rows) atomicExch(err, HB_ERR_INVALID);  // no such row: the output row stays as it was
+    warp_copy_rows16((id >= 0 && id < sh.num_rows) ? shard_row(sh, id, row_bytes) : nullptr,
+                     out + base * row_bytes, row_bytes);
   }
-}
-
-int make_view(const hb_peer_table* t, ShardView* out) {
-  memset(out, 0, sizeof(*out));
-  out->world = t->world;
-  for (int r = 0; r < t->world; ++r) {
-    if (!t->peer[r]) {
-      set_error("hb_peer_table: shard of rank %d is not mapped (connect or set_peer first)", r);
-      return HB_ERR_INVALID;
-    }
-    out->p[r] = t->peer[r];
-  }
-  return HB_OK;
 }
 
 int64_t grid_for(int64_t n) {
@@ -219,10 +205,10 @@ int hb_peer_table_gather(hb_peer_table_t* t, const int64_t* ids, int64_t n, cons
   HB_CHECK_ARG(((uintptr_t)dst & 15) == 0, "hb_peer_table_gather: dst must be 16-byte aligned");
   if (n == 0) return HB_OK;
   ShardView sv;
-  int rc = make_view(t, &sv);
+  int rc = make_shard_view(t, &sv);
   if (rc != HB_OK) return rc;
   HB_LAUNCH(sharded_gather_kernel, (int)grid_for(n), kBlock, 0, (cudaStream_t)stream, sv, ids, n, n_dev,
-            t->row_bytes, (char*)dst);
+            t->row_bytes, (char*)dst, device_error_word());
   return HB_OK;
 }
 
@@ -242,14 +228,14 @@ int hb_lookup_fetch_sharded(hb_index_t* h, const int64_t* ids, int64_t n, const 
     if (rc != HB_OK) return rc;
   }
   ShardView sv;
-  int rc = make_view(table, &sv);
+  int rc = make_shard_view(table, &sv);
   if (rc != HB_OK) return rc;
   if (mode == HB_LOOKUP_SORTED)
     HB_LAUNCH(sharded_lookup_fetch_kernel<HB_LOOKUP_SORTED>, (int)grid_for(n), kBlock, 0, st, h->view, sv,
-              ids, n, (const char*)cache_rows, table->row_bytes, (char*)out_rows, locs, found);
+              ids, n, (const char*)cache_rows, table->row_bytes, (char*)out_rows, locs, found, device_error_word());
   else
     HB_LAUNCH(sharded_lookup_fetch_kernel<HB_LOOKUP_SETASSOC>, (int)grid_for(n), kBlock, 0, st, h->view, sv,
-              ids, n, (const char*)cache_rows, table->row_bytes, (char*)out_rows, locs, found);
+              ids, n, (const char*)cache_rows, table->row_bytes, (char*)out_rows, locs, found, device_error_word());
   return HB_OK;
 }
 

@@ -1,0 +1,475 @@
+// Sort-once step: the batch of ids is sorted ONCE (radix sort of (id, position)), its runs
+// of equal ids are numbered, and everything that the reference does per occurrence is then
+// done per distinct id:
+//   * hb_runs_build         sort + run heads + class and per-class position of every
+//                           distinct id (torch.unique of python/EmbCache/sparse_optim.py:133
+//                           and the class lookups of dist_emb.py:174-191, sparse_optim.py:243-259)
+//   * hb_lookup_fetch_runs  cache lookup + cached fetch over the sorted batch: consecutive
+//                           copies of an id reuse the row already in registers, so a row is read
+//                           once per warp that meets it (dist_emb.py:184-243; a DGL sampler hands
+//                           the reference unique ids, a raw id stream does not)
+//   * hb_runs_miss_list     ids of one class that the cache did not hold, ascending, with
+//                           the batch position whose output row holds their embedding
+//                           (the uncached cold ids sent to the server, dist_emb.py:218-259)
+// The backward aggregation (segsum.cu) and the LRU ageing (index.cu) take the same runs.
+#include <cub/device/device_radix_sort.cuh>
+
+#include "compact.cuh"
+#include "index.cuh"
+#include "runs.cuh"
+#include "shard.cuh"
+
+namespace hb {
+int* device_error_word();  // runtime.cu
+
+namespace {
+
+constexpr int kBlock = 256;
+
+size_t sort_temp_bytes(int64_t n) {
+  size_t b64 = 0, b32 = 0;
+  cub::DoubleBuffer<int64_t> k(nullptr, nullptr);
+  cub::DoubleBuffer<uint32_t> k32(nullptr, nullptr);
+  cub::DoubleBuffer<uint32_t> v(nullptr, nullptr);
+  cub::DeviceRadixSort::SortPairs(nullptr, b64, k, v, (int)n, 0, 64, (cudaStream_t)0);
+  cub::DeviceRadixSort::SortPairs(nullptr, b32, k32, v, (int)n, 0, 32, (cudaStream_t)0);
+  return b64 > b32 ? b64 : b32;
+}
+
+// number of valid entries of a segmented input = sum of the segment counts
+__global__ void sum_counts_kernel(const int64_t* __restrict__ seg_counts, int64_t num_segs,
+                                  int64_t seg_cap, int64_t* __restrict__ out) {
+  if (threadIdx.x || blockIdx.x) return;
+  int64_t t = 0;
+  for (int64_t k = 0; k < num_segs; ++k) {
+    const int64_t c = seg_counts[k];
+    t += c < 0 ? 0 : (c > seg_cap ? seg_cap : c);
+  }
+  *out = t;
+}
+
+// keys = ids (entries at and beyond the device count, or beyond their segment's count, get
+// the largest key of id_bits bits, so they sort last), perm = 0..n-1.  A valid id that does
+// not fit below that key raises HB_ERR_INVALID in the device status word: it would collide
+// with another id or with the padding.
+template <typename KeyT>
+__global__ void prepare_keys_kernel(const int64_t* __restrict__ ids, int64_t n,
+                                    const int64_t* __restrict__ n_dev,
+                                    const int64_t* __restrict__ seg_counts, int64_t seg_cap,
+                                    int64_t sentinel, KeyT* __restrict__ keys,
+                                    uint32_t* __restrict__ perm, int* __restrict__ err) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const bool keep = seg_counts ? (i % seg_cap) < seg_counts[i / seg_cap] : (!n_dev || i < *n_dev);
+  int64_t id = keep ? ids[i] : sentinel;
+  if (keep && (id < 0 || id >= sentinel)) {
+    atomicExch(err, HB_ERR_INVALID);
+    id = sentinel;
+  }
+  keys[i] = (KeyT)id;
+  perm[i] = (uint32_t)i;
+}
+
+// run heads of the sorted keys, numbered over all runs and inside their class
+template <typename KeyT>
+struct HeadPolicy {
+  const KeyT* keys;
+  const int64_t* n_dev;
+  int64_t n;
+  const int8_t* table;   // nullable: no classes
+  int64_t table_len;
+  uint8_t* head;
+  int64_t* uniq;
+  int64_t* uniq2;        // nullable second copy (the caller's buffer)
+  int64_t* run_start;
+  int8_t* dclass;
+  int32_t* dpos;
+  int64_t* out_ids[3];
+  int64_t* num_runs;
+  int64_t* num_runs2;    // nullable second copy
+  int64_t* class_counts;
+  int64_t* class_counts2;
+  __device__ __forceinline__ int64_t valid_entries() const {
+    if (!n_dev) return n;
+    const int64_t d = *n_dev;
+    return d < n ? (d > 0 ? d : 0) : n;
+  }
+  __device__ __forceinline__ int classify(int64_t i) const {
+    const bool is_head = i < valid_entries() && (i == 0 || __ldg(keys + i - 1) != __ldg(keys + i));
+    head[i] = is_head;
+    if (!is_head) return -1;
+    if (!table) return 0;
+    const int64_t id = (int64_t)__ldg(keys + i);
+    if (id >= table_len) return 3;
+    const int8_t v = __ldg(table + id);
+    return (v >= 0 && v <= 2) ? (int)v : 3;
+  }
+  __device__ __forceinline__ void emit(int64_t i, int cls, const int4& before) const {
+    const int64_t u = (int64_t)before.x + before.y + before.z + before.w;
+    const int64_t id = (int64_t)keys[i];
+    uniq[u] = id;
+    if (uniq2) uniq2[u] = id;
+    run_start[u] = i;
+    if (table) {
+      const int pos = cls == 0 ? before.x : (cls == 1 ? before.y : (cls == 2 ? before.z : before.w));
+      dclass[u] = cls < 3 ? (int8_t)cls : (int8_t)-1;
+      dpos[u] = pos;
+      if (cls < 3 && out_ids[cls]) out_ids[cls][pos] = id;
+    }
+  }
+  __device__ __forceinline__ void finish(const int4& tot) const {
+    const int64_t u = (int64_t)tot.x + tot.y + tot.z + tot.w;
+    *num_runs = u;
+    if (num_runs2) *num_runs2 = u;
+    run_start[u] = valid_entries();
+    class_counts[0] = tot.x; class_counts[1] = tot.y; class_counts[2] = tot.z; class_counts[3] = tot.w;
+    if (class_counts2) { class_counts2[0] = tot.x; class_counts2[1] = tot.y; class_counts2[2] = tot.z; }
+  }
+};
+
+// ---- forward: lookup + fetch over the sorted batch -----------------------------------------
+struct RowSource {
+  const char* backing;  // one table on this GPU, or null
+  int64_t backing_rows;
+  ShardView shards;     // used when PEER
+};
+
+template <bool PEER>
+__device__ __forceinline__ uint4 load_row16(const uint4* p) {
+  if (PEER) return *p;  // may be a peer GPU's memory that its owner rewrites between steps
+  return __ldg(p);
+}
+
+// One warp takes 32 consecutive entries of the sorted batch.  Lane l looks its id up
+// (duplicates probe the same line, which is then a cache hit) and writes slot and found flag
+// to the entry's batch position; the rows are then moved four at a time, 16 bytes per lane,
+// and an entry whose id equals its predecessor's takes the predecessor's registers instead
+// of loading again.
+template <int MODE, typename KeyT, bool PEER, bool V16>
+__global__ void __launch_bounds__(kBlock) runs_lookup_fetch_kernel(
+    IndexView v, hb_runs_t r, RowSource rs, const char* __restrict__ cache_rows, int64_t row_bytes,
+    int vb, char* __restrict__ out, int64_t* __restrict__ locs, uint8_t* __restrict__ found,
+    int* __restrict__ err) {
+  __shared__ int64_t s_top[MODE == HB_LOOKUP_SORTED ? kTopMax : 1];
+  if (MODE == HB_LOOKUP_SORTED) {
+    stage_top_level(v, s_top);
+    __syncthreads();
+  }
+  const KeyT* keys = reinterpret_cast<const KeyT*>(r.keys);
+  const int64_t n = runs_valid_entries(r);
+  const int lane = lane_id();
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t limit = PEER ? rs.shards.num_rows : rs.backing_rows;
+  for (int64_t base = warp * 32; base < n; base += nwarps * 32) {
+    const int64_t j = base + lane;
+    const bool valid = j < n;
+    const int64_t id = valid ? (int64_t)__ldg(keys + j) : -1;
+    const uint32_t pos = valid ? __ldg(r.perm + j) : 0u;
+    const int64_t slot = warp_lookup<MODE>(v, s_top, id);
+    if (valid) {
+      if (locs) locs[pos] = slot;
+      if (found) found[pos] = slot >= 0;
+    }
+    const char* src = nullptr;
+    if (slot >= 0) {
+      src = cache_rows + slot * row_bytes;
+    } else if (valid && id < limit) {
+      src = PEER ? shard_row(rs.shards, id, row_bytes) : (rs.backing ? rs.backing + id * row_bytes : nullptr);
+    } else if (valid && (PEER || rs.backing)) {
+      atomicExch(err, HB_ERR_INVALID);  // no such row: the output row stays as it was
+    }
+    const int64_t prev = __shfl_up_sync(0xffffffffu, id, 1);
+    const unsigned have = __ballot_sync(0xffffffffu, src != nullptr);
+    unsigned fresh = __ballot_sync(0xffffffffu, lane == 0 || id != prev);
+    const unsigned long long src_bits = (unsigned long long)src;
+    if (V16) {
+      const int64_t vpr = row_bytes >> 4;
+      if (vpr <= 32) {
+        const bool on = lane < vpr;
+        uint4 last = make_uint4(0, 0, 0, 0);
+        for (int q0 = 0; q0 < 32; q0 += 4) {
+          if (((have >> q0) & 0xfu) == 0u) continue;
+          uint4 val[4];
+          uint32_t pq[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int q = q0 + u;
+            const unsigned long long sb = __shfl_sync(0xffffffffu, src_bits, q);
+            pq[u] = __shfl_sync(0xffffffffu, pos, q);
+            if (((have & fresh) >> q) & 1u)
+              if (on) val[u] = load_row16<PEER>(reinterpret_cast<const uint4*>(sb) + lane);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int q = q0 + u;
+            if (!((have >> q) & 1u)) continue;
+            if (!((fresh >> q) & 1u)) val[u] = last;
+            last = val[u];
+            if (on) __stcs(reinterpret_cast<uint4*>(out + (int64_t)pq[u] * row_bytes) + lane, val[u]);
+          }
+        }
+      } else {
+        for (int q0 = 0; q0 < 32; q0 += 4) {
+          if (((have >> q0) & 0xfu) == 0u) continue;
+          const uint4* s[4];
+          uint4* d[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int q = q0 + u;
+            const unsigned long long sb = __shfl_sync(0xffffffffu, src_bits, q);
+            const uint32_t pq = __shfl_sync(0xffffffffu, pos, q);
+            s[u] = ((have >> q) & 1u) ? reinterpret_cast<const uint4*>(sb) : nullptr;
+            d[u] = reinterpret_cast<uint4*>(out + (int64_t)pq * row_bytes);
+          }
+          for (int64_t k = lane; k < vpr; k += 32) {
+            uint4 val[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (s[u]) val[u] = load_row16<PEER>(s[u] + k);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (s[u]) __stcs(d[u] + k, val[u]);
+          }
+        }
+      }
+    } else {
+      // rows that are not a multiple of 16 bytes (or unaligned buffers): words or bytes
+      for (int q = 0; q < 32; ++q) {
+        const unsigned long long sb = __shfl_sync(0xffffffffu, src_bits, q);
+        const uint32_t pq = __shfl_sync(0xffffffffu, pos, q);
+        if (!((have >> q) & 1u)) continue;
+        char* d = out + (int64_t)pq * row_bytes;
+        if (vb == 4) {
+          const uint32_t* s4 = reinterpret_cast<const uint32_t*>(sb);
+          for (int64_t k = lane; k < (row_bytes >> 2); k += 32) reinterpret_cast<uint32_t*>(d)[k] = s4[k];
+        } else {
+          const char* s1 = reinterpret_cast<const char*>(sb);
+          for (int64_t k = lane; k < row_bytes; k += 32) d[k] = s1[k];
+        }
+      }
+    }
+  }
+}
+
+// ---- ids of one class that missed the cache -----------------------------------------------
+struct MissPolicy {
+  hb_runs_t r;
+  const int64_t* locs;   // slot per batch position
+  int want_class;        // < 0: every class
+  int64_t cap;
+  int64_t* miss_ids;     // [cap], filled from entry 0
+  int64_t* miss_src;     // [cap] batch position whose output row holds the embedding
+  int64_t* miss_count;
+  __device__ __forceinline__ int classify(int64_t u) const {
+    if (u >= *r.num_runs) return -1;
+    if (want_class >= 0 && (!r.dclass || r.dclass[u] != want_class)) return -1;
+    const int64_t pos = (int64_t)r.perm[r.run_start[u]];
+    return locs[pos] < 0 ? 0 : -1;
+  }
+  __device__ __forceinline__ void emit(int64_t u, int, const int4& before) const {
+    if (before.x >= cap) return;
+    miss_ids[before.x] = r.uniq_ids[u];
+    miss_src[before.x] = (int64_t)r.perm[r.run_start[u]];
+  }
+  __device__ __forceinline__ void finish(const int4& tot) const {
+    *miss_count = tot.x < cap ? tot.x : cap;
+  }
+};
+
+__global__ void fill_i64_kernel(int64_t* p, int64_t n, int64_t v) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    p[i] = v;
+}
+
+int64_t warp_grid(int64_t n) {
+  int64_t blocks = ceil_div(ceil_div(n, 32) * 32, kBlock);
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  return blocks < 1 ? 1 : blocks;
+}
+
+}  // namespace
+
+RunsPlan make_runs_plan(void* ws, int64_t n) {
+  RunsPlan s;
+  Carver cv(ws ? ws : (void*)256);  // a null workspace still yields the sizes
+  const int64_t m = n > 0 ? n : 1;
+  s.k0 = cv.take<int64_t>(m);
+  s.k1 = cv.take<int64_t>(m);
+  s.p0 = cv.take<uint32_t>(m);
+  s.p1 = cv.take<uint32_t>(m);
+  s.sort_temp_bytes = sort_temp_bytes(m);
+  s.sort_temp = cv.take<char>(s.sort_temp_bytes);
+  s.run_start = cv.take<int64_t>(m + 1);
+  s.head = cv.take<uint8_t>(m + 1);
+  s.n_valid = cv.take<int64_t>(1);
+  s.num_runs = cv.take<int64_t>(1);
+  s.class_counts = cv.take<int64_t>(4);
+  s.dclass = cv.take<int8_t>(m + 1);
+  s.dpos = cv.take<int32_t>(m + 1);
+  s.uniq = cv.take<int64_t>(m + 1);
+  s.compact_ws_bytes = compact_workspace_bytes(m);
+  s.compact_ws = cv.take<char>(s.compact_ws_bytes);
+  s.total = cv.used() + 256;
+  return s;
+}
+
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" {
+
+size_t hb_runs_workspace_bytes(int64_t n) { return make_runs_plan(nullptr, n).total; }
+
+int hb_runs_build(const int64_t* ids, int64_t n, const int64_t* n_dev, const int64_t* seg_counts,
+                  int64_t seg_cap, int id_bits, const int8_t* class_table, int64_t table_len,
+                  int64_t* const* class_ids_out, int64_t* class_counts_out, int64_t* uniq_ids_out,
+                  int64_t* num_unique_out, void* workspace, size_t workspace_bytes,
+                  hb_runs_t* runs_out, hb_stream_t stream) {
+  HB_CHECK_ARG(runs_out != nullptr, "hb_runs_build: runs_out is null");
+  HB_CHECK_ARG(n >= 0 && n < ((int64_t)1 << 31), "hb_runs_build: n out of range");
+  HB_CHECK_ARG(n == 0 || ids, "hb_runs_build: null ids");
+  HB_CHECK_ARG(id_bits >= 1 && id_bits <= 64, "hb_runs_build: id_bits must be in [1, 64]");
+  HB_CHECK_ARG(!seg_counts || (seg_cap > 0 && n % seg_cap == 0),
+               "hb_runs_build: a segmented input holds whole segments of seg_cap entries");
+  HB_CHECK_ARG(!class_table || table_len > 0, "hb_runs_build: a class table needs its length");
+  RunsPlan s = make_runs_plan(workspace, n);
+  if (!workspace || workspace_bytes < s.total) {
+    set_error("hb_runs_build: workspace of %zu bytes needed, %zu given", s.total, workspace_bytes);
+    return HB_ERR_WORKSPACE;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  memset(runs_out, 0, sizeof(*runs_out));
+  runs_out->n = n;
+  runs_out->num_runs = s.num_runs;
+  runs_out->class_counts = s.class_counts;
+  runs_out->run_start = s.run_start;
+  runs_out->head = s.head;
+  runs_out->uniq_ids = s.uniq;
+  runs_out->dclass = class_table ? s.dclass : nullptr;
+  runs_out->dpos = class_table ? s.dpos : nullptr;
+  if (n == 0) {
+    HB_CUDA(cudaMemsetAsync(s.num_runs, 0, sizeof(int64_t), st));
+    HB_CUDA(cudaMemsetAsync(s.class_counts, 0, 4 * sizeof(int64_t), st));
+    HB_CUDA(cudaMemsetAsync(s.run_start, 0, sizeof(int64_t), st));
+    if (num_unique_out) HB_CUDA(cudaMemsetAsync(num_unique_out, 0, sizeof(int64_t), st));
+    if (class_counts_out) HB_CUDA(cudaMemsetAsync(class_counts_out, 0, 3 * sizeof(int64_t), st));
+    return HB_OK;
+  }
+  if (seg_counts) {
+    // valid entries are scattered over the segments; their number becomes the device count
+    HB_LAUNCH(sum_counts_kernel, 1, 32, 0, st, seg_counts, n / seg_cap, seg_cap, s.n_valid);
+    n_dev = s.n_valid;
+  }
+  runs_out->n_dev = n_dev;
+  const int64_t sentinel = id_bits >= 63 ? INT64_MAX : (((int64_t)1 << id_bits) - 1);
+  cub::DoubleBuffer<uint32_t> perm(s.p0, s.p1);
+  int rc;
+  int64_t* cls_out[3] = {class_ids_out ? class_ids_out[0] : nullptr, class_ids_out ? class_ids_out[1] : nullptr,
+                         class_ids_out ? class_ids_out[2] : nullptr};
+  if (id_bits <= 32) {
+    uint32_t* k0 = reinterpret_cast<uint32_t*>(s.k0);
+    uint32_t* k1 = reinterpret_cast<uint32_t*>(s.k1);
+    HB_LAUNCH(prepare_keys_kernel<uint32_t>, (int)ceil_div(n, kBlock), kBlock, 0, st, ids, n, n_dev,
+              seg_counts, seg_cap, sentinel, k0, s.p0, device_error_word());
+    cub::DoubleBuffer<uint32_t> keys(k0, k1);
+    HB_CUDA(cub::DeviceRadixSort::SortPairs(s.sort_temp, s.sort_temp_bytes, keys, perm, (int)n, 0,
+                                            id_bits, st));
+    HeadPolicy<uint32_t> pol{keys.Current(), n_dev, n, class_table, table_len, s.head, s.uniq, uniq_ids_out,
+                             s.run_start, s.dclass, s.dpos, {cls_out[0], cls_out[1], cls_out[2]},
+                             s.num_runs, num_unique_out, s.class_counts, class_counts_out};
+    rc = run_compact(pol, n, s.compact_ws, s.compact_ws_bytes, st);
+    runs_out->keys = keys.Current();
+    runs_out->key_bytes = 4;
+  } else {
+    HB_LAUNCH(prepare_keys_kernel<int64_t>, (int)ceil_div(n, kBlock), kBlock, 0, st, ids, n, n_dev,
+              seg_counts, seg_cap, sentinel, s.k0, s.p0, device_error_word());
+    cub::DoubleBuffer<int64_t> keys(s.k0, s.k1);
+    HB_CUDA(cub::DeviceRadixSort::SortPairs(s.sort_temp, s.sort_temp_bytes, keys, perm, (int)n, 0,
+                                            id_bits, st));
+    HeadPolicy<int64_t> pol{keys.Current(), n_dev, n, class_table, table_len, s.head, s.uniq, uniq_ids_out,
+                            s.run_start, s.dclass, s.dpos, {cls_out[0], cls_out[1], cls_out[2]},
+                            s.num_runs, num_unique_out, s.class_counts, class_counts_out};
+    rc = run_compact(pol, n, s.compact_ws, s.compact_ws_bytes, st);
+    runs_out->keys = keys.Current();
+    runs_out->key_bytes = 8;
+  }
+  count_library_launches(1 + (id_bits + 7) / 8);
+  runs_out->perm = perm.Current();
+  return rc;
+}
+
+int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows,
+                         const void* backing_rows, int64_t backing_num_rows, hb_peer_table_t* table,
+                         int64_t row_bytes, void* out_rows, int64_t* locs, uint8_t* found, int mode,
+                         hb_stream_t stream) {
+  HB_CHECK_ARG(h && runs, "hb_lookup_fetch_runs: null argument");
+  HB_CHECK_ARG(row_bytes > 0, "hb_lookup_fetch_runs: bad row size");
+  HB_CHECK_ARG(runs->n == 0 || (cache_rows && out_rows && runs->keys && runs->perm),
+               "hb_lookup_fetch_runs: null argument");
+  HB_CHECK_ARG(mode == HB_LOOKUP_SETASSOC || mode == HB_LOOKUP_SORTED,
+               "hb_lookup_fetch_runs: unknown mode %d", mode);
+  HB_CHECK_ARG(!(table && backing_rows), "hb_lookup_fetch_runs: give a backing table or a sharded one");
+  HB_CHECK_ARG(!table || table->row_bytes == row_bytes, "hb_lookup_fetch_runs: row size differs from the table's");
+  HB_CHECK_ARG(!backing_rows || backing_num_rows > 0, "hb_lookup_fetch_runs: a backing table needs its row count");
+  if (runs->n == 0) return HB_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (mode == HB_LOOKUP_SORTED && h->sorted_stale) {
+    int rc = hb_index_build_sorted(h, stream);
+    if (rc != HB_OK) return rc;
+  }
+  RowSource rs;
+  memset(&rs, 0, sizeof(rs));
+  rs.backing = (const char*)backing_rows;
+  rs.backing_rows = backing_rows ? backing_num_rows : 0;
+  if (table) {
+    int rc = make_shard_view(table, &rs.shards);
+    if (rc != HB_OK) return rc;
+  }
+  uintptr_t bits = (uintptr_t)row_bytes | (uintptr_t)cache_rows | (uintptr_t)out_rows | (uintptr_t)backing_rows;
+  const bool v16 = (bits & 15) == 0;  // shards come from cudaMalloc and hold whole rows
+  const int vb = (bits & 3) == 0 ? 4 : 1;
+  const int grid = (int)warp_grid(runs->n);
+  int* err = device_error_word();
+#define HB_RLF(MODE, KEY, PEER, V16)                                                                   \
+  HB_LAUNCH((runs_lookup_fetch_kernel<MODE, KEY, PEER, V16>), grid, kBlock, 0, st, h->view, *runs, rs, \
+            (const char*)cache_rows, row_bytes, vb, (char*)out_rows, locs, found, err)
+#define HB_RLF_V(MODE, KEY, PEER) \
+  do { if (v16) HB_RLF(MODE, KEY, PEER, true); else HB_RLF(MODE, KEY, PEER, false); } while (0)
+#define HB_RLF_P(MODE, KEY) \
+  do { if (table) HB_RLF_V(MODE, KEY, true); else HB_RLF_V(MODE, KEY, false); } while (0)
+#define HB_RLF_K(MODE) \
+  do { if (runs->key_bytes == 4) HB_RLF_P(MODE, uint32_t); else HB_RLF_P(MODE, int64_t); } while (0)
+  if (mode == HB_LOOKUP_SORTED) HB_RLF_K(HB_LOOKUP_SORTED); else HB_RLF_K(HB_LOOKUP_SETASSOC);
+#undef HB_RLF_K
+#undef HB_RLF_P
+#undef HB_RLF_V
+#undef HB_RLF
+  return HB_OK;
+}
+
+size_t hb_runs_miss_list_workspace_bytes(int64_t n) { return compact_workspace_bytes(n); }
+
+int hb_runs_miss_list(const hb_runs_t* runs, const int64_t* locs, int want_class, int64_t cap,
+                      int64_t* miss_ids, int64_t* miss_src, int64_t* miss_count, void* workspace,
+                      size_t workspace_bytes, hb_stream_t stream) {
+  HB_CHECK_ARG(runs && locs && miss_ids && miss_src && miss_count && cap > 0,
+               "hb_runs_miss_list: null argument");
+  HB_CHECK_ARG(want_class < 0 || runs->dclass || runs->n == 0,
+               "hb_runs_miss_list: the runs were built without a class table");
+  cudaStream_t st = (cudaStream_t)stream;
+  // entries beyond the count hold -1, which the index's add() ignores
+  int64_t blocks = ceil_div(cap, kBlock);
+  if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
+  HB_LAUNCH(fill_i64_kernel, (int)blocks, kBlock, 0, st, miss_ids, cap, (int64_t)-1);
+  if (runs->n == 0) {
+    HB_CUDA(cudaMemsetAsync(miss_count, 0, sizeof(int64_t), st));
+    return HB_OK;
+  }
+  MissPolicy pol{*runs, locs, want_class, cap, miss_ids, miss_src, miss_count};
+  return run_compact(pol, runs->n, workspace, workspace_bytes, st);
+}
+
+}  // extern "C"

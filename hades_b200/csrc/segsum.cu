@@ -4,8 +4,9 @@
 // index_add_).
 //
 // Deterministic, no floating-point atomics:
-//   1. radix sort of (id, position) pairs (CUB), stable
-//   2. run heads compacted into unique ids + run starts (partition core, 1 class)
+//   1. radix sort of (id, position) pairs (CUB), stable          } hb_runs_build (runs.cu); a step
+//   2. run heads numbered: unique ids, run starts, class/position } that fetched the same ids first
+//                                                                   hands its runs over instead
 //   3. main pass: the sorted positions are cut into fixed chunks of R rows; a
 //      group of G lanes (G*4 floats wide) walks its chunk in order, reading
 //      gradient rows through the permutation, broadcasting positions with warp
@@ -19,9 +20,8 @@
 // The order of additions depends only on the sorted order and the chunk size, so
 // two runs on the same input give the same bits.  Counts are integers, so they
 // use atomicAdd (order cannot change an integer sum).
-#include <cub/device/device_radix_sort.cuh>
-
-#include "partition_core.cuh"
+#include "launch.cuh"
+#include "runs.cuh"
 
 namespace hb {
 namespace {
@@ -335,34 +335,6 @@ __global__ void __launch_bounds__(kLongBlock) segsum_fix_long_b_kernel(SegArgs a
 }
 
 // ---- small helpers ----------------------------------------------------------------------------
-// keys = ids (entries at and beyond the device count get the largest key of
-// id_bits bits, so they sort last), perm = 0..n-1
-// number of valid entries of a segmented input = sum of the segment counts
-__global__ void sum_counts_kernel(const int64_t* __restrict__ seg_counts, int64_t num_segs,
-                                  int64_t seg_cap, int64_t* __restrict__ out) {
-  if (threadIdx.x || blockIdx.x) return;
-  int64_t t = 0;
-  for (int64_t k = 0; k < num_segs; ++k) {
-    const int64_t c = seg_counts[k];
-    t += c < 0 ? 0 : (c > seg_cap ? seg_cap : c);
-  }
-  *out = t;
-}
-
-template <typename KeyT>
-__global__ void prepare_keys_kernel(const int64_t* __restrict__ ids, int64_t n,
-                                    const int64_t* __restrict__ n_dev,
-                                    const int64_t* __restrict__ seg_counts, int64_t seg_cap,
-                                    int64_t sentinel, KeyT* __restrict__ keys,
-                                    uint32_t* __restrict__ perm) {
-  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  // valid entries: a prefix of the input (n_dev) or a prefix of every segment (seg_counts)
-  const bool keep = seg_counts ? (i % seg_cap) < seg_counts[i / seg_cap] : (!n_dev || i < *n_dev);
-  keys[i] = (KeyT)(keep ? ids[i] : sentinel);
-  perm[i] = (uint32_t)i;
-}
-
 // counts -> the denominators the reference reports (1 + sum of cnt when cnt is given)
 __global__ void finish_counts_kernel(const unsigned long long* __restrict__ raw,
                                      const int64_t* __restrict__ num_runs, int plus_one,
@@ -384,49 +356,6 @@ __global__ void finish_counts_split_kernel(const unsigned long long* __restrict_
   if (out) out[dpos[i]] = (int64_t)raw[i] + plus_one;
 }
 
-// unique ids -> class by a per-node table, position inside the class, compacted ids
-struct ClassOfRunPolicy {
-  const int64_t* uniq;
-  const int64_t* num_runs;
-  const int8_t* table;
-  int8_t* dclass;
-  int32_t* dpos;
-  int64_t n;
-  int64_t* out_ids[3];
-  __device__ __forceinline__ int classify(int64_t u) const {
-    if (u >= *num_runs) return -1;
-    const int8_t v = __ldg(table + __ldg(uniq + u));
-    return (v >= 0 && v <= 2) ? (int)v : -1;
-  }
-  __device__ __forceinline__ void emit(int64_t u, int c, int64_t pos, int64_t, bool active) const {
-    if (u < n) {
-      dclass[u] = (int8_t)c;
-      dpos[u] = (int32_t)pos;
-    }
-    if (active && out_ids[c]) out_ids[c][pos] = uniq[u];
-  }
-};
-
-template <typename KeyT>
-struct RunHeadPolicy {
-  const KeyT* keys;
-  const int64_t* n_dev;
-  int64_t n;
-  int64_t* uniq;
-  int64_t* run_start;
-  uint8_t* head;
-  __device__ __forceinline__ int classify(int64_t i) const {
-    if (n_dev && i >= *n_dev) return -1;
-    return (i == 0 || __ldg(keys + i - 1) != __ldg(keys + i)) ? 0 : -1;
-  }
-  __device__ __forceinline__ void emit(int64_t i, int, int64_t pos, int64_t, bool active) const {
-    if (i < n) head[i] = active;
-    if (!active) return;
-    uniq[pos] = (int64_t)keys[i];
-    run_start[pos] = i;
-  }
-};
-
 int choose_chunk(int64_t n) {
   // at least ~16 chunks per SM, between 32 and 128 rows
   int64_t target = n / ((int64_t)sm_count() * 16);
@@ -435,40 +364,11 @@ int choose_chunk(int64_t n) {
   return r;
 }
 
-size_t sort_temp_bytes(int64_t n) {
-  size_t b64 = 0, b32 = 0;
-  cub::DoubleBuffer<int64_t> k(nullptr, nullptr);
-  cub::DoubleBuffer<uint32_t> k32(nullptr, nullptr);
-  cub::DoubleBuffer<uint32_t> v(nullptr, nullptr);
-  cub::DeviceRadixSort::SortPairs(nullptr, b64, k, v, (int)n, 0, 64, (cudaStream_t)0);
-  cub::DeviceRadixSort::SortPairs(nullptr, b32, k32, v, (int)n, 0, 32, (cudaStream_t)0);
-  return b64 > b32 ? b64 : b32;
-}
-
-// Items per thread of the class/position partition.  Only the first U of the n positions hold a
-// unique id, so few of its CTAs have work: small tiles spread that work over more of them (each
-// item of a tile costs a dependent table read and three barriers in turn).
-constexpr int kClassItems = 2;
-
 struct SegPlan {
-  int64_t *k0, *k1;
-  uint32_t *p0, *p1;
-  void* sort_temp;
-  size_t sort_temp_bytes;
-  int64_t* run_start;
-  uint8_t* head;
-  int64_t* n_valid;
-  int8_t* dclass;
-  int32_t* dpos;
-  int64_t* uniq_tmp;
-  void* class_ws;
-  size_t class_ws_bytes;
   unsigned long long* raw_counts;
   float *head_part, *tail_part, *slice_part;
   int2 *short_list, *long_list;
   int* list_counts;
-  void* part_ws;
-  size_t part_ws_bytes;
   int chunk;
   int64_t num_chunks;
   int cols_max;
@@ -479,20 +379,6 @@ SegPlan make_plan(void* ws, int64_t n, int64_t dim) {
   SegPlan s;
   Carver cv(ws ? ws : (void*)256);  // a null workspace still yields the sizes
   const int64_t m = n > 0 ? n : 1;
-  s.k0 = cv.take<int64_t>(m);
-  s.k1 = cv.take<int64_t>(m);
-  s.p0 = cv.take<uint32_t>(m);
-  s.p1 = cv.take<uint32_t>(m);
-  s.sort_temp_bytes = sort_temp_bytes(m);
-  s.sort_temp = cv.take<char>(s.sort_temp_bytes);
-  s.run_start = cv.take<int64_t>(m + 1);
-  s.head = cv.take<uint8_t>(m + 1);
-  s.n_valid = cv.take<int64_t>(1);
-  s.dclass = cv.take<int8_t>(m + 1);
-  s.dpos = cv.take<int32_t>(m + 1);
-  s.uniq_tmp = cv.take<int64_t>(m + 1);
-  s.class_ws_bytes = partition_workspace_bytes(m, 3, kClassItems);
-  s.class_ws = cv.take<char>(s.class_ws_bytes);
   s.raw_counts = cv.take<unsigned long long>(m);
   s.chunk = choose_chunk(m);
   s.num_chunks = ceil_div(m, s.chunk);
@@ -505,8 +391,6 @@ SegPlan make_plan(void* ws, int64_t n, int64_t dim) {
   s.short_list = cv.take<int2>(s.num_chunks);
   s.long_list = cv.take<int2>(s.num_chunks);
   s.list_counts = cv.take<int>(4);
-  s.part_ws_bytes = partition_workspace_bytes(m, 1);
-  s.part_ws = cv.take<char>(s.part_ws_bytes);
   s.total = cv.used() + 256;
   return s;
 }
@@ -559,8 +443,77 @@ using namespace hb;
 
 extern "C" {
 
+size_t hb_segsum_runs_workspace_bytes(int64_t n, int64_t dim) { return make_plan(nullptr, n, dim).total; }
+
+int hb_segsum_runs_f32(const hb_runs_t* runs, const float* grads, const int64_t* cnt_in, int64_t dim,
+                       int mean, float* sums, int64_t* counts, const hb_class_split_t* split,
+                       void* workspace, size_t workspace_bytes, hb_stream_t stream) {
+  HB_CHECK_ARG(runs != nullptr && dim > 0, "hb_segsum_runs_f32: bad argument");
+  const int64_t n = runs->n;
+  HB_CHECK_ARG(n == 0 || (grads && runs->perm && runs->head && runs->run_start && runs->num_runs),
+               "hb_segsum_runs_f32: null argument");
+  HB_CHECK_ARG(n == 0 || split || sums, "hb_segsum_runs_f32: null output");
+  HB_CHECK_ARG(!split || n == 0 || (runs->dclass && runs->dpos),
+               "hb_segsum_runs_f32: a split needs runs built with the class table");
+  if (n == 0) return HB_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  SegPlan s = make_plan(workspace, n, dim);
+  if (!workspace || workspace_bytes < s.total) {
+    set_error("hb_segsum_runs_f32: workspace of %zu bytes needed, %zu given", s.total, workspace_bytes);
+    return HB_ERR_WORKSPACE;
+  }
+  HB_CUDA(cudaMemsetAsync(s.raw_counts, 0, n * sizeof(unsigned long long), st));
+  uintptr_t align_bits = (uintptr_t)grads | (uintptr_t)sums;
+  if (split)
+    for (int c = 0; c < 3; ++c) align_bits |= (uintptr_t)split->out_rows[c];
+  const bool vec4 = (dim % 4 == 0) && (align_bits & 15) == 0;
+  SegArgs a;
+  a.head = runs->head;
+  a.perm = runs->perm;
+  a.run_start = runs->run_start;
+  a.num_runs = runs->num_runs;
+  a.grads = grads;
+  a.cnt_in = cnt_in;
+  a.n_dev = runs->n_dev;
+  a.n = n;
+  a.dim = dim;
+  a.chunk = s.chunk;
+  a.num_chunks = s.num_chunks;
+  a.mean = mean;
+  a.sums = sums;
+  a.dclass = split ? runs->dclass : nullptr;
+  a.dpos = runs->dpos;
+  for (int c = 0; c < 3; ++c) a.class_rows[c] = split ? split->out_rows[c] : nullptr;
+  a.counts = s.raw_counts;
+  a.head_part = s.head_part;
+  a.tail_part = s.tail_part;
+  a.short_list = s.short_list;
+  a.long_list = s.long_list;
+  a.list_counts = s.list_counts;
+  a.slice_part = s.slice_part;
+  const int tile = vec4 ? 512 : 128;
+  int rc;
+  for (int64_t col0 = 0; col0 < dim; col0 += tile) {
+    a.col0 = col0;
+    a.cols = (int)((dim - col0) < tile ? (dim - col0) : tile);
+    if (col0 == 0) HB_CUDA(cudaMemsetAsync(s.list_counts, 0, 4 * sizeof(int), st));
+    rc = dispatch_pass(a, vec4, st);
+    if (rc != HB_OK) return rc;
+  }
+  if (counts) {
+    HB_LAUNCH(finish_counts_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, s.raw_counts,
+              runs->num_runs, (cnt_in && mean) ? 1 : 0, counts, n);
+  }
+  if (split && (split->out_cnt[0] || split->out_cnt[1] || split->out_cnt[2])) {
+    HB_LAUNCH(finish_counts_split_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, s.raw_counts,
+              runs->num_runs, (cnt_in && mean) ? 1 : 0, runs->dclass, runs->dpos, split->out_cnt[0],
+              split->out_cnt[1], split->out_cnt[2], n);
+  }
+  return HB_OK;
+}
+
 size_t hb_unique_segsum_workspace_bytes(int64_t n, int64_t dim) {
-  return make_plan(nullptr, n, dim).total;
+  return align_up(hb_runs_workspace_bytes(n), 256) + make_plan(nullptr, n, dim).total;
 }
 
 int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* cnt_in, int64_t n,
@@ -574,120 +527,26 @@ int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* 
   HB_CHECK_ARG(num_unique != nullptr, "hb_unique_segsum_f32: num_unique is null");
   HB_CHECK_ARG(n == 0 || (ids && grads), "hb_unique_segsum_f32: null argument");
   HB_CHECK_ARG(n == 0 || split || (uniq_ids && sums), "hb_unique_segsum_f32: null output");
-  HB_CHECK_ARG(!split || (split->table && split->class_counts),
-               "hb_unique_segsum_f32: a split needs the class table and class_counts");
-  HB_CHECK_ARG(id_bits >= 1 && id_bits <= 64, "hb_unique_segsum_f32: id_bits must be in [1, 64]");
-  HB_CHECK_ARG(!seg_counts || (seg_cap > 0 && n % seg_cap == 0),
-               "hb_unique_segsum_f32: a segmented input holds whole segments of seg_cap entries");
-  cudaStream_t st = (cudaStream_t)stream;
-  if (runs_out) {
-    runs_out->perm = nullptr;
-    runs_out->run_start = nullptr;
-    runs_out->num_runs = num_unique;
-    runs_out->n = n;
-  }
-  if (n == 0) {
-    HB_CUDA(cudaMemsetAsync(num_unique, 0, sizeof(int64_t), st));
-    if (split) HB_CUDA(cudaMemsetAsync(split->class_counts, 0, 3 * sizeof(int64_t), st));
-    return HB_OK;
-  }
-  SegPlan s = make_plan(workspace, n, dim);
-  if (!uniq_ids) uniq_ids = s.uniq_tmp;
-  if (!workspace || workspace_bytes < s.total) {
-    set_error("hb_unique_segsum_f32: workspace of %zu bytes needed, %zu given", s.total,
-              workspace_bytes);
+  HB_CHECK_ARG(!split || (split->table && split->class_counts && split->table_len > 0),
+               "hb_unique_segsum_f32: a split needs the class table, its length and class_counts");
+  const size_t runs_bytes = align_up(hb_runs_workspace_bytes(n), 256);
+  if (!workspace || workspace_bytes < hb_unique_segsum_workspace_bytes(n, dim)) {
+    set_error("hb_unique_segsum_f32: workspace of %zu bytes needed, %zu given",
+              hb_unique_segsum_workspace_bytes(n, dim), workspace_bytes);
     return HB_ERR_WORKSPACE;
   }
-  // 1. sort (id, position); 32-bit keys when the ids fit
-  const int64_t sentinel = id_bits >= 63 ? INT64_MAX : (((int64_t)1 << id_bits) - 1);
-  cub::DoubleBuffer<uint32_t> perm(s.p0, s.p1);
-  int rc;
-  if (seg_counts) {
-    // valid entries are scattered over the segments; their number becomes the device count
-    HB_LAUNCH(sum_counts_kernel, 1, 32, 0, st, seg_counts, n / seg_cap, seg_cap, s.n_valid);
-    n_dev = s.n_valid;
-  }
-  if (id_bits <= 32) {
-    uint32_t* k0 = reinterpret_cast<uint32_t*>(s.k0);
-    uint32_t* k1 = reinterpret_cast<uint32_t*>(s.k1);
-    HB_LAUNCH(prepare_keys_kernel<uint32_t>, (int)ceil_div(n, kBlock), kBlock, 0, st, ids, n, n_dev,
-              seg_counts, seg_cap, sentinel, k0, s.p0);
-    cub::DoubleBuffer<uint32_t> keys(k0, k1);
-    HB_CUDA(cub::DeviceRadixSort::SortPairs(s.sort_temp, s.sort_temp_bytes, keys, perm, (int)n, 0,
-                                            id_bits, st));
-    // 2. run heads -> unique ids, run starts, head flags, U
-    RunHeadPolicy<uint32_t> pol{keys.Current(), n_dev, n, uniq_ids, s.run_start, s.head};
-    rc = run_partition(pol, n, 1, s.part_ws, s.part_ws_bytes, num_unique, st);
-  } else {
-    HB_LAUNCH(prepare_keys_kernel<int64_t>, (int)ceil_div(n, kBlock), kBlock, 0, st, ids, n, n_dev,
-              seg_counts, seg_cap, sentinel, s.k0, s.p0);
-    cub::DoubleBuffer<int64_t> keys(s.k0, s.k1);
-    HB_CUDA(cub::DeviceRadixSort::SortPairs(s.sort_temp, s.sort_temp_bytes, keys, perm, (int)n, 0,
-                                            id_bits, st));
-    RunHeadPolicy<int64_t> pol{keys.Current(), n_dev, n, uniq_ids, s.run_start, s.head};
-    rc = run_partition(pol, n, 1, s.part_ws, s.part_ws_bytes, num_unique, st);
-  }
-  count_library_launches(1 + (id_bits + 7) / 8);
+  hb_runs_t runs;
+  int64_t* cls_ids[3] = {split ? split->out_ids[0] : nullptr, split ? split->out_ids[1] : nullptr,
+                         split ? split->out_ids[2] : nullptr};
+  int rc = hb_runs_build(ids, n, n_dev, seg_counts, seg_cap, id_bits, split ? split->table : nullptr,
+                         split ? split->table_len : 0, split ? cls_ids : nullptr,
+                         split ? split->class_counts : nullptr, uniq_ids, num_unique, workspace,
+                         runs_bytes, &runs, stream);
   if (rc != HB_OK) return rc;
-  // 2b. optional split: class and position of every unique id
-  if (split) {
-    ClassOfRunPolicy cp{uniq_ids, num_unique, split->table, s.dclass, s.dpos, n,
-                        {split->out_ids[0], split->out_ids[1], split->out_ids[2]}};
-    rc = run_partition(cp, n, 3, s.class_ws, s.class_ws_bytes, split->class_counts, st, kClassItems);
-    if (rc != HB_OK) return rc;
-  }
-  // 3./4. column passes
-  HB_CUDA(cudaMemsetAsync(s.raw_counts, 0, n * sizeof(unsigned long long), st));
-  uintptr_t align_bits = (uintptr_t)grads | (uintptr_t)sums;
-  if (split)
-    for (int c = 0; c < 3; ++c) align_bits |= (uintptr_t)split->out_rows[c];
-  const bool vec4 = (dim % 4 == 0) && (align_bits & 15) == 0;
-  SegArgs a;
-  a.head = s.head;
-  a.perm = perm.Current();
-  if (runs_out) {
-    runs_out->perm = perm.Current();
-    runs_out->run_start = s.run_start;
-  }
-  a.run_start = s.run_start;
-  a.num_runs = num_unique;
-  a.grads = grads;
-  a.cnt_in = cnt_in;
-  a.n_dev = n_dev;
-  a.n = n;
-  a.dim = dim;
-  a.chunk = s.chunk;
-  a.num_chunks = s.num_chunks;
-  a.mean = mean;
-  a.sums = sums;
-  a.dclass = split ? s.dclass : nullptr;
-  a.dpos = s.dpos;
-  for (int c = 0; c < 3; ++c) a.class_rows[c] = split ? split->out_rows[c] : nullptr;
-  a.counts = s.raw_counts;
-  a.head_part = s.head_part;
-  a.tail_part = s.tail_part;
-  a.short_list = s.short_list;
-  a.long_list = s.long_list;
-  a.list_counts = s.list_counts;
-  a.slice_part = s.slice_part;
-  const int tile = vec4 ? 512 : 128;
-  for (int64_t col0 = 0; col0 < dim; col0 += tile) {
-    a.col0 = col0;
-    a.cols = (int)((dim - col0) < tile ? (dim - col0) : tile);
-    if (col0 == 0) HB_CUDA(cudaMemsetAsync(s.list_counts, 0, 4 * sizeof(int), st));
-    rc = dispatch_pass(a, vec4, st);
-    if (rc != HB_OK) return rc;
-  }
-  if (counts) {
-    HB_LAUNCH(finish_counts_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, s.raw_counts,
-              num_unique, (cnt_in && mean) ? 1 : 0, counts, n);
-  }
-  if (split && (split->out_cnt[0] || split->out_cnt[1] || split->out_cnt[2])) {
-    HB_LAUNCH(finish_counts_split_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, s.raw_counts,
-              num_unique, (cnt_in && mean) ? 1 : 0, s.dclass, s.dpos, split->out_cnt[0],
-              split->out_cnt[1], split->out_cnt[2], n);
-  }
-  return HB_OK;
+  if (runs_out) *runs_out = runs;
+  return hb_segsum_runs_f32(&runs, grads, cnt_in, dim, mean, sums, counts, split,
+                            static_cast<char*>(workspace) + runs_bytes, workspace_bytes - runs_bytes,
+                            stream);
 }
 
 }  // extern "C"

@@ -142,6 +142,7 @@ struct FlushPolicy {
   hb_staging_t s;
   int32_t cnt_threshold;
   int num_clients;
+  int64_t out_cap;    // rows the output can take (only with one client); the rest stays staged
   int64_t* line_ids;  // nullable: the cache index entries of flushed ids are reset
   int32_t* lru;
   int64_t* out_ids;
@@ -156,7 +157,7 @@ struct FlushPolicy {
   __device__ __forceinline__ void emit(int64_t i, int, int64_t pos, int64_t start,
                                        bool active) const {
     const int64_t d = start + pos;
-    if (active) {
+    if (active && d < out_cap) {
       const int64_t id = s.idx[i];
       out_ids[d] = id;
       out_cnt[d] = i;
@@ -165,7 +166,7 @@ struct FlushPolicy {
         lru[i] = 0;
       }
     } else if (i < s.slots && s.cnt[i] > 0) {
-      s.iter_count[i] += 1;  // server.py:418
+      s.iter_count[i] += 1;  // server.py:418 (a stale row the output had no room for waits for the next flush)
     }
   }
 };
@@ -174,11 +175,12 @@ struct FlushPolicy {
 // and starts again (server.py:419), its row goes out and is zeroed.  VB: bytes per vector.
 template <int VB>
 __global__ void __launch_bounds__(kBlock) staging_flush_move_kernel(
-    hb_staging_t s, const int64_t* __restrict__ counts, int num_clients,
+    hb_staging_t s, const int64_t* __restrict__ counts, int num_clients, int64_t out_cap,
     int64_t* __restrict__ out_cnt, float* __restrict__ out_rows) {
   using V = typename std::conditional<VB == 16, uint4, uint32_t>::type;
   int64_t total = 0;
   for (int c = 0; c < num_clients; ++c) total += counts[c];
+  if (total > out_cap) total = out_cap;
   const int lane = lane_id();
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -225,7 +227,8 @@ __global__ void __launch_bounds__(kBlock) staging_flush_move_kernel(
 template <int VEC_BYTES>
 __global__ void __launch_bounds__(kBlock) staging_insert_kernel(
     hb_staging_t s, const int64_t* __restrict__ locs, const uint8_t* __restrict__ last_writer,
-    const char* __restrict__ emb_rows, char* __restrict__ cache_rows, int64_t row_bytes, int64_t n) {
+    const char* __restrict__ emb_rows, const int64_t* __restrict__ row_index,
+    char* __restrict__ cache_rows, int64_t row_bytes, int64_t n) {
   const int lane = lane_id();
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -238,7 +241,8 @@ __global__ void __launch_bounds__(kBlock) staging_insert_kernel(
       s.cnt[slot] = 0;   // server.py:539-541
       s.idx[slot] = -1;
     }
-    warp_move_rows(emb_rows + i * row_bytes, cache_rows + (ok ? slot : 0) * row_bytes, ok, row_bytes,
+    const int64_t from = (ok && row_index) ? __ldg(row_index + i) : i;  // row of entry i in emb_rows
+    warp_move_rows(emb_rows + from * row_bytes, cache_rows + (ok ? slot : 0) * row_bytes, ok, row_bytes,
                    VEC_BYTES);
     if (s.grad) {
       const unsigned act = __ballot_sync(0xffffffffu, ok);
@@ -333,29 +337,32 @@ size_t hb_staging_flush_workspace_bytes(int64_t slots, int num_clients) {
 }
 
 int hb_staging_flush(hb_index_t* h, const hb_staging_t* s, int32_t cnt_threshold, int num_clients,
-                     int64_t* out_ids, float* out_rows, int64_t* out_cnt, int64_t* counts,
-                     void* workspace, size_t workspace_bytes, hb_stream_t stream) {
+                     int64_t out_cap, int64_t* out_ids, float* out_rows, int64_t* out_cnt,
+                     int64_t* counts, void* workspace, size_t workspace_bytes, hb_stream_t stream) {
   int rc = check_staging(s, "hb_staging_flush");
   if (rc) return rc;
+  if (out_cap <= 0 || out_cap > s->slots) out_cap = s->slots;
+  HB_CHECK_ARG(out_cap == s->slots || num_clients == 1,
+               "hb_staging_flush: an output smaller than the table needs num_clients == 1");
   HB_CHECK_ARG(out_ids && out_rows && out_cnt && counts, "hb_staging_flush: null output");
   HB_CHECK_ARG(num_clients >= 1, "hb_staging_flush: num_clients must be positive");
   HB_CHECK_ARG(s->slots < ((int64_t)1 << 31), "hb_staging_flush: too many slots");
   HB_CHECK_ARG(!h || h->cache_size == s->slots,
                "hb_staging_flush: the staging table must have one slot per cache slot");
-  FlushPolicy pol{*s, cnt_threshold, num_clients, h ? h->line_ids : nullptr, h ? h->lru : nullptr,
-                  out_ids, out_cnt};
+  FlushPolicy pol{*s, cnt_threshold, num_clients, out_cap, h ? h->line_ids : nullptr,
+                  h ? h->lru : nullptr, out_ids, out_cnt};
   rc = run_partition(pol, s->slots, num_clients, workspace, workspace_bytes, counts,
                      (cudaStream_t)stream, 8);
   if (rc != HB_OK) return rc;
   if (h) h->sorted_stale = true;
-  // the number of stale rows is only known on the device: size the grid for a full table
-  const int grid = warp_grid(s->slots < (int64_t)sm_count() * 16 * 256 ? s->slots : (int64_t)sm_count() * 16 * 256);
+  // the number of stale rows is only known on the device: size the grid for a full output
+  const int grid = warp_grid(out_cap);
   if (payload_vec_bytes(s->dim * (int64_t)sizeof(float), s->grad, out_rows) == 16)
     HB_LAUNCH(staging_flush_move_kernel<16>, grid, kBlock, 0, (cudaStream_t)stream, *s, counts, num_clients,
-              out_cnt, out_rows);
+              out_cap, out_cnt, out_rows);
   else
     HB_LAUNCH(staging_flush_move_kernel<4>, grid, kBlock, 0, (cudaStream_t)stream, *s, counts, num_clients,
-              out_cnt, out_rows);
+              out_cap, out_cnt, out_rows);
   return HB_OK;
 }
 
@@ -367,6 +374,14 @@ int hb_staging_insert(hb_index_t* h, const hb_staging_t* s, const int64_t* ids,
                       const void* emb_rows, int64_t n, void* cache_rows, int64_t row_bytes,
                       int64_t* locs_out, void* workspace, size_t workspace_bytes,
                       hb_stream_t stream) {
+  return hb_staging_insert_gather(h, s, ids, emb_rows, nullptr, n, cache_rows, row_bytes, locs_out,
+                                  workspace, workspace_bytes, stream);
+}
+
+int hb_staging_insert_gather(hb_index_t* h, const hb_staging_t* s, const int64_t* ids,
+                             const void* emb_rows, const int64_t* row_index, int64_t n,
+                             void* cache_rows, int64_t row_bytes, int64_t* locs_out, void* workspace,
+                             size_t workspace_bytes, hb_stream_t stream) {
   HB_CHECK_ARG(h != nullptr, "hb_staging_insert: null index");
   HB_CHECK_ARG(n >= 0 && row_bytes > 0, "hb_staging_insert: bad sizes");
   HB_CHECK_ARG(n == 0 || (ids && emb_rows && cache_rows && locs_out), "hb_staging_insert: null argument");
@@ -390,13 +405,13 @@ int hb_staging_insert(hb_index_t* h, const hb_staging_t* s, const int64_t* ids,
   cudaStream_t st = (cudaStream_t)stream;
   if (vb == 16)
     HB_LAUNCH(staging_insert_kernel<16>, warp_grid(n), kBlock, 0, st, st_desc, locs_out, last_writer,
-              (const char*)emb_rows, (char*)cache_rows, row_bytes, n);
+              (const char*)emb_rows, row_index, (char*)cache_rows, row_bytes, n);
   else if (vb == 4)
     HB_LAUNCH(staging_insert_kernel<4>, warp_grid(n), kBlock, 0, st, st_desc, locs_out, last_writer,
-              (const char*)emb_rows, (char*)cache_rows, row_bytes, n);
+              (const char*)emb_rows, row_index, (char*)cache_rows, row_bytes, n);
   else
     HB_LAUNCH(staging_insert_kernel<1>, warp_grid(n), kBlock, 0, st, st_desc, locs_out, last_writer,
-              (const char*)emb_rows, (char*)cache_rows, row_bytes, n);
+              (const char*)emb_rows, row_index, (char*)cache_rows, row_bytes, n);
   return HB_OK;
 }
 

@@ -70,7 +70,7 @@ class DistEmbeddingTensor:
             self._replays += 1
             serial = self._replays
         else:
-            rows, locs, _ = self.path.forward(ids, defer_touch=True)
+            rows, locs, _ = self.path.forward(ids)
             serial = 0
         emb = rows.detach().requires_grad_(True)
         if torch.is_grad_enabled():
@@ -120,16 +120,11 @@ class DistembSparseGradOptimizer:
                 # replayed it since: its ids and slots are still in the graph's buffers
                 st = emb.path.backward_replay(trace[0][1].grad)
             else:
-                # the slots an earlier replayed call found are gone from the graph's buffer:
-                # look them up again for the LRU ageing
-                stale = any(t[3] and t[3] != emb._replays for t in trace)
+                # (every forward call has aged the LRU counters of its own lookup; the backward
+                # pass sorts the concatenated ids itself unless they are the last call's batch)
                 ids = torch.cat([t[0] for t in trace]) if len(trace) > 1 else trace[0][0]
                 grads = torch.cat([t[1].grad for t in trace]) if len(trace) > 1 else trace[0][1].grad
-                if stale:
-                    locs = emb.path.cold.index.cudalookup(ids)
-                else:
-                    locs = torch.cat([t[2] for t in trace]) if len(trace) > 1 else trace[0][2]
-                st = emb.path.backward(ids, grads.contiguous(), locs)
+                st = emb.path.backward(ids, grads.contiguous())
             self.last_stats[emb.name] = st
         if self._clean_grad:
             for emb in self._params:

@@ -116,6 +116,17 @@ class PeerExchange:
             else:
                 dist.all_reduce(self._token, group=self.group)
 
+    def reset(self) -> None:
+        """Back to the state after set-up (``hb_a2a_reset``): every rank calls it, after the host
+        side has agreed that all ranks are alive, and nobody pushes until all have returned."""
+        if self.world > 1:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)  # nobody still pushes or polls
+        _lib.check(self.lib.hb_a2a_reset(self._h, _lib.stream_ptr()))
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)  # every area is clean before the next push
+
     def received(self, parity: int):
         """(ids [world*cap], rows [world*cap, dim], cnt [world*cap], counts [world]) of this
         rank's receive area: segment s holds counts[s] valid rows from rank s."""

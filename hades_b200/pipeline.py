@@ -1,19 +1,27 @@
 """One trainer's embedding hot path on one GPU, end to end:
 
-    forward   lookup + cached fetch (+ the LRU ageing of the reference's CPU lookup)
-    backward  local aggregation -> hot/cold split -> cold-cache accumulate ->
-              owner-partitioned exchange of the hot rows -> optimiser update on the owner;
-              every ``flush_every`` steps the cold cache is flushed through the same exchange
-              and refilled
+    forward   sort the batch once -> cache lookup + cached fetch over the runs of equal ids
+              (each distinct id looked up and read once per warp) -> LRU ageing of the lookup
+              -> the cold ids that missed go into the cache with the rows just fetched
+    backward  local aggregation over the same runs -> hot rows to their owners (exchange,
+              merge, optimiser update) while the cold rows are staged in the cold cache;
+              every ``flush_every`` steps the stale staged rows leave for their owners too
 
 It strings together what ``DistEmb.__call__`` (python/EmbCache/dist_emb.py:167-292),
 ``DistembSparseGradOptimizer.step`` (python/EmbCache/sparse_optim.py:212-448) and the cache
 server loop (python/EmbCache/server.py:259-298) do across three processes in the reference.
-Everything is ordered on the current CUDA stream (the cold accumulate forks to a side stream and
-joins before the step ends); the only host reads are the exchange sizes when NCCL carries the
-exchange (world > 1) and the flushed-row counts on flush steps.  With several GPUs the table
-exists once, sharded by owner and readable from every GPU (``peer_table.PeerTable``): cache misses
-read the owner's current row.
+
+Which rows the cache may serve: only ids of the COLD class are ever cached (the cache is
+filled with cold ids and only cold misses are inserted), exactly the ids whose updates the
+reference defers (dist_emb.py:179-212).  HOT ids always miss and are read from the authoritative
+table -- this GPU's table with one trainer, the owner's shard (``peer_table.PeerTable``) with
+several -- so a hot row updated in step t is what step t+1 fetches.  A cached cold row keeps
+the value it was inserted with until a flush evicts it (server.py:413) and a later miss brings
+the updated row back (server.py:499-544), as in the reference.
+
+Everything is ordered on the current CUDA stream (cache insert and cold accumulate run on a
+side stream and join before the step ends); no step reads a size on the host unless NCCL
+carries the exchange.
 """
 from __future__ import annotations
 
@@ -22,7 +30,7 @@ from dataclasses import dataclass, field
 import torch
 
 from . import EmbCacheLib as E
-from .cold_cache import ColdCache
+from .cold_cache import ColdCache, flush_thresholds
 from .sparse_optim import ShardedEmbedding, SparseAdam, SparseAdagrad, exchange_packed
 
 HOT, COLD = 1, 2  # classes of the per-node table (remote hot / remote cold, src/cuda/split.cu:39-43)
@@ -34,25 +42,43 @@ class StepStats:
     num_unique: torch.Tensor | None = None
     split_counts: torch.Tensor | None = None
     sent_counts: torch.Tensor | None = None
-    flushed: int = 0
+    flushed_dev: torch.Tensor | None = None   # stale rows the flush of this step found
+    flush_cap: int = 0
     extra: dict = field(default_factory=dict)
+
+    @property
+    def flushed(self) -> int:
+        """Rows the flush of this step sent (0 on other steps); one host read."""
+        if self.flushed_dev is None:
+            return 0
+        n = int(self.flushed_dev.sum().item())
+        return min(n, self.flush_cap) if self.flush_cap else n
 
 
 class EmbeddingPath:
     def __init__(self, table: torch.Tensor, class_table: torch.Tensor, cold: ColdCache,
                  optimizer, rank: int = 0, world: int = 1, flush_every: int = 8, id_bits: int = 64,
                  lookup_mode: int = E.LOOKUP_SETASSOC, mover: int = E.MOVER_AUTO,
-                 touch_lru: bool = True, group=None, peer_exchange=None):
+                 touch_lru: bool = True, group=None, peer_exchange=None, flush_exchange=None,
+                 insert_misses: bool = True, miss_cap: int = 1 << 17, flush_cap: int = 1 << 19):
         """table: backing rows for cache misses, [num_nodes, dim] fp32 on this GPU; None when the
         optimiser's shard is a ``PeerTable`` (misses then read the owners' shards).
         class_table: int8 per node, HOT or COLD.  optimizer: SparseAdam / SparseAdagrad on this
-        rank's shard (owner = id % world)."""
+        rank's shard (owner = id % world).  peer_exchange / flush_exchange: ``PeerExchange`` for
+        the per-step hot rows and for the flushed rows (None: NCCL all-to-all, sizes read on the
+        host).  insert_misses: cold ids that miss the cache are inserted in the forward pass (at
+        most miss_cap distinct ids per step; the rest stay uncached until they miss again).
+        flush_cap: rows one flush can send (the other stale rows wait for the next flush)."""
         self.table, self.class_table, self.cold, self.opt = table, class_table, cold, optimizer
         self.rank, self.world = rank, world
         self.flush_every, self.id_bits = flush_every, id_bits
         self.lookup_mode, self.mover, self.touch_lru = lookup_mode, mover, touch_lru
         self.group = group
-        self.px = peer_exchange  # PeerExchange for the per-step hot rows (None: NCCL all-to-all)
+        self.px = peer_exchange
+        self.px_flush = flush_exchange
+        self.insert_misses = insert_misses
+        self.miss_cap = int(miss_cap)
+        self.flush_cap = int(min(flush_cap, cold.remote.slots))
         self.step_no = 0
         self._graphs, self._g_ids, self._g_grads, self._g_out, self._g_next = [], None, None, None, 0
         self._whole_step_graphs = True
@@ -64,20 +90,69 @@ class EmbeddingPath:
         # owner (table is then None); otherwise misses read `table` on this GPU
         self.shared = getattr(optimizer.emb, "peer_table", None)
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self._side, self._cold_done, self._cold_refs = None, None, None
+        self._side = None
+        self._side_done, self._side_refs = None, []
+        self._runs_ws, self._side_ws = None, None
+        self._last = None  # (BatchRuns, locs) of the last forward pass
+
+    # ---- streams ---------------------------------------------------------------------------
+    def _on_side(self):
+        """Context: the side stream, ordered after everything the current stream holds so far."""
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        forked = torch.cuda.Event()
+        forked.record(torch.cuda.current_stream())
+        self._side.wait_event(forked)
+        return torch.cuda.stream(self._side)
+
+    def _side_finished(self, *refs) -> None:
+        """Called inside ``_on_side``: note where the side stream stands and keep what it reads
+        (buffers of the main stream's allocator) until the join."""
+        self._side_done = torch.cuda.Event()
+        self._side_done.record(self._side)
+        self._side_refs.append(refs)
+
+    def _join_side(self) -> None:
+        if self._side_done is not None:
+            torch.cuda.current_stream().wait_event(self._side_done)
+            self._side_done, self._side_refs = None, []
+
+    def _ws(self, which: str, nbytes: int) -> torch.Tensor:
+        """Scratch that belongs to this path (the library-wide scratch is used by whatever runs
+        on the main stream meanwhile)."""
+        cur = getattr(self, which)
+        if cur is None or cur.numel() < nbytes:
+            cur = torch.empty(int(nbytes), dtype=torch.uint8, device=self.device)
+            setattr(self, which, cur)
+        return cur
 
     # ---- forward -------------------------------------------------------------------------
-    def forward(self, ids: torch.Tensor, out_rows: torch.Tensor | None = None, defer_touch: bool = False):
-        """defer_touch: leave the LRU ageing of this lookup to ``backward(..., locs=locs)``,
-        which sorts the same ids anyway and can age the counters without a sort of its own."""
-        if self.shared is not None:
-            rows, locs, found = self.shared.lookup_fetch(self.cold.index, ids, self.cold.emb, out_rows,
-                                                         self.lookup_mode)
-        else:
-            rows, locs, found = E.cudaLookupFetch(self.cold.index, ids, self.cold.emb, self.table,
-                                                  out_rows=out_rows, mode=self.lookup_mode, mover=self.mover)
-        if self.touch_lru and not defer_touch:
-            self.cold.index.cuda_touch_lru(locs)
+    def forward(self, ids: torch.Tensor, out_rows: torch.Tensor | None = None, join: bool = True):
+        """(rows, locs, found) at the batch positions.  join=False leaves the cache insert
+        running on the side stream (``backward`` joins it)."""
+        lib = E._lib.load()
+        n = ids.numel()
+        runs = E.cudaRunsBuild(ids, self.id_bits, self.class_table, keep=(False, True, True),
+                               caps=(None, self.num_hot_ids, None),
+                               ws=self._ws("_runs_ws", lib.hb_runs_workspace_bytes(n)))
+        self._runs_ws = runs.ws
+        rows, locs, found = E.cudaLookupFetchRuns(self.cold.index, runs, self.cold.emb, self.table, self.shared,
+                                                  out_rows, self.lookup_mode)
+        if self.touch_lru:
+            self.cold.index.cuda_touch_lru_runs(locs, runs)
+        if self.insert_misses and n:
+            # the uncached cold ids and their rows go to the cache (dist_emb.py:218-259 ->
+            # server.py:499-544), before this step's cold gradients look the cache up
+            with self._on_side():
+                need = max(lib.hb_runs_miss_list_workspace_bytes(n),
+                           lib.hb_staging_insert_workspace_bytes(self.miss_cap))
+                ws = self._ws("_side_ws", need)
+                miss_ids, miss_src, miss_n = E.cudaRunsMissList(runs, locs, COLD, self.miss_cap, ws=ws)
+                self.cold.insert_gather(miss_ids, rows, miss_src, ws=ws)
+                self._side_finished(miss_ids, miss_src, miss_n, rows, locs, runs)
+            if join:
+                self._join_side()
+        self._last = (runs, locs)
         return rows, locs, found
 
     def _fence_shards(self) -> None:
@@ -94,67 +169,59 @@ class EmbeddingPath:
 
     # ---- exchange ------------------------------------------------------------------------
     def _exchange(self, ids, rows, cnt, n_dev):
-        """Bucket by owner and deliver to the owners.  Returns (ids, rows, cnt, n_dev)."""
+        """Bucket by owner and deliver to the owners over NCCL.  Returns (ids, rows, cnt, sent)."""
         p_ids, p_rows, p_cnt, counts = E.cudaBucketPack(ids, rows, cnt, self.world, n_dev=n_dev)
-        if self.world == 1:
-            return p_ids, p_rows, p_cnt, counts, counts
         r_ids, r_rows, r_cnt = exchange_packed(p_ids, p_rows, p_cnt, counts, self.group)
-        return r_ids, r_rows, r_cnt, None, counts
+        return r_ids, r_rows, r_cnt, counts
 
     # ---- backward ------------------------------------------------------------------------
     def backward(self, ids: torch.Tensor, grads: torch.Tensor, locs: torch.Tensor | None = None) -> StepStats:
-        """locs: the slots the forward pass found for `ids`, when its LRU ageing was deferred."""
-        st = self._backward_core(ids, grads, locs)
+        """ids: the ids the gradients belong to.  When they are the batch of the last ``forward``
+        its sort is reused; otherwise (several forward calls before one step) they are sorted
+        here.  locs is accepted for callers of the earlier interface and not used: every
+        forward pass ages the LRU counters of its own lookup."""
+        st = self._backward_core(ids, grads)
         self._after_step(st)
         return st
 
     def _after_step(self, st: StepStats) -> None:
         self.step_no += 1
+        st.flushed_dev = None
         if self.flush_every > 0 and self.step_no % self.flush_every == 0:
-            st.flushed = self.flush()
+            self.flush(st)
 
-    def _backward_local(self, ids, grads, locs, join: bool = True):
-        """Backward up to the exchange: aggregation, LRU ageing, hot/cold split, cold
-        accumulate.  No host read and no collective.  Returns (stats, hot ids, rows, cnt).
+    def _runs_for(self, ids: torch.Tensor) -> E.BatchRuns:
+        if self._last is not None and self._last[0].matches(ids):
+            return self._last[0]
+        lib = E._lib.load()
+        return E.cudaRunsBuild(ids, self.id_bits, self.class_table, keep=(False, True, True),
+                               caps=(None, self.num_hot_ids, None),
+                               ws=self._ws("_runs_ws", lib.hb_runs_workspace_bytes(ids.numel())))
+
+    def _backward_local(self, ids, grads, join: bool = True):
+        """Backward up to the exchange: aggregation over the runs with the hot / cold selects
+        (only_unique_grads, sparse_optim.py:132-139; the selects of :243-259) fused into its
+        output, and the cold accumulate.  No host read and no collective.  Returns (stats, hot
+        ids, rows, cnt).
 
         The cold accumulate touches only the staging table and the index, the hot rows' way to
-        their owners only the exchange buffers and the optimiser state, so the former runs on a
-        side stream; join=False leaves the join to the caller (``_join_cold``)."""
+        their owners only the exchange buffers and the optimiser state, so the former runs on
+        the side stream (behind this step's cache insert); join=False leaves the join to the
+        caller (``_join_side``)."""
         st = StepStats()
-        # hot-node local aggregation (only_unique_grads, sparse_optim.py:132-139) with the hot /
-        # cold selects (sparse_optim.py:243-259) fused into its output
-        outs, split_counts, num, runs = E.cudaUniqueSegSumSplit(
-            ids, grads, self.class_table, keep=(False, True, True), caps=(None, self.num_hot_ids, None),
-            id_bits=self.id_bits, want_runs=True)
-        if locs is not None and self.touch_lru:
-            self.cold.index.cuda_touch_lru_runs(locs, runs)
-        st.num_unique = num
-        st.split_counts = split_counts
-        hot_ids, hot_rows, hot_cnt = outs[HOT]
-        cold_ids, cold_rows, _ = outs[COLD]
-        # cold rows wait in the staging table
-        main = torch.cuda.current_stream()
-        if self._side is None:
-            self._side = torch.cuda.Stream(device=self.device)
-        forked = torch.cuda.Event()
-        forked.record(main)
-        with torch.cuda.stream(self._side):
-            self._side.wait_event(forked)
-            self.cold.accumulate_remote(cold_ids, cold_rows, n_dev=split_counts[COLD:COLD + 1],
+        runs = self._runs_for(ids)
+        outs = E.cudaSegSumRuns(runs, grads, split_keep=(False, True, True))
+        st.num_unique = runs.num_unique
+        st.split_counts = runs.class_counts
+        hot_ids, (hot_rows, hot_cnt) = runs.class_ids[HOT], outs[HOT]
+        cold_ids, (cold_rows, _) = runs.class_ids[COLD], outs[COLD]
+        with self._on_side():
+            self.cold.accumulate_remote(cold_ids, cold_rows, n_dev=runs.class_counts[COLD:COLD + 1],
                                         touch_lru=self.touch_lru)
-            self._cold_done = torch.cuda.Event()
-            self._cold_done.record(self._side)
-        # the side stream reads buffers that belong to this stream's allocator: keep them
-        # until the join is enqueued, so that nothing allocated in between can reuse them
-        self._cold_refs = (outs, split_counts)
+            self._side_finished(outs, runs)
         if join:
-            self._join_cold()
+            self._join_side()
         return st, hot_ids, hot_rows, hot_cnt
-
-    def _join_cold(self) -> None:
-        if self._cold_done is not None:
-            torch.cuda.current_stream().wait_event(self._cold_done)
-            self._cold_done, self._cold_refs = None, None
 
     def _owner_update_from_slabs(self, parity: int) -> None:
         """Owner side after a peer-memory push: merge the senders' slabs and update."""
@@ -163,10 +230,10 @@ class EmbeddingPath:
         self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=self.id_bits,
                         seg_counts=seg_counts, seg_cap=self.px.cap, sorted_segments=True)
 
-    def _backward_core(self, ids, grads, locs) -> StepStats:
+    def _backward_core(self, ids, grads) -> StepStats:
         """Everything of the backward path that runs every step (no host read unless NCCL
         carries the exchange)."""
-        st, hot_ids, hot_rows, hot_cnt = self._backward_local(ids, grads, locs, join=False)
+        st, hot_ids, hot_rows, hot_cnt = self._backward_local(ids, grads, join=False)
         n_hot = st.split_counts[HOT:HOT + 1]
         # hot rows go to their owners now
         if self.world == 1:
@@ -180,56 +247,51 @@ class EmbeddingPath:
             self.px.fence()
             self._owner_update_from_slabs(parity)
         else:
-            r_ids, r_rows, r_cnt, r_n, sent = self._exchange(hot_ids, hot_rows, hot_cnt, n_hot)
+            r_ids, r_rows, r_cnt, sent = self._exchange(hot_ids, hot_rows, hot_cnt, n_hot)
             st.sent_counts = sent
-            if r_n is not None:
-                r_n = r_n[:1]
             # owner: merge the senders' rows (unique_grads with counts) and update
-            self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, n_dev=r_n, id_bits=self.id_bits)
-        self._join_cold()
+            self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=self.id_bits)
+        self._join_side()
         self._fence_shards()
         return st
 
-    def flush(self) -> int:
-        """Stale cold rows leave through the same exchange; their cache entries are evicted by
-        the flush (server.py:413) and come back with the current table rows, as the next
-        forward pass of the reference would re-insert them (server.py:499-544)."""
-        f_ids, f_rows, f_cnt, counts = self.cold.flush_remote(sync=True)
-        n = f_ids.numel()
-        if n == 0 and self.world == 1:
-            return 0
+    def flush(self, st: StepStats | None = None) -> None:
+        """Stale cold rows leave for their owners; their cache entries are evicted by the flush
+        (server.py:413) and come back, with the owner's current row, when a later forward pass
+        misses them (server.py:499-544).  No host read: the flush fills a buffer of
+        ``flush_cap`` rows and hands the count over on the device."""
+        if self.world > 1 and self.px_flush is None:
+            return self._flush_nccl(st)
+        f_ids, f_rows, f_cnt, counts = self.cold.flush_remote(sync=False, out_cap=self.flush_cap)
+        if st is not None:
+            st.flushed_dev, st.flush_cap = counts, self.flush_cap
         if self.world == 1:
             # one trainer: every flushed row is its own (is_unique=True, sparse_optim.py:405-421)
-            self.opt.update(f_ids, f_rows, f_cnt, is_unique=True)
-            if n:
-                fresh = torch.empty((n, self.dim), dtype=self.table.dtype, device=f_ids.device)
-                E.cudaFetch2(self.table, f_ids, fresh)
-                self.cold.insert(f_ids, fresh)
-            return n
-        import torch.distributed as dist
+            self.opt.update(f_ids, f_rows, f_cnt, is_unique=True, n_dev=counts)
+        else:
+            # owner = id % world: the push buckets; what arrives is in slot order, so the owner
+            # sorts (unique_grads, sparse_optim.py:142-157) instead of merging
+            parity = self.px_flush.push(f_ids, f_rows, f_cnt, counts)
+            self.px_flush.fence()
+            r_ids, r_rows, r_cnt, seg_counts = self.px_flush.received(parity)
+            self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=self.id_bits, seg_counts=seg_counts,
+                            seg_cap=self.px_flush.cap)
+            self._fence_shards()
+        if self.lookup_mode == E.LOOKUP_SORTED:
+            self.cold.index.build_sorted()  # the flush reset entries: captured steps expect a fresh view
 
-        # the flush already leaves its rows bucketed by owner (num_clients = world)
-        r_ids, r_rows, r_cnt, (sent, received) = exchange_packed(
-            f_ids, f_rows, f_cnt, counts, self.group, return_splits=True,
-            counts_host=self.cold.remote.last_counts_host)
+    def _flush_nccl(self, st: StepStats | None) -> None:
+        """The flush over NCCL all_to_all_single (sizes read on the host, as the reference's
+        swap_gradients does, sparse_optim.py:55,77)."""
+        f_ids, f_rows, f_cnt, counts = self.cold.flush_remote(sync=True)
+        if st is not None:
+            st.flushed_dev, st.flush_cap = counts, 0
+        r_ids, r_rows, r_cnt = exchange_packed(f_ids, f_rows, f_cnt, counts, self.group,
+                                               counts_host=self.cold.remote.last_counts_host)
         self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=self.id_bits)
-        if self.shared is not None:
-            # The exchange in reverse: every owner returns the rows it now holds, in the order
-            # the ids arrived, so the refill costs one local gather and one all-to-all instead of
-            # row-by-row reads over NVLink.  A rank has all its rows back only after every
-            # owner's update, so this is also the fence before the next read of a shard.
-            w = self.opt.emb.weight
-            back = torch.empty((r_ids.numel(), self.dim), dtype=w.dtype, device=w.device)
-            E.cudaFetch2(w, r_ids // self.world, back)
-            fresh = torch.empty((sum(sent), self.dim), dtype=w.dtype, device=w.device)
-            dist.all_to_all_single(fresh, back, sent, received, group=self.group)
-            if n:
-                self.cold.insert(f_ids, fresh)
-        elif n:
-            fresh = torch.empty((n, self.dim), dtype=self.table.dtype, device=f_ids.device)
-            E.cudaFetch2(self.table, f_ids, fresh)
-            self.cold.insert(f_ids, fresh)
-        return n
+        self._fence_shards()
+        if self.lookup_mode == E.LOOKUP_SORTED:
+            self.cold.index.build_sorted()
 
     def step(self, ids: torch.Tensor, grads: torch.Tensor, out_rows: torch.Tensor | None = None):
         if self._graphs and grads is self._g_grads and out_rows is self._g_out:
@@ -250,11 +312,10 @@ class EmbeddingPath:
                 self.px.fence()
                 self._graphs[1 + parity][0].replay()
                 self._fence_shards()
-            st.flushed = 0
             self._after_step(st)
             return rows, locs, found, st
-        rows, locs, found = self.forward(ids, out_rows, defer_touch=True)
-        st = self.backward(ids, grads, locs)
+        rows, locs, found = self.forward(ids, out_rows, join=False)
+        st = self.backward(ids, grads)
         return rows, locs, found, st
 
     def capture(self, ids_buf: torch.Tensor, grads: torch.Tensor, out_rows: torch.Tensor) -> None:
@@ -277,14 +338,14 @@ class EmbeddingPath:
             for _ in range(1 if self.world == 1 else 2):  # the push picks the areas in turn
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
-                    rows, locs, found = self.forward(ids_buf, out_rows, defer_touch=True)
-                    st = self._backward_core(ids_buf, grads, locs)
+                    rows, locs, found = self.forward(ids_buf, out_rows, join=False)
+                    st = self._backward_core(ids_buf, grads)
                 graphs.append((g, (rows, locs, found, st)))
         else:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                rows, locs, found = self.forward(ids_buf, out_rows, defer_touch=True)
-                st, hot_ids, hot_rows, hot_cnt = self._backward_local(ids_buf, grads, locs)
+                rows, locs, found = self.forward(ids_buf, out_rows, join=False)
+                st, hot_ids, hot_rows, hot_cnt = self._backward_local(ids_buf, grads)
             graphs.append((g, (rows, locs, found, st, hot_ids, hot_rows, hot_cnt)))
             for parity in (0, 1):
                 gp = torch.cuda.CUDAGraph()
@@ -292,7 +353,6 @@ class EmbeddingPath:
                     self._owner_update_from_slabs(parity)
                 graphs.append((gp, None))
         self._graphs, self._g_ids, self._g_grads, self._g_out, self._g_next = graphs, ids_buf, grads, out_rows, 0
-
 
     # ---- forward and backward as separate graphs (a model runs between them) -------------------
     def capture_split(self, ids_buf: torch.Tensor, grads_buf: torch.Tensor, out_rows: torch.Tensor) -> None:
@@ -304,12 +364,12 @@ class EmbeddingPath:
             raise RuntimeError("split capture on several GPUs needs the peer-memory exchange with the device fence")
         fg = torch.cuda.CUDAGraph()
         with torch.cuda.graph(fg):
-            rows, locs, found = self.forward(ids_buf, out_rows, defer_touch=True)
+            rows, locs, found = self.forward(ids_buf, out_rows, join=True)
         back = []
         for _ in range(1 if self.world == 1 else 2):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                st = self._backward_core(ids_buf, grads_buf, locs)
+                st = self._backward_core(ids_buf, grads_buf)
             back.append((g, st))
         self._split = dict(fwd=fg, back=back, next=0, ids=ids_buf, grads=grads_buf, out=(rows, locs, found))
 
@@ -328,9 +388,22 @@ class EmbeddingPath:
         g, st = sp["back"][sp["next"]]
         sp["next"] = (sp["next"] + 1) % len(sp["back"])
         g.replay()
-        st.flushed = 0
         self._after_step(st)
         return st
+
+    def reset_exchange(self) -> None:
+        """After a fence timed out on a missing peer and the host side has agreed that every rank
+        is back: all ranks call this (a collective; host barriers inside), then go on stepping."""
+        import torch.distributed as dist
+
+        for px in (self.px, self.px_flush):
+            if px is not None:
+                px.reset()
+        self._g_next = 0
+        if getattr(self, "_split", None):
+            self._split["next"] = 0
+        if self.world > 1:
+            dist.barrier(group=self.group)
 
     # ---- save / resume ---------------------------------------------------------------------------
     def state_dict(self) -> dict:
@@ -363,6 +436,7 @@ class EmbeddingPath:
         self.opt.emb.weight.copy_(sd["weight"])
         if "table" in sd:
             self.table.copy_(sd["table"])
+        self._last = None
 
 
 def _warm_collectives(world: int, device, group) -> None:
@@ -400,11 +474,29 @@ def assemble_path(name: str, table: torch.Tensor, class_table: torch.Tensor, cac
                   hot_per_owner_max: int, rank: int, world: int, device, optimizer: str, flush_every: int,
                   lookup_mode: int, mover: int, touch_lru: bool, group, exchange: str,
                   cache_entries: int, table_dtype=torch.float32, table_sigma: float = 0.01,
-                  generator=None) -> EmbeddingPath:
-    """Cold cache filled with `cache_ids` (rows from `table`), optimiser shard, exchange."""
+                  generator=None, threshold: torch.Tensor | None = None, default_threshold: int = 0,
+                  cnt_threshold: int = 16, insert_misses: bool = True, flush_cap: int = 1 << 19,
+                  miss_cap: int = 1 << 17) -> EmbeddingPath:
+    """Cold cache filled with `cache_ids` (rows from `table`), optimiser shard, exchange.
+    threshold: int32 per-node flush period (``cold_cache.flush_thresholds`` of the presampled
+    hotness, server.py:87-88); None: every staged row is stale at every flush."""
     rows_total, dim = table.shape
-    cold = ColdCache(f"{name}_r{rank}", cache_entries, dim, threshold=None, cnt_threshold=16,
-                     default_threshold=0, num_clients=world, lookup_mode=lookup_mode, device=device)
+    _warm_collectives(world, device, group)
+    slots = -(-int(cache_entries) // 8) * 8  # the index rounds its capacity up to whole lines
+    flush_cap = int(min(flush_cap, slots))
+    px = px_flush = None
+    if world > 1 and exchange in ("push", "push_nccl_fence"):
+        fence = "device" if exchange == "push" else "nccl"
+        px = _peer_exchange(rank, world, hot_per_owner_max, dim, device, group, fence)
+        if px is not None:
+            # a rank may find all its stale rows owned by one peer: a slab holds a whole flush
+            px_flush = _peer_exchange(rank, world, flush_cap, dim, device, group, fence)
+            if px_flush is None:
+                px = None
+    push = px is not None
+    cold = ColdCache(f"{name}_r{rank}", cache_entries, dim, threshold=threshold, cnt_threshold=cnt_threshold,
+                     default_threshold=default_threshold, num_clients=1 if (world == 1 or push) else world,
+                     lookup_mode=lookup_mode, device=device)
     rows = torch.empty((cache_ids.numel(), dim), dtype=torch.float32, device=device)
     E.cudaFetch2(table, cache_ids, rows)
     cold.insert(cache_ids, rows)
@@ -425,13 +517,9 @@ def assemble_path(name: str, table: torch.Tensor, class_table: torch.Tensor, cac
             dist.barrier(group=group)  # every shard is filled before anyone reads it
     opt = SparseAdam(shard, lr=0.01) if optimizer == "adam" else SparseAdagrad(shard, lr=0.01)
     id_bits = max(int(rows_total).bit_length() + 1, 8)
-    _warm_collectives(world, device, group)
-    px = None
-    if world > 1 and exchange in ("push", "push_nccl_fence"):
-        px = _peer_exchange(rank, world, hot_per_owner_max, dim, device, group,
-                            "device" if exchange == "push" else "nccl")
     path = EmbeddingPath(table, class_table, cold, opt, rank, world, flush_every, id_bits,
-                         lookup_mode, mover, touch_lru, group, px)
+                         lookup_mode, mover, touch_lru, group, px, px_flush, insert_misses=insert_misses,
+                         miss_cap=miss_cap, flush_cap=flush_cap)
     path.cache_fill_ids = cache_ids  # what the cold cache was filled with, in insertion order
     return path
 
@@ -439,12 +527,23 @@ def assemble_path(name: str, table: torch.Tensor, class_table: torch.Tensor, cac
 def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str = "adam",
                hot_fraction: float = 0.01, lookup_mode: int = E.LOOKUP_SETASSOC,
                mover: int = E.MOVER_AUTO, touch_lru: bool = True, table_dtype=torch.float32,
-               seed_config: int | None = None, group=None, exchange: str = "push") -> EmbeddingPath:
+               seed_config: int | None = None, group=None, exchange: str = "push",
+               hotness: torch.Tensor | None = None, hot_threshold: float | None = None,
+               cnt_threshold: int = 16, insert_misses: bool = True, flush_cap: int = 1 << 19,
+               miss_cap: int = 1 << 17) -> EmbeddingPath:
     """Build the state of one trainer for a cached-fetch configuration (``synth.CacheFetchConfig``):
-    backing table, hot cache filled with the most popular ids, class table (the top
-    ``hot_fraction`` of the popularity ranking is HOT), cold cache and optimiser shard."""
+    backing table, class table, cold cache filled with the most popular COLD ids, optimiser shard.
+
+    Without `hotness` the popularity ranking of the synthetic stream stands in for it: the top
+    ``hot_fraction`` of the ranking is HOT, the cache holds the next ``cache_entries`` ids, and
+    every staged row is stale at every flush.  With `hotness` (float32 per node, accesses per
+    sampled batch: ``hotness.presampling``) everything is derived from it as the reference
+    does: HOT = hotness >= hot_threshold (dist_emb.py:108-120), per-node flush periods
+    ceil(1 / (0.001 + hotness)) capped at 100 (server.py:87-88) with the count threshold
+    `cnt_threshold` (dist_emb.py:139), and the cache starts with the hottest COLD ids."""
     import numpy as np
 
+    from . import hotness as H
     from . import synth
 
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
@@ -452,22 +551,39 @@ def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str =
     gen.manual_seed(1000 * (seed_config or cfg.config))  # the same table on every rank
     table = torch.empty((cfg.table_rows, cfg.dim), dtype=torch.float32, device=device)
     table.normal_(0.0, cfg.table_sigma, generator=gen)
-    n_hot = max(int(cfg.table_rows * hot_fraction), 1)
-    hot_ranked = synth.rank_to_id(np.arange(n_hot, dtype=np.int64), cfg.table_rows)
-    cls = np.full(cfg.table_rows, COLD, dtype=np.int8)
-    cls[hot_ranked] = HOT
-    class_table = torch.from_numpy(cls).to(device)
-    cache_ids = torch.from_numpy(synth.hot_ids(cfg.table_rows, cfg.cache_entries)).to(device)
-    # a rank can receive from one source at most the hot ids it owns
-    cap = int(np.bincount(hot_ranked % world, minlength=world).max())
-    return assemble_path(cfg.name, table, class_table, cache_ids, cap, rank, world, device, optimizer,
+    threshold, default_threshold = None, 0
+    if hotness is not None:
+        hotness = hotness.to(device=device, dtype=torch.float32)
+        if hot_threshold is None:
+            # the value that makes about hot_fraction of the nodes hot
+            k = max(int(cfg.table_rows * hot_fraction), 1)
+            hot_threshold = float(torch.topk(hotness, k).values[-1].item())
+        class_table = H.class_table(hotness, hot_threshold)
+        threshold = flush_thresholds(hotness)
+        cache_ids = H.hottest_ids(hotness, class_table == COLD, cfg.cache_entries)
+        hot_owner = torch.nonzero(class_table == HOT).flatten() % world
+        cap = int(torch.bincount(hot_owner, minlength=world).max().item()) if hot_owner.numel() else 1
+    else:
+        n_hot = max(int(cfg.table_rows * hot_fraction), 1)
+        hot_ranked = synth.rank_to_id(np.arange(n_hot, dtype=np.int64), cfg.table_rows)
+        cls = np.full(cfg.table_rows, COLD, dtype=np.int8)
+        cls[hot_ranked] = HOT
+        class_table = torch.from_numpy(cls).to(device)
+        # the most popular ids that are not hot, in popularity order
+        last = min(n_hot + cfg.cache_entries, cfg.table_rows)
+        cache_ids = torch.from_numpy(synth.rank_to_id(np.arange(n_hot, last, dtype=np.int64), cfg.table_rows)).to(device)
+        # a rank can receive from one source at most the hot ids it owns
+        cap = int(np.bincount(hot_ranked % world, minlength=world).max())
+    return assemble_path(cfg.name, table, class_table, cache_ids, max(cap, 1), rank, world, device, optimizer,
                          cfg.flush_every, lookup_mode, mover, touch_lru, group, exchange,
-                         cfg.cache_entries, table_dtype, cfg.table_sigma, gen)
+                         cfg.cache_entries, table_dtype, cfg.table_sigma, gen, threshold, default_threshold,
+                         cnt_threshold, insert_misses, flush_cap, miss_cap)
 
 
 def build_rmat_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str = "adam",
                     lookup_mode: int = E.LOOKUP_SETASSOC, mover: int = E.MOVER_AUTO,
-                    touch_lru: bool = True, group=None, exchange: str = "push") -> EmbeddingPath:
+                    touch_lru: bool = True, group=None, exchange: str = "push",
+                    insert_misses: bool = True) -> EmbeddingPath:
     """State of one trainer for the sampled-GraphSAGE configuration (``synth.RmatConfig``).
     Under R-MAT a vertex is the more popular the fewer one-bits its id has, so the HOT class
     is ``popcount(id) <= cfg.hot_popcount`` and the cold cache starts with the most popular
@@ -504,4 +620,4 @@ def build_rmat_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: 
     del pc, hot
     return assemble_path(cfg.name, table, class_table, cache_ids, cap, rank, world, device, optimizer,
                          cfg.flush_every, lookup_mode, mover, touch_lru, group, exchange,
-                         cfg.cache_entries, torch.float32, cfg.table_sigma, gen)
+                         cfg.cache_entries, torch.float32, cfg.table_sigma, gen, insert_misses=insert_misses)

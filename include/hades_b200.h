@@ -52,6 +52,7 @@ int hb_device_status(int* status_host, hb_stream_t stream);
 /* slot = (id % lines) * 8 + way; -1 = absent.  ids must be >= 0.              */
 /* ------------------------------------------------------------------------- */
 typedef struct hb_index hb_index_t;
+typedef struct hb_peer_table hb_peer_table_t; /* a table sharded over the GPUs of a box, see the end of this file */
 
 #define HB_WAYS 8
 
@@ -294,14 +295,27 @@ int hb_grad_split3(const int64_t* ids, const void* rows, const uint8_t* hot_mask
  * seg_counts (nullable, device int64[n / seg_cap]): the input is a sequence of
  * segments of seg_cap entries and only the first seg_counts[s] entries of segment
  * s are valid -- the receive slabs of hb_a2a_push, consumed in place. */
-/* The grouping that hb_unique_segsum_f32 computed, as pointers into its workspace
- * (valid until the workspace is written again): the input positions sorted by
- * id and the start of every run of equal ids. */
+/* The grouping of a batch into runs of equal ids: the input positions sorted by id
+ * (stable, so positions ascend inside a run) and the start of every run, with the
+ * distinct ids and, when a class table was given, the class of every distinct id and
+ * its position among the ids of its class.  What torch.unique(return_inverse,
+ * return_counts) computes at python/EmbCache/sparse_optim.py:133, kept so that the
+ * forward fetch, the LRU ageing, the miss list and the backward aggregation of one
+ * step share one sort.  All pointers are device pointers into the workspace given to
+ * hb_runs_build (valid until that workspace is written again). */
 typedef struct hb_runs {
-  const uint32_t* perm;     /* [n] input position of each sorted element */
-  const int64_t* run_start; /* [num_runs] */
-  const int64_t* num_runs;  /* device int64 (= num_unique) */
+  const uint32_t* perm;       /* [n] input position of each sorted element */
+  const int64_t* run_start;   /* [num_runs + 1]; run_start[num_runs] = valid entries */
+  const int64_t* num_runs;    /* device int64 (= number of distinct ids) */
   int64_t n;
+  const void* keys;           /* [n] sorted ids: uint32 (key_bytes 4) or int64 (key_bytes 8) */
+  int key_bytes;
+  const uint8_t* head;        /* [n] 1 where a run starts */
+  const int64_t* uniq_ids;    /* [num_runs] ascending */
+  const int8_t* dclass;       /* [num_runs] class of the id, -1 = none; NULL without a table */
+  const int32_t* dpos;        /* [num_runs] position among the ids of its class */
+  const int64_t* class_counts;/* device int64[4]: distinct ids of class 0, 1, 2, other */
+  const int64_t* n_dev;       /* nullable device count of valid input entries */
 } hb_runs_t;
 
 /* Optional split of the aggregated rows by a per-node class table (class =
@@ -313,6 +327,7 @@ typedef struct hb_runs {
  * class c.  class_counts: device int64[3]. */
 typedef struct hb_class_split {
   const int8_t* table;
+  int64_t table_len;          /* entries of table; ids at and beyond it have no class */
   int64_t* out_ids[3];
   float* out_rows[3];
   int64_t* out_cnt[3];
@@ -329,6 +344,57 @@ int hb_unique_segsum_f32(const int64_t* ids, const float* grads, const int64_t* 
                          const hb_class_split_t* split /* nullable, host; then uniq_ids, sums,
                          counts may be NULL */, void* workspace, size_t workspace_bytes,
                          hb_stream_t stream);
+
+/* Sort a batch once: runs of equal ids (hb_runs_t above).  class_table (nullable, int8
+ * per node, table_len entries): class and per-class position of every distinct id; with
+ * class_ids_out (nullable host array of 3 device buffers, each nullable) the distinct
+ * ids of class c are also written to class_ids_out[c] from entry 0, ascending -- the id
+ * half of the hot / cold selects of python/EmbCache/sparse_optim.py:243-259 --
+ * and class_counts_out (nullable device int64[3]) receives their numbers.
+ * uniq_ids_out / num_unique_out: nullable second copies in caller memory.  n_dev,
+ * seg_counts, seg_cap, id_bits as for hb_unique_segsum_f32.  An id that is negative or
+ * not below 2^id_bits - 1 raises HB_ERR_INVALID in the device status word. */
+size_t hb_runs_workspace_bytes(int64_t n);
+int hb_runs_build(const int64_t* ids, int64_t n, const int64_t* n_dev /* nullable */,
+                  const int64_t* seg_counts /* nullable */, int64_t seg_cap, int id_bits,
+                  const int8_t* class_table /* nullable */, int64_t table_len,
+                  int64_t* const* class_ids_out /* nullable, host */,
+                  int64_t* class_counts_out /* nullable */, int64_t* uniq_ids_out /* nullable */,
+                  int64_t* num_unique_out /* nullable */, void* workspace, size_t workspace_bytes,
+                  hb_runs_t* runs_out /* host */, hb_stream_t stream);
+
+/* The aggregation half of hb_unique_segsum_f32 over runs that already exist (the ids of
+ * `grads` are the ids the runs were built from, same order): per-id sums or means into
+ * `sums` [num_runs][dim] (+ counts), or with `split` straight into the class buffers
+ * out_rows / out_cnt (table, out_ids and class_counts of `split` are not used here: the
+ * runs carry the classes).  python/EmbCache/sparse_optim.py:134-139 (index_add_). */
+size_t hb_segsum_runs_workspace_bytes(int64_t n, int64_t dim);
+int hb_segsum_runs_f32(const hb_runs_t* runs /* host */, const float* grads,
+                       const int64_t* cnt_in /* nullable */, int64_t dim, int mean, float* sums,
+                       int64_t* counts /* nullable */, const hb_class_split_t* split /* nullable */,
+                       void* workspace, size_t workspace_bytes, hb_stream_t stream);
+
+/* hb_lookup_fetch (or hb_lookup_fetch_sharded when `table` is given) over a batch that
+ * hb_runs_build has sorted: same outputs at the same batch positions (locs, found,
+ * out_rows), but every distinct id is read once per warp that meets it instead of once
+ * per occurrence -- over NVLink, for a row of another GPU's shard.  A miss whose id is
+ * not below the table's row count leaves its output row untouched and raises
+ * HB_ERR_INVALID in the device status word.  python/EmbCache/dist_emb.py:184-243. */
+int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs /* host */, const void* cache_rows,
+                         const void* backing_rows /* nullable */, int64_t backing_num_rows,
+                         hb_peer_table_t* table /* nullable */, int64_t row_bytes, void* out_rows,
+                         int64_t* locs /* nullable */, uint8_t* found /* nullable */, int mode,
+                         hb_stream_t stream);
+
+/* The distinct ids of class want_class (< 0: any) that the lookup missed (locs[position]
+ * < 0), ascending, at most cap of them: miss_ids[cap] (entries past the count are -1, which
+ * hb_index_add ignores), miss_src[cap] = a batch position of the id (its row in the fetch
+ * output), *miss_count.  The uncached cold ids that DistEmbeddingTensor.__call__ sends to
+ * the cache server, python/EmbCache/dist_emb.py:218-259. */
+size_t hb_runs_miss_list_workspace_bytes(int64_t n);
+int hb_runs_miss_list(const hb_runs_t* runs /* host */, const int64_t* locs, int want_class,
+                      int64_t cap, int64_t* miss_ids, int64_t* miss_src, int64_t* miss_count,
+                      void* workspace, size_t workspace_bytes, hb_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
 /* Cold-gradient staging table (the reference's cache-server buffers).         */
@@ -375,11 +441,14 @@ int hb_staging_accumulate_direct(const hb_staging_t* s, const int64_t* ids, cons
  * are reset in it; other slots with cnt > 0 age by one iteration.  (The
  * reference zeroes a temporary copy of the rows, server.py:414, so its buffers
  * are never cleared; this library implements the intended read-and-zero.)
- * Outputs must hold `slots` entries. */
+ * out_cap: entries the outputs hold; 0 = `slots`.  A smaller output needs num_clients
+ * == 1 (no bucketing): the first out_cap stale slots in slot order leave, the others
+ * stay staged and age like live ones until the next flush; counts[0] then still reports
+ * ALL stale slots, so a consumer takes min(counts[0], out_cap) rows. */
 size_t hb_staging_flush_workspace_bytes(int64_t slots, int num_clients);
 int hb_staging_flush(hb_index_t* h /* nullable */, const hb_staging_t* s, int32_t cnt_threshold,
-                     int num_clients, int64_t* out_ids, float* out_rows, int64_t* out_cnt,
-                     int64_t* counts, void* workspace, size_t workspace_bytes,
+                     int num_clients, int64_t out_cap, int64_t* out_ids, float* out_rows,
+                     int64_t* out_cnt, int64_t* counts, void* workspace, size_t workspace_bytes,
                      hb_stream_t stream);
 
 /* _update_cache, server.py:499-544: locs = add(ids); cache_rows[locs[i]] =
@@ -390,6 +459,16 @@ int hb_staging_insert(hb_index_t* h, const hb_staging_t* s /* nullable */, const
                       const void* emb_rows, int64_t n, void* cache_rows, int64_t row_bytes,
                       int64_t* locs_out, void* workspace, size_t workspace_bytes,
                       hb_stream_t stream);
+/* The same with the embedding of ids[i] at emb_rows[row_index[i]] (row_index NULL: at
+ * emb_rows[i]): a step inserts the cold ids its lookup missed from the rows its fetch
+ * has just written (hb_runs_miss_list gives ids and row_index), as the reference's
+ * trainer ships them to the server (python/EmbCache/dist_emb.py:218-259).  Negative
+ * ids (padding) are ignored and get locs_out = -1. */
+int hb_staging_insert_gather(hb_index_t* h, const hb_staging_t* s /* nullable */,
+                             const int64_t* ids, const void* emb_rows,
+                             const int64_t* row_index /* nullable */, int64_t n, void* cache_rows,
+                             int64_t row_bytes, int64_t* locs_out, void* workspace,
+                             size_t workspace_bytes, hb_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
 /* Sparse optimiser update on the owning shard.                                */
@@ -449,6 +528,14 @@ int hb_a2a_push(hb_a2a_t* a, const int64_t* ids, const void* rows, const int64_t
  * the ranks must be on different GPUs.  The exchange number lives on the device,
  * so a captured graph holding push + fence can be replayed. */
 int hb_a2a_fence(hb_a2a_t* a, hb_stream_t stream);
+/* Back to the state after hb_a2a_connect (exchange number 0, flags and counts cleared,
+ * next push into area 0).  After a fence gave up on a missing peer the ranks' exchange
+ * numbers differ; when the host side has agreed that every rank is back, ALL ranks call
+ * this between two host barriers (before: nobody still pushes or polls; after: nobody
+ * pushes into an area that is being cleared) and the exchange works again.  Graphs
+ * captured over the exchange stay valid (they hold no exchange number), but their
+ * alternation restarts with the graph of area 0. */
+int hb_a2a_reset(hb_a2a_t* a, hb_stream_t stream);
 /* The bounded wait that hb_a2a_fence uses, on its own: a one-thread kernel polls
  * the device word *flag until it is >= value, for at most about a second; if it
  * gives up it records HB_ERR_TIMEOUT for hb_device_status and returns, and the
@@ -493,7 +580,6 @@ int hb_merge_sorted_slabs_f32(const int64_t* ids, const float* rows, const int64
  * Ordering is the caller's: all ranks pass a fence (hb_a2a_fence or a
  * collective on the stream) between an owner's update of its shard and the
  * next read by anyone. */
-typedef struct hb_peer_table hb_peer_table_t;
 int hb_peer_table_create(int rank, int world, int64_t num_rows /* whole table */, int64_t row_bytes,
                          hb_peer_table_t** out);
 size_t hb_peer_table_handle_bytes(void);

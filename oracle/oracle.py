@@ -516,12 +516,17 @@ class OracleStaging:
             self.cnt[s] += 1
             self.idx[s] = ids
 
-    def flush(self, index: OracleIndex | None, num_clients):
+    def flush(self, index: OracleIndex | None, num_clients, out_cap=0):
         """_send_staled_gradients, server.py:346-425: returns (ids, rows, cnt, counts) with
-        rows bucketed by id % num_clients, slot order inside a bucket."""
+        rows bucketed by id % num_clients, slot order inside a bucket.  out_cap > 0 (one client
+        only; no counterpart in the reference): at most that many rows leave, in slot order; the
+        other stale slots stay staged and age like live ones."""
         live = np.nonzero(self.cnt > 0)[0]
         stale_mask = (self.iter_count[live] >= self.iter_threshold[live]) | (self.cnt[live] >= self.cnt_threshold)
         stale = live[stale_mask]
+        if out_cap and stale.size > out_cap:
+            assert num_clients == 1
+            stale = stale[:out_cap]
         ids = self.idx[stale]
         rows = self.grad[stale].copy()
         cnts = self.cnt[stale].astype(np.int64)

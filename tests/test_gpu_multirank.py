@@ -1,6 +1,6 @@
-"""Two ranks on two GPUs over NCCL: the owner-partitioned exchange and the whole backward path
-against a numpy simulation of both ranks built from the oracle's functions.  Skipped when fewer
-than two GPUs are visible."""
+"""Two ranks on two GPUs: the owner-partitioned exchange (NCCL and peer-memory push) and the whole
+step against a numpy simulation of both ranks built from the oracle's functions
+(oracle/pipeline_oracle.py).  Skipped when fewer than two GPUs are visible."""
 import os
 import socket
 import sys
@@ -72,34 +72,28 @@ def _worker(rank, port, exchange):
 
     # --- the whole step on both ranks vs a simulation of both -------------------------------
     # The table is sharded by owner and every GPU reads every shard: cache misses of the
-    # forward fetch and the refill after a flush see the owners' current rows.
+    # forward fetch (hot ids always, cold ids until they are inserted) see the owners' rows.
+    from oracle.pipeline_oracle import PipelineOracle, compare_rank
+
     cfg = _cfg()
     path = pipeline.build_path(cfg, rank, WORLD, hot_fraction=0.02,
                                exchange={"nccl": "nccl", "push": "push", "push_graph": "push",
                                          "push_nccl_fence_graph": "push_nccl_fence"}[exchange])
     assert (path.px is not None) == exchange.startswith("push")
+    assert (path.px_flush is not None) == exchange.startswith("push")
     assert path.shared is not None and path.table is None
-    cls = path.class_table.cpu().numpy()
     # the whole table from the shards, through the same reads the kernels do
     all_ids = torch.arange(cfg.table_rows, dtype=torch.int64, device="cuda")
     w = path.shared.gather(all_ids).cpu().numpy()
     assert np.array_equal(w[rank::WORLD], path.opt.emb.weight.cpu().numpy())
-    step = np.zeros(cfg.table_rows, np.float32)
-    mem = np.zeros((cfg.table_rows, cfg.dim), np.float32)
-    power = np.zeros((cfg.table_rows, cfg.dim), np.float32)
-    # cold state (index, cached rows, staging) of BOTH ranks
-    sim = []
-    hot_ids = synth.hot_ids(cfg.table_rows, cfg.cache_entries)
-    for r in range(WORLD):
-        ox = om.OracleIndex(cfg.cache_entries)
-        stg = om.OracleStaging(ox.get_capacity(), cfg.dim, cnt_threshold=16)
-        cache = np.zeros((ox.get_capacity(), cfg.dim), np.float32)
-        stg.insert(ox, hot_ids, w[hot_ids], cache)
-        sim.append((ox, stg, cache))
+    orc = PipelineOracle(om, w, path.class_table.cpu().numpy(), cfg.cache_entries,
+                         path.cache_fill_ids.cpu().numpy(), world=WORLD, flush_every=cfg.flush_every,
+                         miss_cap=path.miss_cap, flush_cap=path.flush_cap)
     use_graph = exchange.endswith("_graph")
     g_ids = torch.empty(cfg.batch, dtype=torch.int64, device="cuda")
     g_grads = torch.empty((cfg.batch, cfg.dim), device="cuda")
     g_out = torch.empty((cfg.batch, cfg.dim), device="cuda")
+    flushed_total = 0
     for it in range(1, 6):
         ids, grads = _batch(cfg, rank, it)
         if use_graph and it == 2:  # one eager step first, then the captured graphs
@@ -108,46 +102,15 @@ def _worker(rank, port, exchange):
         g_grads.copy_(torch.from_numpy(grads))
         rows, locs, found, st = path.step(torch.from_numpy(ids).cuda(), g_grads, g_out)
         rows, locs, found = rows.cpu().numpy(), locs.cpu().numpy(), found.cpu().numpy()
-        # every rank's forward reads the table as the previous step left it
-        uniq = []
-        for r in range(WORLD):
-            i_r, g_r = _batch(cfg, r, it)
-            ox, stg, cache = sim[r]
-            out = np.zeros((i_r.size, cfg.dim), np.float32)
-            l_r, hit_r = om.lookup_fetch(ox, i_r, cache, w, out)
-            ox.touch(l_r)
-            if r == rank:
-                assert np.array_equal(locs, l_r) and np.array_equal(found, hit_r), (rank, it)
-                np.testing.assert_allclose(rows, out, rtol=1e-4, atol=2e-6)
-            u, s, c = om.only_unique_grads(i_r, g_r)
-            k = cls[u]
-            stg.accumulate_cached(ox, u[k == 2], s[k == 2], None, 0)
-            uniq.append((u[k == 1], s[k == 1], c[k == 1]))
-        for owner in range(WORLD):
-            inbox = [(u[u % WORLD == owner], s[u % WORLD == owner], c[u % WORLD == owner]) for u, s, c in uniq]
-            hu, hm, _ = om.unique_grads(*[np.concatenate([x[j] for x in inbox]) for j in range(3)])
-            om.sparse_adam_update(hu, hm, step, mem, power, w, 0.01)
-        if it % cfg.flush_every == 0:
-            flushed = []
-            for r in range(WORLD):
-                ox, stg, cache = sim[r]
-                fi, fr, fc, _ = stg.flush(ox, WORLD)
-                flushed.append((fi, fr, fc))
-            for owner in range(WORLD):
-                inbox = [(fi[fi % WORLD == owner], fr[fi % WORLD == owner], fc[fi % WORLD == owner])
-                         for fi, fr, fc in flushed]
-                fu, fm, _ = om.unique_grads(*[np.concatenate([x[j] for x in inbox]) for j in range(3)])
-                om.sparse_adam_update(fu, fm, step, mem, power, w, 0.01)
-            for r in range(WORLD):  # refill with the rows every owner has just written
-                ox, stg, cache = sim[r]
-                stg.insert(ox, flushed[r][0], w[flushed[r][0]], cache)
-        assert np.array_equal(path.opt.state_step.cpu().numpy(), step[rank::WORLD]), (rank, it)
-        np.testing.assert_allclose(path.opt.state_mem.cpu().numpy(), mem[rank::WORLD], rtol=1e-4, atol=1e-9)
-        np.testing.assert_allclose(path.opt.emb.weight.cpu().numpy(), w[rank::WORLD], rtol=1e-4, atol=2e-6)
-        gi, gl = path.cold.index.export_state()
-        oi, ol = sim[rank][0].export()
-        assert np.array_equal(gi.cpu().numpy(), oi) and np.array_equal(gl.cpu().numpy(), ol), (rank, it)
-        np.testing.assert_allclose(path.cold.emb.cpu().numpy(), sim[rank][2], rtol=1e-4, atol=2e-6)
+        both = [_batch(cfg, r, it) for r in range(WORLD)]
+        outs, flushed = orc.step([b[0] for b in both], [b[1] for b in both])
+        out, l_r, hit_r = outs[rank]
+        assert np.array_equal(locs, l_r) and np.array_equal(found, hit_r), (rank, it)
+        np.testing.assert_allclose(rows, out, rtol=1e-4, atol=2e-6)
+        assert st.flushed == flushed[rank], (rank, it)
+        flushed_total += flushed[rank]
+        compare_rank(path, orc, rank, where=f"rank {rank} step {it}")
+    assert flushed_total > 0
     assert path.step_no == 5
     torch.cuda.synchronize()
     dist.barrier()

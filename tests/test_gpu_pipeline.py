@@ -1,7 +1,9 @@
-"""The whole per-step path (forward fetch, local aggregation, hot/cold split, cold-cache
-accumulate, owner update, periodic flush and refill) on one GPU against the same steps composed
-from the oracle's functions: index state, staging state and found masks bit-exact, optimiser
-state and table within 1e-5 relative."""
+"""The whole per-step path (sorted forward fetch, LRU ageing, insertion of the cold misses, local
+aggregation, hot/cold split, cold-cache accumulate, owner update, periodic flush) on one GPU against
+the same steps composed from the oracle's functions (oracle/pipeline_oracle.py): slots, found
+masks, index state, LRU counters and staging counters bit-exact, optimiser state and table within
+1e-4 relative (they carry Adam updates whose first steps amplify roundings of nearly cancelling
+means by 1 / |mean|)."""
 import numpy as np
 import pytest
 import torch
@@ -9,75 +11,134 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _oracle_step(o, ids, grads, step_no, flush_every):
-    om = o["mod"]
-    # forward
-    out = np.zeros((ids.size, o["dim"]), np.float32)
-    locs, hit = om.lookup_fetch(o["index"], ids, o["cache"], o["table"], out)
-    o["index"].touch(locs)
-    # backward
-    u, s, c = om.only_unique_grads(ids, grads)
-    cls = o["cls"][u]
-    hot, cold = cls == 1, cls == 2
-    o["staging"].accumulate_cached(o["index"], u[cold], s[cold], None, 0)
-    hu, hm, _ = om.unique_grads(u[hot], s[hot], c[hot])
-    om.sparse_adam_update(hu, hm, o["step"], o["mem"], o["power"], o["table"], 0.01)
-    flushed = 0
-    if step_no % flush_every == 0:
-        fi, fr, fc, _ = o["staging"].flush(o["index"], 1)
-        flushed = fi.size
-        if flushed:
-            om.sparse_adam_update(fi, fr, o["step"], o["mem"], o["power"], o["table"], 0.01, cnt=fc)
-            o["staging"].insert(o["index"], fi, o["table"][fi], o["cache"])
-    return out, locs, hit, flushed
+def _oracle_for(path, oracle_mod, cfg, **kw):
+    from oracle.pipeline_oracle import PipelineOracle
+
+    table = (path.table if path.table is not None else path.opt.emb.weight).cpu().numpy()
+    return PipelineOracle(oracle_mod, table, path.class_table.cpu().numpy(), cfg.cache_entries,
+                          path.cache_fill_ids.cpu().numpy(), world=1, flush_every=cfg.flush_every,
+                          miss_cap=path.miss_cap, flush_cap=path.flush_cap, **kw)
 
 
-@pytest.mark.parametrize("mode,mover", [(0, 1), (1, 2)])
-def test_pipeline_matches_oracle(cuda_lib, oracle_mod, mode, mover):
+def _check_step(path, orc, ids, grads, it):
+    from oracle.pipeline_oracle import compare_rank
+
+    rows, locs, found, st = path.step(torch.from_numpy(ids).cuda(), torch.from_numpy(grads).cuda())
+    (outs,), (wflushed,) = orc.step([ids], [grads])
+    wout, wlocs, whit = outs
+    assert np.array_equal(locs.cpu().numpy(), wlocs), it
+    assert np.array_equal(found.cpu().numpy(), whit), it
+    np.testing.assert_allclose(rows.cpu().numpy(), wout, rtol=1e-4, atol=1e-6)
+    assert st.flushed == wflushed, it
+    compare_rank(path, orc, 0, where=f"step {it}")
+    return wflushed, int(whit.sum())
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_pipeline_matches_oracle(cuda_lib, oracle_mod, mode):
     from hades_b200 import pipeline, synth
 
     cfg = synth.scaled(synth.CONFIG1, 0.05, "pipe_test")
-    cfg = synth.CacheFetchConfig(cfg.name, cfg.config, cfg.table_rows, 64, cfg.cache_entries, cfg.batch,
+    cfg = synth.CacheFetchConfig(cfg.name, cfg.config, cfg.table_rows, 64, cfg.cache_entries // 4, cfg.batch,
                                  cfg.zipf_s, flush_every=3)
-    path = pipeline.build_path(cfg, lookup_mode=mode, mover=mover, hot_fraction=0.02)
-    # oracle state from the same initial table
-    table = path.table.cpu().numpy().copy()
-    ox = oracle_mod.OracleIndex(cfg.cache_entries)
-    slots = ox.get_capacity()
-    staging = oracle_mod.OracleStaging(slots, cfg.dim, cnt_threshold=16)
-    cache = np.zeros((slots, cfg.dim), np.float32)
-    hot_ids = synth.hot_ids(cfg.table_rows, cfg.cache_entries)
-    staging.insert(ox, hot_ids, table[hot_ids], cache)
-    o = dict(mod=oracle_mod, index=ox, cache=cache, table=table, staging=staging, dim=cfg.dim,
-             cls=path.class_table.cpu().numpy(), step=np.zeros(cfg.table_rows, np.float32),
-             mem=np.zeros((cfg.table_rows, cfg.dim), np.float32),
-             power=np.zeros((cfg.table_rows, cfg.dim), np.float32))
-    assert np.array_equal(path.cold.emb.cpu().numpy(), cache)
+    path = pipeline.build_path(cfg, lookup_mode=mode, hot_fraction=0.02)
+    orc = _oracle_for(path, oracle_mod, cfg)
+    cls = path.class_table.cpu().numpy()
+    fill = path.cache_fill_ids.cpu().numpy()
+    assert (cls[fill] == 2).all(), "the cold cache is filled with cold ids only"
+    assert np.array_equal(path.cold.emb.cpu().numpy(), orc.ranks[0]["cache"])
     rng = synth.rng_for(1, 0, 7)
     sampler = synth.ZipfSampler(cfg.table_rows, cfg.zipf_s)
-    total_flushed = 0
+    total_flushed = hits = 0
+    valid0 = path.cold.index.get_valid_entries_num()
     for it in range(1, 8):
         ids = sampler.ids(rng, cfg.batch)
         grads = synth.normal_rows(rng, cfg.batch, cfg.dim, cfg.grad_sigma)
-        rows, locs, found, st = path.step(torch.from_numpy(ids).cuda(), torch.from_numpy(grads).cuda())
-        wout, wlocs, whit, wflushed = _oracle_step(o, ids, grads, it, cfg.flush_every)
-        assert np.array_equal(locs.cpu().numpy(), wlocs), it
-        assert np.array_equal(found.cpu().numpy(), whit), it
-        np.testing.assert_allclose(rows.cpu().numpy(), wout, rtol=1e-4, atol=1e-6)  # rows carry Adam updates
-        assert st.flushed == wflushed, it
-        total_flushed += wflushed
-        gi, gl = path.cold.index.export_state()
-        oi, ol = ox.export()
-        assert np.array_equal(gi.cpu().numpy(), oi), it
-        assert np.array_equal(gl.cpu().numpy(), ol), it
-        assert np.array_equal(path.cold.remote.cnt.cpu().numpy(), staging.cnt), it
-        assert np.array_equal(path.cold.remote.idx.cpu().numpy(), staging.idx), it
-        np.testing.assert_allclose(path.cold.remote.grad.cpu().numpy(), staging.grad, rtol=1e-5, atol=1e-10)
-        assert np.array_equal(path.opt.state_step.cpu().numpy(), o["step"]), it
-        np.testing.assert_allclose(path.opt.state_mem.cpu().numpy(), o["mem"], rtol=1e-4, atol=1e-10)
-        np.testing.assert_allclose(path.table.cpu().numpy(), o["table"], rtol=1e-4, atol=1e-7)
-    assert total_flushed > 0
-    assert int(path.cold.dropped.item()) > 0
+        f, h = _check_step(path, orc, ids, grads, it)
+        total_flushed += f
+        hits += h
+    assert total_flushed > 0 and hits > 0
+    # cold misses were inserted (the small cache evicts by LRU and refuses where no way was ever hit)
+    assert path.cold.index.get_valid_entries_num() != valid0 or int(path.cold.dropped.item()) > 0
+
+
+def test_hot_rows_are_fresh_and_cold_rows_wait_for_the_flush(cuda_lib):
+    """A HOT id is never served from the cache: the row fetched after an update is the updated
+    one.  A cached COLD id keeps its row until the flush that applies its staged gradient evicts
+    it; the next fetch then misses, reads the updated row and caches it again."""
+    from hades_b200 import pipeline, synth
+
+    base = synth.scaled(synth.CONFIG1, 0.05, "fresh_test")
+    cfg = synth.CacheFetchConfig(base.name, base.config, base.table_rows, 32, base.cache_entries, 4096, base.zipf_s,
+                                 flush_every=2)
+    path = pipeline.build_path(cfg, hot_fraction=0.02)
+    cls = path.class_table.cpu().numpy()
+    hot_id = int(np.nonzero(cls == 1)[0][0])
+    cold_id = int(path.cache_fill_ids[0].item())
+    ids = torch.tensor([hot_id, cold_id] * 8, dtype=torch.int64, device="cuda")
+    g = torch.full((16, cfg.dim), 1e-3, device="cuda")
+    r1, _, f1, _ = path.step(ids, g)
+    assert not bool(f1[0]) and bool(f1[1]), "hot ids miss the cache by construction, cached cold ids hit"
+    hot_before, cold_before = r1[0].clone(), r1[1].clone()
+    r2, _, f2, st2 = path.step(ids, g)          # step 2 ends with a flush
+    assert not torch.equal(r2[0], hot_before), "the hot row carries the update of step 1"
+    assert torch.equal(r2[1], cold_before) and bool(f2[1]), "the cold row is served from the cache until the flush"
+    assert st2.flushed == 1
+    r3, _, f3, _ = path.step(ids, g)
+    assert not bool(f3[1]), "the flush evicted the cold id"
+    assert not torch.equal(r3[1], cold_before), "its staged gradient reached the table"
+    assert torch.equal(r3[1], path.table[cold_id])
+    r4, _, f4, _ = path.step(ids, g)
+    assert bool(f4[1]), "the miss of step 3 put it back into the cache"
+
+
+def test_presampled_hotness_drives_classes_periods_and_fill(cuda_lib, oracle_mod):
+    """A path built from presampled hotness as the reference builds its own: HOT = hotness >=
+    threshold, per-node flush periods ceil(1 / (0.001 + hotness)) capped at 100 with count
+    threshold 3, cache filled with the hottest cold ids; stepped against the oracle with the same
+    tables."""
+    from hades_b200 import hotness as H
+    from hades_b200 import pipeline, synth
+
+    base = synth.scaled(synth.CONFIG1, 0.03, "hotness_test")
+    cfg = synth.CacheFetchConfig(base.name, base.config, base.table_rows, 32, base.cache_entries, base.batch,
+                                 base.zipf_s, flush_every=1)
+    sampler = synth.ZipfSampler(cfg.table_rows, cfg.zipf_s)
+    rng = synth.rng_for(1, 0, 9)
+    heat = H.presampling([torch.from_numpy(sampler.ids(rng, cfg.batch)) for _ in range(6)], cfg.table_rows)
+    path = pipeline.build_path(cfg, hotness=heat, hot_threshold=0.99, cnt_threshold=3)
+    cls = path.class_table.cpu().numpy()
+    assert np.array_equal(cls == 1, heat.numpy() >= 0.99) and (cls == 1).sum() > 0
+    thr = oracle_mod.flush_thresholds(heat.numpy())
+    assert np.array_equal(path.cold.threshold.cpu().numpy(), thr)
+    assert thr.min() == 1 and thr.max() == 100 and ((thr > 1) & (thr < 100)).any()
+    orc = _oracle_for(path, oracle_mod, cfg, threshold=thr, cnt_threshold=3)
+    flushed = []
+    for it in range(1, 9):
+        ids = sampler.ids(rng, cfg.batch)
+        grads = synth.normal_rows(rng, cfg.batch, cfg.dim, cfg.grad_sigma)
+        flushed.append(_check_step(path, orc, ids, grads, it)[0])
+    assert sum(flushed) > 0 and flushed[0] == 0, "rows wait for their period (or three messages) before they leave"
+    assert int((path.cold.remote.cnt > 0).sum().item()) > 0, "colder rows are still staged"
+
+
+def test_flush_cap_leaves_the_rest_staged(cuda_lib, oracle_mod):
+    from hades_b200 import pipeline, synth
+
+    base = synth.scaled(synth.CONFIG1, 0.05, "cap_test")
+    cfg = synth.CacheFetchConfig(base.name, base.config, base.table_rows, 16, base.cache_entries, base.batch,
+                                 base.zipf_s, flush_every=2)
+    path = pipeline.build_path(cfg, flush_cap=100)
+    orc = _oracle_for(path, oracle_mod, cfg)
+    assert path.flush_cap == 100 == orc.flush_cap
+    rng = synth.rng_for(1, 0, 13)
+    sampler = synth.ZipfSampler(cfg.table_rows, cfg.zipf_s)
+    sent = []
+    for it in range(1, 7):
+        ids = sampler.ids(rng, cfg.batch)
+        grads = synth.normal_rows(rng, cfg.batch, cfg.dim, cfg.grad_sigma)
+        sent.append(_check_step(path, orc, ids, grads, it)[0])
+    assert sent == [0, 100, 0, 100, 0, 100]
 
 
 def test_graph_replay_equals_eager(cuda_lib):
@@ -86,7 +147,7 @@ def test_graph_replay_equals_eager(cuda_lib):
     from hades_b200 import pipeline, synth
 
     base = synth.scaled(synth.CONFIG1, 0.05, "graph_test")
-    cfg = synth.CacheFetchConfig(base.name, base.config, base.table_rows, 128, base.cache_entries, base.batch,
+    cfg = synth.CacheFetchConfig(base.name, base.config, base.table_rows, 128, base.cache_entries // 4, base.batch,
                                  base.zipf_s, flush_every=3)
     paths = [pipeline.build_path(synth.CacheFetchConfig(cfg.name + str(i), *list(cfg.__dict__.values())[1:]))
              for i in range(2)]
@@ -111,6 +172,7 @@ def test_graph_replay_equals_eager(cuda_lib):
     assert torch.equal(paths[0].table, paths[1].table)
     assert torch.equal(paths[0].opt.state_mem, paths[1].opt.state_mem)
     assert torch.equal(paths[0].cold.remote.grad, paths[1].cold.remote.grad)
+    assert torch.equal(paths[0].cold.emb, paths[1].cold.emb)
     for a, b in zip(paths[0].cold.index.export_state(), paths[1].cold.index.export_state()):
         assert torch.equal(a, b)
 
@@ -123,35 +185,15 @@ def test_rmat_frontier_path_matches_oracle(cuda_lib, oracle_mod):
     cfg = synth.scaled_rmat(synth.CONFIG5, 16, seeds=64)
     cfg = synth.RmatConfig(**{**cfg.__dict__, "dim": 32, "flush_every": 2})
     path = pipeline.build_rmat_path(cfg)
-    table = path.table.cpu().numpy().copy()
     cls = path.class_table.cpu().numpy()
-    ids_all = np.arange(cfg.num_nodes)
-    pop = np.array([bin(int(i)).count("1") for i in ids_all])
+    pop = np.array([bin(int(i)).count("1") for i in np.arange(cfg.num_nodes)])
     assert np.array_equal(cls == 1, pop <= cfg.hot_popcount)
     fill = path.cache_fill_ids.cpu().numpy()
     assert (pop[fill] > cfg.hot_popcount).all() and fill.size == min(cfg.cache_entries, (pop > cfg.hot_popcount).sum())
-    ox = oracle_mod.OracleIndex(cfg.cache_entries)
-    slots = ox.get_capacity()
-    staging = oracle_mod.OracleStaging(slots, cfg.dim, cnt_threshold=16)
-    cache = np.zeros((slots, cfg.dim), np.float32)
-    staging.insert(ox, fill, table[fill], cache)
-    o = dict(mod=oracle_mod, index=ox, cache=cache, table=table, staging=staging, dim=cfg.dim, cls=cls,
-             step=np.zeros(cfg.table_rows, np.float32), mem=np.zeros((cfg.table_rows, cfg.dim), np.float32),
-             power=np.zeros((cfg.table_rows, cfg.dim), np.float32))
+    orc = _oracle_for(path, oracle_mod, cfg)
     rng = synth.rng_for(5, 0, 1)
     for it in range(1, 5):
         ids = synth.rmat_frontier(cfg, rng)
         assert ids.size == cfg.batch
         grads = synth.normal_rows(rng, ids.size, cfg.dim, cfg.grad_sigma)
-        rows, locs, found, st = path.step(torch.from_numpy(ids).cuda(), torch.from_numpy(grads).cuda())
-        wout, wlocs, whit, wflushed = _oracle_step(o, ids, grads, it, cfg.flush_every)
-        assert np.array_equal(locs.cpu().numpy(), wlocs) and np.array_equal(found.cpu().numpy(), whit), it
-        assert st.flushed == wflushed, it
-        # fetched rows carry earlier Adam updates (lr = 1e-2), whose first step lr*g/(|g|+eps)
-        # amplifies the rounding of a nearly cancelling mean: bound relative to lr
-        np.testing.assert_allclose(rows.cpu().numpy(), wout, rtol=1e-4, atol=1e-6)
-        assert np.array_equal(path.opt.state_step.cpu().numpy(), o["step"]), it
-        np.testing.assert_allclose(path.table.cpu().numpy(), o["table"], rtol=1e-4, atol=1e-6)
-        gi, gl = path.cold.index.export_state()
-        oi, ol = ox.export()
-        assert np.array_equal(gi.cpu().numpy(), oi) and np.array_equal(gl.cpu().numpy(), ol), it
+        _check_step(path, orc, ids, grads, it)

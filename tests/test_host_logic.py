@@ -92,18 +92,17 @@ class _FakePath:
         self.num_nodes, self.dim, self.row_dtype, self.device = nodes, dim, torch.float32, torch.device("cpu")
         self.shared, self.calls = None, []
 
-    def forward(self, ids, out_rows=None, defer_touch=False):
-        assert defer_touch
+    def forward(self, ids, out_rows=None):
         return self.table[ids].clone(), ids * 10, torch.ones_like(ids, dtype=torch.bool)
 
-    def backward(self, ids, grads, locs):
-        self.calls.append((ids.clone(), grads.clone(), locs.clone()))
+    def backward(self, ids, grads):
+        self.calls.append((ids.clone(), grads.clone()))
         return "stats"
 
 
 def test_layer_trace_and_optimizer_step_follow_the_reference_protocol():
     """zero_grad only arms the clearing of the trace at the next step (sparse_optim.py:350-354,
-    468-470); a step hands the concatenated (ids, grads, slots) of every traced call to the path."""
+    468-470); a step hands the concatenated (ids, grads) of every traced call to the path."""
     from hades_b200.dist_emb import DistEmb, DistembSparseGradOptimizer
 
     path = _FakePath()
@@ -115,8 +114,8 @@ def test_layer_trace_and_optimizer_step_follow_the_reference_protocol():
     opt.zero_grad()
     (ha.sum() * 2 + hb.sum() * 3).backward()
     opt.step()
-    ids, grads, locs = path.calls[-1]
-    assert torch.equal(ids, torch.tensor([3, 5, 3, 7])) and torch.equal(locs, ids * 10)
+    ids, grads = path.calls[-1]
+    assert torch.equal(ids, torch.tensor([3, 5, 3, 7]))
     assert torch.equal(grads, torch.cat([torch.full((3, 4), 2.0), torch.full((1, 4), 3.0)]))
     assert layer.sparse_emb.trace == [] and opt.last_stats[layer.sparse_emb.name] == "stats"
     # without zero_grad the trace stays and the next step applies it again, as in the reference
