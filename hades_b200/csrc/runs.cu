@@ -140,13 +140,14 @@ __device__ __forceinline__ uint4 load_row16(const uint4* p) {
   return __ldg(p);
 }
 
-// One warp takes 32 consecutive entries of the sorted batch.  Lane l looks its id up
-// (duplicates probe the same line, which is then a cache hit) and writes slot and found flag
-// to the entry's batch position; the rows are then moved four at a time, 16 bytes per lane,
-// and an entry whose id equals its predecessor's takes the predecessor's registers instead
-// of loading again.
+// One warp takes 32 consecutive entries of the sorted batch.  Only the first entry of every
+// run of equal ids inside the warp probes the index (the others take its slot by shuffle) and
+// only it loads the row; slot and found flag go to every entry's batch position, the rows are
+// moved four at a time, 16 bytes per lane, an entry whose id equals its predecessor's storing
+// the predecessor's registers.  The ids and positions of the warp's next 32 entries are
+// requested before the rows of the current ones move.
 template <int MODE, typename KeyT, bool PEER, bool V16>
-__global__ void __launch_bounds__(kBlock) runs_lookup_fetch_kernel(
+__global__ void __launch_bounds__(kBlock, MODE == HB_LOOKUP_SORTED ? 2 : 3) runs_lookup_fetch_kernel(
     IndexView v, hb_runs_t r, RowSource rs, const char* __restrict__ cache_rows, int64_t row_bytes,
     int vb, char* __restrict__ out, int64_t* __restrict__ locs, uint8_t* __restrict__ found,
     int* __restrict__ err) {
@@ -159,14 +160,30 @@ __global__ void __launch_bounds__(kBlock) runs_lookup_fetch_kernel(
   const int64_t n = runs_valid_entries(r);
   const int lane = lane_id();
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t stride = (((int64_t)gridDim.x * blockDim.x) >> 5) * 32;
   const int64_t limit = PEER ? rs.shards.num_rows : rs.backing_rows;
-  for (int64_t base = warp * 32; base < n; base += nwarps * 32) {
-    const int64_t j = base + lane;
-    const bool valid = j < n;
-    const int64_t id = valid ? (int64_t)__ldg(keys + j) : -1;
-    const uint32_t pos = valid ? __ldg(r.perm + j) : 0u;
-    const int64_t slot = warp_lookup<MODE>(v, s_top, id);
+  int64_t base = warp * 32;
+  KeyT key_next = 0;
+  uint32_t pos_next = 0;
+  if (base + lane < n) {
+    key_next = __ldg(keys + base + lane);
+    pos_next = __ldg(r.perm + base + lane);
+  }
+  for (; base < n; base += stride) {
+    const bool valid = base + lane < n;
+    const int64_t id = valid ? (int64_t)key_next : -1;
+    const uint32_t pos = pos_next;
+    if (base + stride + lane < n) {
+      key_next = __ldg(keys + base + stride + lane);
+      pos_next = __ldg(r.perm + base + stride + lane);
+    }
+    const int64_t prev = __shfl_up_sync(0xffffffffu, id, 1);
+    const bool first = lane == 0 || id != prev;  // first entry of its run inside this warp
+    const unsigned fresh = __ballot_sync(0xffffffffu, first);
+    int64_t slot = warp_lookup<MODE>(v, s_top, first ? id : (int64_t)-1);
+    // every entry takes the slot of the first entry of its run (the nearest `first` lane at or below it)
+    const int leader = 31 - __clz(fresh & (0xffffffffu >> (31 - lane)));
+    slot = __shfl_sync(0xffffffffu, slot, leader);
     if (valid) {
       if (locs) locs[pos] = slot;
       if (found) found[pos] = slot >= 0;
@@ -179,9 +196,7 @@ __global__ void __launch_bounds__(kBlock) runs_lookup_fetch_kernel(
     } else if (valid && (PEER || rs.backing)) {
       atomicExch(err, HB_ERR_INVALID);  // no such row: the output row stays as it was
     }
-    const int64_t prev = __shfl_up_sync(0xffffffffu, id, 1);
     const unsigned have = __ballot_sync(0xffffffffu, src != nullptr);
-    unsigned fresh = __ballot_sync(0xffffffffu, lane == 0 || id != prev);
     const unsigned long long src_bits = (unsigned long long)src;
     if (V16) {
       const int64_t vpr = row_bytes >> 4;

@@ -117,7 +117,11 @@ def _accumulate_no_touch(om, r, ids, grads, threshold, default_threshold):
 def compare_rank(path, oracle: PipelineOracle, rank: int, where="", rtol=1e-4):
     """Assert that an EmbeddingPath's state equals the oracle's for `rank`: index lines and LRU
     counters, staging counters and ids bit-exact; staged gradient sums within 1e-5 of their
-    terms; optimiser state and owned table rows within `rtol`."""
+    terms; optimiser state within `rtol`; table and cached rows within `rtol` plus 1e-3 of the
+    learning rate (an early Adam step moves a weight by about lr whatever the gradient's size,
+    lr * g / (|g| + eps), so where the duplicates of an id nearly cancel, the rounding of their
+    mean is amplified by 1 / |mean|: the bound is relative to lr, not to the weight)."""
+    atol_w = 1e-3 * oracle.lr
     r = oracle.ranks[rank]
     gi, gl = path.cold.index.export_state()
     oi, ol = r["index"].export()
@@ -129,11 +133,11 @@ def compare_rank(path, oracle: PipelineOracle, rank: int, where="", rtol=1e-4):
     assert np.array_equal(st.iter_count.cpu().numpy(), r["staging"].iter_count), f"iter_count differs {where}"
     np.testing.assert_allclose(st.grad.cpu().numpy(), r["staging"].grad, rtol=1e-5, atol=1e-9,
                                err_msg=f"staged gradients differ {where}")
-    np.testing.assert_allclose(path.cold.emb.cpu().numpy(), r["cache"], rtol=rtol, atol=1e-6,
+    np.testing.assert_allclose(path.cold.emb.cpu().numpy(), r["cache"], rtol=rtol, atol=atol_w,
                                err_msg=f"cached rows differ {where}")
     assert int(path.cold.dropped.item()) == r["dropped"], f"dropped count differs {where}"
     w, world = path.opt.emb.weight.float().cpu().numpy(), oracle.world
-    np.testing.assert_allclose(w, oracle.table[rank::world], rtol=rtol, atol=1e-6,
+    np.testing.assert_allclose(w, oracle.table[rank::world], rtol=rtol, atol=atol_w,
                                err_msg=f"owned table rows differ {where}")
     if hasattr(path.opt, "state_step"):
         assert np.array_equal(path.opt.state_step.cpu().numpy(), oracle.step_state[rank::world]), f"Adam step {where}"

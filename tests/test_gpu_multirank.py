@@ -106,7 +106,7 @@ def _worker(rank, port, exchange):
         outs, flushed = orc.step([b[0] for b in both], [b[1] for b in both])
         out, l_r, hit_r = outs[rank]
         assert np.array_equal(locs, l_r) and np.array_equal(found, hit_r), (rank, it)
-        np.testing.assert_allclose(rows, out, rtol=1e-4, atol=2e-6)
+        np.testing.assert_allclose(rows, out, rtol=1e-4, atol=1e-5)
         assert st.flushed == flushed[rank], (rank, it)
         flushed_total += flushed[rank]
         compare_rank(path, orc, rank, where=f"rank {rank} step {it}")
