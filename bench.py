@@ -517,6 +517,7 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
         sampler = synth.ZipfSampler(cfg.table_rows, cfg.zipf_s)
         rng = synth.rng_for(2, rank, 1)
         host_batches = [torch.from_numpy(sampler.ids(rng, cfg.batch)).pin_memory() for _ in range(4)]
+    path.want_locs = False  # the step needs the slots in sorted order only (a coalesced write)
     dev_batches = [b.to(dev) for b in host_batches]
     gen = torch.Generator(device=dev)
     gen.manual_seed(2000 + rank)
@@ -654,7 +655,7 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
         "sort_runs": time_local(lambda: E.cudaRunsBuild(ids0, path.id_bits, path.class_table, keep=(False, True, True),
                                                         caps=(None, path.num_hot_ids, None), ws=runs0.ws)),
         "lookup_fetch": time_local(lambda: E.cudaLookupFetchRuns(path.cold.index, runs0, path.cold.emb, path.table,
-                                                                 path.shared, out_rows, mode)),
+                                                                 path.shared, out_rows, mode, want_locs=False)),
         "segsum": time_local(lambda: E.cudaSegSumRuns(runs0, grads, split_keep=(False, True, True))),
     }
     no_reuse_ms = None
@@ -662,7 +663,7 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
         unif = torch.randint(0, cfg.table_rows, (cfg.batch,), device=dev, generator=gen)
         runs_u = E.cudaRunsBuild(unif, path.id_bits)
         no_reuse_ms = time_local(lambda: E.cudaLookupFetchRuns(path.cold.index, runs_u, path.cold.emb, path.table,
-                                                               None, out_rows, mode))
+                                                               None, out_rows, mode, want_locs=False))
         del runs_u, unif
     nvlink = None
     if world > 1 and path.px is not None:

@@ -44,7 +44,7 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_index_lookup": (_int, [_p, _p, _i64, _p, _p, _int, _p]),
     "hb_index_touch_lru_workspace_bytes": (_sz, [_i64]),
     "hb_index_touch_lru": (_int, [_p, _p, _i64, _p, _sz, _p]),
-    "hb_index_touch_lru_runs": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p]),
+    "hb_index_touch_lru_runs": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _int, _p]),
     "hb_index_reset": (_int, [_p, _p, _i64, _p]),
     "hb_index_getall": (_int, [_p, _p, _p, _i64, _p, _p]),
     "hb_index_build_sorted": (_int, [_p, _p]),
@@ -74,9 +74,9 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_runs_build": (_int, [_p, _i64, _p, _p, _i64, _int, _p, _i64, _p, _p, _p, _p, _p, _sz, _p, _p]),
     "hb_segsum_runs_workspace_bytes": (_sz, [_i64, _i64]),
     "hb_segsum_runs_f32": (_int, [_p, _p, _p, _i64, _int, _p, _p, _p, _p, _sz, _p]),
-    "hb_lookup_fetch_runs": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p, _p, _int, _p]),
+    "hb_lookup_fetch_runs": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p, _p, _p, _int, _p]),
     "hb_runs_miss_list_workspace_bytes": (_sz, [_i64]),
-    "hb_runs_miss_list": (_int, [_p, _p, _int, _i64, _p, _p, _p, _p, _sz, _p]),
+    "hb_runs_miss_list": (_int, [_p, _p, _int, _int, _i64, _p, _p, _p, _p, _sz, _p]),
     "hb_staging_accumulate_cached": (_int, [_p, _p, _p, _p, _i64, _p, _p, C.c_int32, _int, _p, _p, _p]),
     "hb_staging_accumulate_direct": (_int, [_p, _p, _p, _i64, _p, _i64, _i64, _p]),
     "hb_staging_flush_workspace_bytes": (_sz, [_i64, _int]),

@@ -228,13 +228,18 @@ __global__ void touch_apply_kernel(const uint32_t* __restrict__ keys,
 // "hits on the line after my last hit" counted by binary search in the position
 // lists of the other hit ways of the line.
 struct RunsView {
-  const int64_t* locs;       // slot of every batch position
+  const int64_t* locs;       // slot of every batch position (or of every sorted entry, see below)
   const uint32_t* perm;      // nullable: position list of the runs (identity when null)
   const int64_t* run_start;  // nullable: run u = [run_start[u], run_start[u+1]) (run u = {u} when null)
   const int64_t* num_runs;   // nullable device count
   const int64_t* n_dev;      // nullable device count of positions
   int64_t max_runs;
   int64_t n;
+  int locs_sorted;           // locs[j] belongs to sorted entry j, not to batch position j
+  __device__ __forceinline__ int64_t slot_of_run(int64_t u) const {
+    const int64_t j = start(u);
+    return locs[locs_sorted ? j : pos(j)];
+  }
   __device__ __forceinline__ int64_t positions() const {
     if (!n_dev) return n;
     const int64_t d = *n_dev;
@@ -263,7 +268,7 @@ __global__ void touch_runs_mark_kernel(RunsView v, int64_t capacity, const int32
   const int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (u >= v.runs()) return;
   const int32_t epoch = *epoch_dev;
-  const int64_t slot = v.locs[v.pos(v.start(u))];
+  const int64_t slot = v.slot_of_run(u);
   if (slot < 0 || slot >= capacity) return;
   slot_run[slot] = (int32_t)u;
   slot_epoch[slot] = epoch;
@@ -278,7 +283,7 @@ __global__ void touch_runs_apply_kernel(RunsView v, int64_t capacity, const int3
   if (u >= nruns) return;
   const int32_t epoch = *epoch_dev;
   const int64_t npos = v.positions();
-  const int64_t slot = v.locs[v.pos(v.start(u))];
+  const int64_t slot = v.slot_of_run(u);
   if (slot < 0 || slot >= capacity) return;
   const int64_t line = slot >> 3;
   const int way = (int)(slot & 7);
@@ -547,7 +552,7 @@ int hb_index_touch_lru(hb_index_t* h, const int64_t* locs, int64_t n, void* work
 
 int hb_index_touch_lru_runs(hb_index_t* h, const int64_t* locs, const uint32_t* perm,
                             const int64_t* run_start, int64_t max_runs, const int64_t* num_runs,
-                            int64_t n, const int64_t* n_dev, hb_stream_t stream) {
+                            int64_t n, const int64_t* n_dev, int locs_sorted, hb_stream_t stream) {
   HB_CHECK_ARG(h && (n == 0 || locs), "hb_index_touch_lru_runs: null argument");
   HB_CHECK_ARG(n >= 0 && n < ((int64_t)1 << 31) && max_runs >= 0 && max_runs <= n,
                "hb_index_touch_lru_runs: sizes out of range");
@@ -562,7 +567,7 @@ int hb_index_touch_lru_runs(hb_index_t* h, const int64_t* locs, const uint32_t* 
     HB_CUDA(cudaMemsetAsync(h->slot_epoch, 0, (cap + 1) * sizeof(int32_t), st));
   }
   int32_t* epoch_dev = h->slot_epoch + cap;  // the batch counter sits after the marks
-  RunsView v{locs, perm, run_start, num_runs, n_dev, max_runs, n};
+  RunsView v{locs, perm, run_start, num_runs, n_dev, max_runs, n, locs_sorted ? 1 : 0};
   HB_LAUNCH(touch_runs_next_epoch_kernel, 1, 1, 0, st, epoch_dev);
   HB_LAUNCH(touch_runs_mark_kernel, grid_for(max_runs), kBlock, 0, st, v, cap, epoch_dev, h->slot_run,
             h->slot_epoch);

@@ -146,16 +146,20 @@ __device__ __forceinline__ uint4 load_row16(const uint4* p) {
 // moved four at a time, 16 bytes per lane, an entry whose id equals its predecessor's storing
 // the predecessor's registers.  The ids and positions of the warp's next 32 entries are
 // requested before the rows of the current ones move.
-template <int MODE, typename KeyT, bool PEER, bool V16>
+// RB: 512 = rows of exactly 512 bytes (128 fp32: the address arithmetic folds, no lane is idle);
+// 16 = any multiple of 16 bytes; 0 = words or bytes.
+template <int MODE, typename KeyT, bool PEER, int RB>
 __global__ void __launch_bounds__(kBlock, MODE == HB_LOOKUP_SORTED ? 2 : 3) runs_lookup_fetch_kernel(
-    IndexView v, hb_runs_t r, RowSource rs, const char* __restrict__ cache_rows, int64_t row_bytes,
+    IndexView v, hb_runs_t r, RowSource rs, const char* __restrict__ cache_rows, int64_t row_bytes_arg,
     int vb, char* __restrict__ out, int64_t* __restrict__ locs, uint8_t* __restrict__ found,
-    int* __restrict__ err) {
+    int64_t* __restrict__ locs_sorted, int* __restrict__ err) {
   __shared__ int64_t s_top[MODE == HB_LOOKUP_SORTED ? kTopMax : 1];
   if (MODE == HB_LOOKUP_SORTED) {
     stage_top_level(v, s_top);
     __syncthreads();
   }
+  constexpr bool V16 = RB != 0;
+  const int64_t row_bytes = RB == 512 ? (int64_t)512 : row_bytes_arg;
   const KeyT* keys = reinterpret_cast<const KeyT*>(r.keys);
   const int64_t n = runs_valid_entries(r);
   const int lane = lane_id();
@@ -185,7 +189,8 @@ __global__ void __launch_bounds__(kBlock, MODE == HB_LOOKUP_SORTED ? 2 : 3) runs
     const int leader = 31 - __clz(fresh & (0xffffffffu >> (31 - lane)));
     slot = __shfl_sync(0xffffffffu, slot, leader);
     if (valid) {
-      if (locs) locs[pos] = slot;
+      if (locs_sorted) locs_sorted[base + lane] = slot;  // coalesced
+      if (locs) locs[pos] = slot;                        // 8 bytes scattered over the batch: costly
       if (found) found[pos] = slot >= 0;
     }
     const char* src = nullptr;
@@ -200,15 +205,16 @@ __global__ void __launch_bounds__(kBlock, MODE == HB_LOOKUP_SORTED ? 2 : 3) runs
     const unsigned long long src_bits = (unsigned long long)src;
     if (V16) {
       const int64_t vpr = row_bytes >> 4;
-      if (vpr <= 32) {
-        const bool on = lane < vpr;
+      if (RB == 512 || vpr <= 32) {
+        const bool on = RB == 512 || lane < vpr;
         uint4 last = make_uint4(0, 0, 0, 0);
-        for (int q0 = 0; q0 < 32; q0 += 4) {
-          if (((have >> q0) & 0xfu) == 0u) continue;
-          uint4 val[4];
-          uint32_t pq[4];
+        constexpr int kFly = RB == 512 ? 8 : 4;  // rows whose loads are in flight together
+        for (int q0 = 0; q0 < 32; q0 += kFly) {
+          if (((have >> q0) & ((1u << kFly) - 1u)) == 0u) continue;
+          uint4 val[kFly];
+          uint32_t pq[kFly];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < kFly; ++u) {
             const int q = q0 + u;
             const unsigned long long sb = __shfl_sync(0xffffffffu, src_bits, q);
             pq[u] = __shfl_sync(0xffffffffu, pos, q);
@@ -216,7 +222,7 @@ __global__ void __launch_bounds__(kBlock, MODE == HB_LOOKUP_SORTED ? 2 : 3) runs
               if (on) val[u] = load_row16<PEER>(reinterpret_cast<const uint4*>(sb) + lane);
           }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < kFly; ++u) {
             const int q = q0 + u;
             if (!((have >> q) & 1u)) continue;
             if (!((fresh >> q) & 1u)) val[u] = last;
@@ -270,7 +276,8 @@ __global__ void __launch_bounds__(kBlock, MODE == HB_LOOKUP_SORTED ? 2 : 3) runs
 // ---- ids of one class that missed the cache -----------------------------------------------
 struct MissPolicy {
   hb_runs_t r;
-  const int64_t* locs;   // slot per batch position
+  const int64_t* locs;   // slot per batch position, or per sorted entry
+  int locs_sorted;
   int want_class;        // < 0: every class
   int64_t cap;
   int64_t* miss_ids;     // [cap], filled from entry 0
@@ -279,8 +286,8 @@ struct MissPolicy {
   __device__ __forceinline__ int classify(int64_t u) const {
     if (u >= *r.num_runs) return -1;
     if (want_class >= 0 && (!r.dclass || r.dclass[u] != want_class)) return -1;
-    const int64_t pos = (int64_t)r.perm[r.run_start[u]];
-    return locs[pos] < 0 ? 0 : -1;
+    const int64_t j = r.run_start[u];
+    return locs[locs_sorted ? j : (int64_t)r.perm[j]] < 0 ? 0 : -1;
   }
   __device__ __forceinline__ void emit(int64_t u, int, const int4& before) const {
     if (before.x >= cap) return;
@@ -295,13 +302,6 @@ struct MissPolicy {
 __global__ void fill_i64_kernel(int64_t* p, int64_t n, int64_t v) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
     p[i] = v;
-}
-
-int64_t warp_grid(int64_t n) {
-  int64_t blocks = ceil_div(ceil_div(n, 32) * 32, kBlock);
-  const int64_t cap = (int64_t)sm_count() * 16;
-  if (blocks > cap) blocks = cap;
-  return blocks < 1 ? 1 : blocks;
 }
 
 }  // namespace
@@ -418,8 +418,8 @@ int hb_runs_build(const int64_t* ids, int64_t n, const int64_t* n_dev, const int
 
 int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows,
                          const void* backing_rows, int64_t backing_num_rows, hb_peer_table_t* table,
-                         int64_t row_bytes, void* out_rows, int64_t* locs, uint8_t* found, int mode,
-                         hb_stream_t stream) {
+                         int64_t row_bytes, void* out_rows, int64_t* locs, uint8_t* found,
+                         int64_t* locs_sorted, int mode, hb_stream_t stream) {
   HB_CHECK_ARG(h && runs, "hb_lookup_fetch_runs: null argument");
   HB_CHECK_ARG(row_bytes > 0, "hb_lookup_fetch_runs: bad row size");
   HB_CHECK_ARG(runs->n == 0 || (cache_rows && out_rows && runs->keys && runs->perm),
@@ -446,13 +446,19 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache
   uintptr_t bits = (uintptr_t)row_bytes | (uintptr_t)cache_rows | (uintptr_t)out_rows | (uintptr_t)backing_rows;
   const bool v16 = (bits & 15) == 0;  // shards come from cudaMalloc and hold whole rows
   const int vb = (bits & 3) == 0 ? 4 : 1;
-  const int grid = (int)warp_grid(runs->n);
+  int64_t blocks = ceil_div(ceil_div(runs->n, 32) * 32, kBlock);
+  if (blocks > (int64_t)sm_count() * 32) blocks = (int64_t)sm_count() * 32;
+  const int grid = (int)(blocks < 1 ? 1 : blocks);
   int* err = device_error_word();
-#define HB_RLF(MODE, KEY, PEER, V16)                                                                   \
-  HB_LAUNCH((runs_lookup_fetch_kernel<MODE, KEY, PEER, V16>), grid, kBlock, 0, st, h->view, *runs, rs, \
-            (const char*)cache_rows, row_bytes, vb, (char*)out_rows, locs, found, err)
-#define HB_RLF_V(MODE, KEY, PEER) \
-  do { if (v16) HB_RLF(MODE, KEY, PEER, true); else HB_RLF(MODE, KEY, PEER, false); } while (0)
+#define HB_RLF(MODE, KEY, PEER, RB)                                                                   \
+  HB_LAUNCH((runs_lookup_fetch_kernel<MODE, KEY, PEER, RB>), grid, kBlock, 0, st, h->view, *runs, rs, \
+            (const char*)cache_rows, row_bytes, vb, (char*)out_rows, locs, found, locs_sorted, err)
+#define HB_RLF_V(MODE, KEY, PEER)                               \
+  do {                                                          \
+    if (v16 && row_bytes == 512) HB_RLF(MODE, KEY, PEER, 512);  \
+    else if (v16) HB_RLF(MODE, KEY, PEER, 16);                  \
+    else HB_RLF(MODE, KEY, PEER, 0);                            \
+  } while (0)
 #define HB_RLF_P(MODE, KEY) \
   do { if (table) HB_RLF_V(MODE, KEY, true); else HB_RLF_V(MODE, KEY, false); } while (0)
 #define HB_RLF_K(MODE) \
@@ -467,9 +473,9 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache
 
 size_t hb_runs_miss_list_workspace_bytes(int64_t n) { return compact_workspace_bytes(n); }
 
-int hb_runs_miss_list(const hb_runs_t* runs, const int64_t* locs, int want_class, int64_t cap,
-                      int64_t* miss_ids, int64_t* miss_src, int64_t* miss_count, void* workspace,
-                      size_t workspace_bytes, hb_stream_t stream) {
+int hb_runs_miss_list(const hb_runs_t* runs, const int64_t* locs, int locs_sorted, int want_class,
+                      int64_t cap, int64_t* miss_ids, int64_t* miss_src, int64_t* miss_count,
+                      void* workspace, size_t workspace_bytes, hb_stream_t stream) {
   HB_CHECK_ARG(runs && locs && miss_ids && miss_src && miss_count && cap > 0,
                "hb_runs_miss_list: null argument");
   HB_CHECK_ARG(want_class < 0 || runs->dclass || runs->n == 0,
@@ -483,7 +489,7 @@ int hb_runs_miss_list(const hb_runs_t* runs, const int64_t* locs, int want_class
     HB_CUDA(cudaMemsetAsync(miss_count, 0, sizeof(int64_t), st));
     return HB_OK;
   }
-  MissPolicy pol{*runs, locs, want_class, cap, miss_ids, miss_src, miss_count};
+  MissPolicy pol{*runs, locs, locs_sorted ? 1 : 0, want_class, cap, miss_ids, miss_src, miss_count};
   return run_compact(pol, runs->n, workspace, workspace_bytes, st);
 }
 

@@ -60,7 +60,8 @@ class EmbeddingPath:
                  optimizer, rank: int = 0, world: int = 1, flush_every: int = 8, id_bits: int = 64,
                  lookup_mode: int = E.LOOKUP_SETASSOC, mover: int = E.MOVER_AUTO,
                  touch_lru: bool = True, group=None, peer_exchange=None, flush_exchange=None,
-                 insert_misses: bool = True, miss_cap: int = 1 << 17, flush_cap: int = 1 << 19):
+                 insert_misses: bool = True, miss_cap: int = 1 << 17, flush_cap: int = 1 << 19,
+                 want_locs: bool = True):
         """table: backing rows for cache misses, [num_nodes, dim] fp32 on this GPU; None when the
         optimiser's shard is a ``PeerTable`` (misses then read the owners' shards).
         class_table: int8 per node, HOT or COLD.  optimizer: SparseAdam / SparseAdagrad on this
@@ -68,7 +69,9 @@ class EmbeddingPath:
         the per-step hot rows and for the flushed rows (None: NCCL all-to-all, sizes read on the
         host).  insert_misses: cold ids that miss the cache are inserted in the forward pass (at
         most miss_cap distinct ids per step; the rest stay uncached until they miss again).
-        flush_cap: rows one flush can send (the other stale rows wait for the next flush)."""
+        flush_cap: rows one flush can send (the other stale rows wait for the next flush).
+        want_locs: ``forward`` also returns the slots by batch position (False: None; the path
+        itself uses the slots in sorted order, which cost a coalesced write)."""
         self.table, self.class_table, self.cold, self.opt = table, class_table, cold, optimizer
         self.rank, self.world = rank, world
         self.flush_every, self.id_bits = flush_every, id_bits
@@ -77,6 +80,7 @@ class EmbeddingPath:
         self.px = peer_exchange
         self.px_flush = flush_exchange
         self.insert_misses = insert_misses
+        self.want_locs = want_locs
         self.miss_cap = int(miss_cap)
         self.flush_cap = int(min(flush_cap, cold.remote.slots))
         self.step_no = 0
@@ -137,19 +141,25 @@ class EmbeddingPath:
                                ws=self._ws("_runs_ws", lib.hb_runs_workspace_bytes(n)))
         self._runs_ws = runs.ws
         rows, locs, found = E.cudaLookupFetchRuns(self.cold.index, runs, self.cold.emb, self.table, self.shared,
-                                                  out_rows, self.lookup_mode)
-        if self.touch_lru:
-            self.cold.index.cuda_touch_lru_runs(locs, runs)
-        if self.insert_misses and n:
-            # the uncached cold ids and their rows go to the cache (dist_emb.py:218-259 ->
-            # server.py:499-544), before this step's cold gradients look the cache up
+                                                  out_rows, self.lookup_mode, want_locs=self.want_locs)
+        if n and (self.touch_lru or self.insert_misses):
+            # Off the main stream, which goes on to whatever uses the rows: the LRU ageing of
+            # this lookup (cache.h:101), then the uncached cold ids and their rows go to the
+            # cache (dist_emb.py:218-259 -> server.py:499-544), before this step's cold
+            # gradients look the cache up.
             with self._on_side():
-                need = max(lib.hb_runs_miss_list_workspace_bytes(n),
-                           lib.hb_staging_insert_workspace_bytes(self.miss_cap))
-                ws = self._ws("_side_ws", need)
-                miss_ids, miss_src, miss_n = E.cudaRunsMissList(runs, locs, COLD, self.miss_cap, ws=ws)
-                self.cold.insert_gather(miss_ids, rows, miss_src, ws=ws)
-                self._side_finished(miss_ids, miss_src, miss_n, rows, locs, runs)
+                if self.touch_lru:
+                    self.cold.index.cuda_touch_lru_runs(runs.slots, runs, locs_sorted=True)
+                if self.insert_misses:
+                    need = max(lib.hb_runs_miss_list_workspace_bytes(n),
+                               lib.hb_staging_insert_workspace_bytes(self.miss_cap))
+                    ws = self._ws("_side_ws", need)
+                    miss_ids, miss_src, miss_n = E.cudaRunsMissList(runs, runs.slots, COLD, self.miss_cap, ws=ws,
+                                                                    locs_sorted=True)
+                    self.cold.insert_gather(miss_ids, rows, miss_src, ws=ws)
+                    self._side_finished(miss_ids, miss_src, miss_n, rows, runs)
+                else:
+                    self._side_finished(rows, runs)
             if join:
                 self._join_side()
         self._last = (runs, locs)

@@ -106,6 +106,13 @@ def test_lookup_fetch_runs_equals_unsorted_fetch(cuda_lib, oracle_mod, mode, dim
     assert np.array_equal(found.cpu().numpy(), want_hit)
     assert np.array_equal(out.cpu().numpy(), want)
     assert 0 < want_hit.sum() < q.size
+    # the slots in sorted order (the coalesced output) are the per-position slots through the permutation
+    from hades_b200.exchange import _as_tensor
+
+    perm = _as_tensor(runs.desc.perm, (q.size,), "<i4", locs_g.device).long()
+    assert torch.equal(runs.slots[: q.size], locs_g[perm])
+    out2, none_locs, found2 = E.cudaLookupFetchRuns(ix, runs, _t(cache), _t(table), want_locs=False)
+    assert none_locs is None and torch.equal(out2, out) and torch.equal(found2, found)
     # without a backing table a miss leaves the output row untouched
     want1 = np.full((q.size, dim), -7.0, dtype)
     oracle_mod.lookup_fetch(ora, q, cache, None, want1)
@@ -186,6 +193,8 @@ def test_miss_list_and_gathered_insert(cuda_lib, oracle_mod):
         cc.index.cuda_touch_lru_runs(locs, runs)
         ox.touch(wl)
         miss_ids, miss_src, miss_n = E.cudaRunsMissList(runs, locs, 2, cap)
+        ms_ids, ms_src, ms_n = E.cudaRunsMissList(runs, runs.slots, 2, cap, locs_sorted=True)
+        assert torch.equal(ms_ids, miss_ids) and torch.equal(ms_src, miss_src) and torch.equal(ms_n, miss_n)
         u, fi = np.unique(q, return_index=True)
         want = u[(cls[u] == 2) & (wl[fi] < 0)][:cap]
         m = int(miss_n.item())
