@@ -68,16 +68,29 @@ __device__ __forceinline__ void bump4(int4& c, int cls) {
   c.w += cls == 3;
 }
 
+// The classes of a thread's 8 consecutive items.  A policy may bring its own
+// classify8(base, n, cls) (e.g. vector loads of the 8 keys); otherwise classify(i) is asked
+// item by item.
+template <typename Policy>
+__device__ __forceinline__ auto classify_items(const Policy& pol, int64_t base, int64_t n, int* cls, int)
+    -> decltype(pol.classify8(base, n, cls), void()) {
+  pol.classify8(base, n, cls);
+}
+template <typename Policy>
+__device__ __forceinline__ void classify_items(const Policy& pol, int64_t base, int64_t n, int* cls, long) {
+#pragma unroll
+  for (int k = 0; k < kCompItems; ++k) cls[k] = base + k < n ? pol.classify(base + k) : -1;
+}
+
 template <typename Policy>
 __global__ void __launch_bounds__(kCompBlock) compact_count_kernel(Policy pol, CompactPlan p) {
   __shared__ int4 s_warp[kCompBlock / 32];
   const int64_t base = (int64_t)blockIdx.x * kCompTile + (int64_t)threadIdx.x * kCompItems;
   int4 c = make_int4(0, 0, 0, 0);
+  int cls[kCompItems];
+  classify_items(pol, base, p.n, cls, 0);
 #pragma unroll
-  for (int k = 0; k < kCompItems; ++k) {
-    const int64_t i = base + k;
-    if (i < p.n) bump4(c, pol.classify(i));
-  }
+  for (int k = 0; k < kCompItems; ++k) bump4(c, cls[k]);
   const int4 t = block_sum4(c, s_warp);
   if (threadIdx.x == 0) p.tile_counts[blockIdx.x] = t;
 }
@@ -139,12 +152,9 @@ __global__ void __launch_bounds__(kCompBlock) compact_scatter_kernel(Policy pol,
   const int64_t base = tile * kCompTile + (int64_t)threadIdx.x * kCompItems;
   int cls[kCompItems];
   int4 mine = make_int4(0, 0, 0, 0);
+  classify_items(pol, base, p.n, cls, 0);
 #pragma unroll
-  for (int k = 0; k < kCompItems; ++k) {
-    const int64_t i = base + k;
-    cls[k] = i < p.n ? pol.classify(i) : -1;
-    bump4(mine, cls[k]);
-  }
+  for (int k = 0; k < kCompItems; ++k) bump4(mine, cls[k]);
   // exclusive scan of the per-thread counts over the block
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int4 inc = mine;

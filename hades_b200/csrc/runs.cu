@@ -104,6 +104,43 @@ struct HeadPolicy {
     const int8_t v = __ldg(table + id);
     return (v >= 0 && v <= 2) ? (int)v : 3;
   }
+  // the 8 items of a thread at once: their keys come in two 16-byte loads (32-bit keys) and
+  // the head flags leave in one 8-byte store
+  __device__ __forceinline__ void classify8(int64_t base, int64_t n_items, int* cls) const {
+    const int64_t ne = valid_entries();
+    if (base + 8 > n_items || sizeof(KeyT) != 4) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) cls[k] = base + k < n_items ? classify(base + k) : -1;
+      return;
+    }
+    uint32_t key[9];
+    key[0] = base > 0 ? (uint32_t)__ldg(keys + base - 1) : 0u;
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(keys + base));
+    const uint4 b = __ldg(reinterpret_cast<const uint4*>(keys + base) + 1);
+    key[1] = a.x; key[2] = a.y; key[3] = a.z; key[4] = a.w;
+    key[5] = b.x; key[6] = b.y; key[7] = b.z; key[8] = b.w;
+    unsigned long long flags = 0ull;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int64_t i = base + k;
+      const bool is_head = i < ne && (i == 0 || key[k] != key[k + 1]);
+      flags |= (unsigned long long)is_head << (8 * k);
+      int c = -1;
+      if (is_head) {
+        c = 0;
+        if (table) {
+          const int64_t id = (int64_t)key[k + 1];
+          c = 3;
+          if (id < table_len) {
+            const int8_t v = __ldg(table + id);
+            if (v >= 0 && v <= 2) c = (int)v;
+          }
+        }
+      }
+      cls[k] = c;
+    }
+    *reinterpret_cast<unsigned long long*>(head + base) = flags;
+  }
   __device__ __forceinline__ void emit(int64_t i, int cls, const int4& before) const {
     const int64_t u = (int64_t)before.x + before.y + before.z + before.w;
     const int64_t id = (int64_t)keys[i];

@@ -35,6 +35,7 @@ struct SegArgs {
   const uint32_t* perm;       // position in the input of each sorted element [n]
   const int64_t* run_start;   // [U] first sorted position of each run
   const int64_t* num_runs;    // device scalar U
+  // (run_start holds U + 1 entries: the last is the number of valid rows)
   const float* grads;         // [n][dim]
   const int64_t* cnt_in;      // nullable [n]
   const int64_t* n_dev;       // nullable device count that caps n
@@ -90,9 +91,16 @@ __device__ __forceinline__ float* out_row(const SegArgs& a, int64_t u) {
   return base ? base + (int64_t)a.dpos[u] * a.dim + a.col0 : nullptr;
 }
 
-__device__ __forceinline__ float denominator(const SegArgs& a, unsigned long long c) {
+// rows of run u (no weights) or the sum of their weights: the weights are added up with
+// integer atomics in the main pass, the plain count is the length of the run
+__device__ __forceinline__ long long run_count(const SegArgs& a, int64_t u) {
+  if (a.cnt_in) return (long long)a.counts[u];
+  return (long long)(__ldg(a.run_start + u + 1) - __ldg(a.run_start + u));
+}
+
+__device__ __forceinline__ float denominator(const SegArgs& a, long long c) {
   // unique_grads starts its counts from ones when cnt is given (sparse_optim.py:145-148)
-  return (float)(a.cnt_in ? (long long)c + 1 : (long long)c);
+  return (float)(a.cnt_in ? c + 1 : c);
 }
 
 __device__ __forceinline__ int64_t effective_n(const SegArgs& a) {
@@ -137,7 +145,7 @@ __global__ void __launch_bounds__(kBlock, 3) segsum_main_kernel(SegArgs a) {
     else if (first_partial) dst = a.head_part + c * a.cols;
     else dst = a.tail_part + c * a.cols;
     if (complete && a.mean) {
-      const float d = denominator(a, cacc);
+      const float d = denominator(a, (long long)cacc);
 #pragma unroll
       for (int v = 0; v < VPL; ++v) vdiv(acc[v], d);
     }
@@ -148,7 +156,7 @@ __global__ void __launch_bounds__(kBlock, 3) segsum_main_kernel(SegArgs a) {
         if (k < vpr) reinterpret_cast<V*>(dst)[k] = acc[v];
       }
     }
-    if (sub == 0 && a.col0 == 0 && cacc) atomicAdd(a.counts + u, cacc);
+    if (HAS_CNT && sub == 0 && a.col0 == 0 && cacc) atomicAdd(a.counts + u, cacc);
   };
 
   const int steps = a.chunk / G;  // uniform trip count (chunk is a multiple of 32)
@@ -212,7 +220,7 @@ __global__ void __launch_bounds__(kBlock, 3) segsum_main_kernel(SegArgs a) {
     const bool tail = j1 < n_eff && __ldg(a.head + j1) == 0;
     if (tail && !first_partial && sub == 0 && a.col0 == 0) {
       // this chunk holds the head of a crossing run: enter it in a fix-up list
-      const int64_t run_end = (u + 1 < U_runs) ? __ldg(a.run_start + u + 1) : n_eff;
+      const int64_t run_end = __ldg(a.run_start + u + 1);
       const int64_t last_chunk = (run_end - 1) / a.chunk;
       const bool is_short = (last_chunk - c) <= kShortSpan;
       const int slot = atomicAdd(a.list_counts + (is_short ? 0 : 1), 1);
@@ -222,20 +230,59 @@ __global__ void __launch_bounds__(kBlock, 3) segsum_main_kernel(SegArgs a) {
   }
 }
 
-// ---- fix-up of short crossing runs: one lane group per entry ---------------------------
+// ---- after the main pass (and stage A of the long runs): one launch, three kinds of blocks ----
+// Blocks [0, g_short): short crossing runs, one lane group per entry.  Blocks [g_short,
+// g_short + g_long): stage B of the long crossing runs.  The rest: the counts of every run in
+// the form the reference reports them, to `counts` or to the class buffers.
+struct CountsOut {
+  int plus_one;        // 1 + sum of cnt when cnt is given and the mean is asked (sparse_optim.py:145-148)
+  int64_t* counts;     // [U], nullable
+  int64_t* cls[3];     // per class, nullable
+  int64_t n;
+};
+
 template <int VEC, int G, int VPL>
-__global__ void __launch_bounds__(kBlock) segsum_fix_short_kernel(SegArgs a) {
+__global__ void __launch_bounds__(kBlock) segsum_finish_kernel(SegArgs a, CountsOut co, int g_short, int g_long) {
   using V = typename VecF<VEC>::T;
+  const int64_t U_runs = *a.num_runs;
+  if ((int)blockIdx.x >= g_short + g_long) {
+    const int64_t i = (int64_t)(blockIdx.x - g_short - g_long) * blockDim.x + threadIdx.x;
+    if (i >= co.n || i >= U_runs) return;
+    const int64_t c = (int64_t)run_count(a, i) + co.plus_one;
+    if (co.counts) co.counts[i] = c;
+    if (a.dclass) {
+      const int k = a.dclass[i];
+      int64_t* out = (k >= 0 && k < 3) ? co.cls[k] : nullptr;
+      if (out) out[a.dpos[i]] = c;
+    }
+    return;
+  }
+  if ((int)blockIdx.x >= g_short) {
+    // stage B of a long run: tail partial + the slice sums 0..kSlices-1, in that order
+    const int count = a.list_counts[1];
+    const int cols = a.cols;
+    for (int64_t e = blockIdx.x - g_short; e < count; e += g_long) {
+      const int2 ent = a.long_list[e];
+      const int64_t c = ent.x, u = ent.y;
+      for (int col = threadIdx.x; col < cols; col += blockDim.x) {
+        float acc = a.tail_part[c * cols + col];
+        for (int sl = 0; sl < 32; ++sl) acc += a.slice_part[(e * 32 + sl) * cols + col];
+        if (a.mean) acc /= denominator(a, run_count(a, u));
+        float* dst = out_row(a, u);
+        if (dst) dst[col] = acc;
+      }
+    }
+    return;
+  }
   const int sub = threadIdx.x & (G - 1);
   const int64_t grp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) / G;
-  const int64_t ngrp = ((int64_t)gridDim.x * blockDim.x) / G;
+  const int64_t ngrp = ((int64_t)g_short * blockDim.x) / G;
   const int count = a.list_counts[0];
-  const int64_t U_runs = *a.num_runs;
   const int vpr = a.cols / VEC;
   for (int64_t e = grp; e < count; e += ngrp) {
     const int2 ent = a.short_list[e];
     const int64_t c = ent.x, u = ent.y;
-    const int64_t run_end = (u + 1 < U_runs) ? __ldg(a.run_start + u + 1) : effective_n(a);
+    const int64_t run_end = __ldg(a.run_start + u + 1);
     const int64_t last_chunk = (run_end - 1) / a.chunk;
     V acc[VPL];
 #pragma unroll
@@ -251,7 +298,7 @@ __global__ void __launch_bounds__(kBlock) segsum_fix_short_kernel(SegArgs a) {
       }
     }
     if (a.mean) {
-      const float d = denominator(a, a.counts[u]);
+      const float d = denominator(a, run_count(a, u));
 #pragma unroll
       for (int v = 0; v < VPL; ++v) vdiv(acc[v], d);
     }
@@ -318,44 +365,7 @@ __global__ void __launch_bounds__(kLongBlock) segsum_fix_long_a_kernel(SegArgs a
   }
 }
 
-__global__ void __launch_bounds__(kLongBlock) segsum_fix_long_b_kernel(SegArgs a) {
-  const int count = a.list_counts[1];
-  const int cols = a.cols;
-  for (int64_t e = blockIdx.x; e < count; e += gridDim.x) {
-    const int2 ent = a.long_list[e];
-    const int64_t c = ent.x, u = ent.y;
-    for (int col = threadIdx.x; col < cols; col += kLongBlock) {
-      float acc = a.tail_part[c * cols + col];
-      for (int sl = 0; sl < kSlices; ++sl) acc += a.slice_part[(e * kSlices + sl) * cols + col];
-      if (a.mean) acc /= denominator(a, a.counts[u]);
-      float* dst = out_row(a, u);
-      if (dst) dst[col] = acc;
-    }
-  }
-}
-
 // ---- small helpers ----------------------------------------------------------------------------
-// counts -> the denominators the reference reports (1 + sum of cnt when cnt is given)
-__global__ void finish_counts_kernel(const unsigned long long* __restrict__ raw,
-                                     const int64_t* __restrict__ num_runs, int plus_one,
-                                     int64_t* __restrict__ out, int64_t n) {
-  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (i < n && i < *num_runs) out[i] = (int64_t)raw[i] + plus_one;
-}
-
-// with a split: counts go to the class buffers too
-__global__ void finish_counts_split_kernel(const unsigned long long* __restrict__ raw,
-                                           const int64_t* __restrict__ num_runs, int plus_one,
-                                           const int8_t* __restrict__ dclass,
-                                           const int32_t* __restrict__ dpos, int64_t* c0, int64_t* c1,
-                                           int64_t* c2, int64_t n) {
-  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (i >= n || i >= *num_runs) return;
-  const int c = dclass[i];
-  int64_t* out = c == 0 ? c0 : (c == 1 ? c1 : (c == 2 ? c2 : nullptr));
-  if (out) out[dpos[i]] = (int64_t)raw[i] + plus_one;
-}
-
 int choose_chunk(int64_t n) {
   // at least ~16 chunks per SM, between 32 and 128 rows
   int64_t target = n / ((int64_t)sm_count() * 16);
@@ -396,44 +406,47 @@ SegPlan make_plan(void* ws, int64_t n, int64_t dim) {
 }
 
 template <int VEC, int G, int VPL>
-int launch_pass(const SegArgs& a, cudaStream_t st) {
+int launch_pass(const SegArgs& a, const CountsOut& co, cudaStream_t st) {
   const int64_t threads = a.num_chunks * G;
   if (a.cnt_in)
     HB_LAUNCH((segsum_main_kernel<VEC, G, VPL, true>), (int)ceil_div(threads, kBlock), kBlock, 0, st, a);
   else
     HB_LAUNCH((segsum_main_kernel<VEC, G, VPL, false>), (int)ceil_div(threads, kBlock), kBlock, 0, st, a);
-  int fix_grid = (int)ceil_div(a.num_chunks * G, kBlock);
-  const int cap = sm_count() * 8;
-  if (fix_grid > cap) fix_grid = cap;
-  HB_LAUNCH((segsum_fix_short_kernel<VEC, G, VPL>), fix_grid, kBlock, 0, st, a);
   const int strands = kLongBlock / a.cols > 0 ? kLongBlock / a.cols : 1;
   const size_t smem = (size_t)strands * a.cols * sizeof(float);
   HB_LAUNCH(segsum_fix_long_a_kernel, kSlices * kEntriesInFlight, kLongBlock, smem, st, a);
-  HB_LAUNCH(segsum_fix_long_b_kernel, 64, kLongBlock, 0, st, a);
+  int g_short = (int)ceil_div(a.num_chunks * G, kBlock);
+  const int cap = sm_count() * 8;
+  if (g_short > cap) g_short = cap;
+  const int g_long = 64;
+  // counts are the same for every column pass: written with the first
+  const bool want_counts = a.col0 == 0 && (co.counts || co.cls[0] || co.cls[1] || co.cls[2]);
+  const int g_counts = want_counts ? (int)ceil_div(co.n, kBlock) : 0;
+  HB_LAUNCH((segsum_finish_kernel<VEC, G, VPL>), g_short + g_long + g_counts, kBlock, 0, st, a, co, g_short, g_long);
   return HB_OK;
 }
 
-int dispatch_pass(const SegArgs& a, bool vec4, cudaStream_t st) {
+int dispatch_pass(const SegArgs& a, const CountsOut& co, bool vec4, cudaStream_t st) {
   if (vec4) {
     const int vpr = a.cols / 4;
-    if (vpr > 64) return launch_pass<4, 32, 4>(a, st);
-    if (vpr > 32) return launch_pass<4, 32, 2>(a, st);
-    if (vpr > 16) return launch_pass<4, 32, 1>(a, st);
-    if (vpr > 8) return launch_pass<4, 16, 1>(a, st);
-    if (vpr > 4) return launch_pass<4, 8, 1>(a, st);
-    if (vpr > 2) return launch_pass<4, 4, 1>(a, st);
-    if (vpr > 1) return launch_pass<4, 2, 1>(a, st);
-    return launch_pass<4, 1, 1>(a, st);
+    if (vpr > 64) return launch_pass<4, 32, 4>(a, co, st);
+    if (vpr > 32) return launch_pass<4, 32, 2>(a, co, st);
+    if (vpr > 16) return launch_pass<4, 32, 1>(a, co, st);
+    if (vpr > 8) return launch_pass<4, 16, 1>(a, co, st);
+    if (vpr > 4) return launch_pass<4, 8, 1>(a, co, st);
+    if (vpr > 2) return launch_pass<4, 4, 1>(a, co, st);
+    if (vpr > 1) return launch_pass<4, 2, 1>(a, co, st);
+    return launch_pass<4, 1, 1>(a, co, st);
   }
   const int vpr = a.cols;
-  if (vpr > 64) return launch_pass<1, 32, 4>(a, st);
-  if (vpr > 32) return launch_pass<1, 32, 2>(a, st);
-  if (vpr > 16) return launch_pass<1, 32, 1>(a, st);
-  if (vpr > 8) return launch_pass<1, 16, 1>(a, st);
-  if (vpr > 4) return launch_pass<1, 8, 1>(a, st);
-  if (vpr > 2) return launch_pass<1, 4, 1>(a, st);
-  if (vpr > 1) return launch_pass<1, 2, 1>(a, st);
-  return launch_pass<1, 1, 1>(a, st);
+  if (vpr > 64) return launch_pass<1, 32, 4>(a, co, st);
+  if (vpr > 32) return launch_pass<1, 32, 2>(a, co, st);
+  if (vpr > 16) return launch_pass<1, 32, 1>(a, co, st);
+  if (vpr > 8) return launch_pass<1, 16, 1>(a, co, st);
+  if (vpr > 4) return launch_pass<1, 8, 1>(a, co, st);
+  if (vpr > 2) return launch_pass<1, 4, 1>(a, co, st);
+  if (vpr > 1) return launch_pass<1, 2, 1>(a, co, st);
+  return launch_pass<1, 1, 1>(a, co, st);
 }
 
 }  // namespace
@@ -462,7 +475,7 @@ int hb_segsum_runs_f32(const hb_runs_t* runs, const float* grads, const int64_t*
     set_error("hb_segsum_runs_f32: workspace of %zu bytes needed, %zu given", s.total, workspace_bytes);
     return HB_ERR_WORKSPACE;
   }
-  HB_CUDA(cudaMemsetAsync(s.raw_counts, 0, n * sizeof(unsigned long long), st));
+  if (cnt_in) HB_CUDA(cudaMemsetAsync(s.raw_counts, 0, n * sizeof(unsigned long long), st));
   uintptr_t align_bits = (uintptr_t)grads | (uintptr_t)sums;
   if (split)
     for (int c = 0; c < 3; ++c) align_bits |= (uintptr_t)split->out_rows[c];
@@ -491,23 +504,19 @@ int hb_segsum_runs_f32(const hb_runs_t* runs, const float* grads, const int64_t*
   a.long_list = s.long_list;
   a.list_counts = s.list_counts;
   a.slice_part = s.slice_part;
+  CountsOut co;
+  co.plus_one = (cnt_in && mean) ? 1 : 0;
+  co.counts = counts;
+  for (int c = 0; c < 3; ++c) co.cls[c] = split ? split->out_cnt[c] : nullptr;
+  co.n = n;
   const int tile = vec4 ? 512 : 128;
   int rc;
   for (int64_t col0 = 0; col0 < dim; col0 += tile) {
     a.col0 = col0;
     a.cols = (int)((dim - col0) < tile ? (dim - col0) : tile);
     if (col0 == 0) HB_CUDA(cudaMemsetAsync(s.list_counts, 0, 4 * sizeof(int), st));
-    rc = dispatch_pass(a, vec4, st);
+    rc = dispatch_pass(a, co, vec4, st);
     if (rc != HB_OK) return rc;
-  }
-  if (counts) {
-    HB_LAUNCH(finish_counts_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, s.raw_counts,
-              runs->num_runs, (cnt_in && mean) ? 1 : 0, counts, n);
-  }
-  if (split && (split->out_cnt[0] || split->out_cnt[1] || split->out_cnt[2])) {
-    HB_LAUNCH(finish_counts_split_kernel, (int)ceil_div(n, kBlock), kBlock, 0, st, s.raw_counts,
-              runs->num_runs, (cnt_in && mean) ? 1 : 0, runs->dclass, runs->dpos, split->out_cnt[0],
-              split->out_cnt[1], split->out_cnt[2], n);
   }
   return HB_OK;
 }
