@@ -481,6 +481,7 @@ def parity_steps(rank, world, dev, exchange, lookup_mode) -> dict:
            "rows_flushed_rank0": flushed_total}
     if err:
         out["error_rank0"] = err
+    path.close()
     del path
     torch.cuda.empty_cache()
     return out
@@ -759,6 +760,7 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
             line["e2e"] = e2e
         if parity is not None:
             line["parity_check"] = parity
+    path.close()
     del path
     torch.cuda.empty_cache()
     return line
@@ -926,6 +928,8 @@ def run_exchange(args, steps: int, warmup: int) -> dict:
                            "peak_source": "measured peer copy on this pool (cudaMemcpyPeer, 1 GiB, per direction)",
                            "nominal_peak": NVLINK_NOMINAL_GBS,
                            "frac_of_nominal": res["push_gbs_out_of_each_gpu"] / NVLINK_NOMINAL_GBS, "traffic": None}
+    px.close()
+    px_nf.close()
     del px, px_nf, shard, opt
     torch.cuda.empty_cache()
     return res
@@ -1029,6 +1033,8 @@ def run_hot_aggregation(args, steps: int, warmup: int) -> dict:
                         "frac": alg / (out["local"] * 1e-3) / 1e9 / peak,
                         "peak_source": "measured" if peaks else "fallback", "traffic": None},
            "device_status": status}
+    if px is not None:
+        px.close()
     del px, table, state
     torch.cuda.empty_cache()
     return res

@@ -92,6 +92,7 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_a2a_handle_bytes": (_sz, []),
     "hb_a2a_export_handle": (_int, [_p, _p]),
     "hb_a2a_connect": (_int, [_p, _p]),
+    "hb_a2a_disconnect": (_int, [_p]),
     "hb_a2a_destroy": (_int, [_p]),
     "hb_a2a_push_workspace_bytes": (_sz, [_i64, _int]),
     "hb_a2a_push": (_int, [_p, _p, _p, _p, _i64, _p, _p, _p, _p, _sz, _p]),
@@ -107,6 +108,7 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_peer_table_connect": (_int, [_p, _p]),
     "hb_peer_table_set_peer": (_int, [_p, _int, _p]),
     "hb_peer_table_local": (_int, [_p, _p, _p]),
+    "hb_peer_table_disconnect": (_int, [_p]),
     "hb_peer_table_destroy": (_int, [_p]),
     "hb_peer_table_gather": (_int, [_p, _p, _i64, _p, _p, _p]),
     "hb_lookup_fetch_sharded": (_int, [_p, _p, _i64, _p, _p, _p, _p, _p, _int, _p]),

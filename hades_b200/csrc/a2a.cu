@@ -220,6 +220,23 @@ int hb_a2a_connect(hb_a2a_t* a, const void* handles) {
   return HB_OK;
 }
 
+// Close this process's mappings of the peers' areas.  Tear-down in two steps, with a
+// barrier of all ranks before each: first every rank disconnects (nobody touches a peer's
+// memory any more), then every rank destroys (frees its own areas).  Freeing an area that a
+// peer still has mapped is undefined behaviour of the CUDA IPC interface.
+int hb_a2a_disconnect(hb_a2a_t* a) {
+  if (!a) return HB_OK;
+  for (int r = 0; r < a->world; ++r) {
+    if (!a->opened[r]) continue;
+    for (int p = 0; p < 2; ++p) {
+      cudaIpcCloseMemHandle(a->peer[p][r]);
+      a->peer[p][r] = nullptr;
+    }
+    a->opened[r] = false;
+  }
+  return HB_OK;
+}
+
 int hb_a2a_destroy(hb_a2a_t* a) {
   if (!a) return HB_OK;
   for (int r = 0; r < a->world; ++r)

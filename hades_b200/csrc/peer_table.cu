@@ -189,6 +189,19 @@ int hb_peer_table_local(hb_peer_table_t* t, void** rows, int64_t* rows_local) {
   return HB_OK;
 }
 
+// Close this process's mappings of the peers' shards; see hb_a2a_disconnect for the order of
+// a tear-down (all ranks disconnect, barrier, all ranks destroy).
+int hb_peer_table_disconnect(hb_peer_table_t* t) {
+  if (!t) return HB_OK;
+  for (int r = 0; r < t->world; ++r) {
+    if (!t->opened[r]) continue;
+    cudaIpcCloseMemHandle(t->peer[r]);
+    t->peer[r] = nullptr;
+    t->opened[r] = false;
+  }
+  return HB_OK;
+}
+
 int hb_peer_table_destroy(hb_peer_table_t* t) {
   if (!t) return HB_OK;
   for (int r = 0; r < t->world; ++r)

@@ -89,6 +89,23 @@ class PeerExchange:
         if world > 1:
             dist.barrier(group=group)  # every rank has mapped every area before anyone pushes
 
+    def close(self) -> None:
+        """Release the shared memory.  A collective when world > 1: every rank calls it, at a
+        point where no kernel of any rank touches a peer's memory any more.  (Mappings are closed
+        on all ranks before any rank frees: freeing memory a peer still has mapped is undefined
+        behaviour of the CUDA IPC interface.  Dropping the last reference without close() only
+        frees this rank's side, which is safe at process exit.)"""
+        if not getattr(self, "_h", None):
+            return
+        if self.world > 1:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+        self.lib.hb_a2a_disconnect(self._h)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self.lib.hb_a2a_destroy(self._h)
+        self._h = None
+
     def __del__(self):
         if getattr(self, "_h", None):
             try:

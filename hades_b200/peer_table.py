@@ -25,6 +25,7 @@ class PeerTable:
         process driving several GPUs, or tests)."""
         self.lib = _lib.load()
         self.rank, self.world, self.num_rows, self.dim, self.dtype = rank, world, int(num_rows), int(dim), dtype
+        self.group = group
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         elem = torch.empty(0, dtype=dtype).element_size()
         self.row_bytes = dim * elem
@@ -62,6 +63,23 @@ class PeerTable:
         _lib.check(self.lib.hb_peer_table_local(self._h, C.byref(ptr), C.byref(rows)))
         self.rows_local = rows.value
         self.weight = _as_tensor(ptr.value, (max(self.rows_local, 1), dim), _TYPESTR[dtype], self.device)[: self.rows_local]
+
+    def close(self) -> None:
+        """Release the shared memory.  A collective when world > 1: every rank calls it, at a
+        point where no kernel of any rank touches a peer's memory any more.  (Mappings are closed
+        on all ranks before any rank frees: freeing memory a peer still has mapped is undefined
+        behaviour of the CUDA IPC interface.  Dropping the last reference without close() only
+        frees this rank's side, which is safe at process exit.)"""
+        if not getattr(self, "_h", None):
+            return
+        if self.world > 1:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+        self.lib.hb_peer_table_disconnect(self._h)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self.lib.hb_peer_table_destroy(self._h)
+        self._h = None
 
     def __del__(self):
         if getattr(self, "_h", None):

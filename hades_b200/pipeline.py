@@ -415,6 +415,16 @@ class EmbeddingPath:
         if self.world > 1:
             dist.barrier(group=self.group)
 
+    def close(self) -> None:
+        """Release what this path shares with the other ranks (exchange areas, the owner shard);
+        every rank calls it, after its last step.  The path cannot step afterwards."""
+        torch.cuda.synchronize()
+        self._graphs, self._split = [], None
+        for obj in (self.px, self.px_flush, self.shared):
+            if obj is not None:
+                obj.close()
+        self.px = self.px_flush = None
+
     # ---- save / resume ---------------------------------------------------------------------------
     def state_dict(self) -> dict:
         """Everything a resumed run needs to continue bit for bit: index lines and LRU counters,

@@ -520,6 +520,7 @@ int hb_a2a_create(int rank, int world, int64_t cap_rows, int64_t row_bytes, hb_a
 size_t hb_a2a_handle_bytes(void);
 int hb_a2a_export_handle(hb_a2a_t* a, void* handle_out /* host */);
 int hb_a2a_connect(hb_a2a_t* a, const void* handles /* host, world entries in rank order */);
+int hb_a2a_disconnect(hb_a2a_t* a); /* first step of a tear-down, see hb_peer_table_disconnect */
 int hb_a2a_destroy(hb_a2a_t* a);
 size_t hb_a2a_push_workspace_bytes(int64_t n, int world);
 /* sent_counts (nullable): device int64[world], rows sent to each owner.
@@ -595,6 +596,11 @@ int hb_peer_table_connect(hb_peer_table_t* t, const void* handles /* host, world
 int hb_peer_table_set_peer(hb_peer_table_t* t, int rank, const void* shard_rows);
 /* This rank's shard: rows_local = ceil((num_rows - rank) / world) rows. */
 int hb_peer_table_local(hb_peer_table_t* t, void** rows, int64_t* rows_local);
+/* Tear-down of anything shared through CUDA IPC (this table, an exchange) takes two steps
+ * with a barrier of all ranks before each: every rank disconnects (closes its mappings of the
+ * peers' memory), then every rank destroys (frees its own).  Freeing memory that a peer still
+ * has mapped is undefined behaviour of the IPC interface. */
+int hb_peer_table_disconnect(hb_peer_table_t* t);
 int hb_peer_table_destroy(hb_peer_table_t* t);
 /* dst[i, :] = row of ids[i] from its owner's shard, i < min(n, *n_dev). */
 int hb_peer_table_gather(hb_peer_table_t* t, const int64_t* ids, int64_t n,

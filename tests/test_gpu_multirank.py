@@ -112,6 +112,7 @@ def _worker(rank, port, exchange):
         compare_rank(path, orc, rank, where=f"rank {rank} step {it}")
     assert flushed_total > 0
     assert path.step_no == 5
+    path.close()
     torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()
