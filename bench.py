@@ -881,7 +881,10 @@ def run_exchange(args, steps: int, warmup: int) -> dict:
     cnt = torch.ones(n, dtype=torch.int64, device=dev)
     sent_to_others = int((ids_np % world != rank).sum())
     bytes_out = sent_to_others * (8 + 8 + dim * 4)
-    cap = int(np.bincount(ids_np % world, minlength=world).max() * 1.05) + 16
+    cap_t = torch.tensor([int(np.bincount(ids_np % world, minlength=world).max() * 1.05) + 16], device=dev)
+    if world > 1:
+        dist.all_reduce(cap_t, op=dist.ReduceOp.MAX)  # the slabs have one size on every rank
+    cap = int(cap_t.item())
     px = PeerExchange(rank, world, cap, dim, torch.float32, dev)                    # device-side fence
     px_nf = PeerExchange(rank, world, cap, dim, torch.float32, dev, fence="nccl")   # all-reduce as the fence
     shard = ShardedEmbedding(table_rows, dim, rank, world, dtype=torch.float16, device=dev, init_sigma=0.01, seed=4)

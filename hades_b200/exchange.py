@@ -51,10 +51,14 @@ class PeerExchange:
         if world > 1:
             # collectives are entered by every rank, whether or not its local set-up worked
             gathered = [None] * world
-            dist.all_gather_object(gathered, (err, bytes(mine.raw)), group=group)
+            dist.all_gather_object(gathered, (err, bytes(mine.raw), (self.cap, dim * elem)), group=group)
             errs = [g[0] for g in gathered if g[0]]
             if errs:
                 raise RuntimeError("peer exchange set-up failed on a rank: " + errs[0])
+            shapes = {g[2] for g in gathered}
+            if len(shapes) != 1:
+                # every rank computes the offsets inside a peer's area from its own numbers
+                raise RuntimeError(f"peer exchange: (slab rows, row bytes) differ between the ranks: {sorted(shapes)}")
             blob = b"".join(g[1] for g in gathered)
         else:
             if err:
