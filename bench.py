@@ -631,6 +631,24 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
         path.step_no = 0
         flush_ms = (ms_step - ms_noflush) * cfg.flush_every
 
+    # forward and backward on their own, eager, every rank in step with the others (with several
+    # GPUs the forward pass reads the peers' shards while the peers do the same)
+    saved = path.flush_every
+    path.flush_every = 0
+
+    def fwd_only(k):
+        path.forward(ids_stage, out_rows, join=True)
+
+    def bwd_only(k):
+        path.backward(ids_stage, grads)
+
+    fwd_only(0)
+    breakdown = {"forward_ms": timed(fwd_only, 10), "backward_ms": timed(bwd_only, 10),
+                 "what": "eager launches, all ranks in step; forward = sort + lookup/fetch (+ LRU ageing and cache insert "
+                         "on the side stream, joined); backward = aggregation, cold accumulate, exchange, owner update"}
+    path.flush_every = saved
+    path.step_no = 0
+
     e2e = None
     if not args.no_e2e:
         for k in range(2):
@@ -717,7 +735,7 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
                        "table_rows": cfg.table_rows, "dim": cfg.dim, "cache_entries": cfg.cache_entries,
                        "batch_per_gpu": cfg.batch, "zipf_s": None if c5 else cfg.zipf_s,
                        "flush_every": cfg.flush_every, "steps_with_flush": K // cfg.flush_every if cfg.flush_every else 0,
-                       "flush_ms": flush_ms,
+                       "flush_ms": flush_ms, "breakdown": breakdown,
                        "lookup": args.lookup, "lru_ageing": not args.no_lru, "insert_cold_misses": not args.no_insert,
                        "cuda_graph": use_graph, "untimed_settling_steps_after_warmup": settle,
                        "optimizer": "SparseAdam fp32" if args.optimizer == "adam" else "SparseAdagrad fp32",
