@@ -168,13 +168,13 @@ class IndexCache:
                                                 ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
 
     def cuda_touch_lru_runs(self, locs: torch.Tensor, runs=None, n_dev: torch.Tensor | None = None,
-                            locs_sorted: bool = False) -> None:
+                            locs_kind: int = 0) -> None:
         """LRU ageing for a batch grouped in runs of equal ids (no sort).  runs: the
         ``BatchRuns`` of ``cudaRunsBuild`` (or the ``RunsDesc`` returned by
         ``cudaUniqueSegSum(..., want_runs=True)``, valid until another call uses the shared
         workspace) for the ids that were looked up; None: the batch holds each id once (every
-        position is its own run).  locs_sorted: locs[j] is the slot of the j-th sorted entry
-        (``BatchRuns.slots`` after ``cudaLookupFetchRuns``), not of batch position j."""
+        position is its own run).  locs_kind: locs holds a slot per batch position (0), per
+        sorted entry (1) or per run (2: ``BatchRuns.slots`` after ``cudaLookupFetchRuns``)."""
         n = locs.numel()
         if runs is None:
             _lib.check(self._lib.hb_index_touch_lru_runs(self._h, locs.data_ptr(), None, None, n, None, n,
@@ -183,7 +183,7 @@ class IndexCache:
             runs = getattr(runs, "desc", runs)  # a BatchRuns or its RunsDesc
             cap = _lib.ptr(n_dev) if n_dev is not None else runs.n_dev
             _lib.check(self._lib.hb_index_touch_lru_runs(self._h, locs.data_ptr(), runs.perm, runs.run_start,
-                                                         n, runs.num_runs, n, cap, int(locs_sorted),
+                                                         n, runs.num_runs, n, cap, int(locs_kind),
                                                          _lib.stream_ptr()))
 
     def cuda_lookup_found(self, ids: torch.Tensor, mode: int | None = None):
@@ -656,7 +656,8 @@ class BatchRuns:
         self.num_unique, self.class_counts, self.class_ids, self.uniq_ids = num_unique, class_counts, class_ids, uniq_ids
         self.n = ids.numel()
         self._version = ids._version
-        self.slots = None  # slot of every SORTED entry, written by cudaLookupFetchRuns
+        self.slots = None  # slot of every RUN (distinct id), written by cudaLookupFetchRuns
+        self.fetch_ws = None
 
     def matches(self, ids: torch.Tensor) -> bool:
         """True when `ids` is the tensor these runs were built from, unchanged since."""
@@ -699,13 +700,15 @@ def cudaRunsBuild(ids, id_bits: int = 64, table=None, keep=(True, True, True), c
 
 
 def cudaLookupFetchRuns(index: IndexCache, runs: BatchRuns, cache_rows, backing_rows=None, peer_table=None,
-                        out_rows=None, mode: int | None = None, want_locs: bool = True):
+                        out_rows=None, mode: int | None = None, want_locs: bool = True,
+                        ws: torch.Tensor | None = None):
     """``cudaLookupFetch`` over a batch that ``cudaRunsBuild`` sorted: (out_rows, locs, found) at
     the batch positions, every distinct id read once per warp that meets it.  Misses read
     backing_rows on this GPU, or the owners' shards of peer_table (``peer_table.PeerTable``).
-    The slots are also left in ``runs.slots`` in SORTED order (a coalesced write); want_locs=False
-    skips the per-position ``locs`` (8-byte writes scattered over the batch, about 15 % of the
-    kernel's time) and returns None for them."""
+    The slot of every RUN (distinct id, in the order of ``runs.uniq_ids``) is left in
+    ``runs.slots``; want_locs=False skips the per-position ``locs`` (8-byte writes scattered over
+    the batch, about 15 % of the time) and returns None for them.  Rows of other GPUs' shards are
+    first copied, once per distinct id, into a staging buffer on this GPU."""
     n = runs.n
     dev = runs.ids.device
     if out_rows is None:
@@ -718,13 +721,20 @@ def cudaLookupFetchRuns(index: IndexCache, runs: BatchRuns, cache_rows, backing_
     if runs.slots is None:
         runs.slots = torch.empty(max(n, 1), dtype=torch.int64, device=dev)
     lib = _lib.load()
+    sharded = peer_table is not None and peer_table.world > 1
+    need = lib.hb_lookup_fetch_runs_workspace_bytes(n, _row_bytes(cache_rows), int(sharded))
+    if ws is not None and ws.numel() >= need:
+        runs.fetch_ws = ws  # the caller's scratch (hb_lookup_fetch_runs_workspace_bytes)
+    elif runs.fetch_ws is None or runs.fetch_ws.numel() < need:
+        runs.fetch_ws = torch.empty(need, dtype=torch.uint8, device=dev)
     _lib.check(lib.hb_lookup_fetch_runs(index.handle, C.byref(runs.desc), _dev_ptr(cache_rows, "cache_rows"),
                                         None if backing_rows is None else _dev_ptr(backing_rows, "backing_rows"),
                                         0 if backing_rows is None else backing_rows.size(0),
                                         None if peer_table is None else peer_table.handle,
                                         _row_bytes(cache_rows), out_rows.data_ptr(), _lib.ptr(locs),
                                         found.data_ptr(), runs.slots.data_ptr(),
-                                        index.lookup_mode if mode is None else mode, _lib.stream_ptr()))
+                                        index.lookup_mode if mode is None else mode, runs.fetch_ws.data_ptr(),
+                                        runs.fetch_ws.numel(), _lib.stream_ptr()))
     return out_rows, locs, found
 
 
@@ -768,11 +778,11 @@ def cudaSegSumRuns(runs: BatchRuns, grads, cnt=None, mean: bool = False, split_k
 
 
 def cudaRunsMissList(runs: BatchRuns, locs, want_class: int, cap: int, ws: torch.Tensor | None = None,
-                     locs_sorted: bool = False):
+                     locs_kind: int = 0):
     """The distinct ids of class want_class (< 0: any) whose lookup missed, ascending, at most
     cap: (miss_ids [cap] padded with -1, miss_src [cap] = a batch position of the id,
-    miss_count on the device).  locs: the slots by batch position, or (locs_sorted=True) by
-    sorted entry (``runs.slots``).  What DistEmbeddingTensor.__call__ ships to the cache server,
+    miss_count on the device).  locs: the slots by batch position (locs_kind 0), by sorted entry
+    (1) or by run (2: ``runs.slots``).  What DistEmbeddingTensor.__call__ ships to the cache server,
     python/EmbCache/dist_emb.py:218-259."""
     dev = locs.device
     lib = _lib.load()
@@ -783,7 +793,7 @@ def cudaRunsMissList(runs: BatchRuns, locs, want_class: int, cap: int, ws: torch
     miss_ids = torch.empty(cap, dtype=torch.int64, device=dev)
     miss_src = torch.zeros(cap, dtype=torch.int64, device=dev)
     count = torch.zeros(1, dtype=torch.int64, device=dev)
-    _lib.check(lib.hb_runs_miss_list(C.byref(runs.desc), locs.data_ptr(), int(locs_sorted), int(want_class), int(cap),
+    _lib.check(lib.hb_runs_miss_list(C.byref(runs.desc), locs.data_ptr(), int(locs_kind), int(want_class), int(cap),
                                      miss_ids.data_ptr(), miss_src.data_ptr(), count.data_ptr(), ws.data_ptr(),
                                      ws.numel(), _lib.stream_ptr()))
     return miss_ids, miss_src, count

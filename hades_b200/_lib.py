@@ -74,7 +74,8 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_runs_build": (_int, [_p, _i64, _p, _p, _i64, _int, _p, _i64, _p, _p, _p, _p, _p, _sz, _p, _p]),
     "hb_segsum_runs_workspace_bytes": (_sz, [_i64, _i64]),
     "hb_segsum_runs_f32": (_int, [_p, _p, _p, _i64, _int, _p, _p, _p, _p, _sz, _p]),
-    "hb_lookup_fetch_runs": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p, _p, _p, _int, _p]),
+    "hb_lookup_fetch_runs_workspace_bytes": (_sz, [_i64, _i64, _int]),
+    "hb_lookup_fetch_runs": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p, _p, _p, _int, _p, _sz, _p]),
     "hb_runs_miss_list_workspace_bytes": (_sz, [_i64]),
     "hb_runs_miss_list": (_int, [_p, _p, _int, _int, _i64, _p, _p, _p, _p, _sz, _p]),
     "hb_staging_accumulate_cached": (_int, [_p, _p, _p, _p, _i64, _p, _p, C.c_int32, _int, _p, _p, _p]),
@@ -119,7 +120,7 @@ class RunsDesc(C.Structure):
     """hb_runs_t"""
     _fields_ = [("perm", _p), ("run_start", _p), ("num_runs", _p), ("n", _i64), ("keys", _p),
                 ("key_bytes", _int), ("head", _p), ("uniq_ids", _p), ("dclass", _p), ("dpos", _p),
-                ("class_counts", _p), ("n_dev", _p)]
+                ("class_counts", _p), ("n_dev", _p), ("base8", _p)]
 
 
 class ClassSplitDesc(C.Structure):

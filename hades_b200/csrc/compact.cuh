@@ -82,6 +82,16 @@ __device__ __forceinline__ void classify_items(const Policy& pol, int64_t base, 
   for (int k = 0; k < kCompItems; ++k) cls[k] = base + k < n ? pol.classify(base + k) : -1;
 }
 
+// A policy may ask for the number of kept items ahead of every thread's 8 items
+// (thread_begin(base, before)), e.g. to leave a coarse index of the compaction behind.
+template <typename Policy>
+__device__ __forceinline__ auto thread_begin_hook(const Policy& pol, int64_t base, const int4& before, int)
+    -> decltype(pol.thread_begin(base, before), void()) {
+  pol.thread_begin(base, before);
+}
+template <typename Policy>
+__device__ __forceinline__ void thread_begin_hook(const Policy&, int64_t, const int4&, long) {}
+
 template <typename Policy>
 __global__ void __launch_bounds__(kCompBlock) compact_count_kernel(Policy pol, CompactPlan p) {
   __shared__ int4 s_warp[kCompBlock / 32];
@@ -174,6 +184,7 @@ __global__ void __launch_bounds__(kCompBlock) compact_scatter_kernel(Policy pol,
     run.x += x.x; run.y += x.y; run.z += x.z; run.w += x.w;
   }
   run.x += inc.x - mine.x; run.y += inc.y - mine.y; run.z += inc.z - mine.z; run.w += inc.w - mine.w;
+  if (base < p.n) thread_begin_hook(pol, base, run, 0);
 #pragma unroll
   for (int k = 0; k < kCompItems; ++k) {
     if (cls[k] >= 0) {

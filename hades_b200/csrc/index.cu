@@ -235,10 +235,11 @@ struct RunsView {
   const int64_t* n_dev;      // nullable device count of positions
   int64_t max_runs;
   int64_t n;
-  int locs_sorted;           // locs[j] belongs to sorted entry j, not to batch position j
+  int locs_kind;             // locs holds a slot per batch position (0), per sorted entry (1), per run (2)
   __device__ __forceinline__ int64_t slot_of_run(int64_t u) const {
+    if (locs_kind == 2) return locs[u];
     const int64_t j = start(u);
-    return locs[locs_sorted ? j : pos(j)];
+    return locs[locs_kind == 1 ? j : pos(j)];
   }
   __device__ __forceinline__ int64_t positions() const {
     if (!n_dev) return n;
@@ -552,11 +553,12 @@ int hb_index_touch_lru(hb_index_t* h, const int64_t* locs, int64_t n, void* work
 
 int hb_index_touch_lru_runs(hb_index_t* h, const int64_t* locs, const uint32_t* perm,
                             const int64_t* run_start, int64_t max_runs, const int64_t* num_runs,
-                            int64_t n, const int64_t* n_dev, int locs_sorted, hb_stream_t stream) {
+                            int64_t n, const int64_t* n_dev, int locs_kind, hb_stream_t stream) {
   HB_CHECK_ARG(h && (n == 0 || locs), "hb_index_touch_lru_runs: null argument");
   HB_CHECK_ARG(n >= 0 && n < ((int64_t)1 << 31) && max_runs >= 0 && max_runs <= n,
                "hb_index_touch_lru_runs: sizes out of range");
   HB_CHECK_ARG(!(perm && !run_start), "hb_index_touch_lru_runs: a position list needs run starts");
+  HB_CHECK_ARG(locs_kind >= 0 && locs_kind <= 2, "hb_index_touch_lru_runs: locs_kind is 0, 1 or 2");
   if (n == 0 || max_runs == 0) return HB_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t cap = h->cache_size;
@@ -567,7 +569,7 @@ int hb_index_touch_lru_runs(hb_index_t* h, const int64_t* locs, const uint32_t* 
     HB_CUDA(cudaMemsetAsync(h->slot_epoch, 0, (cap + 1) * sizeof(int32_t), st));
   }
   int32_t* epoch_dev = h->slot_epoch + cap;  // the batch counter sits after the marks
-  RunsView v{locs, perm, run_start, num_runs, n_dev, max_runs, n, locs_sorted ? 1 : 0};
+  RunsView v{locs, perm, run_start, num_runs, n_dev, max_runs, n, locs_kind};
   HB_LAUNCH(touch_runs_next_epoch_kernel, 1, 1, 0, st, epoch_dev);
   HB_LAUNCH(touch_runs_mark_kernel, grid_for(max_runs), kBlock, 0, st, v, cap, epoch_dev, h->slot_run,
             h->slot_epoch);

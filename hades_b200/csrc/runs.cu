@@ -89,6 +89,10 @@ struct HeadPolicy {
   int64_t* num_runs2;    // nullable second copy
   int64_t* class_counts;
   int64_t* class_counts2;
+  int32_t* base8;        // [ceil(n / 8)] runs that start before entry 8k
+  __device__ __forceinline__ void thread_begin(int64_t base, const int4& before) const {
+    base8[base >> 3] = before.x + before.y + before.z + before.w;
+  }
   __device__ __forceinline__ int64_t valid_entries() const {
     if (!n_dev) return n;
     const int64_t d = *n_dev;
@@ -165,10 +169,21 @@ struct HeadPolicy {
 };
 
 // ---- forward: lookup + fetch over the sorted batch -----------------------------------------
+// Two launches.  RESOLVE works per distinct id (one lane per run): the index probe, the slot
+// of the run, and where the row of the run is to be read from -- the cache row, the row of the
+// table on this GPU, or, for a row that lives on ANOTHER GPU, a copy that this kernel makes in
+// a staging buffer on this GPU, so that every remote row crosses NVLink once per step however
+// often its id occurs in the batch (a row read again by every warp that meets the id, from
+// seven GPUs at once, serialises on one L2 slice of its owner).  EXPAND works per entry of the
+// sorted batch: the row goes to the entry's batch position; entries of one run inside a warp
+// take the registers of the first.
 struct RowSource {
   const char* backing;  // one table on this GPU, or null
   int64_t backing_rows;
   ShardView shards;     // used when PEER
+  int rank;             // whose shard is local (PEER)
+  char* stage;          // [stage_cap][row_bytes] copies of remote rows, by run (PEER)
+  int64_t stage_cap;
 };
 
 template <bool PEER>
@@ -177,69 +192,132 @@ __device__ __forceinline__ uint4 load_row16(const uint4* p) {
   return __ldg(p);
 }
 
-// One warp takes 32 consecutive entries of the sorted batch.  Only the first entry of every
-// run of equal ids inside the warp probes the index (the others take its slot by shuffle) and
-// only it loads the row; slot and found flag go to every entry's batch position, the rows are
-// moved four at a time, 16 bytes per lane, an entry whose id equals its predecessor's storing
-// the predecessor's registers.  The ids and positions of the warp's next 32 entries are
-// requested before the rows of the current ones move.
-// RB: 512 = rows of exactly 512 bytes (128 fp32: the address arithmetic folds, no lane is idle);
-// 16 = any multiple of 16 bytes; 0 = words or bytes.
-template <int MODE, typename KeyT, bool PEER, int RB>
-__global__ void __launch_bounds__(kBlock, MODE == HB_LOOKUP_SORTED ? 2 : 3) runs_lookup_fetch_kernel(
-    IndexView v, hb_runs_t r, RowSource rs, const char* __restrict__ cache_rows, int64_t row_bytes_arg,
-    int vb, char* __restrict__ out, int64_t* __restrict__ locs, uint8_t* __restrict__ found,
-    int64_t* __restrict__ locs_sorted, int* __restrict__ err) {
+// run_src[u]: address of the run's row (16-byte aligned, 0 = none) | 1 when it is a cache row
+template <int MODE, bool PEER>
+__global__ void __launch_bounds__(kBlock) runs_resolve_kernel(
+    IndexView v, hb_runs_t r, RowSource rs, const char* __restrict__ cache_rows, int64_t row_bytes,
+    int vb, unsigned long long* __restrict__ run_src, int64_t* __restrict__ run_slots,
+    int* __restrict__ err) {
   __shared__ int64_t s_top[MODE == HB_LOOKUP_SORTED ? kTopMax : 1];
   if (MODE == HB_LOOKUP_SORTED) {
     stage_top_level(v, s_top);
     __syncthreads();
   }
+  const int64_t U = *r.num_runs;
+  const int lane = lane_id();
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t limit = PEER ? rs.shards.num_rows : rs.backing_rows;
+  for (int64_t u0 = warp * 32; u0 < U; u0 += nwarps * 32) {
+    const int64_t u = u0 + lane;
+    const bool valid = u < U;
+    const int64_t id = valid ? __ldg(r.uniq_ids + u) : -1;
+    const int64_t slot = warp_lookup<MODE>(v, s_top, id);
+    const char* src = nullptr;
+    const char* remote = nullptr;  // to be copied to the stage
+    if (slot >= 0) {
+      src = cache_rows + slot * row_bytes;
+    } else if (valid && id < limit) {
+      if (PEER) {
+        const char* row = shard_row(rs.shards, id, row_bytes);
+        const bool mine = rs.shards.world == 1 || mod_nonneg(id, rs.shards.world) == rs.rank;
+        if (mine || u >= rs.stage_cap) {
+          src = row;  // local shard, or no room in the stage: EXPAND reads the owner's memory itself
+        } else {
+          remote = row;
+          src = rs.stage + u * row_bytes;
+        }
+      } else {
+        src = rs.backing ? rs.backing + id * row_bytes : nullptr;
+      }
+    } else if (valid && (PEER || rs.backing)) {
+      atomicExch(err, HB_ERR_INVALID);  // no such row: the output rows of the run stay as they were
+    }
+    if (valid) {
+      run_src[u] = (unsigned long long)src | (slot >= 0 ? 1ull : 0ull);
+      if (run_slots) run_slots[u] = slot;
+    }
+    if (PEER) {
+      // remote rows -> stage, 8 rows in flight, 16 bytes (or a word / a byte) per lane and step
+      const unsigned todo = __ballot_sync(0xffffffffu, remote != nullptr);
+      const unsigned long long from = (unsigned long long)remote, to = (unsigned long long)src;
+      for (int q0 = 0; q0 < 32 && todo; q0 += 8) {
+        if (((todo >> q0) & 0xffu) == 0u) continue;
+        unsigned long long f[8], t[8];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          f[x] = __shfl_sync(0xffffffffu, from, q0 + x);
+          t[x] = __shfl_sync(0xffffffffu, to, q0 + x);
+        }
+        if (vb == 16) {
+          for (int64_t k = lane; k < (row_bytes >> 4); k += 32) {
+            uint4 val[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+              if (f[x]) val[x] = *(reinterpret_cast<const uint4*>(f[x]) + k);
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+              if (f[x]) *(reinterpret_cast<uint4*>(t[x]) + k) = val[x];
+          }
+        } else {
+          for (int x = 0; x < 8; ++x) {
+            if (!f[x]) continue;
+            for (int64_t k = lane; k < row_bytes; k += 32)
+              reinterpret_cast<char*>(t[x])[k] = reinterpret_cast<const char*>(f[x])[k];
+          }
+        }
+      }
+    }
+  }
+}
+
+// the run an entry of the sorted batch belongs to: runs that start before its group of 8
+// entries (base8) + the heads inside the group up to the entry
+__device__ __forceinline__ int64_t run_of_entry(const hb_runs_t& r, int64_t j) {
+  const unsigned long long flags = *reinterpret_cast<const unsigned long long*>(r.head + (j & ~(int64_t)7));
+  const int k = (int)(j & 7);
+  const unsigned long long mask = k == 7 ? ~0ull : ((1ull << (8 * (k + 1))) - 1ull);
+  return (int64_t)__ldg(r.base8 + (j >> 3)) + __popcll(flags & mask) - 1;
+}
+
+// RB: 512 = rows of exactly 512 bytes (128 fp32: the address arithmetic folds, no lane is idle);
+// 16 = any multiple of 16 bytes; 0 = words or bytes.  PEER: a source may be another GPU's memory
+// (runs that found no room in the stage), so rows are read with plain loads.
+template <bool PEER, int RB>
+__global__ void __launch_bounds__(kBlock, 3) runs_expand_kernel(
+    hb_runs_t r, const unsigned long long* __restrict__ run_src, const int64_t* __restrict__ run_slots,
+    int64_t row_bytes_arg, int vb, char* __restrict__ out, int64_t* __restrict__ locs,
+    uint8_t* __restrict__ found) {
   constexpr bool V16 = RB != 0;
   const int64_t row_bytes = RB == 512 ? (int64_t)512 : row_bytes_arg;
-  const KeyT* keys = reinterpret_cast<const KeyT*>(r.keys);
   const int64_t n = runs_valid_entries(r);
   const int lane = lane_id();
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t stride = (((int64_t)gridDim.x * blockDim.x) >> 5) * 32;
-  const int64_t limit = PEER ? rs.shards.num_rows : rs.backing_rows;
   int64_t base = warp * 32;
-  KeyT key_next = 0;
   uint32_t pos_next = 0;
+  int64_t run_next = -1;
   if (base + lane < n) {
-    key_next = __ldg(keys + base + lane);
     pos_next = __ldg(r.perm + base + lane);
+    run_next = run_of_entry(r, base + lane);
   }
   for (; base < n; base += stride) {
     const bool valid = base + lane < n;
-    const int64_t id = valid ? (int64_t)key_next : -1;
     const uint32_t pos = pos_next;
+    const int64_t u = valid ? run_next : -1;
     if (base + stride + lane < n) {
-      key_next = __ldg(keys + base + stride + lane);
       pos_next = __ldg(r.perm + base + stride + lane);
+      run_next = run_of_entry(r, base + stride + lane);
     }
-    const int64_t prev = __shfl_up_sync(0xffffffffu, id, 1);
-    const bool first = lane == 0 || id != prev;  // first entry of its run inside this warp
-    const unsigned fresh = __ballot_sync(0xffffffffu, first);
-    int64_t slot = warp_lookup<MODE>(v, s_top, first ? id : (int64_t)-1);
-    // every entry takes the slot of the first entry of its run (the nearest `first` lane at or below it)
-    const int leader = 31 - __clz(fresh & (0xffffffffu >> (31 - lane)));
-    slot = __shfl_sync(0xffffffffu, slot, leader);
+    const int64_t prev = __shfl_up_sync(0xffffffffu, u, 1);
+    const unsigned fresh = __ballot_sync(0xffffffffu, lane == 0 || u != prev);
+    const unsigned long long word = valid ? run_src[u] : 0ull;
+    const unsigned long long src_bits = word & ~1ull;
     if (valid) {
-      if (locs_sorted) locs_sorted[base + lane] = slot;  // coalesced
-      if (locs) locs[pos] = slot;                        // 8 bytes scattered over the batch: costly
-      if (found) found[pos] = slot >= 0;
+      if (found) found[pos] = (uint8_t)(word & 1ull);
+      if (locs) locs[pos] = run_slots[u];  // 8 bytes scattered over the batch: costly
     }
-    const char* src = nullptr;
-    if (slot >= 0) {
-      src = cache_rows + slot * row_bytes;
-    } else if (valid && id < limit) {
-      src = PEER ? shard_row(rs.shards, id, row_bytes) : (rs.backing ? rs.backing + id * row_bytes : nullptr);
-    } else if (valid && (PEER || rs.backing)) {
-      atomicExch(err, HB_ERR_INVALID);  // no such row: the output row stays as it was
-    }
-    const unsigned have = __ballot_sync(0xffffffffu, src != nullptr);
-    const unsigned long long src_bits = (unsigned long long)src;
+    const unsigned have = __ballot_sync(0xffffffffu, src_bits != 0ull);
     if (V16) {
       const int64_t vpr = row_bytes >> 4;
       if (RB == 512 || vpr <= 32) {
@@ -251,43 +329,43 @@ __global__ void __launch_bounds__(kBlock, MODE == HB_LOOKUP_SORTED ? 2 : 3) runs
           uint4 val[kFly];
           uint32_t pq[kFly];
 #pragma unroll
-          for (int u = 0; u < kFly; ++u) {
-            const int q = q0 + u;
+          for (int x = 0; x < kFly; ++x) {
+            const int q = q0 + x;
             const unsigned long long sb = __shfl_sync(0xffffffffu, src_bits, q);
-            pq[u] = __shfl_sync(0xffffffffu, pos, q);
+            pq[x] = __shfl_sync(0xffffffffu, pos, q);
             if (((have & fresh) >> q) & 1u)
-              if (on) val[u] = load_row16<PEER>(reinterpret_cast<const uint4*>(sb) + lane);
+              if (on) val[x] = load_row16<PEER>(reinterpret_cast<const uint4*>(sb) + lane);
           }
 #pragma unroll
-          for (int u = 0; u < kFly; ++u) {
-            const int q = q0 + u;
+          for (int x = 0; x < kFly; ++x) {
+            const int q = q0 + x;
             if (!((have >> q) & 1u)) continue;
-            if (!((fresh >> q) & 1u)) val[u] = last;
-            last = val[u];
-            if (on) __stcs(reinterpret_cast<uint4*>(out + (int64_t)pq[u] * row_bytes) + lane, val[u]);
+            if (!((fresh >> q) & 1u)) val[x] = last;
+            last = val[x];
+            if (on) __stcs(reinterpret_cast<uint4*>(out + (int64_t)pq[x] * row_bytes) + lane, val[x]);
           }
         }
       } else {
         for (int q0 = 0; q0 < 32; q0 += 4) {
           if (((have >> q0) & 0xfu) == 0u) continue;
-          const uint4* s[4];
-          uint4* d[4];
+          const uint4* sp[4];
+          uint4* dp[4];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int q = q0 + u;
+          for (int x = 0; x < 4; ++x) {
+            const int q = q0 + x;
             const unsigned long long sb = __shfl_sync(0xffffffffu, src_bits, q);
             const uint32_t pq = __shfl_sync(0xffffffffu, pos, q);
-            s[u] = ((have >> q) & 1u) ? reinterpret_cast<const uint4*>(sb) : nullptr;
-            d[u] = reinterpret_cast<uint4*>(out + (int64_t)pq * row_bytes);
+            sp[x] = ((have >> q) & 1u) ? reinterpret_cast<const uint4*>(sb) : nullptr;
+            dp[x] = reinterpret_cast<uint4*>(out + (int64_t)pq * row_bytes);
           }
           for (int64_t k = lane; k < vpr; k += 32) {
             uint4 val[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if (s[u]) val[u] = load_row16<PEER>(s[u] + k);
+            for (int x = 0; x < 4; ++x)
+              if (sp[x]) val[x] = load_row16<PEER>(sp[x] + k);
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if (s[u]) __stcs(d[u] + k, val[u]);
+            for (int x = 0; x < 4; ++x)
+              if (sp[x]) __stcs(dp[x] + k, val[x]);
           }
         }
       }
@@ -313,8 +391,8 @@ __global__ void __launch_bounds__(kBlock, MODE == HB_LOOKUP_SORTED ? 2 : 3) runs
 // ---- ids of one class that missed the cache -----------------------------------------------
 struct MissPolicy {
   hb_runs_t r;
-  const int64_t* locs;   // slot per batch position, or per sorted entry
-  int locs_sorted;
+  const int64_t* locs;   // slot per batch position (kind 0), per sorted entry (1) or per run (2)
+  int locs_kind;
   int want_class;        // < 0: every class
   int64_t cap;
   int64_t* miss_ids;     // [cap], filled from entry 0
@@ -324,7 +402,8 @@ struct MissPolicy {
     if (u >= *r.num_runs) return -1;
     if (want_class >= 0 && (!r.dclass || r.dclass[u] != want_class)) return -1;
     const int64_t j = r.run_start[u];
-    return locs[locs_sorted ? j : (int64_t)r.perm[j]] < 0 ? 0 : -1;
+    const int64_t at = locs_kind == 2 ? u : (locs_kind == 1 ? j : (int64_t)r.perm[j]);
+    return locs[at] < 0 ? 0 : -1;
   }
   __device__ __forceinline__ void emit(int64_t u, int, const int4& before) const {
     if (before.x >= cap) return;
@@ -361,6 +440,7 @@ RunsPlan make_runs_plan(void* ws, int64_t n) {
   s.dclass = cv.take<int8_t>(m + 1);
   s.dpos = cv.take<int32_t>(m + 1);
   s.uniq = cv.take<int64_t>(m + 1);
+  s.base8 = cv.take<int32_t>(m / 8 + 2);
   s.compact_ws_bytes = compact_workspace_bytes(m);
   s.compact_ws = cv.take<char>(s.compact_ws_bytes);
   s.total = cv.used() + 256;
@@ -400,6 +480,7 @@ int hb_runs_build(const int64_t* ids, int64_t n, const int64_t* n_dev, const int
   runs_out->run_start = s.run_start;
   runs_out->head = s.head;
   runs_out->uniq_ids = s.uniq;
+  runs_out->base8 = s.base8;
   runs_out->dclass = class_table ? s.dclass : nullptr;
   runs_out->dpos = class_table ? s.dpos : nullptr;
   if (n == 0) {
@@ -431,7 +512,7 @@ int hb_runs_build(const int64_t* ids, int64_t n, const int64_t* n_dev, const int
                                             id_bits, st));
     HeadPolicy<uint32_t> pol{keys.Current(), n_dev, n, class_table, table_len, s.head, s.uniq, uniq_ids_out,
                              s.run_start, s.dclass, s.dpos, {cls_out[0], cls_out[1], cls_out[2]},
-                             s.num_runs, num_unique_out, s.class_counts, class_counts_out};
+                             s.num_runs, num_unique_out, s.class_counts, class_counts_out, s.base8};
     rc = run_compact(pol, n, s.compact_ws, s.compact_ws_bytes, st);
     runs_out->keys = keys.Current();
     runs_out->key_bytes = 4;
@@ -443,7 +524,7 @@ int hb_runs_build(const int64_t* ids, int64_t n, const int64_t* n_dev, const int
                                             id_bits, st));
     HeadPolicy<int64_t> pol{keys.Current(), n_dev, n, class_table, table_len, s.head, s.uniq, uniq_ids_out,
                             s.run_start, s.dclass, s.dpos, {cls_out[0], cls_out[1], cls_out[2]},
-                            s.num_runs, num_unique_out, s.class_counts, class_counts_out};
+                            s.num_runs, num_unique_out, s.class_counts, class_counts_out, s.base8};
     rc = run_compact(pol, n, s.compact_ws, s.compact_ws_bytes, st);
     runs_out->keys = keys.Current();
     runs_out->key_bytes = 8;
@@ -453,13 +534,47 @@ int hb_runs_build(const int64_t* ids, int64_t n, const int64_t* n_dev, const int
   return rc;
 }
 
+namespace {
+// scratch of hb_lookup_fetch_runs: where every run's row is read from, the slot of every run
+// when the caller does not ask for it, and (sharded table) the copies of the remote rows
+struct FetchPlan {
+  unsigned long long* run_src;
+  int64_t* run_slots;
+  char* stage;
+  int64_t stage_cap;
+  size_t total;
+};
+constexpr int64_t kStageMaxBytes = (int64_t)1 << 30;  // at most 1 GiB of staged remote rows
+
+FetchPlan make_fetch_plan(void* ws, int64_t n, int64_t row_bytes, bool sharded) {
+  FetchPlan f;
+  Carver cv(ws ? ws : (void*)256);
+  const int64_t m = n > 0 ? n : 1;
+  f.run_src = cv.take<unsigned long long>(m);
+  f.run_slots = cv.take<int64_t>(m);
+  f.stage_cap = 0;
+  f.stage = nullptr;
+  if (sharded) {
+    f.stage_cap = kStageMaxBytes / row_bytes < m ? kStageMaxBytes / row_bytes : m;
+    f.stage = cv.take<char>((size_t)f.stage_cap * row_bytes);
+  }
+  f.total = cv.used() + 256;
+  return f;
+}
+}  // namespace
+
+size_t hb_lookup_fetch_runs_workspace_bytes(int64_t n, int64_t row_bytes, int sharded) {
+  return make_fetch_plan(nullptr, n, row_bytes > 0 ? row_bytes : 1, sharded != 0).total;
+}
+
 int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows,
                          const void* backing_rows, int64_t backing_num_rows, hb_peer_table_t* table,
                          int64_t row_bytes, void* out_rows, int64_t* locs, uint8_t* found,
-                         int64_t* locs_sorted, int mode, hb_stream_t stream) {
+                         int64_t* run_slots, int mode, void* workspace, size_t workspace_bytes,
+                         hb_stream_t stream) {
   HB_CHECK_ARG(h && runs, "hb_lookup_fetch_runs: null argument");
   HB_CHECK_ARG(row_bytes > 0, "hb_lookup_fetch_runs: bad row size");
-  HB_CHECK_ARG(runs->n == 0 || (cache_rows && out_rows && runs->keys && runs->perm),
+  HB_CHECK_ARG(runs->n == 0 || (cache_rows && out_rows && runs->perm && runs->head && runs->base8 && runs->uniq_ids),
                "hb_lookup_fetch_runs: null argument");
   HB_CHECK_ARG(mode == HB_LOOKUP_SETASSOC || mode == HB_LOOKUP_SORTED,
                "hb_lookup_fetch_runs: unknown mode %d", mode);
@@ -467,6 +582,12 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache
   HB_CHECK_ARG(!table || table->row_bytes == row_bytes, "hb_lookup_fetch_runs: row size differs from the table's");
   HB_CHECK_ARG(!backing_rows || backing_num_rows > 0, "hb_lookup_fetch_runs: a backing table needs its row count");
   if (runs->n == 0) return HB_OK;
+  const bool sharded = table != nullptr && table->world > 1;
+  FetchPlan f = make_fetch_plan(workspace, runs->n, row_bytes, sharded);
+  if (!workspace || workspace_bytes < f.total) {
+    set_error("hb_lookup_fetch_runs: workspace of %zu bytes needed, %zu given", f.total, workspace_bytes);
+    return HB_ERR_WORKSPACE;
+  }
   cudaStream_t st = (cudaStream_t)stream;
   if (mode == HB_LOOKUP_SORTED && h->sorted_stale) {
     int rc = hb_index_build_sorted(h, stream);
@@ -476,45 +597,59 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache
   memset(&rs, 0, sizeof(rs));
   rs.backing = (const char*)backing_rows;
   rs.backing_rows = backing_rows ? backing_num_rows : 0;
+  rs.stage = f.stage;
+  rs.stage_cap = f.stage_cap;
   if (table) {
     int rc = make_shard_view(table, &rs.shards);
     if (rc != HB_OK) return rc;
+    rs.rank = table->rank;
   }
   uintptr_t bits = (uintptr_t)row_bytes | (uintptr_t)cache_rows | (uintptr_t)out_rows | (uintptr_t)backing_rows;
+  HB_CHECK_ARG((bits & 1) == 0, "hb_lookup_fetch_runs: rows must start at even addresses");
   const bool v16 = (bits & 15) == 0;  // shards come from cudaMalloc and hold whole rows
-  const int vb = (bits & 3) == 0 ? 4 : 1;
+  const int vb = v16 ? 16 : ((bits & 3) == 0 ? 4 : 1);
+  int* err = device_error_word();
+  int64_t* slots = run_slots ? run_slots : f.run_slots;
+  {
+    int64_t blocks = ceil_div(ceil_div(runs->n, 32) * 32, kBlock);  // one lane per run, at most n runs
+    if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
+    const int grid = (int)(blocks < 1 ? 1 : blocks);
+#define HB_RES(MODE, PEER)                                                                              \
+  HB_LAUNCH((runs_resolve_kernel<MODE, PEER>), grid, kBlock, 0, st, h->view, *runs, rs,                \
+            (const char*)cache_rows, row_bytes, vb, f.run_src, slots, err)
+    if (mode == HB_LOOKUP_SORTED) {
+      if (table) HB_RES(HB_LOOKUP_SORTED, true); else HB_RES(HB_LOOKUP_SORTED, false);
+    } else {
+      if (table) HB_RES(HB_LOOKUP_SETASSOC, true); else HB_RES(HB_LOOKUP_SETASSOC, false);
+    }
+#undef HB_RES
+  }
   int64_t blocks = ceil_div(ceil_div(runs->n, 32) * 32, kBlock);
   if (blocks > (int64_t)sm_count() * 32) blocks = (int64_t)sm_count() * 32;
   const int grid = (int)(blocks < 1 ? 1 : blocks);
-  int* err = device_error_word();
-#define HB_RLF(MODE, KEY, PEER, RB)                                                                   \
-  HB_LAUNCH((runs_lookup_fetch_kernel<MODE, KEY, PEER, RB>), grid, kBlock, 0, st, h->view, *runs, rs, \
-            (const char*)cache_rows, row_bytes, vb, (char*)out_rows, locs, found, locs_sorted, err)
-#define HB_RLF_V(MODE, KEY, PEER)                               \
-  do {                                                          \
-    if (v16 && row_bytes == 512) HB_RLF(MODE, KEY, PEER, 512);  \
-    else if (v16) HB_RLF(MODE, KEY, PEER, 16);                  \
-    else HB_RLF(MODE, KEY, PEER, 0);                            \
+#define HB_EXP(PEER, RB)                                                                         \
+  HB_LAUNCH((runs_expand_kernel<PEER, RB>), grid, kBlock, 0, st, *runs, f.run_src, slots, row_bytes, \
+            vb, (char*)out_rows, locs, found)
+#define HB_EXP_V(PEER)                                \
+  do {                                                \
+    if (v16 && row_bytes == 512) HB_EXP(PEER, 512);   \
+    else if (v16) HB_EXP(PEER, 16);                   \
+    else HB_EXP(PEER, 0);                             \
   } while (0)
-#define HB_RLF_P(MODE, KEY) \
-  do { if (table) HB_RLF_V(MODE, KEY, true); else HB_RLF_V(MODE, KEY, false); } while (0)
-#define HB_RLF_K(MODE) \
-  do { if (runs->key_bytes == 4) HB_RLF_P(MODE, uint32_t); else HB_RLF_P(MODE, int64_t); } while (0)
-  if (mode == HB_LOOKUP_SORTED) HB_RLF_K(HB_LOOKUP_SORTED); else HB_RLF_K(HB_LOOKUP_SETASSOC);
-#undef HB_RLF_K
-#undef HB_RLF_P
-#undef HB_RLF_V
-#undef HB_RLF
+  if (sharded) HB_EXP_V(true); else HB_EXP_V(false);
+#undef HB_EXP_V
+#undef HB_EXP
   return HB_OK;
 }
 
 size_t hb_runs_miss_list_workspace_bytes(int64_t n) { return compact_workspace_bytes(n); }
 
-int hb_runs_miss_list(const hb_runs_t* runs, const int64_t* locs, int locs_sorted, int want_class,
+int hb_runs_miss_list(const hb_runs_t* runs, const int64_t* locs, int locs_kind, int want_class,
                       int64_t cap, int64_t* miss_ids, int64_t* miss_src, int64_t* miss_count,
                       void* workspace, size_t workspace_bytes, hb_stream_t stream) {
   HB_CHECK_ARG(runs && locs && miss_ids && miss_src && miss_count && cap > 0,
                "hb_runs_miss_list: null argument");
+  HB_CHECK_ARG(locs_kind >= 0 && locs_kind <= 2, "hb_runs_miss_list: locs_kind is 0, 1 or 2");
   HB_CHECK_ARG(want_class < 0 || runs->dclass || runs->n == 0,
                "hb_runs_miss_list: the runs were built without a class table");
   cudaStream_t st = (cudaStream_t)stream;
@@ -526,7 +661,7 @@ int hb_runs_miss_list(const hb_runs_t* runs, const int64_t* locs, int locs_sorte
     HB_CUDA(cudaMemsetAsync(miss_count, 0, sizeof(int64_t), st));
     return HB_OK;
   }
-  MissPolicy pol{*runs, locs, locs_sorted ? 1 : 0, want_class, cap, miss_ids, miss_src, miss_count};
+  MissPolicy pol{*runs, locs, locs_kind, want_class, cap, miss_ids, miss_src, miss_count};
   return run_compact(pol, runs->n, workspace, workspace_bytes, st);
 }
 

@@ -21,6 +21,7 @@ struct RunsPlan {
   int8_t* dclass;       // [m + 1]
   int32_t* dpos;        // [m + 1]
   int64_t* uniq;        // [m + 1]
+  int32_t* base8;       // [m / 8 + 2]
   void* compact_ws;
   size_t compact_ws_bytes;
   size_t total;

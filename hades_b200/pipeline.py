@@ -71,7 +71,7 @@ class EmbeddingPath:
         most miss_cap distinct ids per step; the rest stay uncached until they miss again).
         flush_cap: rows one flush can send (the other stale rows wait for the next flush).
         want_locs: ``forward`` also returns the slots by batch position (False: None; the path
-        itself uses the slots in sorted order, which cost a coalesced write)."""
+        itself uses the slot of every run)."""
         self.table, self.class_table, self.cold, self.opt = table, class_table, cold, optimizer
         self.rank, self.world = rank, world
         self.flush_every, self.id_bits = flush_every, id_bits
@@ -96,7 +96,7 @@ class EmbeddingPath:
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._side = None
         self._side_done, self._side_refs = None, []
-        self._runs_ws, self._side_ws = None, None
+        self._runs_ws, self._side_ws, self._fetch_ws = None, None, None
         self._last = None  # (BatchRuns, locs) of the last forward pass
 
     # ---- streams ---------------------------------------------------------------------------
@@ -140,8 +140,11 @@ class EmbeddingPath:
                                caps=(None, self.num_hot_ids, None),
                                ws=self._ws("_runs_ws", lib.hb_runs_workspace_bytes(n)))
         self._runs_ws = runs.ws
+        sharded = self.shared is not None and self.world > 1
+        fetch_ws = self._ws("_fetch_ws", lib.hb_lookup_fetch_runs_workspace_bytes(
+            n, self.dim * self.cold.emb.element_size(), int(sharded)))
         rows, locs, found = E.cudaLookupFetchRuns(self.cold.index, runs, self.cold.emb, self.table, self.shared,
-                                                  out_rows, self.lookup_mode, want_locs=self.want_locs)
+                                                  out_rows, self.lookup_mode, want_locs=self.want_locs, ws=fetch_ws)
         if n and (self.touch_lru or self.insert_misses):
             # Off the main stream, which goes on to whatever uses the rows: the LRU ageing of
             # this lookup (cache.h:101), then the uncached cold ids and their rows go to the
@@ -149,13 +152,13 @@ class EmbeddingPath:
             # gradients look the cache up.
             with self._on_side():
                 if self.touch_lru:
-                    self.cold.index.cuda_touch_lru_runs(runs.slots, runs, locs_sorted=True)
+                    self.cold.index.cuda_touch_lru_runs(runs.slots, runs, locs_kind=2)
                 if self.insert_misses:
                     need = max(lib.hb_runs_miss_list_workspace_bytes(n),
                                lib.hb_staging_insert_workspace_bytes(self.miss_cap))
                     ws = self._ws("_side_ws", need)
                     miss_ids, miss_src, miss_n = E.cudaRunsMissList(runs, runs.slots, COLD, self.miss_cap, ws=ws,
-                                                                    locs_sorted=True)
+                                                                    locs_kind=2)
                     self.cold.insert_gather(miss_ids, rows, miss_src, ws=ws)
                     self._side_finished(miss_ids, miss_src, miss_n, rows, runs)
                 else:

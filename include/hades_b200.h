@@ -106,14 +106,13 @@ int hb_index_touch_lru(hb_index_t* h, const int64_t* locs, int64_t n,
  * (hb_runs_t), so a step that aggregates the gradients of the ids it looked up
  * needs no second sort for the ageing.  perm NULL = identity; run_start NULL =
  * every position is its own run (a batch of unique ids); num_runs / n_dev:
- * nullable device counts capping max_runs / n.  locs_sorted != 0: locs[j] is the slot of
- * the j-th SORTED entry (what hb_lookup_fetch_runs writes to locs_sorted) instead of the
- * slot of batch position j.  The first call allocates two int32 arrays of `capacity`
+ * nullable device counts capping max_runs / n.  locs_kind: locs holds a slot per batch
+ * position (0), per sorted entry (1) or per run (2: the run_slots of hb_lookup_fetch_runs).  The first call allocates two int32 arrays of `capacity`
  * entries inside the index. */
 int hb_index_touch_lru_runs(hb_index_t* h, const int64_t* locs, const uint32_t* perm,
                             const int64_t* run_start, int64_t max_runs,
                             const int64_t* num_runs, int64_t n, const int64_t* n_dev,
-                            int locs_sorted, hb_stream_t stream);
+                            int locs_kind, hb_stream_t stream);
 
 /* reset(ids), src/cache/cache.h:106-118,208-211: a hit way becomes empty. */
 int hb_index_reset(hb_index_t* h, const int64_t* ids, int64_t n, hb_stream_t stream);
@@ -318,6 +317,8 @@ typedef struct hb_runs {
   const int32_t* dpos;        /* [num_runs] position among the ids of its class */
   const int64_t* class_counts;/* device int64[4]: distinct ids of class 0, 1, 2, other */
   const int64_t* n_dev;       /* nullable device count of valid input entries */
+  const int32_t* base8;       /* [ceil(n / 8)] runs that start before sorted entry 8k: with the
+                                 head flags it gives the run of any entry in two small loads */
 } hb_runs_t;
 
 /* Optional split of the aggregated rows by a per-node class table (class =
@@ -378,27 +379,34 @@ int hb_segsum_runs_f32(const hb_runs_t* runs /* host */, const float* grads,
 
 /* hb_lookup_fetch (or hb_lookup_fetch_sharded when `table` is given) over a batch that
  * hb_runs_build has sorted: same outputs at the same batch positions (locs, found,
- * out_rows), but every distinct id is read once per warp that meets it instead of once
- * per occurrence -- over NVLink, for a row of another GPU's shard.  locs_sorted[j]
- * (nullable) = slot of the j-th sorted entry: a coalesced write, where the per-position
- * locs are 8-byte writes scattered over the batch (about 15 % of the kernel's time at
- * 512-byte rows); hb_index_touch_lru_runs and hb_runs_miss_list take either.  A miss whose id is
- * not below the table's row count leaves its output row untouched and raises
- * HB_ERR_INVALID in the device status word.  python/EmbCache/dist_emb.py:184-243. */
+ * out_rows), in two launches.  The first works per DISTINCT id: index probe, the slot of
+ * every run (run_slots[u], nullable output, n entries) and the place its row is read from;
+ * a row that lives in another GPU's shard is copied once into a staging buffer on this GPU
+ * (up to 1 GiB of them; the rest is read from the owner directly), so every remote row
+ * crosses NVLink once per step however often its id occurs.  The second writes the row of
+ * every entry to its batch position; entries of one run inside a warp share one read.
+ * locs (nullable): the per-position slots, 8-byte writes scattered over the batch (about
+ * 15 % of the time at 512-byte rows): hb_index_touch_lru_runs and hb_runs_miss_list take
+ * run_slots instead.  A miss whose id is not below the table's row count leaves its output
+ * rows untouched and raises HB_ERR_INVALID in the device status word.
+ * python/EmbCache/dist_emb.py:184-243. */
+size_t hb_lookup_fetch_runs_workspace_bytes(int64_t n, int64_t row_bytes, int sharded);
 int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs /* host */, const void* cache_rows,
                          const void* backing_rows /* nullable */, int64_t backing_num_rows,
                          hb_peer_table_t* table /* nullable */, int64_t row_bytes, void* out_rows,
                          int64_t* locs /* nullable */, uint8_t* found /* nullable */,
-                         int64_t* locs_sorted /* nullable */, int mode, hb_stream_t stream);
+                         int64_t* run_slots /* nullable */, int mode, void* workspace,
+                         size_t workspace_bytes, hb_stream_t stream);
 
 /* The distinct ids of class want_class (< 0: any) that the lookup missed (locs[position]
- * < 0; locs by batch position, or by sorted entry when locs_sorted != 0), ascending, at
+ * < 0; locs_kind: locs holds a slot per batch position (0), per sorted entry (1) or per
+ * run (2, the run_slots of hb_lookup_fetch_runs)), ascending, at
  * most cap of them: miss_ids[cap] (entries past the count are -1, which
  * hb_index_add ignores), miss_src[cap] = a batch position of the id (its row in the fetch
  * output), *miss_count.  The uncached cold ids that DistEmbeddingTensor.__call__ sends to
  * the cache server, python/EmbCache/dist_emb.py:218-259. */
 size_t hb_runs_miss_list_workspace_bytes(int64_t n);
-int hb_runs_miss_list(const hb_runs_t* runs /* host */, const int64_t* locs, int locs_sorted,
+int hb_runs_miss_list(const hb_runs_t* runs /* host */, const int64_t* locs, int locs_kind,
                       int want_class, int64_t cap, int64_t* miss_ids, int64_t* miss_src,
                       int64_t* miss_count, void* workspace, size_t workspace_bytes,
                       hb_stream_t stream);

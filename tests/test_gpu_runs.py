@@ -106,11 +106,13 @@ def test_lookup_fetch_runs_equals_unsorted_fetch(cuda_lib, oracle_mod, mode, dim
     assert np.array_equal(found.cpu().numpy(), want_hit)
     assert np.array_equal(out.cpu().numpy(), want)
     assert 0 < want_hit.sum() < q.size
-    # the slots in sorted order (the coalesced output) are the per-position slots through the permutation
+    # the slot of every run (distinct id) is the per-position slot of the run's first entry
     from hades_b200.exchange import _as_tensor
 
+    U = int(runs.num_unique.item())
     perm = _as_tensor(runs.desc.perm, (q.size,), "<i4", locs_g.device).long()
-    assert torch.equal(runs.slots[: q.size], locs_g[perm])
+    run_start = _as_tensor(runs.desc.run_start, (U,), "<i8", locs_g.device)
+    assert torch.equal(runs.slots[:U], locs_g[perm[run_start]])
     out2, none_locs, found2 = E.cudaLookupFetchRuns(ix, runs, _t(cache), _t(table), want_locs=False)
     assert none_locs is None and torch.equal(out2, out) and torch.equal(found2, found)
     # without a backing table a miss leaves the output row untouched
@@ -193,7 +195,7 @@ def test_miss_list_and_gathered_insert(cuda_lib, oracle_mod):
         cc.index.cuda_touch_lru_runs(locs, runs)
         ox.touch(wl)
         miss_ids, miss_src, miss_n = E.cudaRunsMissList(runs, locs, 2, cap)
-        ms_ids, ms_src, ms_n = E.cudaRunsMissList(runs, runs.slots, 2, cap, locs_sorted=True)
+        ms_ids, ms_src, ms_n = E.cudaRunsMissList(runs, runs.slots, 2, cap, locs_kind=2)
         assert torch.equal(ms_ids, miss_ids) and torch.equal(ms_src, miss_src) and torch.equal(ms_n, miss_n)
         u, fi = np.unique(q, return_index=True)
         want = u[(cls[u] == 2) & (wl[fi] < 0)][:cap]
