@@ -59,3 +59,24 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         _lib.load()
+
+
+def test_reference_side_bridge_compiles():
+    """hades_b200/bridge/hades_b200_bridge.cc (the translation unit INTEGRATION.md gives a
+    maintainer of the reference) against the torch headers and include/hades_b200.h."""
+    import shutil
+    import subprocess
+    import sysconfig
+    from pathlib import Path
+
+    import torch
+
+    root = Path(__file__).resolve().parent.parent
+    tdir = Path(torch.__file__).parent
+    gxx = "/usr/bin/g++" if Path("/usr/bin/g++").exists() else shutil.which("g++")
+    cmd = [gxx, "-std=c++17", "-fsyntax-only", str(root / "hades_b200" / "bridge" / "hades_b200_bridge.cc"),
+           "-I", str(root / "include"), "-I", str(tdir / "include"),
+           "-I", str(tdir / "include/torch/csrc/api/include"), "-I", sysconfig.get_paths()["include"],
+           "-I", "/usr/local/cuda/include"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
