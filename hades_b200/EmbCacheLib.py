@@ -10,14 +10,18 @@ Differences that a caller can observe:
 * kernels run on torch's current stream, not on the legacy default stream
   (the reference launches ``<<<grid, block>>>`` with no stream, e.g. src/cuda/uva_fetch.cu:39);
 * a CUDA error raises instead of ending the process (src/utils.h:12-24 calls ``exit``);
-* ``IndexCache`` keeps its state in HBM.  ``name``/``create`` select a process-local
-  registry entry instead of a POSIX shared-memory segment, and ``pin_memory`` is accepted
-  and ignored (there is no host copy to pin);
+* ``IndexCache`` keeps its state in HBM.  ``create=True`` also leaves a small file
+  ``/dev/shm/hades_b200_index_<name>`` with a CUDA IPC handle, through which
+  ``IndexCache(size, name, create=False)`` in ANOTHER process of the box opens the same lines
+  (the reference opens the creator's POSIX segment, src/cache/cache.h:145-167); inside one
+  process the name resolves in a registry.  ``pin_memory`` is accepted and ignored (there is
+  no host copy to pin);
 * ``IndexCache.add`` applies ids in input order per set, which is the reference's result at
   ``OMP_NUM_THREADS=1`` (its multi-threaded result depends on thread timing).
 """
 from __future__ import annotations
 
+import atexit
 import ctypes as C
 
 import torch
@@ -26,6 +30,27 @@ from . import _lib
 from ._lib import LOOKUP_SETASSOC, LOOKUP_SORTED, MOVER_AUTO, MOVER_BULK, MOVER_LSU  # noqa: F401
 
 _REGISTRY: dict[str, "IndexCache"] = {}
+
+
+def _index_handle_path(name: str) -> str:
+    return "/dev/shm/hades_b200_index_" + name.replace("/", "_")
+
+
+_PUBLISHED: set = set()  # handle files this process left in /dev/shm
+
+
+def _withdraw_published() -> None:
+    import os
+
+    for path in list(_PUBLISHED):
+        try:
+            os.unlink(path)
+        except OSError:
+            pass
+    _PUBLISHED.clear()
+
+
+atexit.register(_withdraw_published)
 
 
 def _check(cond: bool, what: str) -> None:
@@ -69,6 +94,7 @@ class IndexCache:
         self._lib = _lib.load()
         self._name = name
         self.lookup_mode = lookup_mode
+        self._shm_file = None
         if create:
             h = C.c_void_p()
             _lib.check(self._lib.hb_index_create(int(cache_size), C.byref(h)))
@@ -76,15 +102,55 @@ class IndexCache:
             self._owner = True
             self._device = torch.cuda.current_device()
             _REGISTRY[name] = self
-        else:
-            if name not in _REGISTRY:
-                raise RuntimeError(f"fail to open {name}: no such index in this process")
+            self._publish()
+        elif name in _REGISTRY:
             other = _REGISTRY[name]
             self._h = other._h
             self._owner = False
             self._device = other._device
+        else:
+            # another process of this box created it: map its lines (src/cache/cache.h:155-158)
+            path = _index_handle_path(name)
+            try:
+                with open(path, "rb") as f:
+                    blob = f.read()
+            except OSError as e:
+                raise RuntimeError(f"fail to open {name}: no such index on this box ({e.strerror})") from e
+            _check(len(blob) == self._lib.hb_index_handle_bytes(), "index handle file has the expected size")
+            h = C.c_void_p()
+            _lib.check(self._lib.hb_index_open(blob, C.byref(h)))
+            self._h = h
+            self._owner = True  # of the mapping: destroyed (closed) with this object
+            self._device = torch.cuda.current_device()
 
-    def __del__(self):
+    def _publish(self) -> None:
+        """Leave the IPC handle where other processes of the box find it by name."""
+        import os
+
+        buf = C.create_string_buffer(self._lib.hb_index_handle_bytes())
+        try:
+            _lib.check(self._lib.hb_index_export_handle(self._h, buf))
+            path = _index_handle_path(self._name)
+            with open(path + ".tmp", "wb") as f:
+                f.write(buf.raw)
+            os.replace(path + ".tmp", path)
+            self._shm_file = path
+            _PUBLISHED.add(path)
+        except (OSError, _lib.HadesError):
+            self._shm_file = None  # no IPC here (or no /dev/shm): the index stays private to this process
+
+    def close(self) -> None:
+        """Withdraw the published handle and free the index (the creator) or unmap it (an opener).
+        Openers close before the creator does.  The object cannot be used afterwards."""
+        if getattr(self, "_shm_file", None):
+            _PUBLISHED.discard(self._shm_file)
+            try:
+                import os
+
+                os.unlink(self._shm_file)
+            except Exception:
+                pass
+            self._shm_file = None
         if getattr(self, "_owner", False) and getattr(self, "_h", None):
             try:
                 self._lib.hb_index_destroy(self._h)
@@ -92,7 +158,10 @@ class IndexCache:
                     _REGISTRY.pop(self._name, None)
             except Exception:  # interpreter shutdown: modules may already be gone
                 pass
-            self._h = None
+        self._h = None
+
+    def __del__(self):
+        self.close()
 
     # --- sizes -------------------------------------------------------------------------
     def get_size(self) -> int:

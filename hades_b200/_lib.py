@@ -34,6 +34,9 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_device_status": (_int, [_p, _p]),
     "hb_index_create": (_int, [_i64, _p]),
     "hb_index_destroy": (_int, [_p]),
+    "hb_index_handle_bytes": (_sz, []),
+    "hb_index_export_handle": (_int, [_p, _p]),
+    "hb_index_open": (_int, [_p, _p]),
     "hb_index_size": (_i64, [_p]),
     "hb_index_capacity": (_i64, [_p]),
     "hb_index_space": (_i64, [_p]),

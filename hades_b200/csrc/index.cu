@@ -423,6 +423,38 @@ using namespace hb;
 
 extern "C" {
 
+namespace {
+// everything of an index except its lines: the sorted view's storage and the scratch word
+int alloc_derived(hb_index_t* h) {
+  const int64_t cap = h->cache_size;
+  HB_CUDA(cudaMalloc(&h->pairs, (cap + kLeafFan) * sizeof(longlong2)));
+  HB_CUDA(cudaMalloc(&h->scratch_count, 4 * sizeof(int64_t)));
+  // level capacities for a full index
+  int64_t len = h->lines;  // level 1: one id per leaf block
+  int64_t total = 0;
+  for (int l = 1; l < kMaxLevels; ++l) {
+    h->level_off[l] = total;
+    h->level_cap[l] = len + kNodeFan;
+    total += align_up(h->level_cap[l], 32);
+    len = ceil_div(len, kNodeFan);
+  }
+  HB_CUDA(cudaMalloc(&h->level_store, total * sizeof(int64_t)));
+  h->sorted_stale = true;
+  h->view.line_ids = h->line_ids;
+  h->view.lines = h->lines;
+  h->view.pairs = h->pairs;
+  h->view.top = 0;
+  return HB_OK;
+}
+
+struct IndexIpcHandle {
+  int64_t cache_size;
+  int64_t lines;
+  cudaIpcMemHandle_t line_ids;
+  cudaIpcMemHandle_t lru;
+};
+}  // namespace
+
 int hb_index_create(int64_t cache_size, hb_index_t** out) {
   HB_CHECK_ARG(out != nullptr, "hb_index_create: out is null");
   HB_CHECK_ARG(cache_size > 0, "hb_index_create: cache_size must be positive");
@@ -436,34 +468,67 @@ int hb_index_create(int64_t cache_size, hb_index_t** out) {
   const int64_t cap = h->cache_size;
   HB_CUDA(cudaMalloc(&h->line_ids, cap * sizeof(int64_t)));
   HB_CUDA(cudaMalloc(&h->lru, cap * sizeof(int32_t)));
-  HB_CUDA(cudaMalloc(&h->pairs, (cap + kLeafFan) * sizeof(longlong2)));
-  HB_CUDA(cudaMalloc(&h->scratch_count, 4 * sizeof(int64_t)));
-  // level capacities for a full index
-  int64_t len = lines;  // level 1: one id per leaf block
-  int64_t total = 0;
-  for (int l = 1; l < kMaxLevels; ++l) {
-    h->level_off[l] = total;
-    h->level_cap[l] = len + kNodeFan;
-    total += align_up(h->level_cap[l], 32);
-    len = ceil_div(len, kNodeFan);
-  }
-  HB_CUDA(cudaMalloc(&h->level_store, total * sizeof(int64_t)));
+  int rc = alloc_derived(h);
+  if (rc != HB_OK) return rc;
   HB_LAUNCH(fill_i64_kernel, grid_capped(cap), kBlock, 0, 0, h->line_ids, cap, (int64_t)-1);
   HB_LAUNCH(fill_i32_kernel, grid_capped(cap), kBlock, 0, 0, h->lru, cap, 0);
   HB_CUDA(cudaStreamSynchronize(0));
-  h->sorted_stale = true;
-  h->view.line_ids = h->line_ids;
-  h->view.lines = lines;
-  h->view.pairs = h->pairs;
-  h->view.top = 0;
+  *out = h;
+  return HB_OK;
+}
+
+// An index shared between the processes of one box, as the reference shares its index through
+// a named POSIX segment (SACacheIndex(name, create, ...), src/cache/cache.h:145-167): the
+// creating process exports a handle, another process opens it and works on the SAME lines
+// (ids and LRU counters) in the creator's HBM.  As in the reference nothing orders the two
+// processes' calls: callers do (its test does with barriers, test/test_cache.py:20-55).
+size_t hb_index_handle_bytes(void) { return sizeof(IndexIpcHandle); }
+
+int hb_index_export_handle(hb_index_t* h, void* handle_out) {
+  HB_CHECK_ARG(h && handle_out, "hb_index_export_handle: null argument");
+  HB_CHECK_ARG(!h->opened, "hb_index_export_handle: only the creating process exports");
+  IndexIpcHandle x;
+  memset(&x, 0, sizeof(x));
+  x.cache_size = h->cache_size;
+  x.lines = h->lines;
+  HB_CUDA(cudaIpcGetMemHandle(&x.line_ids, h->line_ids));
+  HB_CUDA(cudaIpcGetMemHandle(&x.lru, h->lru));
+  memcpy(handle_out, &x, sizeof(x));
+  return HB_OK;
+}
+
+int hb_index_open(const void* handle, hb_index_t** out) {
+  HB_CHECK_ARG(handle && out, "hb_index_open: null argument");
+  IndexIpcHandle x;
+  memcpy(&x, handle, sizeof(x));
+  HB_CHECK_ARG(x.lines > 0 && x.cache_size == x.lines * kWays, "hb_index_open: not an index handle");
+  hb_index_t* h = new hb_index_t();
+  memset(h, 0, sizeof(*h));
+  HB_CUDA(cudaGetDevice(&h->device));
+  h->lines = x.lines;
+  h->cache_size = x.cache_size;
+  h->shared = true;
+  h->opened = true;
+  void* p = nullptr;
+  HB_CUDA(cudaIpcOpenMemHandle(&p, x.line_ids, cudaIpcMemLazyEnablePeerAccess));
+  h->line_ids = static_cast<int64_t*>(p);
+  HB_CUDA(cudaIpcOpenMemHandle(&p, x.lru, cudaIpcMemLazyEnablePeerAccess));
+  h->lru = static_cast<int32_t*>(p);
+  int rc = alloc_derived(h);
+  if (rc != HB_OK) return rc;
   *out = h;
   return HB_OK;
 }
 
 int hb_index_destroy(hb_index_t* h) {
   if (!h) return HB_OK;
-  cudaFree(h->line_ids);
-  cudaFree(h->lru);
+  if (h->opened) {
+    cudaIpcCloseMemHandle(h->line_ids);
+    cudaIpcCloseMemHandle(h->lru);
+  } else {
+    cudaFree(h->line_ids);
+    cudaFree(h->lru);
+  }
   cudaFree(h->pairs);
   cudaFree(h->level_store);
   cudaFree(h->scratch_count);
@@ -729,7 +794,7 @@ int hb_index_build_sorted(hb_index_t* h, hb_stream_t stream) {
     set_error("hb_index_build_sorted: %s", cudaGetErrorString(e));
     return HB_ERR_CUDA;
   }
-  h->sorted_stale = false;
+  h->sorted_stale = h->shared;  // a shared index may change under this process
   return HB_OK;
 }
 

@@ -54,6 +54,12 @@ struct hb_index {
   int32_t* slot_run;
   int32_t* slot_epoch;
   hb::IndexView view;
+  // An index over another process's lines (hb_index_open): the sorted view is this process's
+  // own and is rebuilt before every use, because the owner may have changed the lines since.
+  // (The owner itself rebuilds after its own changes; after a change by the other process it
+  // calls hb_index_build_sorted.)
+  bool shared;
+  bool opened;  // line_ids / lru are mappings of another process's memory
 };
 
 #ifdef __CUDACC__

@@ -121,6 +121,49 @@ __global__ void __launch_bounds__(kBlock) move_rows_kernel(R rs, int64_t n, int6
   }
 }
 
+// ---- cached gather, rows of up to 512 bytes in 16-byte vectors -----------------------------
+// A warp takes 32 consecutive outputs: lane l reads index[i] and index_map[index[i]] for its own
+// output (32 independent chains, coalesced index reads), then the warp moves the 32 rows eight
+// at a time, 16 bytes per lane.  With one lane group per row (move_rows_kernel) the two
+// dependent index reads of a row are made by every lane of the group and only four rows are in
+// flight per warp.
+template <typename IdxT>
+__global__ void __launch_bounds__(kBlock, 3) cached_gather_warp_kernel(
+    const char* __restrict__ backing, const char* __restrict__ cached, const IdxT* __restrict__ index,
+    const IdxT* __restrict__ map, char* __restrict__ dst, uint8_t* __restrict__ found, int64_t n,
+    int64_t row_bytes) {
+  const int lane = lane_id();
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int vpr = (int)(row_bytes >> 4);
+  const bool on = lane < vpr;
+  for (int64_t base = warp * 32; base < n; base += nwarps * 32) {
+    const int64_t i = base + lane;
+    const char* src = nullptr;
+    if (i < n) {
+      const int64_t idx = (int64_t)__ldg(index + i);
+      const int64_t g = (int64_t)__ldg(map + idx);
+      src = g != -1 ? cached + g * row_bytes : backing + idx * row_bytes;
+      if (found) found[i] = g != -1;
+    }
+    const unsigned have = __ballot_sync(0xffffffffu, src != nullptr);
+    const unsigned long long src_bits = (unsigned long long)src;
+    for (int q0 = 0; q0 < 32; q0 += 8) {
+      if (((have >> q0) & 0xffu) == 0u) continue;
+      uint4 val[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const unsigned long long sb = __shfl_sync(0xffffffffu, src_bits, q0 + u);
+        if (((have >> (q0 + u)) & 1u) && on) val[u] = __ldg(reinterpret_cast<const uint4*>(sb) + lane);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (((have >> (q0 + u)) & 1u) && on)
+          __stcs(reinterpret_cast<uint4*>(dst + (base + q0 + u) * row_bytes) + lane, val[u]);
+    }
+  }
+}
+
 // ---- accumulate: dst[idx[i],:] += src[i,:], cnt[idx[i]] += 1 (unique indices) ------
 template <typename IdxT>
 __global__ void __launch_bounds__(kBlock) accumulate_rows_kernel(
@@ -610,6 +653,16 @@ int hb_rows_gather_cached(const void* backing_src, const void* cached_src, const
                "hb_rows_gather_cached: null argument");
   if (n == 0) return HB_OK;
   const int vb = vec_bytes_for(row_bytes, {backing_src, cached_src, dst});
+  if (vb == 16 && row_bytes <= 512) {
+    int64_t blocks = ceil_div(ceil_div(n, 32) * 32, kBlock);
+    if (blocks > (int64_t)sm_count() * 24) blocks = (int64_t)sm_count() * 24;
+    HB_IDX_SWITCH(idx_bytes, IdxT, {
+      HB_LAUNCH(cached_gather_warp_kernel<IdxT>, (int)blocks, kBlock, 0, (cudaStream_t)stream,
+                (const char*)backing_src, (const char*)cached_src, (const IdxT*)index, (const IdxT*)index_map,
+                (char*)dst, found, n, row_bytes);
+      return HB_OK;
+    })
+  }
   HB_IDX_SWITCH(idx_bytes, IdxT, {
     CachedGatherRes<IdxT> rs{(const char*)backing_src, (const char*)cached_src, (const IdxT*)index,
                              (const IdxT*)index_map, (char*)dst, found, row_bytes};

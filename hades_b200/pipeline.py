@@ -436,6 +436,8 @@ class EmbeddingPath:
         save path; python/EmbCache/server.py:76-175.)"""
         line_ids, lru = self.cold.index.export_state()
         r = self.cold.remote
+        if getattr(self.opt, "state_cache", None) is not None:
+            self.opt.sync_state_to_backing()  # the saved tensors are the pinned backing ones
         opt = {k: v.clone() for k, v in vars(self.opt).items() if isinstance(v, torch.Tensor)}
         sd = {"step_no": self.step_no, "index_ids": line_ids, "index_lru": lru, "cache_emb": self.cold.emb.clone(),
               "staging": {"grad": r.grad.clone(), "cnt": r.cnt.clone(), "idx": r.idx.clone(),
@@ -456,6 +458,8 @@ class EmbeddingPath:
         self.cold.dropped.copy_(sd["dropped"])
         for k, v in sd["optimizer"].items():
             getattr(self.opt, k).copy_(v)
+        if getattr(self.opt, "state_cache", None) is not None:
+            self.opt.reload_state_cache()
         self.opt.emb.weight.copy_(sd["weight"])
         if "table" in sd:
             self.table.copy_(sd["table"])
@@ -499,8 +503,11 @@ def assemble_path(name: str, table: torch.Tensor, class_table: torch.Tensor, cac
                   cache_entries: int, table_dtype=torch.float32, table_sigma: float = 0.01,
                   generator=None, threshold: torch.Tensor | None = None, default_threshold: int = 0,
                   cnt_threshold: int = 16, insert_misses: bool = True, flush_cap: int = 1 << 19,
-                  miss_cap: int = 1 << 17) -> EmbeddingPath:
+                  miss_cap: int = 1 << 17, state_budget_bytes: int | None = None,
+                  hotness: torch.Tensor | None = None) -> EmbeddingPath:
     """Cold cache filled with `cache_ids` (rows from `table`), optimiser shard, exchange.
+    state_budget_bytes / hotness: see ``SparseAdam`` (state tiered between HBM and pinned host
+    memory when it does not fit the budget; hotness per node of the whole table).
     threshold: int32 per-node flush period (``cold_cache.flush_thresholds`` of the presampled
     hotness, server.py:87-88); None: every staged row is stale at every flush."""
     rows_total, dim = table.shape
@@ -538,7 +545,11 @@ def assemble_path(name: str, table: torch.Tensor, class_table: torch.Tensor, cac
 
             torch.cuda.synchronize()
             dist.barrier(group=group)  # every shard is filled before anyone reads it
-    opt = SparseAdam(shard, lr=0.01) if optimizer == "adam" else SparseAdagrad(shard, lr=0.01)
+    if optimizer == "adam":
+        opt = SparseAdam(shard, lr=0.01, state_budget_bytes=state_budget_bytes,
+                         hotness=None if hotness is None else hotness[rank::world].float().cpu())
+    else:
+        opt = SparseAdagrad(shard, lr=0.01)
     id_bits = max(int(rows_total).bit_length() + 1, 8)
     path = EmbeddingPath(table, class_table, cold, opt, rank, world, flush_every, id_bits,
                          lookup_mode, mover, touch_lru, group, px, px_flush, insert_misses=insert_misses,
@@ -553,7 +564,7 @@ def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str =
                seed_config: int | None = None, group=None, exchange: str = "push",
                hotness: torch.Tensor | None = None, hot_threshold: float | None = None,
                cnt_threshold: int = 16, insert_misses: bool = True, flush_cap: int = 1 << 19,
-               miss_cap: int = 1 << 17) -> EmbeddingPath:
+               miss_cap: int = 1 << 17, state_budget_bytes: int | None = None) -> EmbeddingPath:
     """Build the state of one trainer for a cached-fetch configuration (``synth.CacheFetchConfig``):
     backing table, class table, cold cache filled with the most popular COLD ids, optimiser shard.
 
@@ -600,7 +611,7 @@ def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str =
     return assemble_path(cfg.name, table, class_table, cache_ids, max(cap, 1), rank, world, device, optimizer,
                          cfg.flush_every, lookup_mode, mover, touch_lru, group, exchange,
                          cfg.cache_entries, table_dtype, cfg.table_sigma, gen, threshold, default_threshold,
-                         cnt_threshold, insert_misses, flush_cap, miss_cap)
+                         cnt_threshold, insert_misses, flush_cap, miss_cap, state_budget_bytes, hotness)
 
 
 def build_rmat_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str = "adam",

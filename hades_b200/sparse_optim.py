@@ -128,15 +128,84 @@ class _SparseOptimizer:
 
 
 class SparseAdam(_SparseOptimizer):
-    """SparseAdam of the reference (sparse_optim.py:531-702) on this rank's shard."""
+    """SparseAdam of the reference (sparse_optim.py:531-702) on this rank's shard.
 
-    def __init__(self, emb: ShardedEmbedding, lr: float, betas=(0.9, 0.999), eps: float = 1e-8):
+    state_budget_bytes: HBM the optimiser state may take.  When step + mem + power of the whole
+    shard fit (or no budget is given) they live in HBM and one kernel updates state and weights
+    in place.  Otherwise they live in pinned host memory behind a
+    ``cache.LocalSparseAdamStateCache`` whose HBM copy holds the rows of the hottest ids (`hotness`:
+    per row of this shard; None = the first rows), as the reference keeps its state
+    (sparse_optim.py:556-586, cache.py:133-194): an update then gathers the state rows of its
+    ids (cached fetch), runs the same kernel on the gathered rows and scatters them back (cached
+    set), sparse_optim.py:621-681.  That path reads the number of ids on the host."""
+
+    def __init__(self, emb: ShardedEmbedding, lr: float, betas=(0.9, 0.999), eps: float = 1e-8,
+                 state_budget_bytes: int | None = None, hotness: torch.Tensor | None = None):
         super().__init__(emb, lr)
         self._beta1, self._beta2, self._eps = float(betas[0]), float(betas[1]), float(eps)
         dev = emb.weight.device
+        dim = emb.embedding_dim
+        self.state_cache = None
+        full = emb.rows * (4 + 8 * dim)
+        if state_budget_bytes is not None and full > state_budget_bytes:
+            from .cache import LocalSparseAdamStateCache
+
+            step = torch.zeros(emb.rows, dtype=torch.float32).pin_memory()
+            mem = torch.zeros((emb.rows, dim), dtype=torch.float32).pin_memory()
+            power = torch.zeros((emb.rows, dim), dtype=torch.float32).pin_memory()
+            if hotness is None:
+                hotness = torch.zeros(emb.rows, dtype=torch.float32)
+            _check(hotness.numel() == emb.rows, "hotness has one score per row of this shard")
+            # the cache is addressed by the LOCAL row (id // world): one partition, one owner
+            self.state_cache = LocalSparseAdamStateCache(step, mem, power, hotness, 0, 0, 1)
+            self.state_cache_budget = int(state_budget_bytes)
+            self.state_cache_bytes = self.state_cache.create_cache(self.state_cache_budget)
+            self.state_step, self.state_mem, self.state_power = step, mem, power  # the backing tensors
+            return
         self.state_step = torch.zeros(emb.rows, dtype=torch.float32, device=dev)
-        self.state_mem = torch.zeros((emb.rows, emb.embedding_dim), dtype=torch.float32, device=dev)
-        self.state_power = torch.zeros((emb.rows, emb.embedding_dim), dtype=torch.float32, device=dev)
+        self.state_mem = torch.zeros((emb.rows, dim), dtype=torch.float32, device=dev)
+        self.state_power = torch.zeros((emb.rows, dim), dtype=torch.float32, device=dev)
+
+    def full_state(self):
+        """(step, mem, power) of the whole shard as CUDA tensors, whichever tier the rows are in."""
+        if self.state_cache is None:
+            return self.state_step, self.state_mem, self.state_power
+        rows = torch.arange(self.emb.rows, dtype=torch.int64, device=self.emb.weight.device)
+        return self.state_cache[rows]
+
+    def sync_state_to_backing(self) -> None:
+        """Tiered state only: write the rows held in the HBM copy back to the pinned backing
+        tensors (before saving them)."""
+        if self.state_cache is None or not self.state_cache.has_cached:
+            return
+        cached_rows = torch.nonzero(self.state_cache.idx_map != -1).flatten()
+        slots = self.state_cache.idx_map[cached_rows]
+        for backing, cached in zip(self.state_cache.local_state, self.state_cache.cached_state):
+            backing[cached_rows.cpu()] = cached[slots].cpu()
+
+    def reload_state_cache(self) -> None:
+        """Tiered state only: fill the HBM copy from the backing tensors again (after loading them)."""
+        if self.state_cache is not None:
+            self.state_cache.create_cache(int(self.state_cache_budget))
+
+    def _update_tiered(self, idx, grad, cnt, n_dev) -> None:
+        n = idx.numel() if n_dev is None else min(int(n_dev.item()), idx.numel())
+        if n == 0:
+            return
+        idx, grad = idx[:n], grad[:n].contiguous()
+        cnt = None if cnt is None else cnt[:n].contiguous()
+        e = self.emb
+        rows = torch.div(idx - e.rank, e.world, rounding_mode="floor")
+        step, mem, power = self.state_cache[rows]                  # cached fetch, cache.py:66-104
+        w = e.weight[rows].contiguous()
+        ar = torch.arange(n, dtype=torch.int64, device=idx.device)
+        lib = _lib.load()
+        _lib.check(lib.hb_sparse_adam(ar.data_ptr(), grad.data_ptr(), _lib.ptr(cnt), n, None, e.embedding_dim, 0, 1, n,
+                                      step.data_ptr(), mem.data_ptr(), power.data_ptr(), w.data_ptr(),
+                                      w.element_size(), self._lr, self._beta1, self._beta2, self._eps,
+                                      _lib.stream_ptr()))
+        self.state_cache[rows] = (step, mem, power)                # cached set, cache.py:106-131
+        e.weight[rows] = w                                         # emb.tensor[state_idx] -= std, :681
 
     def update(self, idx, grad, cnt=None, is_unique: bool = False, n_dev: torch.Tensor | None = None,
                id_bits: int = 64, seg_counts: torch.Tensor | None = None, seg_cap: int = 0,
@@ -148,6 +217,8 @@ class SparseAdam(_SparseOptimizer):
         if not is_unique:
             idx, grad, n_dev = _merge_duplicates(idx, grad, cnt, n_dev, id_bits, seg_counts, seg_cap, sorted_segments)
             cnt = None
+        if self.state_cache is not None:
+            return self._update_tiered(idx, grad, cnt, n_dev)
         lib = _lib.load()
         w = self.emb.weight
         _lib.check(lib.hb_sparse_adam(idx.data_ptr(), grad.data_ptr(), _lib.ptr(cnt), idx.numel(),

@@ -65,6 +65,19 @@ typedef struct hb_peer_table hb_peer_table_t; /* a table sharded over the GPUs o
  * state on the current device. */
 int hb_index_create(int64_t cache_size, hb_index_t** out);
 int hb_index_destroy(hb_index_t* h);
+
+/* One index for several processes of a box, as IndexCache(name, create=False) opens the
+ * creator's POSIX segment in the reference (src/cache/cache.h:145-167, exercised by
+ * test/test_cache.py:6-61): the creator exports a handle of hb_index_handle_bytes() bytes,
+ * passes it through any host channel, and hb_index_open gives another process an index over
+ * the SAME lines (ids and LRU counters stay in the creator's HBM; the creator destroys last).
+ * Nothing orders the processes' calls against each other: the callers do, as in the
+ * reference.  HB_LOOKUP_SORTED on an opened index rebuilds its sorted view before every
+ * lookup; the creator calls hb_index_build_sorted after the other process changed the
+ * index.  At most 2^31 slots per index (hb_index_create refuses more). */
+size_t hb_index_handle_bytes(void);
+int hb_index_export_handle(hb_index_t* h, void* handle_out /* host */);
+int hb_index_open(const void* handle /* host */, hb_index_t** out);
 /* get_size / get_capacity / get_space, src/cache/cache.h:176-194 */
 int64_t hb_index_size(const hb_index_t* h);
 int64_t hb_index_capacity(const hb_index_t* h);

@@ -68,6 +68,25 @@ def _worker(rank, port):
         assert _lib.device_status() == 5
         assert int(torch.arange(4, device="cuda").sum().item()) == 6  # context usable
     dist.barrier()
+    # recovery: rank 1 is back (the host side has agreed on it: the barrier above).  After the
+    # reset both ranks start again from exchange number 0 and clean receive areas, although rank 0
+    # is one exchange ahead of rank 1.
+    px.reset()
+    for _ in range(3):
+        p = px.push(ids, rows * (rank + 1))
+        px.fence()
+        got = px.received(p)
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0
+        counts = got[3].cpu()
+        assert counts.tolist() == [50, 50]
+        cap = got[0].numel() // 2
+        for src in range(2):
+            seg_ids = got[0][src * cap: src * cap + 50].cpu()
+            assert seg_ids.tolist() == list(range(rank, 100, 2))  # owner = id % 2, in order
+            assert bool((got[1][src * cap: src * cap + 50] == float(src + 1)).all())
+        px.fence()  # nobody pushes into the area again before everyone has read it
+    px.close()
     dist.destroy_process_group()
 
 

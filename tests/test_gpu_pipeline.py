@@ -197,3 +197,31 @@ def test_rmat_frontier_path_matches_oracle(cuda_lib, oracle_mod):
         assert ids.size == cfg.batch
         grads = synth.normal_rows(rng, ids.size, cfg.dim, cfg.grad_sigma)
         _check_step(path, orc, ids, grads, it)
+
+
+def test_path_with_tiered_optimizer_state_equals_all_hbm(cuda_lib):
+    """The same steps with the optimiser state in HBM and with it tiered (pinned host memory + an
+    HBM copy of the hottest rows, python/EmbCache/cache.py:66-194): tables bit-exact."""
+    from hades_b200 import hotness as H
+    from hades_b200 import pipeline, synth
+
+    base = synth.scaled(synth.CONFIG1, 0.03, "tier_a")
+    mk = lambda name: synth.CacheFetchConfig(name, base.config, base.table_rows, 32, base.cache_entries, base.batch,
+                                             base.zipf_s, flush_every=2)
+    sampler = synth.ZipfSampler(base.table_rows, base.zipf_s)
+    rng = synth.rng_for(1, 0, 31)
+    heat = H.presampling([torch.from_numpy(sampler.ids(rng, base.batch)) for _ in range(4)], base.table_rows)
+    full = base.table_rows * (4 + 8 * 32)
+    pa = pipeline.build_path(mk("tier_a"), hotness=heat, hot_threshold=0.7)
+    pb = pipeline.build_path(mk("tier_b"), hotness=heat, hot_threshold=0.7, state_budget_bytes=full // 4)
+    assert pa.opt.state_cache is None and pb.opt.state_cache is not None
+    for it in range(5):
+        ids = torch.from_numpy(sampler.ids(rng, base.batch)).cuda()
+        g = torch.from_numpy(synth.normal_rows(rng, base.batch, 32, 1e-3)).cuda()
+        ra, rb = pa.step(ids, g), pb.step(ids, g)
+        assert torch.equal(ra[0], rb[0]) and torch.equal(ra[2], rb[2]), it
+    assert torch.equal(pa.table, pb.table)
+    for x, y in zip(pa.opt.full_state(), pb.opt.full_state()):
+        assert torch.equal(x, y)
+    hit = pb.opt.state_cache.idx_map != -1
+    assert 0 < int(hit.sum().item()) < base.table_rows

@@ -162,3 +162,43 @@ def test_sparse_adagrad(cuda_lib, oracle_mod, emb_dtype):
             got = emb.weight.float().cpu().numpy()
             assert np.abs(got - w.astype(np.float32)).max() <= 2e-5
             w = emb.weight.cpu().numpy().copy()
+
+
+@pytest.mark.parametrize("unique", [True, False])
+def test_sparse_adam_state_through_the_tiered_cache(cuda_lib, unique):
+    """Optimiser state in pinned host memory behind LocalSparseAdamStateCache (a third of the
+    rows cached in HBM, python/EmbCache/cache.py:66-194 used at sparse_optim.py:621-668) against
+    the all-HBM optimiser on the same updates: the same kernel runs on the same numbers, so
+    state and weights are bit-exact."""
+    from hades_b200.sparse_optim import ShardedEmbedding, SparseAdam
+
+    rng = np.random.default_rng(11)
+    num, dim, world, rank = 24_000, 32, 2, 1
+    ea, eb = ShardedEmbedding(num, dim, rank, world), ShardedEmbedding(num, dim, rank, world)
+    w0 = (rng.standard_normal((ea.rows, dim)) * 0.01).astype(np.float32)
+    ea.weight.copy_(_t(w0))
+    eb.weight.copy_(_t(w0))
+    full = ea.rows * (4 + 8 * dim)
+    hot = torch.from_numpy(rng.random(ea.rows).astype(np.float32))
+    a = SparseAdam(ea, lr=0.01)
+    b = SparseAdam(eb, lr=0.01, state_budget_bytes=full // 3, hotness=hot)
+    assert a.state_cache is None and b.state_cache is not None and b.state_cache.has_cached
+    assert not b.state_mem.is_cuda and b.state_mem.is_pinned()
+    cached_rows = int((b.state_cache.idx_map != -1).sum().item())
+    assert 0 < cached_rows < ea.rows
+    for it in range(4):
+        if unique:
+            ids = (rng.permutation(ea.rows)[:3000] * world + rank).astype(np.int64)
+        else:
+            ids = (rng.integers(0, ea.rows, 5000) * world + rank).astype(np.int64)
+        g = (rng.standard_normal((ids.size, dim)) * 1e-3).astype(np.float32)
+        cnt = rng.integers(1, 5, ids.size, dtype=np.int64) if it % 2 else None
+        for opt in (a, b):
+            opt.update(_t(ids), _t(g), None if cnt is None else _t(cnt), is_unique=unique, id_bits=20)
+        for x, y in zip(a.full_state(), b.full_state()):
+            assert torch.equal(x, y), it
+        assert torch.equal(ea.weight, eb.weight), it
+    # the backing tensors hold the rows that are not cached, the HBM copy the others
+    idx_map = b.state_cache.idx_map.cpu()
+    uncached = torch.nonzero(idx_map == -1).flatten()
+    assert torch.equal(b.state_mem[uncached], a.state_mem.cpu()[uncached])
