@@ -677,6 +677,11 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
                                                                  path.shared, out_rows, mode, want_locs=False)),
         "segsum": time_local(lambda: E.cudaSegSumRuns(runs0, grads, split_keep=(False, True, True))),
     }
+    # the per-distinct-id launch alone: index probe (+ at N > 1 remote rows copied once into this GPU's stage)
+    resolve_ms = None
+    if True:
+        resolve_ms = time_local(lambda: E.cudaLookupFetchRuns(path.cold.index, runs0, path.cold.emb, path.table,
+                                                              path.shared, None, mode, resolve_only=True))
     no_reuse_ms = None
     if path.shared is None and main_line:
         unif = torch.randint(0, cfg.table_rows, (cfg.batch,), device=dev, generator=gen)
@@ -766,6 +771,7 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
                                            "CUDA-event times of the three calls",
                                    "algorithmic_bytes": lf_bytes + seg_bytes, "ms": stage_ms,
                                    "sort_runs_ms": st_ms["sort_runs"], "lookup_fetch_ms": st_ms["lookup_fetch"],
+                                   "resolve_part_of_lookup_fetch_ms": resolve_ms,
                                    "segsum_ms": st_ms["segsum"], "achieved": stage_gbs,
                                    "frac_of_measured": stage_gbs / peak, "frac_of_nominal_8TBs": stage_gbs / HBM_NOMINAL_GBS},
                          "also": {"segsum_gbs": seg_bytes / (st_ms["segsum"] * 1e-3) / 1e9,

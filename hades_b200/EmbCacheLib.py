@@ -770,23 +770,28 @@ def cudaRunsBuild(ids, id_bits: int = 64, table=None, keep=(True, True, True), c
 
 def cudaLookupFetchRuns(index: IndexCache, runs: BatchRuns, cache_rows, backing_rows=None, peer_table=None,
                         out_rows=None, mode: int | None = None, want_locs: bool = True,
-                        ws: torch.Tensor | None = None):
+                        ws: torch.Tensor | None = None, resolve_only: bool = False):
     """``cudaLookupFetch`` over a batch that ``cudaRunsBuild`` sorted: (out_rows, locs, found) at
     the batch positions, every distinct id read once per warp that meets it.  Misses read
     backing_rows on this GPU, or the owners' shards of peer_table (``peer_table.PeerTable``).
     The slot of every RUN (distinct id, in the order of ``runs.uniq_ids``) is left in
     ``runs.slots``; want_locs=False skips the per-position ``locs`` (8-byte writes scattered over
     the batch, about 15 % of the time) and returns None for them.  Rows of other GPUs' shards are
-    first copied, once per distinct id, into a staging buffer on this GPU."""
+    first copied, once per distinct id, into a staging buffer on this GPU.  resolve_only=True runs
+    that first, per-distinct-id launch alone (``runs.slots`` filled, nothing written per position)
+    and returns (None, None, None)."""
     n = runs.n
     dev = runs.ids.device
-    if out_rows is None:
+    if resolve_only:
+        want_locs = False
+    elif out_rows is None:
         out_rows = torch.empty((n, cache_rows.size(1)), dtype=cache_rows.dtype, device=dev)
-    _check(out_rows.size(1) == cache_rows.size(1), "out_rows.size(1) == cache_rows.size(1)")
+    if not resolve_only:
+        _check(out_rows.size(1) == cache_rows.size(1), "out_rows.size(1) == cache_rows.size(1)")
     if backing_rows is not None:
         _check(backing_rows.size(1) == cache_rows.size(1), "backing_rows.size(1) == cache_rows.size(1)")
     locs = torch.empty(n, dtype=torch.int64, device=dev) if want_locs else None
-    found = torch.empty(n, dtype=torch.bool, device=dev)
+    found = None if resolve_only else torch.empty(n, dtype=torch.bool, device=dev)
     if runs.slots is None:
         runs.slots = torch.empty(max(n, 1), dtype=torch.int64, device=dev)
     lib = _lib.load()
@@ -800,10 +805,12 @@ def cudaLookupFetchRuns(index: IndexCache, runs: BatchRuns, cache_rows, backing_
                                         None if backing_rows is None else _dev_ptr(backing_rows, "backing_rows"),
                                         0 if backing_rows is None else backing_rows.size(0),
                                         None if peer_table is None else peer_table.handle,
-                                        _row_bytes(cache_rows), out_rows.data_ptr(), _lib.ptr(locs),
-                                        found.data_ptr(), runs.slots.data_ptr(),
+                                        _row_bytes(cache_rows), None if resolve_only else out_rows.data_ptr(),
+                                        _lib.ptr(locs), _lib.ptr(found), runs.slots.data_ptr(),
                                         index.lookup_mode if mode is None else mode, runs.fetch_ws.data_ptr(),
                                         runs.fetch_ws.numel(), _lib.stream_ptr()))
+    if resolve_only:
+        return None, None, None
     return out_rows, locs, found
 
 

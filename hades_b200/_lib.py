@@ -177,6 +177,7 @@ def ptr(t: torch.Tensor | None) -> int | None:
 
 
 _WORKSPACES: dict[int, torch.Tensor] = {}
+_RETIRED: list = []  # outgrown scratch buffers: captured CUDA graphs may still hold their addresses
 
 
 def workspace(nbytes: int) -> torch.Tensor:
@@ -185,6 +186,8 @@ def workspace(nbytes: int) -> torch.Tensor:
     dev = torch.cuda.current_device()
     ws = _WORKSPACES.get(dev)
     if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _RETIRED.append(ws)
         ws = torch.empty(max(int(nbytes * 1.25), 1 << 20), dtype=torch.uint8, device=f"cuda:{dev}")
         _WORKSPACES[dev] = ws
     return ws

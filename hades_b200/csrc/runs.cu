@@ -194,7 +194,7 @@ __device__ __forceinline__ uint4 load_row16(const uint4* p) {
 
 // run_src[u]: address of the run's row (16-byte aligned, 0 = none) | 1 when it is a cache row
 template <int MODE, bool PEER>
-__global__ void __launch_bounds__(kBlock) runs_resolve_kernel(
+__global__ void __launch_bounds__(kBlock, PEER ? 3 : 1) runs_resolve_kernel(
     IndexView v, hb_runs_t r, RowSource rs, const char* __restrict__ cache_rows, int64_t row_bytes,
     int vb, unsigned long long* __restrict__ run_src, int64_t* __restrict__ run_slots,
     int* __restrict__ err) {
@@ -238,16 +238,21 @@ __global__ void __launch_bounds__(kBlock) runs_resolve_kernel(
       if (run_slots) run_slots[u] = slot;
     }
     if (PEER) {
-      // remote rows -> stage, 8 rows in flight, 16 bytes (or a word / a byte) per lane and step
-      const unsigned todo = __ballot_sync(0xffffffffu, remote != nullptr);
-      const unsigned long long from = (unsigned long long)remote, to = (unsigned long long)src;
-      for (int q0 = 0; q0 < 32 && todo; q0 += 8) {
-        if (((todo >> q0) & 0xffu) == 0u) continue;
-        unsigned long long f[8], t[8];
+      // remote rows -> stage, 8 rows in flight, 16 bytes (or a word / a byte) per lane and step.
+      // The warp's remote runs are taken 8 at a time whichever lanes hold them, so the number of
+      // dependent round trips over NVLink is ceil(remote runs of the warp / 8), not 4.
+      unsigned todo = __ballot_sync(0xffffffffu, remote != nullptr);
+      const unsigned long long from = (unsigned long long)remote;
+      while (todo) {
+        unsigned long long f[8];
+        int qs[8];  // the lane that holds the run; its row of the stage is u0 + lane
 #pragma unroll
         for (int x = 0; x < 8; ++x) {
-          f[x] = __shfl_sync(0xffffffffu, from, q0 + x);
-          t[x] = __shfl_sync(0xffffffffu, to, q0 + x);
+          qs[x] = todo ? __ffs(todo) - 1 : 0;
+          const bool have = todo != 0u;
+          todo &= todo - 1u;  // stays 0 once empty
+          const unsigned long long fq = __shfl_sync(0xffffffffu, from, qs[x]);
+          f[x] = have ? fq : 0ull;
         }
         if (vb == 16) {
           for (int64_t k = lane; k < (row_bytes >> 4); k += 32) {
@@ -257,13 +262,13 @@ __global__ void __launch_bounds__(kBlock) runs_resolve_kernel(
               if (f[x]) val[x] = *(reinterpret_cast<const uint4*>(f[x]) + k);
 #pragma unroll
             for (int x = 0; x < 8; ++x)
-              if (f[x]) *(reinterpret_cast<uint4*>(t[x]) + k) = val[x];
+              if (f[x]) *(reinterpret_cast<uint4*>(rs.stage + (u0 + qs[x]) * row_bytes) + k) = val[x];
           }
         } else {
           for (int x = 0; x < 8; ++x) {
             if (!f[x]) continue;
-            for (int64_t k = lane; k < row_bytes; k += 32)
-              reinterpret_cast<char*>(t[x])[k] = reinterpret_cast<const char*>(f[x])[k];
+            char* t = rs.stage + (u0 + qs[x]) * row_bytes;
+            for (int64_t k = lane; k < row_bytes; k += 32) t[k] = reinterpret_cast<const char*>(f[x])[k];
           }
         }
       }
@@ -574,7 +579,7 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache
                          hb_stream_t stream) {
   HB_CHECK_ARG(h && runs, "hb_lookup_fetch_runs: null argument");
   HB_CHECK_ARG(row_bytes > 0, "hb_lookup_fetch_runs: bad row size");
-  HB_CHECK_ARG(runs->n == 0 || (cache_rows && out_rows && runs->perm && runs->head && runs->base8 && runs->uniq_ids),
+  HB_CHECK_ARG(runs->n == 0 || (cache_rows && runs->perm && runs->head && runs->base8 && runs->uniq_ids),
                "hb_lookup_fetch_runs: null argument");
   HB_CHECK_ARG(mode == HB_LOOKUP_SETASSOC || mode == HB_LOOKUP_SORTED,
                "hb_lookup_fetch_runs: unknown mode %d", mode);
@@ -624,6 +629,7 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache
     }
 #undef HB_RES
   }
+  if (!out_rows) return HB_OK;  // per distinct id only: slots in run_slots, remote rows staged
   int64_t blocks = ceil_div(ceil_div(runs->n, 32) * 32, kBlock);
   if (blocks > (int64_t)sm_count() * 32) blocks = (int64_t)sm_count() * 32;
   const int grid = (int)(blocks < 1 ? 1 : blocks);

@@ -33,6 +33,7 @@ class PeerExchange:
         """fence: "device" = hb_a2a_fence (flags in peer memory, bounded wait, no collective
         library); "nccl" = a 4-byte all-reduce."""
         self.fence_kind = fence
+        self.next_parity = 0  # receive area the next push fills
         self.lib = _lib.load()
         self.rank, self.world, self.cap, self.dim, self.group = rank, world, int(cap_rows), dim, group
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
@@ -126,6 +127,7 @@ class PeerExchange:
         _lib.check(self.lib.hb_a2a_push(self._h, ids.data_ptr(), rows.data_ptr(), _lib.ptr(cnt), n,
                                         _lib.ptr(n_dev), _lib.ptr(sent_counts), C.byref(parity),
                                         ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
+        self.next_parity = parity.value ^ 1
         return parity.value
 
     def fence(self) -> None:
@@ -144,6 +146,7 @@ class PeerExchange:
             torch.cuda.synchronize()
             dist.barrier(group=self.group)  # nobody still pushes or polls
         _lib.check(self.lib.hb_a2a_reset(self._h, _lib.stream_ptr()))
+        self.next_parity = 0
         torch.cuda.synchronize()
         if self.world > 1:
             dist.barrier(group=self.group)  # every area is clean before the next push

@@ -86,6 +86,7 @@ class EmbeddingPath:
         self.step_no = 0
         self._graphs, self._g_ids, self._g_grads, self._g_out, self._g_next = [], None, None, None, 0
         self._whole_step_graphs = True
+        self._flush_graphs, self._flush_next = [], 0
         # unique hot ids of a batch cannot outnumber the hot ids of the table
         self.num_hot_ids = int((class_table == HOT).sum().item())
         self.num_nodes, self.dim, self.row_dtype = class_table.numel(), cold.dim, cold.emb.dtype
@@ -197,11 +198,18 @@ class EmbeddingPath:
         self._after_step(st)
         return st
 
-    def _after_step(self, st: StepStats) -> None:
+    def _after_step(self, st: StepStats, replaying: bool = False) -> None:
         self.step_no += 1
         st.flushed_dev = None
         if self.flush_every > 0 and self.step_no % self.flush_every == 0:
-            self.flush(st)
+            if replaying and self._flush_graphs:
+                # the flush has no host read either: one graph per receive area of its exchange
+                graph, (counts, cap) = self._flush_graphs[self._flush_next]
+                self._flush_next = (self._flush_next + 1) % len(self._flush_graphs)
+                graph.replay()
+                st.flushed_dev, st.flush_cap = counts, cap
+            else:
+                self.flush(st)
 
     def _runs_for(self, ids: torch.Tensor) -> E.BatchRuns:
         if self._last is not None and self._last[0].matches(ids):
@@ -325,7 +333,7 @@ class EmbeddingPath:
                 self.px.fence()
                 self._graphs[1 + parity][0].replay()
                 self._fence_shards()
-            self._after_step(st)
+            self._after_step(st, replaying=True)
             return rows, locs, found, st
         rows, locs, found = self.forward(ids, out_rows, join=False)
         st = self.backward(ids, grads)
@@ -337,7 +345,7 @@ class EmbeddingPath:
         (``ids`` is copied into ``ids_buf`` unless it is that tensor).  Call it after a few eager
         steps: every lazy allocation of the library has to have happened.
 
-        One GPU: one graph holds the whole step (the periodic flush stays eager).  Several GPUs
+        One GPU: one graph holds the whole step, one more the periodic flush.  Several GPUs
         with the peer-memory exchange and its device-side fence: two graphs, one per receive
         area, each holding the whole step; they are replayed alternately.  With the NCCL fence
         the collective is not captured: one graph for everything before the exchange and one
@@ -347,6 +355,8 @@ class EmbeddingPath:
             raise RuntimeError("the NCCL all-to-all exchange reads sizes on the host and cannot be captured")
         graphs = []
         self._whole_step_graphs = self.world == 1 or self.px.fence_kind == "device"
+        # the graph that fills receive area 0 (where an exchange starts again after a reset)
+        self._g_area0 = self.px.next_parity if (self.world > 1 and self._whole_step_graphs) else 0
         if self._whole_step_graphs:
             for _ in range(1 if self.world == 1 else 2):  # the push picks the areas in turn
                 g = torch.cuda.CUDAGraph()
@@ -366,6 +376,21 @@ class EmbeddingPath:
                     self._owner_update_from_slabs(parity)
                 graphs.append((gp, None))
         self._graphs, self._g_ids, self._g_grads, self._g_out, self._g_next = graphs, ids_buf, grads, out_rows, 0
+        # the periodic flush as graphs of its own (it reads nothing on the host): with several GPUs
+        # one per receive area of the flush exchange.  Not with the sorted lookup view (rebuilt on
+        # the host side after a flush), tiered optimiser state, or the NCCL flush.
+        self._flush_graphs, self._flush_next = [], 0
+        capturable = (self._whole_step_graphs and self.flush_every > 0 and self.lookup_mode != E.LOOKUP_SORTED
+                      and getattr(self.opt, "state_cache", None) is None
+                      and (self.world == 1 or (self.px_flush is not None and self.px_flush.fence_kind == "device")))
+        self._flush_area0 = self.px_flush.next_parity if (capturable and self.world > 1) else 0
+        if capturable:
+            for _ in range(1 if self.world == 1 else 2):
+                g = torch.cuda.CUDAGraph()
+                holder = StepStats()
+                with torch.cuda.graph(g):
+                    self.flush(holder)
+                self._flush_graphs.append((g, (holder.flushed_dev, holder.flush_cap)))
 
     # ---- forward and backward as separate graphs (a model runs between them) -------------------
     def capture_split(self, ids_buf: torch.Tensor, grads_buf: torch.Tensor, out_rows: torch.Tensor) -> None:
@@ -379,12 +404,14 @@ class EmbeddingPath:
         with torch.cuda.graph(fg):
             rows, locs, found = self.forward(ids_buf, out_rows, join=True)
         back = []
+        area0 = self.px.next_parity if self.world > 1 else 0
         for _ in range(1 if self.world == 1 else 2):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 st = self._backward_core(ids_buf, grads_buf)
             back.append((g, st))
-        self._split = dict(fwd=fg, back=back, next=0, ids=ids_buf, grads=grads_buf, out=(rows, locs, found))
+        self._split = dict(fwd=fg, back=back, next=0, area0=area0, ids=ids_buf, grads=grads_buf,
+                           out=(rows, locs, found))
 
     def forward_replay(self, ids: torch.Tensor):
         sp = self._split
@@ -412,9 +439,10 @@ class EmbeddingPath:
         for px in (self.px, self.px_flush):
             if px is not None:
                 px.reset()
-        self._g_next = 0
+        self._g_next = getattr(self, "_g_area0", 0) if len(self._graphs) == 2 else 0
+        self._flush_next = getattr(self, "_flush_area0", 0) if len(self._flush_graphs) == 2 else 0
         if getattr(self, "_split", None):
-            self._split["next"] = 0
+            self._split["next"] = self._split.get("area0", 0) if len(self._split["back"]) == 2 else 0
         if self.world > 1:
             dist.barrier(group=self.group)
 
@@ -422,7 +450,7 @@ class EmbeddingPath:
         """Release what this path shares with the other ranks (exchange areas, the owner shard);
         every rank calls it, after its last step.  The path cannot step afterwards."""
         torch.cuda.synchronize()
-        self._graphs, self._split = [], None
+        self._graphs, self._split, self._flush_graphs = [], None, []
         for obj in (self.px, self.px_flush, self.shared):
             if obj is not None:
                 obj.close()

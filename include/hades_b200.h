@@ -400,8 +400,9 @@ int hb_segsum_runs_f32(const hb_runs_t* runs /* host */, const float* grads,
  * every entry to its batch position; entries of one run inside a warp share one read.
  * locs (nullable): the per-position slots, 8-byte writes scattered over the batch (about
  * 15 % of the time at 512-byte rows): hb_index_touch_lru_runs and hb_runs_miss_list take
- * run_slots instead.  A miss whose id is not below the table's row count leaves its output
- * rows untouched and raises HB_ERR_INVALID in the device status word.
+ * run_slots instead.  out_rows == NULL runs the first launch only (the lookup of the distinct
+ * ids; remote rows staged).  A miss whose id is not below the table's row count leaves its
+ * output rows untouched and raises HB_ERR_INVALID in the device status word.
  * python/EmbCache/dist_emb.py:184-243. */
 size_t hb_lookup_fetch_runs_workspace_bytes(int64_t n, int64_t row_bytes, int sharded);
 int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs /* host */, const void* cache_rows,

@@ -162,13 +162,16 @@ def test_graph_replay_equals_eager(cuda_lib):
             p.step(batches[k], grads, o)
     torch.cuda.synchronize()
     paths[1].capture(ids_buf, grads, outs[1])
+    flushed_total = 0
     for k in range(2, 9):
         r0 = paths[0].step(batches[k], grads, outs[0])
         r1 = paths[1].step(batches[k], grads, outs[1])
         assert torch.equal(r0[0], r1[0]) and torch.equal(r0[1], r1[1]) and torch.equal(r0[2], r1[2]), k
         assert r0[3].flushed == r1[3].flushed
+        flushed_total += r1[3].flushed
         assert int(r0[3].num_unique.item()) == int(r1[3].num_unique.item())
-    assert len(paths[1]._graphs) == 1
+    assert len(paths[1]._graphs) == 1 and len(paths[1]._flush_graphs) == 1
+    assert flushed_total > 0  # the flush steps (replayed from a graph of their own) did flush rows
     assert torch.equal(paths[0].table, paths[1].table)
     assert torch.equal(paths[0].opt.state_mem, paths[1].opt.state_mem)
     assert torch.equal(paths[0].cold.remote.grad, paths[1].cold.remote.grad)
