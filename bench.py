@@ -755,8 +755,8 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
                        "cold_gradient_rows_dropped_total": dropped,
                        "note": "found = served by the cold cache: HOT ids (top 1 % of the popularity ranking) are "
                                "never cached and read the authoritative table / owner shard"},
-            "roofline": {"bound": "hbm", "kernel": "runs_lookup_fetch_kernel (fused cache lookup + cached fetch over the "
-                                                   "sorted batch)",
+            "roofline": {"bound": "hbm", "kernel": "runs_resolve_kernel + runs_expand_kernel (hb_lookup_fetch_runs: cache "
+                                                   "lookup per distinct id + cached fetch over the sorted batch)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": "measured" if peaks else "fallback",
                          "algorithmic_bytes": lf_bytes, "ms": st_ms["lookup_fetch"], "traffic": traffic, **prov,

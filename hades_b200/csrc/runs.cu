@@ -169,14 +169,14 @@ struct HeadPolicy {
 };
 
 // ---- forward: lookup + fetch over the sorted batch -----------------------------------------
-// Two launches.  RESOLVE works per distinct id (one lane per run): the index probe, the slot
-// of the run, and where the row of the run is to be read from -- the cache row, the row of the
-// table on this GPU, or, for a row that lives on ANOTHER GPU, a copy that this kernel makes in
-// a staging buffer on this GPU, so that every remote row crosses NVLink once per step however
-// often its id occurs in the batch (a row read again by every warp that meets the id, from
-// seven GPUs at once, serialises on one L2 slice of its owner).  EXPAND works per entry of the
-// sorted batch: the row goes to the entry's batch position; entries of one run inside a warp
-// take the registers of the first.
+// RESOLVE works per distinct id (one lane per run): the index probe, the slot of the run, and
+// where the row of the run is to be read from -- the cache row, the row of the table on this
+// GPU, or, for a row that lives on ANOTHER GPU, its place in a staging buffer on this GPU; such
+// runs go on a list.  STAGE (sharded tables only) copies the listed rows from their owners, so
+// that every remote row crosses NVLink once per step however often its id occurs in the batch
+// (a row read again by every warp that meets the id, from seven GPUs at once, serialises on one
+// L2 slice of its owner).  EXPAND works per entry of the sorted batch: the row goes to the
+// entry's batch position; entries of one run inside a warp take the registers of the first.
 struct RowSource {
   const char* backing;  // one table on this GPU, or null
   int64_t backing_rows;
@@ -184,6 +184,8 @@ struct RowSource {
   int rank;             // whose shard is local (PEER)
   char* stage;          // [stage_cap][row_bytes] copies of remote rows, by run (PEER)
   int64_t stage_cap;
+  int32_t* remote_runs;            // runs whose row STAGE has to copy, in any order (PEER)
+  unsigned long long* remote_count;  // [1], zero before RESOLVE
 };
 
 template <bool PEER>
@@ -194,7 +196,7 @@ __device__ __forceinline__ uint4 load_row16(const uint4* p) {
 
 // run_src[u]: address of the run's row (16-byte aligned, 0 = none) | 1 when it is a cache row
 template <int MODE, bool PEER>
-__global__ void __launch_bounds__(kBlock, PEER ? 3 : 1) runs_resolve_kernel(
+__global__ void __launch_bounds__(kBlock) runs_resolve_kernel(
     IndexView v, hb_runs_t r, RowSource rs, const char* __restrict__ cache_rows, int64_t row_bytes,
     int vb, unsigned long long* __restrict__ run_src, int64_t* __restrict__ run_slots,
     int* __restrict__ err) {
@@ -238,39 +240,56 @@ __global__ void __launch_bounds__(kBlock, PEER ? 3 : 1) runs_resolve_kernel(
       if (run_slots) run_slots[u] = slot;
     }
     if (PEER) {
-      // remote rows -> stage, 8 rows in flight, 16 bytes (or a word / a byte) per lane and step.
-      // The warp's remote runs are taken 8 at a time whichever lanes hold them, so the number of
-      // dependent round trips over NVLink is ceil(remote runs of the warp / 8), not 4.
-      unsigned todo = __ballot_sync(0xffffffffu, remote != nullptr);
-      const unsigned long long from = (unsigned long long)remote;
-      while (todo) {
-        unsigned long long f[8];
-        int qs[8];  // the lane that holds the run; its row of the stage is u0 + lane
+      // remote runs go on a list; STAGE copies their rows with every row in flight at once (the
+      // copy is bound by round trips over NVLink, which a kernel that also probes the index
+      // cannot keep enough of in flight)
+      const unsigned todo = __ballot_sync(0xffffffffu, remote != nullptr);
+      if (todo) {
+        unsigned long long at = 0;
+        if (lane == 0) at = atomicAdd(rs.remote_count, (unsigned long long)__popc(todo));
+        at = __shfl_sync(0xffffffffu, at, 0);
+        if (remote) rs.remote_runs[at + __popc(todo & ((1u << lane) - 1u))] = (int32_t)u;
+      }
+    }
+  }
+}
+
+// STAGE: the rows of the listed runs, from their owners' shards into this GPU's stage.  One
+// warp per row and step, 4 rows in flight per warp, 32 warps per SM: some 19,000 rows are on
+// their way at once, several times what the links need to run at their bandwidth.
+__global__ void __launch_bounds__(kBlock, 4) runs_stage_kernel(hb_runs_t r, RowSource rs, int64_t row_bytes, int vb) {
+  const int64_t cnt = (int64_t)*rs.remote_count;
+  const int lane = lane_id();
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  constexpr int kFly = 4;
+  for (int64_t i0 = warp * kFly; i0 < cnt; i0 += nwarps * kFly) {
+    const char* from[kFly];
+    char* to[kFly];
 #pragma unroll
-        for (int x = 0; x < 8; ++x) {
-          qs[x] = todo ? __ffs(todo) - 1 : 0;
-          const bool have = todo != 0u;
-          todo &= todo - 1u;  // stays 0 once empty
-          const unsigned long long fq = __shfl_sync(0xffffffffu, from, qs[x]);
-          f[x] = have ? fq : 0ull;
-        }
-        if (vb == 16) {
-          for (int64_t k = lane; k < (row_bytes >> 4); k += 32) {
-            uint4 val[8];
+    for (int x = 0; x < kFly; ++x) {
+      from[x] = nullptr;
+      to[x] = nullptr;
+      if (i0 + x < cnt) {
+        const int64_t u = rs.remote_runs[i0 + x];
+        from[x] = shard_row(rs.shards, __ldg(r.uniq_ids + u), row_bytes);
+        to[x] = rs.stage + u * row_bytes;
+      }
+    }
+    if (vb == 16) {
+      for (int64_t k = lane; k < (row_bytes >> 4); k += 32) {
+        uint4 val[kFly];
 #pragma unroll
-            for (int x = 0; x < 8; ++x)
-              if (f[x]) val[x] = *(reinterpret_cast<const uint4*>(f[x]) + k);
+        for (int x = 0; x < kFly; ++x)
+          if (from[x]) val[x] = *(reinterpret_cast<const uint4*>(from[x]) + k);
 #pragma unroll
-            for (int x = 0; x < 8; ++x)
-              if (f[x]) *(reinterpret_cast<uint4*>(rs.stage + (u0 + qs[x]) * row_bytes) + k) = val[x];
-          }
-        } else {
-          for (int x = 0; x < 8; ++x) {
-            if (!f[x]) continue;
-            char* t = rs.stage + (u0 + qs[x]) * row_bytes;
-            for (int64_t k = lane; k < row_bytes; k += 32) t[k] = reinterpret_cast<const char*>(f[x])[k];
-          }
-        }
+        for (int x = 0; x < kFly; ++x)
+          if (from[x]) *(reinterpret_cast<uint4*>(to[x]) + k) = val[x];
+      }
+    } else {
+      for (int x = 0; x < kFly; ++x) {
+        if (!from[x]) continue;
+        for (int64_t k = lane; k < row_bytes; k += 32) to[x][k] = from[x][k];
       }
     }
   }
@@ -289,7 +308,7 @@ __device__ __forceinline__ int64_t run_of_entry(const hb_runs_t& r, int64_t j) {
 // 16 = any multiple of 16 bytes; 0 = words or bytes.  PEER: a source may be another GPU's memory
 // (runs that found no room in the stage), so rows are read with plain loads.
 template <bool PEER, int RB>
-__global__ void __launch_bounds__(kBlock, 3) runs_expand_kernel(
+__global__ void __launch_bounds__(kBlock, RB == 512 ? 4 : 3) runs_expand_kernel(
     hb_runs_t r, const unsigned long long* __restrict__ run_src, const int64_t* __restrict__ run_slots,
     int64_t row_bytes_arg, int vb, char* __restrict__ out, int64_t* __restrict__ locs,
     uint8_t* __restrict__ found) {
@@ -547,6 +566,8 @@ struct FetchPlan {
   int64_t* run_slots;
   char* stage;
   int64_t stage_cap;
+  int32_t* remote_runs;
+  unsigned long long* remote_count;
   size_t total;
 };
 constexpr int64_t kStageMaxBytes = (int64_t)1 << 30;  // at most 1 GiB of staged remote rows
@@ -559,9 +580,13 @@ FetchPlan make_fetch_plan(void* ws, int64_t n, int64_t row_bytes, bool sharded) 
   f.run_slots = cv.take<int64_t>(m);
   f.stage_cap = 0;
   f.stage = nullptr;
+  f.remote_runs = nullptr;
+  f.remote_count = nullptr;
   if (sharded) {
     f.stage_cap = kStageMaxBytes / row_bytes < m ? kStageMaxBytes / row_bytes : m;
     f.stage = cv.take<char>((size_t)f.stage_cap * row_bytes);
+    f.remote_runs = cv.take<int32_t>(m);
+    f.remote_count = cv.take<unsigned long long>(2);
   }
   f.total = cv.used() + 256;
   return f;
@@ -604,6 +629,8 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache
   rs.backing_rows = backing_rows ? backing_num_rows : 0;
   rs.stage = f.stage;
   rs.stage_cap = f.stage_cap;
+  rs.remote_runs = f.remote_runs;
+  rs.remote_count = f.remote_count;
   if (table) {
     int rc = make_shard_view(table, &rs.shards);
     if (rc != HB_OK) return rc;
@@ -615,6 +642,7 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache
   const int vb = v16 ? 16 : ((bits & 3) == 0 ? 4 : 1);
   int* err = device_error_word();
   int64_t* slots = run_slots ? run_slots : f.run_slots;
+  if (sharded) HB_CUDA(cudaMemsetAsync(f.remote_count, 0, sizeof(unsigned long long), st));
   {
     int64_t blocks = ceil_div(ceil_div(runs->n, 32) * 32, kBlock);  // one lane per run, at most n runs
     if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
@@ -629,6 +657,8 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache
     }
 #undef HB_RES
   }
+  if (sharded)
+    HB_LAUNCH(runs_stage_kernel, sm_count() * 4, kBlock, 0, st, *runs, rs, row_bytes, vb);
   if (!out_rows) return HB_OK;  // per distinct id only: slots in run_slots, remote rows staged
   int64_t blocks = ceil_div(ceil_div(runs->n, 32) * 32, kBlock);
   if (blocks > (int64_t)sm_count() * 32) blocks = (int64_t)sm_count() * 32;

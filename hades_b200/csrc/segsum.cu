@@ -113,7 +113,7 @@ __device__ __forceinline__ int64_t effective_n(const SegArgs& a) {
 // HAS_CNT: per-row weights are given (unique_grads with cnt); otherwise the count
 // of a run is the number of its rows and needs no per-row traffic.
 template <int VEC, int G, int VPL, bool HAS_CNT>
-__global__ void __launch_bounds__(kBlock, 3) segsum_main_kernel(SegArgs a) {
+__global__ void __launch_bounds__(kBlock, 4) segsum_main_kernel(SegArgs a) {
   using V = typename VecF<VEC>::T;
   constexpr int U = (8 / VPL) < G ? (8 / VPL) : G;  // rows whose loads are in flight together
   const int lane = threadIdx.x & 31;

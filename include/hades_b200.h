@@ -392,15 +392,16 @@ int hb_segsum_runs_f32(const hb_runs_t* runs /* host */, const float* grads,
 
 /* hb_lookup_fetch (or hb_lookup_fetch_sharded when `table` is given) over a batch that
  * hb_runs_build has sorted: same outputs at the same batch positions (locs, found,
- * out_rows), in two launches.  The first works per DISTINCT id: index probe, the slot of
- * every run (run_slots[u], nullable output, n entries) and the place its row is read from;
- * a row that lives in another GPU's shard is copied once into a staging buffer on this GPU
- * (up to 1 GiB of them; the rest is read from the owner directly), so every remote row
- * crosses NVLink once per step however often its id occurs.  The second writes the row of
- * every entry to its batch position; entries of one run inside a warp share one read.
+ * out_rows), in two launches (three with a sharded table).  The first works per DISTINCT id:
+ * index probe, the slot of every run (run_slots[u], nullable output, n entries) and the place
+ * its row is read from; rows that live in another GPU's shard are then copied once, by a
+ * launch of their own, into a staging buffer on this GPU (up to 1 GiB of them; the rest is
+ * read from the owner directly), so every remote row crosses NVLink once per step however
+ * often its id occurs.  The last launch writes the row of every entry to its batch position;
+ * entries of one run inside a warp share one read.
  * locs (nullable): the per-position slots, 8-byte writes scattered over the batch (about
  * 15 % of the time at 512-byte rows): hb_index_touch_lru_runs and hb_runs_miss_list take
- * run_slots instead.  out_rows == NULL runs the first launch only (the lookup of the distinct
+ * run_slots instead.  out_rows == NULL leaves the last launch out (the lookup of the distinct
  * ids; remote rows staged).  A miss whose id is not below the table's row count leaves its
  * output rows untouched and raises HB_ERR_INVALID in the device status word.
  * python/EmbCache/dist_emb.py:184-243. */
