@@ -43,9 +43,11 @@ NVLINK_MEASURED_GBS = 770.0   # peer copy measured on this pool (cudaMemcpyPeer,
 # that source changes the figure is withheld (traffic = null) until it is captured again.
 TRAFFIC_CAPTURE = {
     "kernel_sources": ["hades_b200/csrc/runs.cu", "hades_b200/csrc/index.cuh"],
-    "sha256": None,
-    "bytes_per_launch": None,
-    "source": None,
+    "sha256": "0a5163f62e8bc154bf6b5915406c250af93d8011572c6db38b198aa912d0228c",
+    "bytes_per_launch": 1_092_748_373,
+    "source": "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none (1 pass) over "
+              "bench.py --steps 8 --warmup 3 --no-graph at full configuration 2 on one B200: runs_resolve_kernel "
+              "17.8 MB read + runs_expand_kernel 105.9 MB read, 969.0 MB written, mean of 3 calls",
 }
 
 
@@ -74,6 +76,8 @@ def parse():
     ap.add_argument("--exchange", default="push", choices=["push", "push_nccl_fence", "nccl"],
                     help="N>1: fused pack+push over peer memory with the device-side fence (default) or "
                          "with an NCCL all-reduce as the fence, or NCCL all_to_all_single")
+    ap.add_argument("--overlap-fetch", default="auto", choices=["auto", "on", "off"],
+                    help="run the forward fetch of a step beside the aggregation of the same step (auto: N > 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the legs on the other configurations")
@@ -427,7 +431,7 @@ def parity_full_size(path, ids_dev, ids_host) -> dict:
             "found_fraction": float((want >= 0).mean())}
 
 
-def parity_steps(rank, world, dev, exchange, lookup_mode) -> dict:
+def parity_steps(rank, world, dev, exchange, lookup_mode, overlap_fetch=False) -> dict:
     """Four steps (the second and fourth end with a flush) of a small configuration through the
     same EmbeddingPath on every rank against a numpy simulation of all ranks
     (oracle/pipeline_oracle.py): slots, found masks, index and LRU state, staging state, optimiser
@@ -447,6 +451,7 @@ def parity_steps(rank, world, dev, exchange, lookup_mode) -> dict:
     cfg = synth.CacheFetchConfig(base.name, base.config, base.table_rows, 64, base.cache_entries, base.batch,
                                  base.zipf_s, flush_every=2)
     path = pipeline.build_path(cfg, rank, world, dev, lookup_mode=lookup_mode, exchange=exchange, hot_fraction=0.02)
+    path.overlap_fetch = overlap_fetch
     if path.shared is not None:
         w = path.shared.gather(torch.arange(cfg.table_rows, dtype=torch.int64, device=dev)).cpu().numpy()
     else:
@@ -519,6 +524,9 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
         rng = synth.rng_for(2, rank, 1)
         host_batches = [torch.from_numpy(sampler.ids(rng, cfg.batch)).pin_memory() for _ in range(4)]
     path.want_locs = False  # the step needs the slots in sorted order only (a coalesced write)
+    # the fetch of a batch beside the aggregation of its gradients: pays when part of the fetch is
+    # bound by NVLink round trips (remote rows), not on one GPU where both are HBM-bound
+    path.overlap_fetch = (world > 1) if args.overlap_fetch == "auto" else (args.overlap_fetch == "on")
     dev_batches = [b.to(dev) for b in host_batches]
     gen = torch.Generator(device=dev)
     gen.manual_seed(2000 + rank)
@@ -533,10 +541,10 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
     if main_line and not args.no_parity:
         if world == 1 and not c5 and args.scale == 1.0:
             parity = parity_full_size(path, dev_batches[0], host_batches[0])
-            small = parity_steps(rank, world, dev, args.exchange, mode)
+            small = parity_steps(rank, world, dev, args.exchange, mode, path.overlap_fetch)
             parity = {"ok": parity["ok"] and small["ok"], "full_size_batch": parity, "steps_small": small}
         else:
-            parity = parity_steps(rank, world, dev, args.exchange, mode)
+            parity = parity_steps(rank, world, dev, args.exchange, mode, path.overlap_fetch)
         if not parity["ok"]:
             if rank == 0:
                 print(json.dumps({"metric": METRIC, "parity_check": parity, "error": "parity self-check failed"}))
@@ -743,6 +751,7 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
                        "flush_ms": flush_ms, "breakdown": breakdown,
                        "lookup": args.lookup, "lru_ageing": not args.no_lru, "insert_cold_misses": not args.no_insert,
                        "cuda_graph": use_graph, "untimed_settling_steps_after_warmup": settle,
+                       "fetch_beside_aggregation": path.overlap_fetch,
                        "optimizer": "SparseAdam fp32" if args.optimizer == "adam" else "SparseAdagrad fp32",
                        "exchange": "local" if world == 1 else (
                            "nccl all_to_all" if path.px is None else

@@ -61,7 +61,7 @@ class EmbeddingPath:
                  lookup_mode: int = E.LOOKUP_SETASSOC, mover: int = E.MOVER_AUTO,
                  touch_lru: bool = True, group=None, peer_exchange=None, flush_exchange=None,
                  insert_misses: bool = True, miss_cap: int = 1 << 17, flush_cap: int = 1 << 19,
-                 want_locs: bool = True):
+                 want_locs: bool = True, overlap_fetch: bool = False):
         """table: backing rows for cache misses, [num_nodes, dim] fp32 on this GPU; None when the
         optimiser's shard is a ``PeerTable`` (misses then read the owners' shards).
         class_table: int8 per node, HOT or COLD.  optimizer: SparseAdam / SparseAdagrad on this
@@ -71,7 +71,9 @@ class EmbeddingPath:
         most miss_cap distinct ids per step; the rest stay uncached until they miss again).
         flush_cap: rows one flush can send (the other stale rows wait for the next flush).
         want_locs: ``forward`` also returns the slots by batch position (False: None; the path
-        itself uses the slot of every run)."""
+        itself uses the slot of every run).  overlap_fetch: ``step`` runs the fetch of a batch beside
+        the aggregation of the same batch's gradients (both need only the sort)."""
+        self.overlap_fetch = bool(overlap_fetch)
         self.table, self.class_table, self.cold, self.opt = table, class_table, cold, optimizer
         self.rank, self.world = rank, world
         self.flush_every, self.id_bits = flush_every, id_bits
@@ -132,9 +134,12 @@ class EmbeddingPath:
         return cur
 
     # ---- forward -------------------------------------------------------------------------
-    def forward(self, ids: torch.Tensor, out_rows: torch.Tensor | None = None, join: bool = True):
+    def forward(self, ids: torch.Tensor, out_rows: torch.Tensor | None = None, join: bool = True,
+                on_side: bool = False):
         """(rows, locs, found) at the batch positions.  join=False leaves the cache insert
-        running on the side stream (``backward`` joins it)."""
+        running on the side stream (``backward`` joins it).  on_side=True (``step`` with
+        overlap_fetch): everything after the sort runs on the side stream and the rows are
+        complete only after the join at the end of the backward pass."""
         lib = E._lib.load()
         n = ids.numel()
         runs = E.cudaRunsBuild(ids, self.id_bits, self.class_table, keep=(False, True, True),
@@ -144,30 +149,50 @@ class EmbeddingPath:
         sharded = self.shared is not None and self.world > 1
         fetch_ws = self._ws("_fetch_ws", lib.hb_lookup_fetch_runs_workspace_bytes(
             n, self.dim * self.cold.emb.element_size(), int(sharded)))
-        rows, locs, found = E.cudaLookupFetchRuns(self.cold.index, runs, self.cold.emb, self.table, self.shared,
-                                                  out_rows, self.lookup_mode, want_locs=self.want_locs, ws=fetch_ws)
-        if n and (self.touch_lru or self.insert_misses):
-            # Off the main stream, which goes on to whatever uses the rows: the LRU ageing of
-            # this lookup (cache.h:101), then the uncached cold ids and their rows go to the
-            # cache (dist_emb.py:218-259 -> server.py:499-544), before this step's cold
-            # gradients look the cache up.
+        if on_side and n:
+            # The whole fetch leaves the main stream, which goes on to the aggregation of the same
+            # batch (it needs the sort only): with several GPUs the copy of the remote rows is bound
+            # by NVLink round trips and hides behind that HBM-bound work.  The main stream joins
+            # before it returns the rows (``_join_side``).
             with self._on_side():
-                if self.touch_lru:
-                    self.cold.index.cuda_touch_lru_runs(runs.slots, runs, locs_kind=2)
-                if self.insert_misses:
-                    need = max(lib.hb_runs_miss_list_workspace_bytes(n),
-                               lib.hb_staging_insert_workspace_bytes(self.miss_cap))
-                    ws = self._ws("_side_ws", need)
-                    miss_ids, miss_src, miss_n = E.cudaRunsMissList(runs, runs.slots, COLD, self.miss_cap, ws=ws,
-                                                                    locs_kind=2)
-                    self.cold.insert_gather(miss_ids, rows, miss_src, ws=ws)
-                    self._side_finished(miss_ids, miss_src, miss_n, rows, runs)
-                else:
-                    self._side_finished(rows, runs)
-            if join:
-                self._join_side()
+                rows, locs, found = E.cudaLookupFetchRuns(self.cold.index, runs, self.cold.emb, self.table,
+                                                          self.shared, out_rows, self.lookup_mode,
+                                                          want_locs=self.want_locs, ws=fetch_ws)
+                self._after_fetch(runs, rows, n, lib)
+            if not torch.cuda.is_current_stream_capturing():
+                for t in (rows, locs, found):  # allocated under the side stream, read on this one
+                    if t is not None:
+                        t.record_stream(torch.cuda.current_stream())
+        else:
+            rows, locs, found = E.cudaLookupFetchRuns(self.cold.index, runs, self.cold.emb, self.table, self.shared,
+                                                      out_rows, self.lookup_mode, want_locs=self.want_locs,
+                                                      ws=fetch_ws)
+            if n and (self.touch_lru or self.insert_misses):
+                # Off the main stream, which goes on to whatever uses the rows: the LRU ageing of
+                # this lookup (cache.h:101), then the uncached cold ids and their rows go to the
+                # cache (dist_emb.py:218-259 -> server.py:499-544), before this step's cold
+                # gradients look the cache up.
+                with self._on_side():
+                    self._after_fetch(runs, rows, n, lib)
+                if join:
+                    self._join_side()
         self._last = (runs, locs)
         return rows, locs, found
+
+    def _after_fetch(self, runs, rows, n: int, lib) -> None:
+        """On the side stream: LRU ageing of the lookup, cold misses into the cache."""
+        if self.touch_lru:
+            self.cold.index.cuda_touch_lru_runs(runs.slots, runs, locs_kind=2)
+        if self.insert_misses:
+            need = max(lib.hb_runs_miss_list_workspace_bytes(n),
+                       lib.hb_staging_insert_workspace_bytes(self.miss_cap))
+            ws = self._ws("_side_ws", need)
+            miss_ids, miss_src, miss_n = E.cudaRunsMissList(runs, runs.slots, COLD, self.miss_cap, ws=ws,
+                                                            locs_kind=2)
+            self.cold.insert_gather(miss_ids, rows, miss_src, ws=ws)
+            self._side_finished(miss_ids, miss_src, miss_n, rows, runs)
+        else:
+            self._side_finished(rows, runs)
 
     def _fence_shards(self) -> None:
         """All ranks' optimiser updates before anyone's next read of a shard (and the other way
@@ -335,7 +360,7 @@ class EmbeddingPath:
                 self._fence_shards()
             self._after_step(st, replaying=True)
             return rows, locs, found, st
-        rows, locs, found = self.forward(ids, out_rows, join=False)
+        rows, locs, found = self.forward(ids, out_rows, join=False, on_side=self.overlap_fetch)
         st = self.backward(ids, grads)
         return rows, locs, found, st
 
@@ -361,7 +386,7 @@ class EmbeddingPath:
             for _ in range(1 if self.world == 1 else 2):  # the push picks the areas in turn
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
-                    rows, locs, found = self.forward(ids_buf, out_rows, join=False)
+                    rows, locs, found = self.forward(ids_buf, out_rows, join=False, on_side=self.overlap_fetch)
                     st = self._backward_core(ids_buf, grads)
                 graphs.append((g, (rows, locs, found, st)))
         else:

@@ -34,14 +34,16 @@ def _check_step(path, orc, ids, grads, it):
     return wflushed, int(whit.sum())
 
 
-@pytest.mark.parametrize("mode", [0, 1])
-def test_pipeline_matches_oracle(cuda_lib, oracle_mod, mode):
+@pytest.mark.parametrize("mode,overlap", [(0, False), (1, False), (0, True)])
+def test_pipeline_matches_oracle(cuda_lib, oracle_mod, mode, overlap):
+    """overlap: the fetch of a step runs on the side stream beside the aggregation of the same step."""
     from hades_b200 import pipeline, synth
 
     cfg = synth.scaled(synth.CONFIG1, 0.05, "pipe_test")
     cfg = synth.CacheFetchConfig(cfg.name, cfg.config, cfg.table_rows, 64, cfg.cache_entries // 4, cfg.batch,
                                  cfg.zipf_s, flush_every=3)
     path = pipeline.build_path(cfg, lookup_mode=mode, hot_fraction=0.02)
+    path.overlap_fetch = overlap
     orc = _oracle_for(path, oracle_mod, cfg)
     cls = path.class_table.cpu().numpy()
     fill = path.cache_fill_ids.cpu().numpy()
