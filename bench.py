@@ -76,6 +76,9 @@ def parse():
     ap.add_argument("--exchange", default="push", choices=["push", "push_nccl_fence", "nccl"],
                     help="N>1: fused pack+push over peer memory with the device-side fence (default) or "
                          "with an NCCL all-reduce as the fence, or NCCL all_to_all_single")
+    ap.add_argument("--remote-fetch", default="auto", choices=["auto", "pull", "deliver"],
+                    help="N > 1, rows of other GPUs' shards in the forward fetch: read by this GPU once per distinct "
+                         "id (pull) or stored into this GPU's stage by their owners (deliver); auto: deliver for N > 2")
     ap.add_argument("--overlap-fetch", default="on", choices=["on", "off"],
                     help="run the forward fetch of a step beside the aggregation of the same step (default on)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -431,7 +434,7 @@ def parity_full_size(path, ids_dev, ids_host) -> dict:
             "found_fraction": float((want >= 0).mean())}
 
 
-def parity_steps(rank, world, dev, exchange, lookup_mode, overlap_fetch=False) -> dict:
+def parity_steps(rank, world, dev, exchange, lookup_mode, overlap_fetch=False, remote_fetch="auto") -> dict:
     """Four steps (the second and fourth end with a flush) of a small configuration through the
     same EmbeddingPath on every rank against a numpy simulation of all ranks
     (oracle/pipeline_oracle.py): slots, found masks, index and LRU state, staging state, optimiser
@@ -450,7 +453,8 @@ def parity_steps(rank, world, dev, exchange, lookup_mode, overlap_fetch=False) -
     base = synth.scaled(synth.CONFIG2, 1.0 / 400.0, "parity_small")
     cfg = synth.CacheFetchConfig(base.name, base.config, base.table_rows, 64, base.cache_entries, base.batch,
                                  base.zipf_s, flush_every=2)
-    path = pipeline.build_path(cfg, rank, world, dev, lookup_mode=lookup_mode, exchange=exchange, hot_fraction=0.02)
+    path = pipeline.build_path(cfg, rank, world, dev, lookup_mode=lookup_mode, exchange=exchange, hot_fraction=0.02,
+                               remote_fetch=remote_fetch)
     path.overlap_fetch = overlap_fetch
     if path.shared is not None:
         w = path.shared.gather(torch.arange(cfg.table_rows, dtype=torch.int64, device=dev)).cpu().numpy()
@@ -512,14 +516,14 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
         cfg = synth.CONFIG5 if not args.rmat_bits else synth.scaled_rmat(synth.CONFIG5, args.rmat_bits)
         path = pipeline.build_rmat_path(cfg, rank, world, dev, optimizer=args.optimizer, lookup_mode=mode,
                                         touch_lru=not args.no_lru, exchange=args.exchange,
-                                        insert_misses=not args.no_insert)
+                                        insert_misses=not args.no_insert, remote_fetch=args.remote_fetch)
         rng = synth.rng_for(5, rank, 1)
         host_batches = [torch.from_numpy(synth.rmat_frontier(cfg, rng)).pin_memory() for _ in range(4)]
     else:
         cfg = synth.CONFIG2 if args.scale == 1.0 else synth.scaled(synth.CONFIG2, args.scale, "config2_scaled")
         path = pipeline.build_path(cfg, rank, world, dev, optimizer=args.optimizer, lookup_mode=mode,
                                    touch_lru=not args.no_lru, exchange=args.exchange,
-                                   insert_misses=not args.no_insert)
+                                   insert_misses=not args.no_insert, remote_fetch=args.remote_fetch)
         sampler = synth.ZipfSampler(cfg.table_rows, cfg.zipf_s)
         rng = synth.rng_for(2, rank, 1)
         host_batches = [torch.from_numpy(sampler.ids(rng, cfg.batch)).pin_memory() for _ in range(4)]
@@ -542,10 +546,10 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
     if main_line and not args.no_parity:
         if world == 1 and not c5 and args.scale == 1.0:
             parity = parity_full_size(path, dev_batches[0], host_batches[0])
-            small = parity_steps(rank, world, dev, args.exchange, mode, path.overlap_fetch)
+            small = parity_steps(rank, world, dev, args.exchange, mode, path.overlap_fetch, args.remote_fetch)
             parity = {"ok": parity["ok"] and small["ok"], "full_size_batch": parity, "steps_small": small}
         else:
-            parity = parity_steps(rank, world, dev, args.exchange, mode, path.overlap_fetch)
+            parity = parity_steps(rank, world, dev, args.exchange, mode, path.overlap_fetch, args.remote_fetch)
         if not parity["ok"]:
             if rank == 0:
                 print(json.dumps({"metric": METRIC, "parity_check": parity, "error": "parity self-check failed"}))
@@ -679,16 +683,25 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
     ids0 = dev_batches[0]
     runs0 = E.cudaRunsBuild(ids0, path.id_bits, path.class_table, keep=(False, True, True),
                             caps=(None, path.num_hot_ids, None))
+    lib = E._lib.load()
+    sharded = path.shared is not None and world > 1
+    fetch_ws = path._ws("_fetch_ws", lib.hb_lookup_fetch_runs_workspace_bytes(
+        cfg.batch, cfg.dim * 4, int(sharded)))
     st_ms = {
         "sort_runs": time_local(lambda: E.cudaRunsBuild(ids0, path.id_bits, path.class_table, keep=(False, True, True),
                                                         caps=(None, path.num_hot_ids, None), ws=runs0.ws)),
-        "lookup_fetch": time_local(lambda: E.cudaLookupFetchRuns(path.cold.index, runs0, path.cold.emb, path.table,
-                                                                 path.shared, out_rows, mode, want_locs=False)),
         "segsum": time_local(lambda: E.cudaSegSumRuns(runs0, grads, split_keep=(False, True, True))),
     }
-    # the per-distinct-id launch alone: index probe (+ at N > 1 remote rows copied once into this GPU's stage)
     resolve_ms = None
-    if True:
+    if path.px_req is not None:
+        # the owners deliver the remote rows: requests, two fences and the owners' stores are part
+        # of the fetch, so every rank runs it at the same time (max over ranks)
+        path._fetch(runs0, out_rows, fetch_ws)
+        st_ms["lookup_fetch"] = timed(lambda k: path._fetch(runs0, out_rows, fetch_ws), 10)
+    else:
+        st_ms["lookup_fetch"] = time_local(lambda: E.cudaLookupFetchRuns(
+            path.cold.index, runs0, path.cold.emb, path.table, path.shared, out_rows, mode, want_locs=False))
+        # the per-distinct-id launch alone: index probe (+ at N > 1 remote rows copied once into this GPU's stage)
         resolve_ms = time_local(lambda: E.cudaLookupFetchRuns(path.cold.index, runs0, path.cold.emb, path.table,
                                                               path.shared, None, mode, resolve_only=True))
     no_reuse_ms = None
@@ -753,6 +766,10 @@ def run_path(args, workload: str, steps: int, warmup: int, main_line: bool) -> d
                        "lookup": args.lookup, "lru_ageing": not args.no_lru, "insert_cold_misses": not args.no_insert,
                        "cuda_graph": use_graph, "untimed_settling_steps_after_warmup": settle,
                        "fetch_beside_aggregation": path.overlap_fetch,
+                       "remote_rows_of_the_fetch": (None if world == 1 else
+                                                    "delivered by their owners (requests pushed, rows stored into the "
+                                                    "requester's stage, two device fences)" if path.px_req is not None
+                                                    else "read by this GPU from the owners' shards, once per distinct id"),
                        "optimizer": "SparseAdam fp32" if args.optimizer == "adam" else "SparseAdagrad fp32",
                        "exchange": "local" if world == 1 else (
                            "nccl all_to_all" if path.px is None else

@@ -814,6 +814,51 @@ def cudaLookupFetchRuns(index: IndexCache, runs: BatchRuns, cache_rows, backing_
     return out_rows, locs, found
 
 
+def cudaRunsResolveRequests(index: IndexCache, runs: BatchRuns, cache_rows, peer_table, stage_rows: torch.Tensor,
+                            req_ids: torch.Tensor, req_runs: torch.Tensor, req_count: torch.Tensor,
+                            mode: int | None = None, ws: torch.Tensor | None = None) -> None:
+    """First third of the forward fetch whose remote rows the OWNERS deliver
+    (``hb_runs_resolve_requests``): index probe per distinct id, slots into ``runs.slots``, and the
+    list of remote runs: req_ids[k] the id, req_runs[k] the run = the row of ``stage_rows`` (this
+    GPU's stage, mapped by the peers) that the owner fills; k < req_count[0].  The caller carries
+    the requests to the owners (``PeerExchange.push`` with req_runs as the counts), the owners
+    answer with ``PeerTable.serve``, then ``cudaRunsExpand`` finishes."""
+    n = runs.n
+    dev = runs.ids.device
+    _check(req_ids.numel() >= n and req_runs.numel() >= n, "request lists hold one entry per id of the batch")
+    if runs.slots is None:
+        runs.slots = torch.empty(max(n, 1), dtype=torch.int64, device=dev)
+    lib = _lib.load()
+    need = lib.hb_lookup_fetch_runs_workspace_bytes(n, _row_bytes(cache_rows), 0)
+    if ws is not None and ws.numel() >= need:
+        runs.fetch_ws = ws
+    elif runs.fetch_ws is None or runs.fetch_ws.numel() < need:
+        runs.fetch_ws = torch.empty(need, dtype=torch.uint8, device=dev)
+    _lib.check(lib.hb_runs_resolve_requests(index.handle, C.byref(runs.desc), _dev_ptr(cache_rows, "cache_rows"),
+                                            peer_table.handle, _row_bytes(cache_rows), stage_rows.data_ptr(),
+                                            stage_rows.size(0), runs.slots.data_ptr(), req_ids.data_ptr(),
+                                            req_runs.data_ptr(), req_count.data_ptr(),
+                                            index.lookup_mode if mode is None else mode, runs.fetch_ws.data_ptr(),
+                                            runs.fetch_ws.numel(), _lib.stream_ptr()))
+
+
+def cudaRunsExpand(runs: BatchRuns, cache_rows, stage_rows, out_rows=None, want_locs: bool = True):
+    """Last third (``hb_runs_expand``): (out_rows, locs, found) at the batch positions from what
+    ``cudaRunsResolveRequests`` left in ``runs`` and the rows the owners delivered."""
+    n = runs.n
+    dev = runs.ids.device
+    if out_rows is None:
+        out_rows = torch.empty((n, cache_rows.size(1)), dtype=cache_rows.dtype, device=dev)
+    locs = torch.empty(n, dtype=torch.int64, device=dev) if want_locs else None
+    found = torch.empty(n, dtype=torch.bool, device=dev)
+    lib = _lib.load()
+    _lib.check(lib.hb_runs_expand(C.byref(runs.desc), _dev_ptr(cache_rows, "cache_rows"), stage_rows.data_ptr(),
+                                  _row_bytes(cache_rows), out_rows.data_ptr(), _lib.ptr(locs), found.data_ptr(),
+                                  runs.slots.data_ptr(), runs.fetch_ws.data_ptr(), runs.fetch_ws.numel(),
+                                  _lib.stream_ptr()))
+    return out_rows, locs, found
+
+
 def cudaSegSumRuns(runs: BatchRuns, grads, cnt=None, mean: bool = False, split_keep=None, caps=(None, None, None),
                    ws: torch.Tensor | None = None):
     """The aggregation of ``cudaUniqueSegSum`` over existing runs (the ids of ``grads`` are the ids

@@ -113,6 +113,59 @@ __global__ void __launch_bounds__(kBlock) sharded_gather_kernel(
   }
 }
 
+// The owner's half of a forward fetch in which the owners deliver: requests (id, row of the
+// requester's stage) lie in per-requester segments of seg_cap entries (the receive view of an
+// hb_a2a exchange: counts[s] valid in segment s); every requested row of this rank's shard is
+// stored into the stage of its requester, which this rank has mapped.  Peer STORES run at the
+// links' bandwidth where scattered peer LOADS of the same rows do not.  One warp per request and
+// step, 4 requests in flight per warp.
+__global__ void __launch_bounds__(kBlock, 4) fetch_serve_kernel(
+    const char* __restrict__ shard, int64_t rows_local, int rank, int world, ShardView stages,
+    int64_t stage_rows, const int64_t* __restrict__ req_ids, const int64_t* __restrict__ req_rows,
+    const int64_t* __restrict__ counts, int64_t seg_cap, int64_t row_bytes, int* __restrict__ err) {
+  const int lane = lane_id();
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  constexpr int kFly = 4;
+  const int64_t vpr = row_bytes >> 4;
+  for (int s = 0; s < world; ++s) {
+    int64_t cnt = counts[s];
+    if (cnt > seg_cap) cnt = seg_cap;
+    char* stage = const_cast<char*>(stages.p[s]);
+    for (int64_t k0 = warp * kFly; k0 < cnt; k0 += nwarps * kFly) {
+      const uint4* from[kFly];
+      uint4* to[kFly];
+#pragma unroll
+      for (int x = 0; x < kFly; ++x) {
+        from[x] = nullptr;
+        to[x] = nullptr;
+        if (k0 + x < cnt) {
+          const int64_t id = __ldg(req_ids + s * seg_cap + k0 + x);
+          const int64_t row = __ldg(req_rows + s * seg_cap + k0 + x);
+          const int64_t local = (id - rank) / world;
+          const bool ok = id >= 0 && mod_nonneg(id, world) == rank && local < rows_local && row >= 0 &&
+                          row < stage_rows;
+          if (ok) {
+            from[x] = reinterpret_cast<const uint4*>(shard + local * row_bytes);
+            to[x] = reinterpret_cast<uint4*>(stage + row * row_bytes);
+          } else if (lane == 0) {
+            atomicExch(err, HB_ERR_INVALID);  // not this rank's row, or no such row of the stage: skipped
+          }
+        }
+      }
+      for (int64_t k = lane; k < vpr; k += 32) {
+        uint4 val[kFly];
+#pragma unroll
+        for (int x = 0; x < kFly; ++x)
+          if (from[x]) val[x] = from[x][k];
+#pragma unroll
+        for (int x = 0; x < kFly; ++x)
+          if (from[x]) to[x][k] = val[x];
+      }
+    }
+  }
+}
+
 int64_t grid_for(int64_t n) {
   int64_t blocks = ceil_div(ceil_div(n, 32) * 32, kBlock);
   const int64_t cap = (int64_t)sm_count() * 16;
@@ -222,6 +275,23 @@ int hb_peer_table_gather(hb_peer_table_t* t, const int64_t* ids, int64_t n, cons
   if (rc != HB_OK) return rc;
   HB_LAUNCH(sharded_gather_kernel, (int)grid_for(n), kBlock, 0, (cudaStream_t)stream, sv, ids, n, n_dev,
             t->row_bytes, (char*)dst, device_error_word());
+  return HB_OK;
+}
+
+int hb_fetch_serve(hb_peer_table_t* table, hb_peer_table_t* stages, const int64_t* req_ids,
+                   const int64_t* req_rows, const int64_t* req_counts, int64_t seg_cap, hb_stream_t stream) {
+  HB_CHECK_ARG(table && stages && req_ids && req_rows && req_counts && seg_cap > 0, "hb_fetch_serve: null argument");
+  HB_CHECK_ARG(table->world == stages->world && table->rank == stages->rank,
+               "hb_fetch_serve: table and stages belong to different groups");
+  HB_CHECK_ARG(table->row_bytes == stages->row_bytes, "hb_fetch_serve: row sizes differ");
+  ShardView sv;
+  int rc = make_shard_view(stages, &sv);
+  if (rc != HB_OK) return rc;
+  // every rank's stage has the rows of the shortest one
+  const int64_t stage_rows = stages->num_rows / stages->world;
+  HB_LAUNCH(fetch_serve_kernel, sm_count() * 4, kBlock, 0, (cudaStream_t)stream, (const char*)table->local,
+            table->rows_local, table->rank, table->world, sv, stage_rows, req_ids, req_rows, req_counts, seg_cap,
+            table->row_bytes, device_error_word());
   return HB_OK;
 }
 

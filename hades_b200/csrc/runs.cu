@@ -186,6 +186,9 @@ struct RowSource {
   int64_t stage_cap;
   int32_t* remote_runs;            // runs whose row STAGE has to copy, in any order (PEER)
   unsigned long long* remote_count;  // [1], zero before RESOLVE
+  // when the OWNERS deliver the remote rows (hb_runs_resolve_requests): what to ask them for
+  int64_t* req_ids;                // [n] id of a remote run
+  int64_t* req_runs;               // [n] the run, i.e. the row of this GPU's stage the owner fills
 };
 
 template <bool PEER>
@@ -248,7 +251,15 @@ __global__ void __launch_bounds__(kBlock) runs_resolve_kernel(
         unsigned long long at = 0;
         if (lane == 0) at = atomicAdd(rs.remote_count, (unsigned long long)__popc(todo));
         at = __shfl_sync(0xffffffffu, at, 0);
-        if (remote) rs.remote_runs[at + __popc(todo & ((1u << lane) - 1u))] = (int32_t)u;
+        if (remote) {
+          const unsigned long long k = at + __popc(todo & ((1u << lane) - 1u));
+          if (rs.req_ids) {
+            rs.req_ids[k] = id;
+            rs.req_runs[k] = u;
+          } else {
+            rs.remote_runs[k] = (int32_t)u;
+          }
+        }
       }
     }
   }
@@ -271,7 +282,12 @@ __global__ void __launch_bounds__(kBlock, 4) runs_stage_kernel(hb_runs_t r, RowS
       from[x] = nullptr;
       to[x] = nullptr;
       if (i0 + x < cnt) {
-        const int64_t u = rs.remote_runs[i0 + x];
+        // every rank starts at another place of its list: the lists of the ranks hold much the same
+        // popular ids in much the same order, and readers that walk an owner's rows in step with
+        // each other queue on the same lines
+        int64_t at = i0 + x + (cnt / rs.shards.world) * rs.rank;
+        if (at >= cnt) at -= cnt;
+        const int64_t u = rs.remote_runs[at];
         from[x] = shard_row(rs.shards, __ldg(r.uniq_ids + u), row_bytes);
         to[x] = rs.stage + u * row_bytes;
       }
@@ -591,35 +607,41 @@ FetchPlan make_fetch_plan(void* ws, int64_t n, int64_t row_bytes, bool sharded) 
   f.total = cv.used() + 256;
   return f;
 }
-}  // namespace
+// Who brings the remote rows: nobody (one table on this GPU), this GPU (STAGE reads the owners'
+// shards), or the owners (`dv`: RESOLVE lists (id, run) requests, the owners store the rows into
+// dv->stage, which they have mapped, before EXPAND runs).
+struct Delivery {
+  char* stage;
+  int64_t stage_cap;
+  int64_t *req_ids, *req_runs, *req_count;
+};
 
-size_t hb_lookup_fetch_runs_workspace_bytes(int64_t n, int64_t row_bytes, int sharded) {
-  return make_fetch_plan(nullptr, n, row_bytes > 0 ? row_bytes : 1, sharded != 0).total;
-}
-
-int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows,
-                         const void* backing_rows, int64_t backing_num_rows, hb_peer_table_t* table,
-                         int64_t row_bytes, void* out_rows, int64_t* locs, uint8_t* found,
-                         int64_t* run_slots, int mode, void* workspace, size_t workspace_bytes,
-                         hb_stream_t stream) {
-  HB_CHECK_ARG(h && runs, "hb_lookup_fetch_runs: null argument");
+int fetch_runs_impl(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows, const void* backing_rows,
+                    int64_t backing_num_rows, hb_peer_table_t* table, int64_t row_bytes, void* out_rows,
+                    int64_t* locs, uint8_t* found, int64_t* run_slots, int mode, void* workspace,
+                    size_t workspace_bytes, hb_stream_t stream, const Delivery* dv, bool resolve, bool expand) {
+  HB_CHECK_ARG((h || !resolve) && runs, "hb_lookup_fetch_runs: null argument");
   HB_CHECK_ARG(row_bytes > 0, "hb_lookup_fetch_runs: bad row size");
-  HB_CHECK_ARG(runs->n == 0 || (cache_rows && runs->perm && runs->head && runs->base8 && runs->uniq_ids),
+  HB_CHECK_ARG(runs->n == 0 || ((cache_rows || !resolve) && runs->perm && runs->head && runs->base8 &&
+                                runs->uniq_ids),
                "hb_lookup_fetch_runs: null argument");
   HB_CHECK_ARG(mode == HB_LOOKUP_SETASSOC || mode == HB_LOOKUP_SORTED,
                "hb_lookup_fetch_runs: unknown mode %d", mode);
   HB_CHECK_ARG(!(table && backing_rows), "hb_lookup_fetch_runs: give a backing table or a sharded one");
   HB_CHECK_ARG(!table || table->row_bytes == row_bytes, "hb_lookup_fetch_runs: row size differs from the table's");
   HB_CHECK_ARG(!backing_rows || backing_num_rows > 0, "hb_lookup_fetch_runs: a backing table needs its row count");
-  if (runs->n == 0) return HB_OK;
-  const bool sharded = table != nullptr && table->world > 1;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (runs->n == 0) {
+    if (dv && dv->req_count) HB_CUDA(cudaMemsetAsync(dv->req_count, 0, sizeof(int64_t), st));
+    return HB_OK;
+  }
+  const bool sharded = !dv && table != nullptr && table->world > 1;  // this GPU copies the remote rows
   FetchPlan f = make_fetch_plan(workspace, runs->n, row_bytes, sharded);
   if (!workspace || workspace_bytes < f.total) {
     set_error("hb_lookup_fetch_runs: workspace of %zu bytes needed, %zu given", f.total, workspace_bytes);
     return HB_ERR_WORKSPACE;
   }
-  cudaStream_t st = (cudaStream_t)stream;
-  if (mode == HB_LOOKUP_SORTED && h->sorted_stale) {
+  if (resolve && mode == HB_LOOKUP_SORTED && h->sorted_stale) {
     int rc = hb_index_build_sorted(h, stream);
     if (rc != HB_OK) return rc;
   }
@@ -631,19 +653,27 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache
   rs.stage_cap = f.stage_cap;
   rs.remote_runs = f.remote_runs;
   rs.remote_count = f.remote_count;
+  if (dv) {
+    rs.stage = dv->stage;
+    rs.stage_cap = dv->stage_cap;
+    rs.req_ids = dv->req_ids;
+    rs.req_runs = dv->req_runs;
+    rs.remote_count = reinterpret_cast<unsigned long long*>(dv->req_count);
+  }
   if (table) {
     int rc = make_shard_view(table, &rs.shards);
     if (rc != HB_OK) return rc;
     rs.rank = table->rank;
   }
-  uintptr_t bits = (uintptr_t)row_bytes | (uintptr_t)cache_rows | (uintptr_t)out_rows | (uintptr_t)backing_rows;
+  uintptr_t bits = (uintptr_t)row_bytes | (uintptr_t)cache_rows | (uintptr_t)out_rows | (uintptr_t)backing_rows |
+                   (uintptr_t)(dv ? dv->stage : nullptr);
   HB_CHECK_ARG((bits & 1) == 0, "hb_lookup_fetch_runs: rows must start at even addresses");
   const bool v16 = (bits & 15) == 0;  // shards come from cudaMalloc and hold whole rows
   const int vb = v16 ? 16 : ((bits & 3) == 0 ? 4 : 1);
   int* err = device_error_word();
   int64_t* slots = run_slots ? run_slots : f.run_slots;
-  if (sharded) HB_CUDA(cudaMemsetAsync(f.remote_count, 0, sizeof(unsigned long long), st));
-  {
+  if (resolve && rs.remote_count) HB_CUDA(cudaMemsetAsync(rs.remote_count, 0, sizeof(unsigned long long), st));
+  if (resolve) {
     int64_t blocks = ceil_div(ceil_div(runs->n, 32) * 32, kBlock);  // one lane per run, at most n runs
     if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
     const int grid = (int)(blocks < 1 ? 1 : blocks);
@@ -657,9 +687,9 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache
     }
 #undef HB_RES
   }
-  if (sharded)
+  if (resolve && sharded)
     HB_LAUNCH(runs_stage_kernel, sm_count() * 4, kBlock, 0, st, *runs, rs, row_bytes, vb);
-  if (!out_rows) return HB_OK;  // per distinct id only: slots in run_slots, remote rows staged
+  if (!expand) return HB_OK;  // per distinct id only: slots in run_slots, remote rows staged or asked for
   int64_t blocks = ceil_div(ceil_div(runs->n, 32) * 32, kBlock);
   if (blocks > (int64_t)sm_count() * 32) blocks = (int64_t)sm_count() * 32;
   const int grid = (int)(blocks < 1 ? 1 : blocks);
@@ -672,10 +702,47 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache
     else if (v16) HB_EXP(PEER, 16);                   \
     else HB_EXP(PEER, 0);                             \
   } while (0)
-  if (sharded) HB_EXP_V(true); else HB_EXP_V(false);
+  if (sharded || dv) HB_EXP_V(true); else HB_EXP_V(false);
 #undef HB_EXP_V
 #undef HB_EXP
   return HB_OK;
+}
+}  // namespace
+
+size_t hb_lookup_fetch_runs_workspace_bytes(int64_t n, int64_t row_bytes, int sharded) {
+  return make_fetch_plan(nullptr, n, row_bytes > 0 ? row_bytes : 1, sharded != 0).total;
+}
+
+int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows,
+                         const void* backing_rows, int64_t backing_num_rows, hb_peer_table_t* table,
+                         int64_t row_bytes, void* out_rows, int64_t* locs, uint8_t* found,
+                         int64_t* run_slots, int mode, void* workspace, size_t workspace_bytes,
+                         hb_stream_t stream) {
+  return fetch_runs_impl(h, runs, cache_rows, backing_rows, backing_num_rows, table, row_bytes, out_rows, locs,
+                         found, run_slots, mode, workspace, workspace_bytes, stream, nullptr, true,
+                         out_rows != nullptr);
+}
+
+int hb_runs_resolve_requests(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows,
+                             hb_peer_table_t* table, int64_t row_bytes, void* stage_rows, int64_t stage_cap,
+                             int64_t* run_slots, int64_t* req_ids, int64_t* req_runs, int64_t* req_count,
+                             int mode, void* workspace, size_t workspace_bytes, hb_stream_t stream) {
+  HB_CHECK_ARG(table && stage_rows && stage_cap > 0 && req_ids && req_runs && req_count,
+               "hb_runs_resolve_requests: null argument");
+  HB_CHECK_ARG(((uintptr_t)stage_rows & 15) == 0, "hb_runs_resolve_requests: the stage is 16-byte aligned");
+  Delivery dv{(char*)stage_rows, stage_cap, req_ids, req_runs, req_count};
+  return fetch_runs_impl(h, runs, cache_rows, nullptr, 0, table, row_bytes, nullptr, nullptr, nullptr, run_slots,
+                         mode, workspace, workspace_bytes, stream, &dv, true, false);
+}
+
+int hb_runs_expand(const hb_runs_t* runs, const void* cache_rows, const void* stage_rows, int64_t row_bytes,
+                   void* out_rows, int64_t* locs, uint8_t* found, const int64_t* run_slots, void* workspace,
+                   size_t workspace_bytes, hb_stream_t stream) {
+  HB_CHECK_ARG(out_rows != nullptr && cache_rows != nullptr, "hb_runs_expand: null argument");
+  Delivery dv{(char*)stage_rows, 0, nullptr, nullptr, nullptr};
+  return fetch_runs_impl(nullptr, runs, cache_rows, nullptr, 0, nullptr, row_bytes, out_rows, locs, found,
+                         const_cast<int64_t*>(run_slots), HB_LOOKUP_SETASSOC, workspace, workspace_bytes, stream,
+                         &dv, false, true);
 }
 
 size_t hb_runs_miss_list_workspace_bytes(int64_t n) { return compact_workspace_bytes(n); }

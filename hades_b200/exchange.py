@@ -119,10 +119,17 @@ class PeerExchange:
                 pass
             self._h = None
 
-    def push(self, ids, rows, cnt=None, n_dev=None, sent_counts=None) -> int:
-        """Bucket by owner and store into the owners' slabs; returns the parity to read."""
+    def push_workspace_bytes(self, n: int) -> int:
+        return self.lib.hb_a2a_push_workspace_bytes(int(n), self.world)
+
+    def push(self, ids, rows, cnt=None, n_dev=None, sent_counts=None, ws=None) -> int:
+        """Bucket by owner and store into the owners' slabs; returns the parity to read.  ws: scratch
+        of ``push_workspace_bytes(n)`` bytes (default: the library-wide scratch of the device, which
+        is only safe on the stream that everything else using it runs on)."""
         n = ids.numel()
-        ws = _lib.workspace(self.lib.hb_a2a_push_workspace_bytes(n, self.world))
+        need = self.lib.hb_a2a_push_workspace_bytes(n, self.world)
+        if ws is None or ws.numel() < need:
+            ws = _lib.workspace(need)
         parity = C.c_int(0)
         _lib.check(self.lib.hb_a2a_push(self._h, ids.data_ptr(), rows.data_ptr(), _lib.ptr(cnt), n,
                                         _lib.ptr(n_dev), _lib.ptr(sent_counts), C.byref(parity),

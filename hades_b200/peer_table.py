@@ -104,6 +104,15 @@ class PeerTable:
                                                  out.data_ptr(), _lib.stream_ptr()))
         return out
 
+    def serve(self, stages: "PeerTable", req_ids: torch.Tensor, req_rows: torch.Tensor, req_counts: torch.Tensor,
+              seg_cap: int) -> None:
+        """The owner's half of a forward fetch in which the owners deliver (``hb_fetch_serve``):
+        requests as they arrived through a ``PeerExchange`` (segment s from rank s, req_counts[s]
+        valid): the row of req_ids[k] in this rank's shard goes into row req_rows[k] of rank s's
+        stage.  stages: a PeerTable whose local shard on every rank is that rank's stage."""
+        _lib.check(self.lib.hb_fetch_serve(self._h, stages.handle, req_ids.data_ptr(), req_rows.data_ptr(),
+                                           req_counts.data_ptr(), int(seg_cap), _lib.stream_ptr()))
+
     def lookup_fetch(self, index, ids: torch.Tensor, cache_rows: torch.Tensor, out_rows: torch.Tensor | None = None,
                      mode: int | None = None):
         """(rows, locs, found) as ``EmbCacheLib.cudaLookupFetch``, misses from the owners' shards."""

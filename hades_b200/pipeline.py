@@ -61,7 +61,8 @@ class EmbeddingPath:
                  lookup_mode: int = E.LOOKUP_SETASSOC, mover: int = E.MOVER_AUTO,
                  touch_lru: bool = True, group=None, peer_exchange=None, flush_exchange=None,
                  insert_misses: bool = True, miss_cap: int = 1 << 17, flush_cap: int = 1 << 19,
-                 want_locs: bool = True, overlap_fetch: bool = False):
+                 want_locs: bool = True, overlap_fetch: bool = False, request_exchange=None,
+                 fetch_stages=None):
         """table: backing rows for cache misses, [num_nodes, dim] fp32 on this GPU; None when the
         optimiser's shard is a ``PeerTable`` (misses then read the owners' shards).
         class_table: int8 per node, HOT or COLD.  optimizer: SparseAdam / SparseAdagrad on this
@@ -74,6 +75,10 @@ class EmbeddingPath:
         itself uses the slot of every run).  overlap_fetch: ``step`` runs the fetch of a batch beside
         the aggregation of the same batch's gradients (both need only the sort)."""
         self.overlap_fetch = bool(overlap_fetch)
+        # several GPUs, owners deliver the remote rows of the forward fetch: the exchange that
+        # carries the requests and the stages (one per rank, mapped by all) the owners store into
+        self.px_req, self.fetch_stages = request_exchange, fetch_stages
+        self._req = None
         self.table, self.class_table, self.cold, self.opt = table, class_table, cold, optimizer
         self.rank, self.world = rank, world
         self.flush_every, self.id_bits = flush_every, id_bits
@@ -99,7 +104,7 @@ class EmbeddingPath:
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._side = None
         self._side_done, self._side_refs = None, []
-        self._runs_ws, self._side_ws, self._fetch_ws = None, None, None
+        self._runs_ws, self._side_ws, self._fetch_ws, self._req_ws = None, None, None, None
         self._last = None  # (BatchRuns, locs) of the last forward pass
 
     # ---- streams ---------------------------------------------------------------------------
@@ -155,18 +160,14 @@ class EmbeddingPath:
             # by NVLink round trips and hides behind that HBM-bound work.  The main stream joins
             # before it returns the rows (``_join_side``).
             with self._on_side():
-                rows, locs, found = E.cudaLookupFetchRuns(self.cold.index, runs, self.cold.emb, self.table,
-                                                          self.shared, out_rows, self.lookup_mode,
-                                                          want_locs=self.want_locs, ws=fetch_ws)
+                rows, locs, found = self._fetch(runs, out_rows, fetch_ws)
                 self._after_fetch(runs, rows, n, lib)
             if not torch.cuda.is_current_stream_capturing():
                 for t in (rows, locs, found):  # allocated under the side stream, read on this one
                     if t is not None:
                         t.record_stream(torch.cuda.current_stream())
         else:
-            rows, locs, found = E.cudaLookupFetchRuns(self.cold.index, runs, self.cold.emb, self.table, self.shared,
-                                                      out_rows, self.lookup_mode, want_locs=self.want_locs,
-                                                      ws=fetch_ws)
+            rows, locs, found = self._fetch(runs, out_rows, fetch_ws)
             if n and (self.touch_lru or self.insert_misses):
                 # Off the main stream, which goes on to whatever uses the rows: the LRU ageing of
                 # this lookup (cache.h:101), then the uncached cold ids and their rows go to the
@@ -178,6 +179,33 @@ class EmbeddingPath:
                     self._join_side()
         self._last = (runs, locs)
         return rows, locs, found
+
+    def _fetch(self, runs, out_rows, fetch_ws):
+        """Lookup per distinct id + rows to the batch positions, on the current stream."""
+        if self.px_req is None or self.world == 1 or runs.n == 0:
+            return E.cudaLookupFetchRuns(self.cold.index, runs, self.cold.emb, self.table, self.shared, out_rows,
+                                         self.lookup_mode, want_locs=self.want_locs, ws=fetch_ws)
+        # The owners deliver: this GPU lists the remote runs, the (id, run) requests travel to the
+        # owners like gradient rows do, every owner stores the rows it was asked for into the
+        # requesters' stages, and the expansion reads local memory only.  Two fences: requests
+        # complete before they are served, rows complete before they are read.
+        n = runs.n
+        if self._req is None or self._req[0].numel() < n:
+            dev = self.device
+            self._req = (torch.empty(n, dtype=torch.int64, device=dev), torch.empty(n, dtype=torch.int64, device=dev),
+                         torch.zeros(1, dtype=torch.int64, device=dev),
+                         torch.zeros((n, self.px_req.dim), dtype=torch.float32, device=dev))
+        req_ids, req_runs, req_n, filler = self._req
+        stage = self.fetch_stages.weight
+        E.cudaRunsResolveRequests(self.cold.index, runs, self.cold.emb, self.shared, stage, req_ids, req_runs, req_n,
+                                  self.lookup_mode, ws=fetch_ws)
+        parity = self.px_req.push(req_ids[:n], filler[:n], req_runs[:n], req_n,
+                                  ws=self._ws("_req_ws", self.px_req.push_workspace_bytes(n)))
+        self.px_req.fence()
+        r_ids, _, r_runs, seg_counts = self.px_req.received(parity)
+        self.shared.serve(self.fetch_stages, r_ids, r_runs, seg_counts, self.px_req.cap)
+        self.px_req.fence()
+        return E.cudaRunsExpand(runs, self.cold.emb, stage, out_rows, want_locs=self.want_locs)
 
     def _after_fetch(self, runs, rows, n: int, lib) -> None:
         """On the side stream: LRU ageing of the lookup, cold misses into the cache."""
@@ -461,7 +489,7 @@ class EmbeddingPath:
         is back: all ranks call this (a collective; host barriers inside), then go on stepping."""
         import torch.distributed as dist
 
-        for px in (self.px, self.px_flush):
+        for px in (self.px, self.px_flush, self.px_req):
             if px is not None:
                 px.reset()
         self._g_next = getattr(self, "_g_area0", 0) if len(self._graphs) == 2 else 0
@@ -476,10 +504,10 @@ class EmbeddingPath:
         every rank calls it, after its last step.  The path cannot step afterwards."""
         torch.cuda.synchronize()
         self._graphs, self._split, self._flush_graphs = [], None, []
-        for obj in (self.px, self.px_flush, self.shared):
+        for obj in (self.px, self.px_flush, self.px_req, self.fetch_stages, self.shared):
             if obj is not None:
                 obj.close()
-        self.px = self.px_flush = None
+        self.px = self.px_flush = self.px_req = self.fetch_stages = None
 
     # ---- save / resume ---------------------------------------------------------------------------
     def state_dict(self) -> dict:
@@ -557,8 +585,14 @@ def assemble_path(name: str, table: torch.Tensor, class_table: torch.Tensor, cac
                   generator=None, threshold: torch.Tensor | None = None, default_threshold: int = 0,
                   cnt_threshold: int = 16, insert_misses: bool = True, flush_cap: int = 1 << 19,
                   miss_cap: int = 1 << 17, state_budget_bytes: int | None = None,
-                  hotness: torch.Tensor | None = None) -> EmbeddingPath:
+                  hotness: torch.Tensor | None = None, remote_fetch: str = "auto",
+                  fetch_stage_rows: int = 0) -> EmbeddingPath:
     """Cold cache filled with `cache_ids` (rows from `table`), optimiser shard, exchange.
+    remote_fetch: who brings the rows of other GPUs' shards in the forward fetch: "pull" (this GPU
+    reads them, once per distinct id), "deliver" (the owners store them into this GPU's stage of
+    fetch_stage_rows rows; needs the peer-memory exchange with the device fence), "auto": deliver
+    with more than two GPUs (scattered peer loads collapse once a GPU reads several peers at a
+    time while all of them read it), pull with two.
     state_budget_bytes / hotness: see ``SparseAdam`` (state tiered between HBM and pinned host
     memory when it does not fit the budget; hotness per node of the whole table).
     threshold: int32 per-node flush period (``cold_cache.flush_thresholds`` of the presampled
@@ -604,9 +638,20 @@ def assemble_path(name: str, table: torch.Tensor, class_table: torch.Tensor, cac
     else:
         opt = SparseAdagrad(shard, lr=0.01)
     id_bits = max(int(rows_total).bit_length() + 1, 8)
+    px_req = stages = None
+    deliver = remote_fetch == "deliver" or (remote_fetch == "auto" and world > 2)
+    if deliver and share and px is not None and px.fence_kind == "device" and fetch_stage_rows > 0:
+        from .peer_table import PeerTable
+
+        # a requester asks one owner for at most the rows that owner has, and for at most one per stage row
+        req_cap = int(min(fetch_stage_rows, -(-rows_total // world)))
+        px_req = _peer_exchange(rank, world, req_cap, 4, device, group, "device")
+        if px_req is not None:
+            stages = PeerTable(world * int(fetch_stage_rows), dim, rank, world, dtype=torch.float32, device=device,
+                               group=group)
     path = EmbeddingPath(table, class_table, cold, opt, rank, world, flush_every, id_bits,
                          lookup_mode, mover, touch_lru, group, px, px_flush, insert_misses=insert_misses,
-                         miss_cap=miss_cap, flush_cap=flush_cap)
+                         miss_cap=miss_cap, flush_cap=flush_cap, request_exchange=px_req, fetch_stages=stages)
     path.cache_fill_ids = cache_ids  # what the cold cache was filled with, in insertion order
     return path
 
@@ -617,7 +662,8 @@ def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str =
                seed_config: int | None = None, group=None, exchange: str = "push",
                hotness: torch.Tensor | None = None, hot_threshold: float | None = None,
                cnt_threshold: int = 16, insert_misses: bool = True, flush_cap: int = 1 << 19,
-               miss_cap: int = 1 << 17, state_budget_bytes: int | None = None) -> EmbeddingPath:
+               miss_cap: int = 1 << 17, state_budget_bytes: int | None = None,
+               remote_fetch: str = "auto", fetch_stage_rows: int | None = None) -> EmbeddingPath:
     """Build the state of one trainer for a cached-fetch configuration (``synth.CacheFetchConfig``):
     backing table, class table, cold cache filled with the most popular COLD ids, optimiser shard.
 
@@ -664,19 +710,24 @@ def build_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str =
     return assemble_path(cfg.name, table, class_table, cache_ids, max(cap, 1), rank, world, device, optimizer,
                          cfg.flush_every, lookup_mode, mover, touch_lru, group, exchange,
                          cfg.cache_entries, table_dtype, cfg.table_sigma, gen, threshold, default_threshold,
-                         cnt_threshold, insert_misses, flush_cap, miss_cap, state_budget_bytes, hotness)
+                         cnt_threshold, insert_misses, flush_cap, miss_cap, state_budget_bytes, hotness,
+                         remote_fetch, cfg.batch if fetch_stage_rows is None else fetch_stage_rows)
 
 
 def build_rmat_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: str = "adam",
                     lookup_mode: int = E.LOOKUP_SETASSOC, mover: int = E.MOVER_AUTO,
                     touch_lru: bool = True, group=None, exchange: str = "push",
-                    insert_misses: bool = True) -> EmbeddingPath:
+                    insert_misses: bool = True, remote_fetch: str = "auto") -> EmbeddingPath:
     """State of one trainer for the sampled-GraphSAGE configuration (``synth.RmatConfig``).
     Under R-MAT a vertex is the more popular the fewer one-bits its id has, so the HOT class
     is ``popcount(id) <= cfg.hot_popcount`` and the cold cache starts with the most popular
     cold vertices (popcount hot_popcount+1, +2, ... in id order)."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
     n, dim = cfg.num_nodes, cfg.dim
+    frontier, layer = cfg.seeds, cfg.seeds  # ids one step fetches: seeds + 1-hop + 2-hop samples
+    for f in cfg.fanout:
+        layer *= f
+        frontier += layer
     need = n * dim * 4 * (1 if world > 1 else 0) + (n // world + 1) * dim * 4 * (3 if optimizer == "adam" else 2)
     need += 2 * (cfg.cache_entries + 8) * dim * 4 + n * 2
     total = torch.cuda.get_device_properties(device).total_memory
@@ -707,4 +758,5 @@ def build_rmat_path(cfg, rank: int = 0, world: int = 1, device=None, optimizer: 
     del pc, hot
     return assemble_path(cfg.name, table, class_table, cache_ids, cap, rank, world, device, optimizer,
                          cfg.flush_every, lookup_mode, mover, touch_lru, group, exchange,
-                         cfg.cache_entries, torch.float32, cfg.table_sigma, gen, insert_misses=insert_misses)
+                         cfg.cache_entries, torch.float32, cfg.table_sigma, gen, insert_misses=insert_misses,
+                         remote_fetch=remote_fetch, fetch_stage_rows=frontier)

@@ -413,6 +413,31 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs /* host */, const 
                          int64_t* run_slots /* nullable */, int mode, void* workspace,
                          size_t workspace_bytes, hb_stream_t stream);
 
+/* The same forward fetch with the OWNERS delivering the remote rows (several GPUs; on this pool
+ * scattered peer loads of rows collapse to a few tens of GB/s once more than one peer is read,
+ * while peer stores run at the links' bandwidth).  Three calls around one exchange:
+ *   hb_runs_resolve_requests  the first launch of hb_lookup_fetch_runs; a run whose row lives on
+ *       another GPU is not copied but listed: req_ids[k] = its id, req_runs[k] = the run u, which
+ *       is also the row of stage_rows the owner is to fill (k < *req_count, any order; the
+ *       arrays hold runs->n entries).  Runs at and beyond stage_cap are read from the owner
+ *       directly by the last launch.  stage_rows: this GPU's stage, [stage_cap][row_bytes], that
+ *       the peers have mapped (the local shard of an hb_peer_table created for the purpose).
+ *   (the caller sends the requests to their owners, id % world: hb_a2a_push with req_runs in the
+ *       cnt field, hb_a2a_fence; every owner answers with hb_fetch_serve; hb_a2a_fence)
+ *   hb_runs_expand            the last launch: rows to their batch positions, with locs / found.
+ * workspace: hb_lookup_fetch_runs_workspace_bytes(n, row_bytes, 0), the same for both calls and
+ * untouched in between.  cache_rows / stage_rows of hb_runs_expand: what the resolve call was
+ * given (alignment decides the width of the copies). */
+int hb_runs_resolve_requests(hb_index_t* h, const hb_runs_t* runs /* host */, const void* cache_rows,
+                             hb_peer_table_t* table, int64_t row_bytes, void* stage_rows, int64_t stage_cap,
+                             int64_t* run_slots /* nullable */, int64_t* req_ids, int64_t* req_runs,
+                             int64_t* req_count, int mode, void* workspace, size_t workspace_bytes,
+                             hb_stream_t stream);
+int hb_runs_expand(const hb_runs_t* runs /* host */, const void* cache_rows, const void* stage_rows,
+                   int64_t row_bytes, void* out_rows, int64_t* locs /* nullable */,
+                   uint8_t* found /* nullable */, const int64_t* run_slots /* nullable: the workspace's */,
+                   void* workspace, size_t workspace_bytes, hb_stream_t stream);
+
 /* The distinct ids of class want_class (< 0: any) that the lookup missed (locs[position]
  * < 0; locs_kind: locs holds a slot per batch position (0), per sorted entry (1) or per
  * run (2, the run_slots of hb_lookup_fetch_runs)), ascending, at
@@ -632,6 +657,15 @@ int hb_peer_table_gather(hb_peer_table_t* t, const int64_t* ids, int64_t n,
  * when the index holds ids[i], else the authoritative row.  The one pass that
  * python/EmbCache/dist_emb.py:184-243 makes of lookup, cache fetch and the
  * DistTensor pull. */
+/* The owner's half of hb_runs_resolve_requests: for every requester s (segment s of seg_cap
+ * entries, req_counts[s] of them valid: the receive view of the hb_a2a exchange that carried the
+ * requests) the row of req_ids[k] in THIS rank's shard of `table` is stored into row req_rows[k] of
+ * rank s's stage.  stages: an hb_peer_table whose local shard on every rank is that rank's stage
+ * (num_rows = world x rows of one stage).  A request for a row this rank does not own, or beyond
+ * the stage, is skipped and raises HB_ERR_INVALID in the device status word. */
+int hb_fetch_serve(hb_peer_table_t* table, hb_peer_table_t* stages, const int64_t* req_ids,
+                   const int64_t* req_rows, const int64_t* req_counts, int64_t seg_cap, hb_stream_t stream);
+
 int hb_lookup_fetch_sharded(hb_index_t* h, const int64_t* ids, int64_t n, const void* cache_rows,
                             hb_peer_table_t* table, void* out_rows, int64_t* locs /* nullable */,
                             uint8_t* found /* nullable */, int mode, hb_stream_t stream);

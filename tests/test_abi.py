@@ -62,8 +62,8 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
 
 
 def test_reference_side_bridge_compiles():
-    """hades_b200/bridge/hades_b200_bridge.cc (the translation unit INTEGRATION.md gives a
-    maintainer of the reference) against the torch headers and include/hades_b200.h."""
+    """hades_b200/bridge/hades_b200_bridge.cc (the translation unit a maintainer of the reference
+    adds beside src/pybind.cc) compiles against the torch headers and include/hades_b200.h."""
     import shutil
     import subprocess
     import sysconfig

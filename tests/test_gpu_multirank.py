@@ -79,7 +79,10 @@ def _worker(rank, port, exchange):
     path = pipeline.build_path(cfg, rank, WORLD, hot_fraction=0.02,
                                exchange={"nccl": "nccl", "push": "push", "push_graph": "push",
                                          "push_overlap": "push", "push_overlap_graph": "push",
-                                         "push_nccl_fence_graph": "push_nccl_fence"}[exchange])
+                                         "push_deliver": "push", "push_deliver_overlap_graph": "push",
+                                         "push_nccl_fence_graph": "push_nccl_fence"}[exchange],
+                               remote_fetch="deliver" if "deliver" in exchange else "pull")
+    assert (path.px_req is not None) == ("deliver" in exchange)
     path.overlap_fetch = "overlap" in exchange
     assert (path.px is not None) == exchange.startswith("push")
     assert (path.px_flush is not None) == exchange.startswith("push")
@@ -121,13 +124,15 @@ def _worker(rank, port, exchange):
 
 
 @pytest.mark.parametrize("exchange", ["nccl", "push", "push_graph", "push_nccl_fence_graph", "push_overlap",
-                                      "push_overlap_graph"])
+                                      "push_overlap_graph", "push_deliver", "push_deliver_overlap_graph"])
 def test_two_ranks(exchange):
     """exchange = "nccl": ragged all_to_all_single; "push": the fused pack+push kernel over
     peer memory with the device-side fence (plain stores, NVLS off); "push_graph": the same
     replayed from two whole-step CUDA graphs; "push_nccl_fence_graph": NCCL all-reduce as the
     fence, graphs around the eagerly launched exchange; "..._overlap": the forward fetch of a step
-    (remote rows included) on the side stream beside the aggregation of the same step."""
+    (remote rows included) on the side stream beside the aggregation of the same step;
+    "..._deliver": the owners store the remote rows of the forward fetch into the requester's stage
+    (requests through a third exchange, two fences) instead of the requester reading them."""
     if not torch.cuda.is_available() or torch.cuda.device_count() < WORLD:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
