@@ -815,17 +815,17 @@ def cudaLookupFetchRuns(index: IndexCache, runs: BatchRuns, cache_rows, backing_
 
 
 def cudaRunsResolveRequests(index: IndexCache, runs: BatchRuns, cache_rows, peer_table, stage_rows: torch.Tensor,
-                            req_ids: torch.Tensor, req_runs: torch.Tensor, req_count: torch.Tensor,
-                            mode: int | None = None, ws: torch.Tensor | None = None) -> None:
+                            requests, mode: int | None = None, ws: torch.Tensor | None = None) -> int:
     """First third of the forward fetch whose remote rows the OWNERS deliver
-    (``hb_runs_resolve_requests``): index probe per distinct id, slots into ``runs.slots``, and the
-    list of remote runs: req_ids[k] the id, req_runs[k] the run = the row of ``stage_rows`` (this
-    GPU's stage, mapped by the peers) that the owner fills; k < req_count[0].  The caller carries
-    the requests to the owners (``PeerExchange.push`` with req_runs as the counts), the owners
-    answer with ``PeerTable.serve``, then ``cudaRunsExpand`` finishes."""
+    (``hb_runs_resolve_requests``): index probe per distinct id, slots into ``runs.slots``, and for
+    every run whose row lives on another GPU the request (id, run) stored straight into the owner's
+    receive area of ``requests`` (an ``exchange.PeerExchange``); the run is also the row of
+    ``stage_rows`` (this GPU's stage, mapped by the peers) that the owner fills.  Returns the
+    receive area (parity) filled.  Then: ``requests.fence()``, every rank serves what it was asked
+    for (``PeerTable.serve`` on ``requests.received(parity)``), ``requests.fence()``,
+    ``cudaRunsExpand``."""
     n = runs.n
     dev = runs.ids.device
-    _check(req_ids.numel() >= n and req_runs.numel() >= n, "request lists hold one entry per id of the batch")
     if runs.slots is None:
         runs.slots = torch.empty(max(n, 1), dtype=torch.int64, device=dev)
     lib = _lib.load()
@@ -834,12 +834,14 @@ def cudaRunsResolveRequests(index: IndexCache, runs: BatchRuns, cache_rows, peer
         runs.fetch_ws = ws
     elif runs.fetch_ws is None or runs.fetch_ws.numel() < need:
         runs.fetch_ws = torch.empty(need, dtype=torch.uint8, device=dev)
+    parity = C.c_int(0)
     _lib.check(lib.hb_runs_resolve_requests(index.handle, C.byref(runs.desc), _dev_ptr(cache_rows, "cache_rows"),
                                             peer_table.handle, _row_bytes(cache_rows), stage_rows.data_ptr(),
-                                            stage_rows.size(0), runs.slots.data_ptr(), req_ids.data_ptr(),
-                                            req_runs.data_ptr(), req_count.data_ptr(),
-                                            index.lookup_mode if mode is None else mode, runs.fetch_ws.data_ptr(),
-                                            runs.fetch_ws.numel(), _lib.stream_ptr()))
+                                            stage_rows.size(0), runs.slots.data_ptr(), requests.handle,
+                                            C.byref(parity), index.lookup_mode if mode is None else mode,
+                                            runs.fetch_ws.data_ptr(), runs.fetch_ws.numel(), _lib.stream_ptr()))
+    requests.next_parity = parity.value ^ 1
+    return parity.value
 
 
 def cudaRunsExpand(runs: BatchRuns, cache_rows, stage_rows, out_rows=None, want_locs: bool = True):

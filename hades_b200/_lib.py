@@ -79,7 +79,7 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_segsum_runs_f32": (_int, [_p, _p, _p, _i64, _int, _p, _p, _p, _p, _sz, _p]),
     "hb_lookup_fetch_runs_workspace_bytes": (_sz, [_i64, _i64, _int]),
     "hb_lookup_fetch_runs": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p, _p, _p, _int, _p, _sz, _p]),
-    "hb_runs_resolve_requests": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p, _p, _p, _int, _p, _sz, _p]),
+    "hb_runs_resolve_requests": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p, _p, _int, _p, _sz, _p]),
     "hb_runs_expand": (_int, [_p, _p, _p, _i64, _p, _p, _p, _p, _p, _sz, _p]),
     "hb_runs_miss_list_workspace_bytes": (_sz, [_i64]),
     "hb_runs_miss_list": (_int, [_p, _p, _int, _int, _i64, _p, _p, _p, _p, _sz, _p]),

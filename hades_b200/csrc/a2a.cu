@@ -20,32 +20,12 @@
 // GPUs, so the waiting kernels do run at the same time.)
 #include <cstring>
 
+#include "a2a.cuh"
 #include "partition_core.cuh"
 
 namespace hb {
 int* device_error_word();  // runtime.cu
 }
-
-struct hb_a2a {
-  int rank, world;
-  int64_t cap;        // rows per source slab
-  int64_t row_bytes;
-  size_t area_bytes;
-  char* local[2];            // this rank's receive areas
-  char* peer[2][64];         // peer[p][r] = rank r's area of parity p in this process
-  bool opened[64];
-  // device copy of the destination pointers for the push kernel
-  struct Dest {
-    unsigned long long* flags[64];  // parity-0 area of every rank
-    int64_t* counts[64];
-    int64_t* ids[64];
-    int64_t* cnt[64];
-    char* rows[64];
-  };
-  Dest* dest_dev[2];
-  unsigned long long* epoch_dev;  // number of fences done, on the device (graph replay safe)
-  int parity;  // parity of the NEXT push
-};
 
 namespace hb {
 namespace {
@@ -98,6 +78,17 @@ __global__ void push_counts_kernel(PartitionPlan p, const hb_a2a::Dest* dest, in
   __threadfence_system();
 }
 
+// the same for a sender that stored its records itself (a2a_direct_publish)
+__global__ void publish_counts_kernel(const unsigned long long* __restrict__ counts, const hb_a2a::Dest* dest,
+                                      int rank, int world, int64_t cap) {
+  const int b = threadIdx.x;
+  if (b >= world) return;
+  int64_t c = (int64_t)counts[b];
+  if (c > cap) c = cap;
+  dest->counts[b][rank] = c;
+  __threadfence_system();
+}
+
 // Poll a flag until it reaches `value`, at most about a second; false = gave up.
 __device__ __forceinline__ bool wait_flag_bounded(const volatile unsigned long long* flag,
                                                   unsigned long long value) {
@@ -129,6 +120,24 @@ __global__ void a2a_fence_kernel(const hb_a2a::Dest* dest, const unsigned long l
 }
 
 }  // namespace
+}  // namespace hb
+
+namespace hb {
+
+int a2a_direct_begin(hb_a2a* a, const hb_a2a::Dest** dest, int* parity) {
+  HB_CHECK_ARG(a && dest && parity, "a2a_direct_begin: null argument");
+  *parity = a->parity;
+  *dest = a->dest_dev[a->parity];
+  a->parity ^= 1;
+  return HB_OK;
+}
+
+int a2a_direct_publish(hb_a2a* a, int parity, const unsigned long long* counts_dev, cudaStream_t st) {
+  HB_CHECK_ARG(a && counts_dev && (parity == 0 || parity == 1), "a2a_direct_publish: bad argument");
+  HB_LAUNCH(publish_counts_kernel, 1, 64, 0, st, counts_dev, a->dest_dev[parity], a->rank, a->world, a->cap);
+  return HB_OK;
+}
+
 }  // namespace hb
 
 using namespace hb;

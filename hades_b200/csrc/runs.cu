@@ -14,6 +14,7 @@
 // The backward aggregation (segsum.cu) and the LRU ageing (index.cu) take the same runs.
 #include <cub/device/device_radix_sort.cuh>
 
+#include "a2a.cuh"
 #include "compact.cuh"
 #include "index.cuh"
 #include "runs.cuh"
@@ -186,9 +187,12 @@ struct RowSource {
   int64_t stage_cap;
   int32_t* remote_runs;            // runs whose row STAGE has to copy, in any order (PEER)
   unsigned long long* remote_count;  // [1], zero before RESOLVE
-  // when the OWNERS deliver the remote rows (hb_runs_resolve_requests): what to ask them for
-  int64_t* req_ids;                // [n] id of a remote run
-  int64_t* req_runs;               // [n] the run, i.e. the row of this GPU's stage the owner fills
+  // when the OWNERS deliver the remote rows (hb_runs_resolve_requests): a remote run becomes the
+  // request (id, run) -- the run is also the row of this GPU's stage that the owner fills --
+  // stored straight into this rank's slab of the owner's receive area
+  const hb_a2a::Dest* req_dest;
+  unsigned long long* req_counts;  // [world] requests so far per owner, zero before RESOLVE
+  int64_t req_cap;                 // requests one owner's slab takes from this rank
 };
 
 template <bool PEER>
@@ -247,19 +251,29 @@ __global__ void __launch_bounds__(kBlock) runs_resolve_kernel(
       // copy is bound by round trips over NVLink, which a kernel that also probes the index
       // cannot keep enough of in flight)
       const unsigned todo = __ballot_sync(0xffffffffu, remote != nullptr);
-      if (todo) {
+      if (todo && rs.req_dest) {
+        if (remote) {
+          // one counter per owner: the lanes that ask the same owner take consecutive places
+          const int owner = (int)mod_nonneg(id, rs.shards.world);
+          const unsigned same = __match_any_sync(todo, owner);
+          const int leader = __ffs(same) - 1;
+          unsigned long long at = 0;
+          if (lane == leader) at = atomicAdd(rs.req_counts + owner, (unsigned long long)__popc(same));
+          at = __shfl_sync(same, at, leader);
+          const int64_t k = (int64_t)at + __popc(same & ((1u << lane) - 1u));
+          if (k < rs.req_cap) {
+            const int64_t slot = (int64_t)rs.rank * rs.req_cap + k;  // my slab in the owner's area
+            rs.req_dest->ids[owner][slot] = id;
+            rs.req_dest->cnt[owner][slot] = u;
+          } else {
+            atomicExch(err, HB_ERR_CAPACITY);  // the row is not delivered: the stage keeps what it held
+          }
+        }
+      } else if (todo) {
         unsigned long long at = 0;
         if (lane == 0) at = atomicAdd(rs.remote_count, (unsigned long long)__popc(todo));
         at = __shfl_sync(0xffffffffu, at, 0);
-        if (remote) {
-          const unsigned long long k = at + __popc(todo & ((1u << lane) - 1u));
-          if (rs.req_ids) {
-            rs.req_ids[k] = id;
-            rs.req_runs[k] = u;
-          } else {
-            rs.remote_runs[k] = (int32_t)u;
-          }
-        }
+        if (remote) rs.remote_runs[at + __popc(todo & ((1u << lane) - 1u))] = (int32_t)u;
       }
     }
   }
@@ -584,6 +598,7 @@ struct FetchPlan {
   int64_t stage_cap;
   int32_t* remote_runs;
   unsigned long long* remote_count;
+  unsigned long long* req_counts;  // [64]
   size_t total;
 };
 constexpr int64_t kStageMaxBytes = (int64_t)1 << 30;  // at most 1 GiB of staged remote rows
@@ -594,6 +609,7 @@ FetchPlan make_fetch_plan(void* ws, int64_t n, int64_t row_bytes, bool sharded) 
   const int64_t m = n > 0 ? n : 1;
   f.run_src = cv.take<unsigned long long>(m);
   f.run_slots = cv.take<int64_t>(m);
+  f.req_counts = cv.take<unsigned long long>(64);
   f.stage_cap = 0;
   f.stage = nullptr;
   f.remote_runs = nullptr;
@@ -613,7 +629,8 @@ FetchPlan make_fetch_plan(void* ws, int64_t n, int64_t row_bytes, bool sharded) 
 struct Delivery {
   char* stage;
   int64_t stage_cap;
-  int64_t *req_ids, *req_runs, *req_count;
+  hb_a2a* requests;  // the exchange that carries the requests (null: expansion only)
+  int* parity_out;   // which of its receive areas this call filled
 };
 
 int fetch_runs_impl(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows, const void* backing_rows,
@@ -631,8 +648,22 @@ int fetch_runs_impl(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows
   HB_CHECK_ARG(!table || table->row_bytes == row_bytes, "hb_lookup_fetch_runs: row size differs from the table's");
   HB_CHECK_ARG(!backing_rows || backing_num_rows > 0, "hb_lookup_fetch_runs: a backing table needs its row count");
   cudaStream_t st = (cudaStream_t)stream;
+  FetchPlan f0 = make_fetch_plan(workspace, runs->n, row_bytes, false);
+  if (resolve && dv && dv->requests) {
+    // also with an empty batch: the owners read this rank's counts after the fence
+    if (!workspace || workspace_bytes < f0.total) {
+      set_error("hb_runs_resolve_requests: workspace of %zu bytes needed, %zu given", f0.total, workspace_bytes);
+      return HB_ERR_WORKSPACE;
+    }
+    HB_CUDA(cudaMemsetAsync(f0.req_counts, 0, 64 * sizeof(unsigned long long), st));
+  }
   if (runs->n == 0) {
-    if (dv && dv->req_count) HB_CUDA(cudaMemsetAsync(dv->req_count, 0, sizeof(int64_t), st));
+    if (resolve && dv && dv->requests) {
+      const hb_a2a::Dest* dest;
+      int rc = a2a_direct_begin(dv->requests, &dest, dv->parity_out);
+      if (rc != HB_OK) return rc;
+      return a2a_direct_publish(dv->requests, *dv->parity_out, f0.req_counts, st);
+    }
     return HB_OK;
   }
   const bool sharded = !dv && table != nullptr && table->world > 1;  // this GPU copies the remote rows
@@ -656,9 +687,14 @@ int fetch_runs_impl(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows
   if (dv) {
     rs.stage = dv->stage;
     rs.stage_cap = dv->stage_cap;
-    rs.req_ids = dv->req_ids;
-    rs.req_runs = dv->req_runs;
-    rs.remote_count = reinterpret_cast<unsigned long long*>(dv->req_count);
+    if (resolve && dv->requests) {
+      HB_CHECK_ARG(dv->requests->world == table->world && dv->requests->rank == table->rank,
+                   "hb_runs_resolve_requests: the exchange and the table belong to different groups");
+      int rc = a2a_direct_begin(dv->requests, &rs.req_dest, dv->parity_out);
+      if (rc != HB_OK) return rc;
+      rs.req_counts = f.req_counts;
+      rs.req_cap = dv->requests->cap;
+    }
   }
   if (table) {
     int rc = make_shard_view(table, &rs.shards);
@@ -672,7 +708,7 @@ int fetch_runs_impl(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows
   const int vb = v16 ? 16 : ((bits & 3) == 0 ? 4 : 1);
   int* err = device_error_word();
   int64_t* slots = run_slots ? run_slots : f.run_slots;
-  if (resolve && rs.remote_count) HB_CUDA(cudaMemsetAsync(rs.remote_count, 0, sizeof(unsigned long long), st));
+  if (resolve && sharded) HB_CUDA(cudaMemsetAsync(rs.remote_count, 0, sizeof(unsigned long long), st));
   if (resolve) {
     int64_t blocks = ceil_div(ceil_div(runs->n, 32) * 32, kBlock);  // one lane per run, at most n runs
     if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
@@ -689,6 +725,10 @@ int fetch_runs_impl(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows
   }
   if (resolve && sharded)
     HB_LAUNCH(runs_stage_kernel, sm_count() * 4, kBlock, 0, st, *runs, rs, row_bytes, vb);
+  if (resolve && dv && dv->requests) {
+    int rc = a2a_direct_publish(dv->requests, *dv->parity_out, f.req_counts, st);
+    if (rc != HB_OK) return rc;
+  }
   if (!expand) return HB_OK;  // per distinct id only: slots in run_slots, remote rows staged or asked for
   int64_t blocks = ceil_div(ceil_div(runs->n, 32) * 32, kBlock);
   if (blocks > (int64_t)sm_count() * 32) blocks = (int64_t)sm_count() * 32;
@@ -725,12 +765,12 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs, const void* cache
 
 int hb_runs_resolve_requests(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows,
                              hb_peer_table_t* table, int64_t row_bytes, void* stage_rows, int64_t stage_cap,
-                             int64_t* run_slots, int64_t* req_ids, int64_t* req_runs, int64_t* req_count,
-                             int mode, void* workspace, size_t workspace_bytes, hb_stream_t stream) {
-  HB_CHECK_ARG(table && stage_rows && stage_cap > 0 && req_ids && req_runs && req_count,
+                             int64_t* run_slots, hb_a2a_t* requests, int* parity_out, int mode, void* workspace,
+                             size_t workspace_bytes, hb_stream_t stream) {
+  HB_CHECK_ARG(table && stage_rows && stage_cap > 0 && requests && parity_out,
                "hb_runs_resolve_requests: null argument");
   HB_CHECK_ARG(((uintptr_t)stage_rows & 15) == 0, "hb_runs_resolve_requests: the stage is 16-byte aligned");
-  Delivery dv{(char*)stage_rows, stage_cap, req_ids, req_runs, req_count};
+  Delivery dv{(char*)stage_rows, stage_cap, requests, parity_out};
   return fetch_runs_impl(h, runs, cache_rows, nullptr, 0, table, row_bytes, nullptr, nullptr, nullptr, run_slots,
                          mode, workspace, workspace_bytes, stream, &dv, true, false);
 }
@@ -739,7 +779,7 @@ int hb_runs_expand(const hb_runs_t* runs, const void* cache_rows, const void* st
                    void* out_rows, int64_t* locs, uint8_t* found, const int64_t* run_slots, void* workspace,
                    size_t workspace_bytes, hb_stream_t stream) {
   HB_CHECK_ARG(out_rows != nullptr && cache_rows != nullptr, "hb_runs_expand: null argument");
-  Delivery dv{(char*)stage_rows, 0, nullptr, nullptr, nullptr};
+  Delivery dv{(char*)stage_rows, 0, nullptr, nullptr};
   return fetch_runs_impl(nullptr, runs, cache_rows, nullptr, 0, nullptr, row_bytes, out_rows, locs, found,
                          const_cast<int64_t*>(run_slots), HB_LOOKUP_SETASSOC, workspace, workspace_bytes, stream,
                          &dv, false, true);

@@ -119,6 +119,10 @@ class PeerExchange:
                 pass
             self._h = None
 
+    @property
+    def handle(self):
+        return self._h
+
     def push_workspace_bytes(self, n: int) -> int:
         return self.lib.hb_a2a_push_workspace_bytes(int(n), self.world)
 

@@ -185,22 +185,13 @@ class EmbeddingPath:
         if self.px_req is None or self.world == 1 or runs.n == 0:
             return E.cudaLookupFetchRuns(self.cold.index, runs, self.cold.emb, self.table, self.shared, out_rows,
                                          self.lookup_mode, want_locs=self.want_locs, ws=fetch_ws)
-        # The owners deliver: this GPU lists the remote runs, the (id, run) requests travel to the
-        # owners like gradient rows do, every owner stores the rows it was asked for into the
+        # The owners deliver: the lookup stores an (id, run) request for every remote run straight into
+        # the owner's receive area, every owner stores the rows it was asked for into the
         # requesters' stages, and the expansion reads local memory only.  Two fences: requests
         # complete before they are served, rows complete before they are read.
-        n = runs.n
-        if self._req is None or self._req[0].numel() < n:
-            dev = self.device
-            self._req = (torch.empty(n, dtype=torch.int64, device=dev), torch.empty(n, dtype=torch.int64, device=dev),
-                         torch.zeros(1, dtype=torch.int64, device=dev),
-                         torch.zeros((n, self.px_req.dim), dtype=torch.float32, device=dev))
-        req_ids, req_runs, req_n, filler = self._req
         stage = self.fetch_stages.weight
-        E.cudaRunsResolveRequests(self.cold.index, runs, self.cold.emb, self.shared, stage, req_ids, req_runs, req_n,
-                                  self.lookup_mode, ws=fetch_ws)
-        parity = self.px_req.push(req_ids[:n], filler[:n], req_runs[:n], req_n,
-                                  ws=self._ws("_req_ws", self.px_req.push_workspace_bytes(n)))
+        parity = E.cudaRunsResolveRequests(self.cold.index, runs, self.cold.emb, self.shared, stage, self.px_req,
+                                           self.lookup_mode, ws=fetch_ws)
         self.px_req.fence()
         r_ids, _, r_runs, seg_counts = self.px_req.received(parity)
         self.shared.serve(self.fetch_stages, r_ids, r_runs, seg_counts, self.px_req.cap)

@@ -53,6 +53,7 @@ int hb_device_status(int* status_host, hb_stream_t stream);
 /* ------------------------------------------------------------------------- */
 typedef struct hb_index hb_index_t;
 typedef struct hb_peer_table hb_peer_table_t; /* a table sharded over the GPUs of a box, see the end of this file */
+typedef struct hb_a2a hb_a2a_t;               /* a peer-memory exchange, see hb_a2a_create */
 
 #define HB_WAYS 8
 
@@ -415,24 +416,27 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs /* host */, const 
 
 /* The same forward fetch with the OWNERS delivering the remote rows (several GPUs; on this pool
  * scattered peer loads of rows collapse to a few tens of GB/s once more than one peer is read,
- * while peer stores run at the links' bandwidth).  Three calls around one exchange:
+ * while peer stores run at the links' bandwidth).  Three calls around two fences:
  *   hb_runs_resolve_requests  the first launch of hb_lookup_fetch_runs; a run whose row lives on
- *       another GPU is not copied but listed: req_ids[k] = its id, req_runs[k] = the run u, which
- *       is also the row of stage_rows the owner is to fill (k < *req_count, any order; the
- *       arrays hold runs->n entries).  Runs at and beyond stage_cap are read from the owner
- *       directly by the last launch.  stage_rows: this GPU's stage, [stage_cap][row_bytes], that
- *       the peers have mapped (the local shard of an hb_peer_table created for the purpose).
- *   (the caller sends the requests to their owners, id % world: hb_a2a_push with req_runs in the
- *       cnt field, hb_a2a_fence; every owner answers with hb_fetch_serve; hb_a2a_fence)
+ *       another GPU is not copied but asked for: the request (id, run u) is stored straight into
+ *       this rank's slab of the owner's receive area of `requests` (an hb_a2a exchange of
+ *       cap_rows >= the distinct ids one owner can be asked for; its row payload is not used),
+ *       id in the ids array and u in the cnt array; u is also the row of stage_rows the owner is
+ *       to fill.  *parity_out: the receive area filled, as from hb_a2a_push.  A slab that is full
+ *       raises HB_ERR_CAPACITY in the device status word.  Runs at and beyond stage_cap are read
+ *       from the owner directly by the last launch.  stage_rows: this GPU's stage,
+ *       [stage_cap][row_bytes], that the peers have mapped (the local shard of an hb_peer_table
+ *       created for the purpose).
+ *   hb_a2a_fence(requests); every rank, as an owner: hb_fetch_serve on the receive view of that
+ *       area; hb_a2a_fence(requests)
  *   hb_runs_expand            the last launch: rows to their batch positions, with locs / found.
  * workspace: hb_lookup_fetch_runs_workspace_bytes(n, row_bytes, 0), the same for both calls and
  * untouched in between.  cache_rows / stage_rows of hb_runs_expand: what the resolve call was
  * given (alignment decides the width of the copies). */
 int hb_runs_resolve_requests(hb_index_t* h, const hb_runs_t* runs /* host */, const void* cache_rows,
                              hb_peer_table_t* table, int64_t row_bytes, void* stage_rows, int64_t stage_cap,
-                             int64_t* run_slots /* nullable */, int64_t* req_ids, int64_t* req_runs,
-                             int64_t* req_count, int mode, void* workspace, size_t workspace_bytes,
-                             hb_stream_t stream);
+                             int64_t* run_slots /* nullable */, hb_a2a_t* requests, int* parity_out /* host */,
+                             int mode, void* workspace, size_t workspace_bytes, hb_stream_t stream);
 int hb_runs_expand(const hb_runs_t* runs /* host */, const void* cache_rows, const void* stage_rows,
                    int64_t row_bytes, void* out_rows, int64_t* locs /* nullable */,
                    uint8_t* found /* nullable */, const int64_t* run_slots /* nullable: the workspace's */,
@@ -563,7 +567,6 @@ int hb_sparse_adagrad(const int64_t* ids, const float* grads, const int64_t* cnt
  * rows beyond it are dropped and HB_ERR_CAPACITY is recorded for
  * hb_device_status.  Set-up: create on every rank, exchange the handles
  * (hb_a2a_handle_bytes() bytes each) by any host channel, connect. */
-typedef struct hb_a2a hb_a2a_t;
 int hb_a2a_create(int rank, int world, int64_t cap_rows, int64_t row_bytes, hb_a2a_t** out);
 size_t hb_a2a_handle_bytes(void);
 int hb_a2a_export_handle(hb_a2a_t* a, void* handle_out /* host */);
