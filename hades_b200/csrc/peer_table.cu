@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(kBlock) sharded_gather_kernel(
 // hb_a2a exchange: counts[s] valid in segment s); every requested row of this rank's shard is
 // stored into the stage of its requester, which this rank has mapped.  Peer STORES run at the
 // links' bandwidth where scattered peer LOADS of the same rows do not.  One warp per request and
-// step, 4 requests in flight per warp.
+// step, 4 requests in flight per warp; the warps take the requesters in rotated order.
 __global__ void __launch_bounds__(kBlock, 4) fetch_serve_kernel(
     const char* __restrict__ shard, int64_t rows_local, int rank, int world, ShardView stages,
     int64_t stage_rows, const int64_t* __restrict__ req_ids, const int64_t* __restrict__ req_rows,
@@ -128,7 +128,10 @@ __global__ void __launch_bounds__(kBlock, 4) fetch_serve_kernel(
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   constexpr int kFly = 4;
   const int64_t vpr = row_bytes >> 4;
-  for (int s = 0; s < world; ++s) {
+  for (int j = 0; j < world; ++j) {
+    // every warp starts with another requester (and every rank with another one again): all
+    // links carry rows all the time, instead of every owner storing into the same GPU first
+    const int s = (int)((warp + rank + 1 + j) % world);
     int64_t cnt = counts[s];
     if (cnt > seg_cap) cnt = seg_cap;
     char* stage = const_cast<char*>(stages.p[s]);
