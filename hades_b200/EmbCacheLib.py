@@ -844,9 +844,14 @@ def cudaRunsResolveRequests(index: IndexCache, runs: BatchRuns, cache_rows, peer
     return parity.value
 
 
-def cudaRunsExpand(runs: BatchRuns, cache_rows, stage_rows, out_rows=None, want_locs: bool = True):
-    """Last third (``hb_runs_expand``): (out_rows, locs, found) at the batch positions from what
-    ``cudaRunsResolveRequests`` left in ``runs`` and the rows the owners delivered."""
+def cudaRunsExpand(runs: BatchRuns, cache_rows, other_rows=None, out_rows=None, want_locs: bool = True,
+                   peer_sources: bool = True):
+    """The last launch of the forward fetch (``hb_runs_expand``): (out_rows, locs, found) at the
+    batch positions from what the per-distinct-id launch left in ``runs`` -- after
+    ``cudaRunsResolveRequests`` and the owners' delivery, or after
+    ``cudaLookupFetchRuns(resolve_only=True)``, so that work which needs only the slots (LRU ageing,
+    insertion of the misses into the index) can run beside it.  other_rows: the backing table or
+    the stage the first call was given; peer_sources: it had a table sharded over several GPUs."""
     n = runs.n
     dev = runs.ids.device
     if out_rows is None:
@@ -854,8 +859,9 @@ def cudaRunsExpand(runs: BatchRuns, cache_rows, stage_rows, out_rows=None, want_
     locs = torch.empty(n, dtype=torch.int64, device=dev) if want_locs else None
     found = torch.empty(n, dtype=torch.bool, device=dev)
     lib = _lib.load()
-    _lib.check(lib.hb_runs_expand(C.byref(runs.desc), _dev_ptr(cache_rows, "cache_rows"), stage_rows.data_ptr(),
-                                  _row_bytes(cache_rows), out_rows.data_ptr(), _lib.ptr(locs), found.data_ptr(),
+    _lib.check(lib.hb_runs_expand(C.byref(runs.desc), _dev_ptr(cache_rows, "cache_rows"),
+                                  None if other_rows is None else other_rows.data_ptr(), _row_bytes(cache_rows),
+                                  int(bool(peer_sources)), out_rows.data_ptr(), _lib.ptr(locs), found.data_ptr(),
                                   runs.slots.data_ptr(), runs.fetch_ws.data_ptr(), runs.fetch_ws.numel(),
                                   _lib.stream_ptr()))
     return out_rows, locs, found

@@ -80,7 +80,7 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_lookup_fetch_runs_workspace_bytes": (_sz, [_i64, _i64, _int]),
     "hb_lookup_fetch_runs": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p, _p, _p, _int, _p, _sz, _p]),
     "hb_runs_resolve_requests": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p, _p, _int, _p, _sz, _p]),
-    "hb_runs_expand": (_int, [_p, _p, _p, _i64, _p, _p, _p, _p, _p, _sz, _p]),
+    "hb_runs_expand": (_int, [_p, _p, _p, _i64, _int, _p, _p, _p, _p, _p, _sz, _p]),
     "hb_runs_miss_list_workspace_bytes": (_sz, [_i64]),
     "hb_runs_miss_list": (_int, [_p, _p, _int, _int, _i64, _p, _p, _p, _p, _sz, _p]),
     "hb_staging_accumulate_cached": (_int, [_p, _p, _p, _p, _i64, _p, _p, C.c_int32, _int, _p, _p, _p]),
@@ -88,6 +88,7 @@ PROTOTYPES: dict[str, tuple] = {
     "hb_staging_flush_workspace_bytes": (_sz, [_i64, _int]),
     "hb_staging_flush": (_int, [_p, _p, C.c_int32, _int, _i64, _p, _p, _p, _p, _p, _sz, _p]),
     "hb_staging_insert_workspace_bytes": (_sz, [_i64]),
+    "hb_staging_insert_rows": (_int, [_p, _p, _p, _i64, _p, _i64, _p, _p, _p]),
     "hb_staging_insert": (_int, [_p, _p, _p, _p, _i64, _p, _i64, _p, _p, _sz, _p]),
     "hb_staging_insert_gather": (_int, [_p, _p, _p, _p, _p, _i64, _p, _i64, _p, _p, _sz, _p]),
     "hb_sparse_adam": (_int, [_p, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _int,

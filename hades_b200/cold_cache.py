@@ -135,6 +135,30 @@ class ColdCache:
                                                 ws.data_ptr(), ws.numel(), _lib.stream_ptr()))
         return locs
 
+    def insert_index(self, ids: torch.Tensor, ws: torch.Tensor):
+        """First half of ``insert_gather``: ``add`` of the ids (negative ones ignored) to the index.
+        Returns (locs, last_writer) for ``insert_rows``; ws as for ``insert_gather``, untouched
+        until then."""
+        lib = _lib.load()
+        n = ids.numel()
+        locs = torch.empty(n, dtype=torch.int64, device=ids.device)
+        need = lib.hb_staging_insert_workspace_bytes(n)
+        _check(ws.numel() >= need, "workspace holds hb_staging_insert_workspace_bytes")
+        flag_bytes = -(-max(n, 1) // 256) * 256
+        _lib.check(lib.hb_index_add(self.index.handle, ids.data_ptr(), n, locs.data_ptr(), ws.data_ptr(),
+                                    ws.data_ptr() + flag_bytes, ws.numel() - flag_bytes, _lib.stream_ptr()))
+        return locs, ws[:max(n, 1)]
+
+    def insert_rows(self, rows: torch.Tensor, row_index: torch.Tensor, locs: torch.Tensor,
+                    last_writer: torch.Tensor) -> None:
+        """Second half: the embeddings rows[row_index[i]] into the cache rows at the slots the index
+        gave, staging slots of the inserted entries reset."""
+        _check(rows.size(1) == self.dim, "rows matches dim")
+        lib = _lib.load()
+        _lib.check(lib.hb_staging_insert_rows(C.byref(self.remote.desc), rows.data_ptr(), row_index.data_ptr(),
+                                              locs.numel(), self.emb.data_ptr(), self.dim * self.emb.element_size(),
+                                              locs.data_ptr(), last_writer.data_ptr(), _lib.stream_ptr()))
+
     # -- server step 3 -------------------------------------------------------------------
     def accumulate_remote(self, ids: torch.Tensor, grads: torch.Tensor, n_dev: torch.Tensor | None = None,
                           touch_lru: bool = True) -> None:

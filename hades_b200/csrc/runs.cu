@@ -631,6 +631,7 @@ struct Delivery {
   int64_t stage_cap;
   hb_a2a* requests;  // the exchange that carries the requests (null: expansion only)
   int* parity_out;   // which of its receive areas this call filled
+  bool peer_sources; // expansion only: a run's row may lie in another GPU's memory (plain loads)
 };
 
 int fetch_runs_impl(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows, const void* backing_rows,
@@ -742,7 +743,7 @@ int fetch_runs_impl(hb_index_t* h, const hb_runs_t* runs, const void* cache_rows
     else if (v16) HB_EXP(PEER, 16);                   \
     else HB_EXP(PEER, 0);                             \
   } while (0)
-  if (sharded || dv) HB_EXP_V(true); else HB_EXP_V(false);
+  if (sharded || (dv && dv->peer_sources)) HB_EXP_V(true); else HB_EXP_V(false);
 #undef HB_EXP_V
 #undef HB_EXP
   return HB_OK;
@@ -770,16 +771,16 @@ int hb_runs_resolve_requests(hb_index_t* h, const hb_runs_t* runs, const void* c
   HB_CHECK_ARG(table && stage_rows && stage_cap > 0 && requests && parity_out,
                "hb_runs_resolve_requests: null argument");
   HB_CHECK_ARG(((uintptr_t)stage_rows & 15) == 0, "hb_runs_resolve_requests: the stage is 16-byte aligned");
-  Delivery dv{(char*)stage_rows, stage_cap, requests, parity_out};
+  Delivery dv{(char*)stage_rows, stage_cap, requests, parity_out, true};
   return fetch_runs_impl(h, runs, cache_rows, nullptr, 0, table, row_bytes, nullptr, nullptr, nullptr, run_slots,
                          mode, workspace, workspace_bytes, stream, &dv, true, false);
 }
 
-int hb_runs_expand(const hb_runs_t* runs, const void* cache_rows, const void* stage_rows, int64_t row_bytes,
-                   void* out_rows, int64_t* locs, uint8_t* found, const int64_t* run_slots, void* workspace,
-                   size_t workspace_bytes, hb_stream_t stream) {
+int hb_runs_expand(const hb_runs_t* runs, const void* cache_rows, const void* other_rows, int64_t row_bytes,
+                   int peer_sources, void* out_rows, int64_t* locs, uint8_t* found, const int64_t* run_slots,
+                   void* workspace, size_t workspace_bytes, hb_stream_t stream) {
   HB_CHECK_ARG(out_rows != nullptr && cache_rows != nullptr, "hb_runs_expand: null argument");
-  Delivery dv{(char*)stage_rows, 0, nullptr, nullptr};
+  Delivery dv{(char*)other_rows, 0, nullptr, nullptr, peer_sources != 0};
   return fetch_runs_impl(nullptr, runs, cache_rows, nullptr, 0, nullptr, row_bytes, out_rows, locs, found,
                          const_cast<int64_t*>(run_slots), HB_LOOKUP_SETASSOC, workspace, workspace_bytes, stream,
                          &dv, false, true);

@@ -398,19 +398,28 @@ int hb_staging_insert_gather(hb_index_t* h, const hb_staging_t* s, const int64_t
   int rc = hb_index_add(h, ids, n, locs_out, last_writer, static_cast<char*>(workspace) + flag_bytes,
                         workspace_bytes - flag_bytes, stream);
   if (rc) return rc;
+  return hb_staging_insert_rows(s, emb_rows, row_index, n, cache_rows, row_bytes, locs_out, last_writer, stream);
+}
+
+int hb_staging_insert_rows(const hb_staging_t* s, const void* emb_rows, const int64_t* row_index, int64_t n,
+                           void* cache_rows, int64_t row_bytes, const int64_t* locs, const uint8_t* last_writer,
+                           hb_stream_t stream) {
+  HB_CHECK_ARG(n >= 0 && row_bytes > 0, "hb_staging_insert_rows: bad sizes");
+  HB_CHECK_ARG(n == 0 || (emb_rows && cache_rows && locs && last_writer), "hb_staging_insert_rows: null argument");
+  if (n == 0) return HB_OK;
   hb_staging_t none;
   memset(&none, 0, sizeof(none));
   const hb_staging_t st_desc = s ? *s : none;
   const int vb = payload_vec_bytes(row_bytes, emb_rows, cache_rows);
   cudaStream_t st = (cudaStream_t)stream;
   if (vb == 16)
-    HB_LAUNCH(staging_insert_kernel<16>, warp_grid(n), kBlock, 0, st, st_desc, locs_out, last_writer,
+    HB_LAUNCH(staging_insert_kernel<16>, warp_grid(n), kBlock, 0, st, st_desc, locs, last_writer,
               (const char*)emb_rows, row_index, (char*)cache_rows, row_bytes, n);
   else if (vb == 4)
-    HB_LAUNCH(staging_insert_kernel<4>, warp_grid(n), kBlock, 0, st, st_desc, locs_out, last_writer,
+    HB_LAUNCH(staging_insert_kernel<4>, warp_grid(n), kBlock, 0, st, st_desc, locs, last_writer,
               (const char*)emb_rows, row_index, (char*)cache_rows, row_bytes, n);
   else
-    HB_LAUNCH(staging_insert_kernel<1>, warp_grid(n), kBlock, 0, st, st_desc, locs_out, last_writer,
+    HB_LAUNCH(staging_insert_kernel<1>, warp_grid(n), kBlock, 0, st, st_desc, locs, last_writer,
               (const char*)emb_rows, row_index, (char*)cache_rows, row_bytes, n);
   return HB_OK;
 }

@@ -25,6 +25,7 @@ carries the exchange.
 """
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass, field
 
 import torch
@@ -103,6 +104,8 @@ class EmbeddingPath:
         self.shared = getattr(optimizer.emb, "peer_table", None)
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._side = None
+        self._maint = None
+        self._req_parity = 0
         self._side_done, self._side_refs = None, []
         self._runs_ws, self._side_ws, self._fetch_ws, self._req_ws = None, None, None, None
         self._last = None  # (BatchRuns, locs) of the last forward pass
@@ -154,64 +157,109 @@ class EmbeddingPath:
         sharded = self.shared is not None and self.world > 1
         fetch_ws = self._ws("_fetch_ws", lib.hb_lookup_fetch_runs_workspace_bytes(
             n, self.dim * self.cold.emb.element_size(), int(sharded)))
-        if on_side and n:
-            # The whole fetch leaves the main stream, which goes on to the aggregation of the same
-            # batch (it needs the sort only): with several GPUs the copy of the remote rows is bound
-            # by NVLink round trips and hides behind that HBM-bound work.  The main stream joins
-            # before it returns the rows (``_join_side``).
-            with self._on_side():
-                rows, locs, found = self._fetch(runs, out_rows, fetch_ws)
-                self._after_fetch(runs, rows, n, lib)
-            if not torch.cuda.is_current_stream_capturing():
-                for t in (rows, locs, found):  # allocated under the side stream, read on this one
-                    if t is not None:
-                        t.record_stream(torch.cuda.current_stream())
-        else:
-            rows, locs, found = self._fetch(runs, out_rows, fetch_ws)
-            if n and (self.touch_lru or self.insert_misses):
-                # Off the main stream, which goes on to whatever uses the rows: the LRU ageing of
-                # this lookup (cache.h:101), then the uncached cold ids and their rows go to the
-                # cache (dist_emb.py:218-259 -> server.py:499-544), before this step's cold
-                # gradients look the cache up.
-                with self._on_side():
-                    self._after_fetch(runs, rows, n, lib)
-                if join:
-                    self._join_side()
+        if n == 0:
+            rows, locs, found = E.cudaLookupFetchRuns(self.cold.index, runs, self.cold.emb, self.table, self.shared,
+                                                      out_rows, self.lookup_mode, want_locs=self.want_locs,
+                                                      ws=fetch_ws)
+            self._last = (runs, locs)
+            return rows, locs, found
+        # on_side: the whole fetch leaves the main stream, which goes on to the aggregation of the
+        # same batch (it needs the sort only); the main stream joins before it returns the rows.
+        with (self._on_side() if on_side else contextlib.nullcontext()):
+            fetch_stream = torch.cuda.current_stream()
+            other_rows = self._resolve(runs, fetch_ws)
+            maintain = self.touch_lru or self.insert_misses
+            pending = None
+            if maintain:
+                # What the index needs from this lookup -- the LRU ageing (cache.h:101), the list of
+                # uncached cold ids and their add() (dist_emb.py:218-259 -> server.py:499-544) --
+                # needs the slots only: it runs beside the expansion, on a stream of its own.
+                resolved = torch.cuda.Event()
+                resolved.record(fetch_stream)
+                if self._maint is None:
+                    self._maint = torch.cuda.Stream(device=self.device)
+                self._maint.wait_event(resolved)
+                with torch.cuda.stream(self._maint):
+                    pending = self._index_maintenance(runs, n, lib)
+            rows, locs, found = self._expand(runs, out_rows, other_rows)
+            if maintain:
+                expanded = torch.cuda.Event()
+                expanded.record(fetch_stream)
+                with torch.cuda.stream(self._maint):
+                    self._maint.wait_event(expanded)
+                    if pending is not None:
+                        # the rows of the inserted ids are taken from the output that has just fetched them
+                        self.cold.insert_rows(rows, pending[1], pending[2], pending[3])
+                    maintained = torch.cuda.Event()
+                    maintained.record(self._maint)
+                # the side stream carries on from here (the cold accumulate looks the cache up)
+                if self._side is None:
+                    self._side = torch.cuda.Stream(device=self.device)
+                self._side.wait_event(maintained)
+                if not on_side:
+                    self._side.wait_event(expanded)
+                self._side_done = torch.cuda.Event()
+                self._side_done.record(self._side)
+                self._side_refs.append((pending, rows, runs))
+        if on_side and not torch.cuda.is_current_stream_capturing():
+            for t in (rows, locs, found):  # allocated under the side stream, read on this one
+                if t is not None:
+                    t.record_stream(torch.cuda.current_stream())
+        if on_side and not maintain:
+            self._side_finished(rows, runs)
+        if join:
+            self._join_side()
         self._last = (runs, locs)
         return rows, locs, found
 
     def _fetch(self, runs, out_rows, fetch_ws):
-        """Lookup per distinct id + rows to the batch positions, on the current stream."""
-        if self.px_req is None or self.world == 1 or runs.n == 0:
+        """Lookup per distinct id + rows to the batch positions, on the current stream (no index
+        maintenance: what ``forward`` does without its other streams; used to time the fetch)."""
+        if runs.n == 0:
             return E.cudaLookupFetchRuns(self.cold.index, runs, self.cold.emb, self.table, self.shared, out_rows,
                                          self.lookup_mode, want_locs=self.want_locs, ws=fetch_ws)
+        return self._expand(runs, out_rows, self._resolve(runs, fetch_ws))
+
+    def _resolve(self, runs, fetch_ws):
+        """The per-distinct-id launch of the fetch on the current stream: slots into runs.slots,
+        where every run's row is read from; rows of other GPUs' shards copied (pull) or asked for
+        (deliver).  Returns the buffer ``_expand`` names as the other source of rows."""
+        if self.px_req is None or self.world == 1:
+            E.cudaLookupFetchRuns(self.cold.index, runs, self.cold.emb, self.table, self.shared, None,
+                                  self.lookup_mode, ws=fetch_ws, resolve_only=True)
+            return self.table
         # The owners deliver: the lookup stores an (id, run) request for every remote run straight into
         # the owner's receive area, every owner stores the rows it was asked for into the
         # requesters' stages, and the expansion reads local memory only.  Two fences: requests
         # complete before they are served, rows complete before they are read.
         stage = self.fetch_stages.weight
-        parity = E.cudaRunsResolveRequests(self.cold.index, runs, self.cold.emb, self.shared, stage, self.px_req,
-                                           self.lookup_mode, ws=fetch_ws)
-        self.px_req.fence()
-        r_ids, _, r_runs, seg_counts = self.px_req.received(parity)
-        self.shared.serve(self.fetch_stages, r_ids, r_runs, seg_counts, self.px_req.cap)
-        self.px_req.fence()
-        return E.cudaRunsExpand(runs, self.cold.emb, stage, out_rows, want_locs=self.want_locs)
+        self._req_parity = E.cudaRunsResolveRequests(self.cold.index, runs, self.cold.emb, self.shared, stage,
+                                                     self.px_req, self.lookup_mode, ws=fetch_ws)
+        return stage
 
-    def _after_fetch(self, runs, rows, n: int, lib) -> None:
-        """On the side stream: LRU ageing of the lookup, cold misses into the cache."""
+    def _expand(self, runs, out_rows, other_rows):
+        """The rest of the fetch: (deliver: fence, serve, fence) rows to their batch positions."""
+        sharded = self.shared is not None and self.world > 1
+        if self.px_req is not None and self.world > 1:
+            self.px_req.fence()
+            r_ids, _, r_runs, seg_counts = self.px_req.received(self._req_parity)
+            self.shared.serve(self.fetch_stages, r_ids, r_runs, seg_counts, self.px_req.cap)
+            self.px_req.fence()
+        return E.cudaRunsExpand(runs, self.cold.emb, other_rows, out_rows, want_locs=self.want_locs,
+                                peer_sources=sharded)
+
+    def _index_maintenance(self, runs, n: int, lib):
+        """On the maintenance stream, after the per-distinct-id launch: LRU ageing of the lookup,
+        cold misses added to the index.  Returns what ``insert_rows`` needs, or None."""
         if self.touch_lru:
             self.cold.index.cuda_touch_lru_runs(runs.slots, runs, locs_kind=2)
-        if self.insert_misses:
-            need = max(lib.hb_runs_miss_list_workspace_bytes(n),
-                       lib.hb_staging_insert_workspace_bytes(self.miss_cap))
-            ws = self._ws("_side_ws", need)
-            miss_ids, miss_src, miss_n = E.cudaRunsMissList(runs, runs.slots, COLD, self.miss_cap, ws=ws,
-                                                            locs_kind=2)
-            self.cold.insert_gather(miss_ids, rows, miss_src, ws=ws)
-            self._side_finished(miss_ids, miss_src, miss_n, rows, runs)
-        else:
-            self._side_finished(rows, runs)
+        if not self.insert_misses:
+            return None
+        need = max(lib.hb_runs_miss_list_workspace_bytes(n), lib.hb_staging_insert_workspace_bytes(self.miss_cap))
+        ws = self._ws("_side_ws", need)
+        miss_ids, miss_src, miss_n = E.cudaRunsMissList(runs, runs.slots, COLD, self.miss_cap, ws=ws, locs_kind=2)
+        locs, last_writer = self.cold.insert_index(miss_ids, ws)
+        return miss_ids, miss_src, locs, last_writer, miss_n
 
     def _fence_shards(self) -> None:
         """All ranks' optimiser updates before anyone's next read of a shard (and the other way

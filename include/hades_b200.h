@@ -431,14 +431,19 @@ int hb_lookup_fetch_runs(hb_index_t* h, const hb_runs_t* runs /* host */, const 
  *       area; hb_a2a_fence(requests)
  *   hb_runs_expand            the last launch: rows to their batch positions, with locs / found.
  * workspace: hb_lookup_fetch_runs_workspace_bytes(n, row_bytes, 0), the same for both calls and
- * untouched in between.  cache_rows / stage_rows of hb_runs_expand: what the resolve call was
- * given (alignment decides the width of the copies). */
+ * untouched in between.
+ * hb_runs_expand also finishes a hb_lookup_fetch_runs call that was given out_rows == NULL (same
+ * workspace), so that a caller can put work between the two launches: the index maintenance of
+ * the batch (LRU ageing, insertion of the misses) needs the first only.  cache_rows / other_rows:
+ * what the first call was given as cache rows and as backing table or stage (their alignment
+ * decides the width of the copies); peer_sources: non-zero when the first call had a table
+ * sharded over several GPUs (rows may then be read from a peer's memory, with plain loads). */
 int hb_runs_resolve_requests(hb_index_t* h, const hb_runs_t* runs /* host */, const void* cache_rows,
                              hb_peer_table_t* table, int64_t row_bytes, void* stage_rows, int64_t stage_cap,
                              int64_t* run_slots /* nullable */, hb_a2a_t* requests, int* parity_out /* host */,
                              int mode, void* workspace, size_t workspace_bytes, hb_stream_t stream);
-int hb_runs_expand(const hb_runs_t* runs /* host */, const void* cache_rows, const void* stage_rows,
-                   int64_t row_bytes, void* out_rows, int64_t* locs /* nullable */,
+int hb_runs_expand(const hb_runs_t* runs /* host */, const void* cache_rows, const void* other_rows /* nullable */,
+                   int64_t row_bytes, int peer_sources, void* out_rows, int64_t* locs /* nullable */,
                    uint8_t* found /* nullable */, const int64_t* run_slots /* nullable: the workspace's */,
                    void* workspace, size_t workspace_bytes, hb_stream_t stream);
 
@@ -523,6 +528,13 @@ int hb_staging_insert(hb_index_t* h, const hb_staging_t* s /* nullable */, const
  * has just written (hb_runs_miss_list gives ids and row_index), as the reference's
  * trainer ships them to the server (python/EmbCache/dist_emb.py:218-259).  Negative
  * ids (padding) are ignored and get locs_out = -1. */
+/* The second half of hb_staging_insert_gather for callers that run hb_index_add themselves (and
+ * put other work between the two): rows emb_rows[row_index[i]] (row_index nullable: i) into the
+ * cache rows at locs[i] where last_writer[i] is set (both from hb_index_add), staging slots of
+ * the inserted entries reset. */
+int hb_staging_insert_rows(const hb_staging_t* s /* nullable */, const void* emb_rows, const int64_t* row_index,
+                           int64_t n, void* cache_rows, int64_t row_bytes, const int64_t* locs,
+                           const uint8_t* last_writer, hb_stream_t stream);
 int hb_staging_insert_gather(hb_index_t* h, const hb_staging_t* s /* nullable */,
                              const int64_t* ids, const void* emb_rows,
                              const int64_t* row_index /* nullable */, int64_t n, void* cache_rows,

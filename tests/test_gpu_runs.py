@@ -115,6 +115,14 @@ def test_lookup_fetch_runs_equals_unsorted_fetch(cuda_lib, oracle_mod, mode, dim
     assert torch.equal(runs.slots[:U], locs_g[perm[run_start]])
     out2, none_locs, found2 = E.cudaLookupFetchRuns(ix, runs, _t(cache), _t(table), want_locs=False)
     assert none_locs is None and torch.equal(out2, out) and torch.equal(found2, found)
+    # the two launches as separate calls (work that needs only the slots can run between them)
+    runs3 = E.cudaRunsBuild(_t(q), 21)
+    cache_t, table_t = _t(cache), _t(table)  # the first call leaves addresses of their rows behind
+    assert E.cudaLookupFetchRuns(ix, runs3, cache_t, table_t, resolve_only=True) == (None, None, None)
+    assert torch.equal(runs3.slots[:U], runs.slots[:U])
+    pre = torch.full((q.size, dim), -7.0, device="cuda", dtype=pre.dtype)
+    out3, locs3, found3 = E.cudaRunsExpand(runs3, cache_t, table_t, out_rows=pre, peer_sources=False)
+    assert torch.equal(out3, out) and torch.equal(locs3, locs_g) and torch.equal(found3, found)
     # without a backing table a miss leaves the output row untouched
     want1 = np.full((q.size, dim), -7.0, dtype)
     oracle_mod.lookup_fetch(ora, q, cache, None, want1)
