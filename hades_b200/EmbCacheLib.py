@@ -756,9 +756,9 @@ def cudaRunsBuild(ids, id_bits: int = 64, table=None, keep=(True, True, True), c
             if keep[c]:
                 m = n if caps[c] is None else min(n, int(caps[c]))
                 class_ids[c] = torch.empty(max(m, 1), dtype=torch.int64, device=dev)
-        class_counts = torch.zeros(3, dtype=torch.int64, device=dev)
+        class_counts = torch.empty(3, dtype=torch.int64, device=dev)  # written by the call (zeros for n == 0)
         arr = (C.c_void_p * 3)(*[(t.data_ptr() if t is not None else None) for t in class_ids])
-    num = torch.zeros(1, dtype=torch.int64, device=dev)
+    num = torch.empty(1, dtype=torch.int64, device=dev)
     uniq = torch.empty(max(n, 1), dtype=torch.int64, device=dev) if want_uniq else None
     desc = _lib.RunsDesc()
     _lib.check(lib.hb_runs_build(ids.data_ptr(), n, _lib.ptr(n_dev), _lib.ptr(seg_counts), int(seg_cap),
@@ -920,8 +920,8 @@ def cudaRunsMissList(runs: BatchRuns, locs, want_class: int, cap: int, ws: torch
         ws = _lib.workspace(need)
     _check(ws.numel() >= need, "workspace holds hb_runs_miss_list_workspace_bytes")
     miss_ids = torch.empty(cap, dtype=torch.int64, device=dev)
-    miss_src = torch.zeros(cap, dtype=torch.int64, device=dev)
-    count = torch.zeros(1, dtype=torch.int64, device=dev)
+    miss_src = torch.empty(cap, dtype=torch.int64, device=dev)  # defined for the first `count` entries
+    count = torch.empty(1, dtype=torch.int64, device=dev)
     _lib.check(lib.hb_runs_miss_list(C.byref(runs.desc), locs.data_ptr(), int(locs_kind), int(want_class), int(cap),
                                      miss_ids.data_ptr(), miss_src.data_ptr(), count.data_ptr(), ws.data_ptr(),
                                      ws.numel(), _lib.stream_ptr()))
