@@ -43,8 +43,8 @@ NVLINK_MEASURED_GBS = 770.0   # peer copy measured on this pool (cudaMemcpyPeer,
 # that source changes the figure is withheld (traffic = null) until it is captured again.
 TRAFFIC_CAPTURE = {
     "kernel_sources": ["hades_b200/csrc/runs.cu", "hades_b200/csrc/index.cuh"],
-    "sha256": "f55e54b7dfbf662a31a58357aed92223d67ed50e73a73c64497797aec6556d99",
-    "bytes_per_launch": 1_092_991_915,
+    "sha256": "946dcb7ba44aa64ec78f9adbd91048d4ce8b226e941bcff7084d467b91d4912b",
+    "bytes_per_launch": 1_092_927_488,
     "source": "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none (1 pass) over "
               "bench.py --steps 8 --warmup 3 --no-graph at full configuration 2 on one B200: runs_resolve_kernel "
               "17.8 MB read + runs_expand_kernel 105.9 MB read, 969.2 MB written, mean of 3 calls",
