@@ -75,3 +75,58 @@ def test_unmapped_peer_is_an_error(cuda_lib):
         t.gather(torch.zeros(4, dtype=torch.int64, device="cuda"))
     with pytest.raises(RuntimeError, match="multiple of 16"):
         PeerTable(100, 3, 0, 1)
+
+
+def test_owner_serves_requested_rows_into_the_requesters_stages(cuda_lib):
+    """hb_fetch_serve (the owner's half of a forward fetch in which the owners deliver): requests
+    (id, stage row) in per-requester segments; every requested row of the owner's shard lands in
+    the stage of its requester; a request for a row of another owner, beyond the table or beyond the
+    stage is skipped and raises the status word."""
+    from hades_b200 import _lib
+
+    world, num_rows, dim, stage_rows, cap = 3, 10_001, 32, 64, 40
+    tabs = _tables(num_rows, dim, world)
+    stages = _tables(world * stage_rows, dim, world)
+    full = torch.randn(num_rows, dim, device="cuda")
+    for t in tabs:
+        t.weight.copy_(full[t.rank::world])
+    for owner in range(world):
+        for s in stages:
+            s.weight.fill_(-1.0)
+        g = torch.Generator().manual_seed(10 + owner)
+        req_ids = torch.full((world * cap,), -5, dtype=torch.int64)
+        req_rows = torch.full((world * cap,), -5, dtype=torch.int64)
+        counts = torch.zeros(world, dtype=torch.int64)
+        want = {}
+        for s in range(world):
+            k = [0, 17, cap][s]  # an empty segment, a partly filled one, a full one
+            owned = torch.arange(owner, num_rows, world)
+            ids = owned[torch.randperm(owned.numel(), generator=g)[:k]]
+            rows = torch.randperm(stage_rows, generator=g)[:k]
+            req_ids[s * cap: s * cap + k], req_rows[s * cap: s * cap + k], counts[s] = ids, rows, k
+            want[s] = (ids, rows)
+        assert _lib.device_status() == 0
+        tabs[owner].serve(stages[owner], req_ids.cuda(), req_rows.cuda(), counts.cuda(), cap)
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0
+        for s in range(world):
+            ids, rows = want[s]
+            got = stages[s].weight
+            assert torch.equal(got[rows.cuda()], full[ids.cuda()])
+            untouched = torch.ones(stage_rows, dtype=torch.bool)
+            untouched[rows] = False
+            assert bool((got[untouched.cuda()] == -1.0).all())
+    # bad requests: not this owner's id, no such id, no such stage row -> skipped, status word raised
+    for s in stages:
+        s.weight.fill_(-1.0)
+    req_ids = torch.tensor([1, num_rows + 3 - (num_rows % 3), 0, 3], dtype=torch.int64)  # owner 0 is asked
+    req_rows = torch.tensor([0, 1, stage_rows, 2], dtype=torch.int64)
+    pad_i = torch.full((world * 4,), -5, dtype=torch.int64)
+    pad_r = torch.full((world * 4,), -5, dtype=torch.int64)
+    pad_i[4:8], pad_r[4:8] = req_ids, req_rows  # all from requester 1
+    counts = torch.tensor([0, 4, 0], dtype=torch.int64)
+    tabs[0].serve(stages[0], pad_i.cuda(), pad_r.cuda(), counts.cuda(), 4)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 1  # HB_ERR_INVALID, cleared by the read
+    assert torch.equal(stages[1].weight[2], full[3])  # the one good request was served
+    assert bool((stages[1].weight[:2] == -1.0).all()) and bool((stages[0].weight == -1.0).all())
