@@ -79,7 +79,6 @@ class EmbeddingPath:
         # several GPUs, owners deliver the remote rows of the forward fetch: the exchange that
         # carries the requests and the stages (one per rank, mapped by all) the owners store into
         self.px_req, self.fetch_stages = request_exchange, fetch_stages
-        self._req = None
         self.table, self.class_table, self.cold, self.opt = table, class_table, cold, optimizer
         self.rank, self.world = rank, world
         self.flush_every, self.id_bits = flush_every, id_bits
@@ -107,7 +106,7 @@ class EmbeddingPath:
         self._maint = None
         self._req_parity = 0
         self._side_done, self._side_refs = None, []
-        self._runs_ws, self._side_ws, self._fetch_ws, self._req_ws = None, None, None, None
+        self._runs_ws, self._side_ws, self._fetch_ws = None, None, None
         self._last = None  # (BatchRuns, locs) of the last forward pass
 
     # ---- streams ---------------------------------------------------------------------------
