@@ -141,3 +141,67 @@ def test_two_ranks(exchange):
 
     build_oracle.build_oracle()
     mp.spawn(_worker, args=(_free_port(), exchange), nprocs=WORLD, join=True)
+
+
+def _deliver_worker(rank, port):
+    """The three calls of a forward fetch whose remote rows the owners deliver, on two GPUs, with a
+    request exchange that is too small on purpose: the requests that do not fit are refused with a
+    status code (HB_ERR_CAPACITY), nothing is written out of bounds, what fitted is served."""
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=torch.device("cuda", rank))
+    from hades_b200 import EmbCacheLib as E
+    from hades_b200 import _lib
+    from hades_b200.exchange import PeerExchange
+    from hades_b200.peer_table import PeerTable
+
+    num_rows, dim, n = 1000, 8, 200
+    table = PeerTable(num_rows, dim, rank, WORLD)
+    full = torch.arange(num_rows * dim, dtype=torch.float32, device="cuda").reshape(num_rows, dim)
+    table.weight.copy_(full[rank::WORLD])
+    stages = PeerTable(WORLD * n, dim, rank, WORLD)
+    stages.weight.fill_(-1.0)
+    torch.cuda.synchronize()
+    dist.barrier()
+    index = E.IndexCache(64, f"deliver_r{rank}", True, False)  # empty: every id misses
+    cache = torch.zeros((index.get_capacity(), dim), device="cuda")
+    ids = torch.arange(n, dtype=torch.int64, device="cuda")    # 100 of them live on the other GPU
+    for cap, want_status in ((8, 6), (128, 0)):                 # HB_ERR_CAPACITY, then room for all
+        px = PeerExchange(rank, WORLD, cap, 4)
+        runs = E.cudaRunsBuild(ids, 12)
+        parity = E.cudaRunsResolveRequests(index, runs, cache, table, stages.weight, px)
+        px.fence()
+        r_ids, _, r_runs, seg = px.received(parity)
+        table.serve(stages, r_ids, r_runs, seg, px.cap)
+        px.fence()
+        out = torch.full((n, dim), -7.0, device="cuda")
+        rows, locs, found = E.cudaRunsExpand(runs, cache, stages.weight, out)
+        torch.cuda.synchronize()
+        assert _lib.device_status() == want_status, (rank, cap)
+        assert int(seg[1 - rank].item()) == min(cap, n // 2) and int(seg[rank].item()) == 0
+        assert not bool(found.any()) and bool((locs == -1).all())
+        mine = ids % WORLD == rank
+        assert torch.equal(rows[mine], full[ids[mine]])          # own rows: read from the local shard
+        theirs = rows[~mine]
+        delivered = (theirs == full[ids[~mine]]).all(dim=1)
+        stale = (theirs == -1.0).all(dim=1)                      # the stage row nobody filled
+        assert bool((delivered | stale).all())
+        assert int(delivered.sum().item()) == min(cap, n // 2), (rank, cap, int(delivered.sum().item()))
+        px.close()
+        stages.weight.fill_(-1.0)
+        torch.cuda.synchronize()
+        dist.barrier()
+    stages.close()
+    table.close()
+    dist.destroy_process_group()
+
+
+def test_delivery_refuses_requests_beyond_the_slab():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < WORLD:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    mp.spawn(_deliver_worker, args=(_free_port(),), nprocs=WORLD, join=True)
