@@ -1381,7 +1381,12 @@ def run_ours(args) -> None:
                     if rank == 0:
                         extra[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
                     if world > 1:
-                        raise  # ranks would fall out of step with one another
+                        # ranks would fall out of step with one another: stop here, but not without the
+                        # headline that has already been measured
+                        if rank == 0:
+                            line["extra"] = extra
+                            print(json.dumps(line), flush=True)
+                        raise
             if rank == 0:
                 line["extra"] = extra
         if rank == 0:
