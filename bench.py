@@ -78,7 +78,7 @@ def parse():
                          "with an NCCL all-reduce as the fence, or NCCL all_to_all_single")
     ap.add_argument("--remote-fetch", default="auto", choices=["auto", "pull", "deliver"],
                     help="N > 1, rows of other GPUs' shards in the forward fetch: read by this GPU once per distinct "
-                         "id (pull) or stored into this GPU's stage by their owners (deliver); auto: deliver for N > 2")
+                         "id (pull) or stored into this GPU's stage by their owners (deliver, the default of auto)")
     ap.add_argument("--overlap-fetch", default="on", choices=["on", "off"],
                     help="run the forward fetch of a step beside the aggregation of the same step (default on)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

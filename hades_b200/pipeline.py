@@ -629,8 +629,8 @@ def assemble_path(name: str, table: torch.Tensor, class_table: torch.Tensor, cac
     remote_fetch: who brings the rows of other GPUs' shards in the forward fetch: "pull" (this GPU
     reads them, once per distinct id), "deliver" (the owners store them into this GPU's stage of
     fetch_stage_rows rows; needs the peer-memory exchange with the device fence), "auto": deliver
-    with more than two GPUs (scattered peer loads collapse once a GPU reads several peers at a
-    time while all of them read it), pull with two.
+    (scattered peer loads collapse once a GPU reads several peers at a time while all of them read
+    it; with two GPUs the two forms measure within 2 % of each other).
     state_budget_bytes / hotness: see ``SparseAdam`` (state tiered between HBM and pinned host
     memory when it does not fit the budget; hotness per node of the whole table).
     threshold: int32 per-node flush period (``cold_cache.flush_thresholds`` of the presampled
@@ -677,7 +677,7 @@ def assemble_path(name: str, table: torch.Tensor, class_table: torch.Tensor, cac
         opt = SparseAdagrad(shard, lr=0.01)
     id_bits = max(int(rows_total).bit_length() + 1, 8)
     px_req = stages = None
-    deliver = remote_fetch == "deliver" or (remote_fetch == "auto" and world > 2)
+    deliver = remote_fetch == "deliver" or (remote_fetch == "auto" and world > 1)
     if deliver and share and px is not None and px.fence_kind == "device" and fetch_stage_rows > 0:
         from .peer_table import PeerTable
 
