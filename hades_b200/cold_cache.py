@@ -166,7 +166,7 @@ class ColdCache:
         (server.py:550 -> src/cache/cache.h:101).  n_dev: device int64 that caps the number
         of ids taken."""
         lib = _lib.load()
-        locs = torch.full_like(ids, -1) if touch_lru else None
+        locs = torch.empty_like(ids) if touch_lru else None  # written for every id the call takes (n_dev)
         _lib.check(lib.hb_staging_accumulate_cached(
             self.index.handle, C.byref(self.remote.desc), ids.data_ptr(), grads.data_ptr(), ids.numel(),
             _lib.ptr(n_dev), _lib.ptr(self.threshold), self.default_threshold, self.lookup_mode,
