@@ -105,6 +105,7 @@ class EmbeddingPath:
         self._side = None
         self._maint = None
         self._req_parity = 0
+        self._evt_resolved = self._evt_expanded = None  # where a fetch beside the backward pass stands
         self._side_done, self._side_refs = None, []
         self._runs_ws, self._side_ws, self._fetch_ws = None, None, None
         self._last = None  # (BatchRuns, locs) of the last forward pass
@@ -167,6 +168,11 @@ class EmbeddingPath:
         with (self._on_side() if on_side else contextlib.nullcontext()):
             fetch_stream = torch.cuda.current_stream()
             other_rows = self._resolve(runs, fetch_ws)
+            if on_side:
+                # this GPU's reads of other GPUs' shards (pull) are done: the backward pass waits for
+                # this before it tells the owners, through the exchange's fence, that they may update
+                self._evt_resolved = torch.cuda.Event()
+                self._evt_resolved.record(fetch_stream)
             maintain = self.touch_lru or self.insert_misses
             pending = None
             if maintain:
@@ -181,6 +187,11 @@ class EmbeddingPath:
                 with torch.cuda.stream(self._maint):
                     pending = self._index_maintenance(runs, n, lib)
             rows, locs, found = self._expand(runs, out_rows, other_rows)
+            if on_side:
+                # every read of this GPU's own shard by this fetch (rows of ids it owns, rows served to
+                # the peers) is done: the owner update of the same step waits for this
+                self._evt_expanded = torch.cuda.Event()
+                self._evt_expanded.record(fetch_stream)
             if maintain:
                 expanded = torch.cuda.Event()
                 expanded.record(fetch_stream)
@@ -342,26 +353,41 @@ class EmbeddingPath:
         self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=self.id_bits,
                         seg_counts=seg_counts, seg_cap=self.px.cap, sorted_segments=True)
 
+    def _after_fetch_event(self, which: str) -> None:
+        """The current stream waits for that point of a fetch that runs beside this backward pass."""
+        evt = getattr(self, which)
+        if evt is not None:
+            torch.cuda.current_stream().wait_event(evt)
+            setattr(self, which, None)
+
     def _backward_core(self, ids, grads) -> StepStats:
         """Everything of the backward path that runs every step (no host read unless NCCL
-        carries the exchange)."""
+        carries the exchange).  When the fetch of the same batch runs beside it (``step`` with
+        overlap_fetch), the exchange waits until that fetch has read what it needs from the other
+        GPUs' shards, and the owner update until it has read what it needs from this GPU's shard:
+        a fetch returns the rows as they were before the step's update."""
         st, hot_ids, hot_rows, hot_cnt = self._backward_local(ids, grads, join=False)
         n_hot = st.split_counts[HOT:HOT + 1]
+        if self.world > 1:
+            self._after_fetch_event("_evt_resolved")
         # hot rows go to their owners now
         if self.world == 1:
             # One trainer: bucketing by owner is the identity (the reference skips the exchange
             # too, sparse_optim.py:263,320), and the hot ids are already unique and ascending, so
             # unique_grads (sparse_optim.py:142-157) reduces to its division by 1 + cnt.
             st.sent_counts = n_hot
+            self._after_fetch_event("_evt_expanded")
             self.opt.update(hot_ids, hot_rows, hot_cnt + 1, is_unique=True, n_dev=n_hot)
         elif self.px is not None:
             parity = self.px.push(hot_ids, hot_rows, hot_cnt, n_hot)
             self.px.fence()
+            self._after_fetch_event("_evt_expanded")
             self._owner_update_from_slabs(parity)
         else:
             r_ids, r_rows, r_cnt, sent = self._exchange(hot_ids, hot_rows, hot_cnt, n_hot)
             st.sent_counts = sent
             # owner: merge the senders' rows (unique_grads with counts) and update
+            self._after_fetch_event("_evt_expanded")
             self.opt.update(r_ids, r_rows, r_cnt, is_unique=False, id_bits=self.id_bits)
         self._join_side()
         self._fence_shards()
